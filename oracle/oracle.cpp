@@ -1,0 +1,460 @@
+// CPU oracle for the int8 quantized-inference path of slexisvn/mlfw (v0.1.6).
+//
+// THIS FILE IS TEST INFRASTRUCTURE.  It is a plain C++ restatement of the
+// arithmetic the reference's TypeScript CPU target performs, written so that
+// the CUDA backend can be checked against it.  Only the tests, the smoke check
+// and the CPU-baseline leg of the benchmark may call it; the product never does.
+//
+// Parity pin: the reference is TypeScript and no JavaScript engine exists in
+// the build image, so the reference itself cannot be run.  The oracle is pinned
+// against every closed-form known answer the reference's own tests hold for
+// this path (tests/compiler/passes/quantization/params.test.js, pass.test.js,
+// tests/e2e/cuda/training-quant.cuda.test.js): those are restated in
+// tests/test_oracle_reference_vectors.py.  Behaviour the reference's tests do
+// not pin (exact ties, NaN/Inf input, tanh-GELU) follows the reference SOURCE
+// and is marked "source-only" where it is restated below.
+//
+// Reference files restated (paths inside the reference project):
+//   src/compiler/ir/graph/quantization_types.ts   QuantizationParams  ("mode P", all binary64)
+//   src/compiler/passes/lowering/quant_math.ts     quantize/dequantize leaf math ("mode C")
+//   src/compiler/passes/lowering/rules/quantization.ts   quantized_dot
+//   src/backend/cpu/codegen.ts                      where Math.fround / Math.round / |0 land
+//   src/compiler/passes/quantization/quantization_pass.ts:390-459  per-channel tail
+//   src/compiler/passes/decompose/decomposition_pass.ts:197-230    sigmoid, gelu(1.702), silu
+//   src/compiler/analysis/calibration.ts           min/max observer
+//   src/util/random.ts, src/tensor/factory/creation_ops.ts, src/nn/init.ts  seeded data
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <limits>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// ECMAScript number semantics
+// ---------------------------------------------------------------------------
+
+// Math.round: nearest integer, ties toward +infinity; NaN and +-Inf pass through.
+// floor(x) and x - floor(x) are exact in binary64, so this is the spec's rule.
+inline double js_round(double x) {
+  if (!std::isfinite(x)) return x;
+  double r = std::floor(x);
+  if (x - r >= 0.5) r += 1.0;
+  return r;
+}
+
+// Math.fround: binary64 -> binary32 (round to nearest even) -> binary64.
+inline double js_fround(double v) { return (double)(float)v; }
+
+// Math.max / Math.min: NaN if either argument is NaN.
+inline double js_max(double a, double b) {
+  if (std::isnan(a) || std::isnan(b)) return std::numeric_limits<double>::quiet_NaN();
+  return a > b ? a : b;
+}
+inline double js_min(double a, double b) {
+  if (std::isnan(a) || std::isnan(b)) return std::numeric_limits<double>::quiet_NaN();
+  return a < b ? a : b;
+}
+
+// ToInt32: NaN/Inf -> 0, otherwise truncate and wrap modulo 2^32.
+inline int32_t js_to_int32(double v) {
+  if (!std::isfinite(v)) return 0;
+  double t = std::trunc(v);
+  double m = std::fmod(t, 4294967296.0);
+  if (m < 0) m += 4294967296.0;
+  return (int32_t)(uint32_t)m;
+}
+// Store into Int8Array / Uint8Array: ToInt32 then keep the low 8 bits.
+inline int8_t js_to_int8(double v) { return (int8_t)(uint8_t)(uint32_t)js_to_int32(v); }
+
+// x || fallback  (0, -0 and NaN are falsy)
+inline double js_or(double x, double fallback) { return (x == 0.0 || std::isnan(x)) ? fallback : x; }
+
+// ---------------------------------------------------------------------------
+// Seeded data: src/util/random.ts:5-14 (mulberry32)
+// ---------------------------------------------------------------------------
+struct Mulberry32 {
+  uint32_t a;
+  explicit Mulberry32(uint32_t seed) : a(seed) {}
+  double next() {
+    a += 0x6d2b79f5u;
+    uint32_t t = (a ^ (a >> 15)) * (1u | a);
+    t = (t + ((t ^ (t >> 7)) * (61u | t))) ^ t;
+    return (double)(t ^ (t >> 14)) / 4294967296.0;
+  }
+};
+
+enum { SCHEME_SYM = 0, SCHEME_ASYM = 1, SCHEME_PER_CHANNEL = 2 };
+enum { DT_I8 = 0, DT_UI8 = 1 };
+
+// quantization_types.ts:62-73
+inline void clamp_range(int scheme, int dtype, int numBits, double* cMin, double* cMax) {
+  if (scheme == SCHEME_SYM) {
+    double b = std::ldexp(1.0, numBits - 1) - 1.0;
+    *cMin = -b; *cMax = b; return;
+  }
+  if (dtype == DT_UI8) { *cMin = 0; *cMax = std::ldexp(1.0, numBits) - 1.0; return; }
+  *cMin = -std::ldexp(1.0, numBits - 1);
+  *cMax = std::ldexp(1.0, numBits - 1) - 1.0;
+}
+
+// quantization_types.ts:75-79 (also the body of quantizeArray / quantizeArrayPerChannel)
+inline double qp_quantize(double x, double scale, double zp, double cMin, double cMax) {
+  double raw = js_round(x / scale + zp);
+  return js_max(cMin, js_min(cMax, raw));
+}
+
+enum { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU_SIGMOID = 2, ACT_GELU_TANH = 3, ACT_SILU = 4 };
+
+// decomposition_pass.ts:197-203 evaluated by the CPU target: every f32 binary
+// op is computed in binary64 and rounded once (cpu/codegen.ts:496); exp is
+// Math.exp in binary64, then rounded (cpu/codegen.ts:532-534).
+inline float sigmoid_ref(float z) {
+  float e = (float)std::exp((double)(-z));
+  float d = (float)(1.0 + (double)e);
+  return (float)(1.0 / (double)d);
+}
+
+inline float activation_ref(float y, int act) {
+  switch (act) {
+    case ACT_NONE: return y;
+    case ACT_RELU: {  // builder.ts:561-565: maximum(x, 0) -> Math.max
+      double m = js_max((double)y, 0.0);
+      return (float)m;
+    }
+    case ACT_GELU_SIGMOID: {  // decomposition_pass.ts:212-222: x * sigmoid(1.702 x); 1.702 is a binary64 immediate
+      float z = (float)(1.702 * (double)y);
+      return (float)((double)y * (double)sigmoid_ref(z));
+    }
+    case ACT_SILU:  // decomposition_pass.ts:224-230
+      return (float)((double)y * (double)sigmoid_ref(y));
+    case ACT_GELU_TANH: {
+      // No reference implementation exists (the reference's gelu is the sigmoid
+      // form above).  Standard tanh form, each binary op rounded to binary32,
+      // tanh computed in binary64 then rounded, constants as binary64 immediates.
+      float y2 = (float)((double)y * (double)y);
+      float y3 = (float)((double)y2 * (double)y);
+      float c = (float)(0.044715 * (double)y3);
+      float in = (float)((double)y + (double)c);
+      float u = (float)(0.7978845608028654 * (double)in);
+      float t = (float)std::tanh((double)u);
+      float o = (float)(1.0 + (double)t);
+      float h = (float)(0.5 * (double)y);
+      return (float)((double)h * (double)o);
+    }
+  }
+  return y;
+}
+
+}  // namespace
+
+extern "C" {
+
+// --------------------------- seeded data -----------------------------------
+
+void orc_rng_uniform(uint32_t seed, int64_t n, double* out) {
+  Mulberry32 g(seed);
+  for (int64_t i = 0; i < n; i++) out[i] = g.next();
+}
+
+// nn/init.ts:40-53 normal_ (== creation_ops.ts:61-75 randn when mean 0, std 1); stored to Float32Array.
+void orc_normal_f32(uint32_t seed, int64_t n, double mean, double stdv, float* out) {
+  Mulberry32 g(seed);
+  for (int64_t i = 0; i < n; i += 2) {
+    double u1 = js_or(g.next(), 1e-10);
+    double u2 = g.next();
+    double r = std::sqrt(-2.0 * std::log(u1));
+    double theta = 6.283185307179586 * u2;
+    out[i] = (float)(mean + stdv * r * std::cos(theta));
+    if (i + 1 < n) out[i + 1] = (float)(mean + stdv * r * std::sin(theta));
+  }
+}
+
+// nn/init.ts:31-38 uniform_
+void orc_uniform_f32(uint32_t seed, int64_t n, double a, double b, float* out) {
+  Mulberry32 g(seed);
+  double range = b - a;
+  for (int64_t i = 0; i < n; i++) out[i] = (float)(a + g.next() * range);
+}
+
+// Integer weights uniform in [lo, hi]: floor(u * (hi-lo+1)) + lo (util/random.ts:36-38 randomInt).
+void orc_randint_i8(uint32_t seed, int64_t n, int lo, int hi, int8_t* out) {
+  Mulberry32 g(seed);
+  double span = (double)(hi - lo + 1);
+  for (int64_t i = 0; i < n; i++) out[i] = (int8_t)((int)std::floor(g.next() * span) + lo);
+}
+
+// --------------------------- QuantizationParams ----------------------------
+
+void orc_qp_clamp_range(int scheme, int dtype, int numBits, double* cMin, double* cMax) {
+  clamp_range(scheme, dtype, numBits, cMin, cMax);
+}
+
+// quantization_types.ts:241-264 fromRange
+void orc_qp_from_range(double mn, double mx, int scheme, int dtype, int numBits, double* scale, double* zp) {
+  if (scheme == SCHEME_SYM) {
+    double absMax = std::fmax(std::fabs(mn), std::fabs(mx));
+    double bound = std::ldexp(1.0, numBits - 1) - 1.0;
+    *scale = js_or(absMax / bound, 1e-10);
+    *zp = 0;
+    return;
+  }
+  double cMin, cMax;
+  if (dtype == DT_UI8) { cMin = 0; cMax = std::ldexp(1.0, numBits) - 1.0; }
+  else { cMin = -std::ldexp(1.0, numBits - 1); cMax = std::ldexp(1.0, numBits - 1) - 1.0; }
+  double range = js_or(mx - mn, 1e-10);
+  *scale = range / (cMax - cMin);
+  double z = js_round(cMin - mn / *scale);
+  *zp = js_max(cMin, js_min(cMax, z));
+}
+
+// quantization_types.ts:287-297 fromConstantArray
+void orc_qp_from_constant_array(const double* data, int64_t n, int scheme, int dtype, int numBits,
+                                double* scale, double* zp) {
+  double mn = INFINITY, mx = -INFINITY;
+  for (int64_t i = 0; i < n; i++) {
+    if (data[i] < mn) mn = data[i];
+    if (data[i] > mx) mx = data[i];
+  }
+  if (!std::isfinite(mn)) mn = -1;
+  if (!std::isfinite(mx)) mx = 1;
+  if (mn == mx) { mn -= 0.5; mx += 0.5; }
+  orc_qp_from_range(mn, mx, scheme, dtype, numBits, scale, zp);
+}
+
+double orc_qp_quantize(double x, double scale, double zp, double cMin, double cMax) {
+  return qp_quantize(x, scale, zp, cMin, cMax);
+}
+double orc_qp_dequantize(double q, double scale, double zp) { return (q - zp) * scale; }
+
+// quantization_types.ts:299-317 + 266-281: per-channel symmetric scales for a
+// tensor viewed as [outer, numCh, stride] (stride = product of dims after axis).
+#define ORC_PER_CHANNEL_SCALES(NAME, T)                                                          \
+  void NAME(const T* data, int64_t outer, int64_t numCh, int64_t stride, int numBits,            \
+            double* scales) {                                                                    \
+    std::vector<double> mins(numCh, INFINITY), maxs(numCh, -INFINITY);                           \
+    for (int64_t o = 0; o < outer; o++)                                                          \
+      for (int64_t c = 0; c < numCh; c++) {                                                      \
+        const T* p = data + (o * numCh + c) * stride;                                            \
+        double mn = mins[c], mx = maxs[c];                                                       \
+        for (int64_t s = 0; s < stride; s++) {                                                   \
+          double v = (double)p[s];                                                               \
+          if (v < mn) mn = v;                                                                    \
+          if (v > mx) mx = v;                                                                    \
+        }                                                                                        \
+        mins[c] = mn; maxs[c] = mx;                                                              \
+      }                                                                                          \
+    double bound = std::ldexp(1.0, numBits - 1) - 1.0;                                           \
+    for (int64_t c = 0; c < numCh; c++) {                                                        \
+      double mn = mins[c], mx = maxs[c];                                                         \
+      if (!std::isfinite(mn)) mn = -1;                                                           \
+      if (!std::isfinite(mx)) mx = 1;                                                            \
+      if (mn == mx) { mn -= 0.5; mx += 0.5; }                                                    \
+      double absMax = std::fmax(std::fabs(mn), std::fabs(mx));                                   \
+      scales[c] = js_or(absMax / bound, 1e-10);                                                  \
+    }                                                                                            \
+  }
+ORC_PER_CHANNEL_SCALES(orc_per_channel_scales_f32, float)
+ORC_PER_CHANNEL_SCALES(orc_per_channel_scales_f64, double)
+
+// quantization_types.ts:118-130 quantizeArrayPerChannel.  Codes are returned as
+// doubles (they may be NaN) and, separately, as they land in an Int8Array.
+#define ORC_QUANT_PER_CHANNEL(NAME, T)                                                           \
+  void NAME(const T* data, int64_t outer, int64_t numCh, int64_t stride, const double* scales,   \
+            double cMin, double cMax, int8_t* q8, double* qd) {                                  \
+    _Pragma("omp parallel for collapse(2) schedule(static)")                                     \
+    for (int64_t o = 0; o < outer; o++)                                                          \
+      for (int64_t c = 0; c < numCh; c++) {                                                      \
+        int64_t base = (o * numCh + c) * stride;                                                 \
+        double sc = scales[c];                                                                   \
+        for (int64_t s = 0; s < stride; s++) {                                                   \
+          double q = qp_quantize((double)data[base + s], sc, 0.0, cMin, cMax);                   \
+          if (q8) q8[base + s] = js_to_int8(q);                                                  \
+          if (qd) qd[base + s] = q;                                                              \
+        }                                                                                        \
+      }                                                                                          \
+  }
+ORC_QUANT_PER_CHANNEL(orc_quantize_per_channel_f32, float)
+ORC_QUANT_PER_CHANNEL(orc_quantize_per_channel_f64, double)
+
+// quantization_types.ts:132-141 dequantizeArrayPerChannel (binary64 result).
+void orc_dequantize_per_channel(const int8_t* q, int64_t outer, int64_t numCh, int64_t stride,
+                                const double* scales, double* out) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t o = 0; o < outer; o++)
+    for (int64_t c = 0; c < numCh; c++) {
+      int64_t base = (o * numCh + c) * stride;
+      for (int64_t s = 0; s < stride; s++) out[base + s] = ((double)q[base + s] - 0.0) * scales[c];
+    }
+}
+
+// Per-token activation quantization = fromConstantArrayPerChannel(x, [M,K], axis 0)
+// + quantizeArrayPerChannel; scales64 keeps the reference's binary64 scales,
+// scales32 is what the device interface carries (Float32Array store of the same number).
+void orc_quantize_per_token(const float* x, int64_t M, int64_t K, double cMin, double cMax,
+                            int8_t* q, double* scales64, float* scales32) {
+  std::vector<double> sc(M);
+  orc_per_channel_scales_f32(x, 1, M, K, 8, sc.data());
+  orc_quantize_per_channel_f32(x, 1, M, K, sc.data(), cMin, cMax, q, nullptr);
+  for (int64_t m = 0; m < M; m++) {
+    if (scales64) scales64[m] = sc[m];
+    if (scales32) scales32[m] = (float)sc[m];
+  }
+}
+
+// Device-interface dequantize: y = fround(q * (double)scale32[m]).
+void orc_dequantize_per_token_f32(const int8_t* q, const float* scales32, int64_t M, int64_t K, float* y) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; m++)
+    for (int64_t k = 0; k < K; k++) y[m * K + k] = (float)((double)q[m * K + k] * (double)scales32[m]);
+}
+
+// --------------------------- compiled ops (mode C) -------------------------
+
+// quant_math.ts:16-27 as emitted by cpu/codegen.ts: fround(x / scale) [fround(+zp)]
+// -> Math.round -> Math.max(cMin) -> Math.min(cMax) -> (v|0) -> Int8Array/Uint8Array store.
+void orc_quantize_static(const float* x, int64_t n, double scale, double zp, int dtype, int8_t* out) {
+  double cMin = dtype == DT_UI8 ? 0 : -128, cMax = dtype == DT_UI8 ? 255 : 127;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) {
+    double t = js_fround((double)x[i] / scale);
+    if (zp != 0) t = js_fround(t + zp);
+    double r = js_round(t);
+    double c = js_min(js_max(r, cMin), cMax);
+    out[i] = js_to_int8((double)js_to_int32(c));
+  }
+}
+
+// quant_math.ts:29-34: (+q) [fround(- zp)] then fround(* scale).  The int->f32
+// cast is emitted as (+x), i.e. NOT rounded to binary32 (cpu/codegen.ts:521).
+void orc_dequantize_static_i8(const int8_t* q, int64_t n, double scale, double zp, float* y) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) {
+    double v = (double)q[i];
+    if (zp != 0) v = js_fround(v - zp);
+    y[i] = (float)(v * scale);
+  }
+}
+void orc_dequantize_static_u8(const uint8_t* q, int64_t n, double scale, double zp, float* y) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) {
+    double v = (double)q[i];
+    if (zp != 0) v = js_fround(v - zp);
+    y[i] = (float)(v * scale);
+  }
+}
+void orc_dequantize_static_i32(const int32_t* q, int64_t n, double scale, double zp, float* y) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) {
+    double v = (double)q[i];
+    if (zp != 0) v = js_fround(v - zp);
+    y[i] = (float)(v * scale);
+  }
+}
+
+// rules/quantization.ts:23-42: C[m,n] = sum_k (A[m,k]-zpA) * (B-zpB), accumulated
+// exactly (binary64 in JS; all partial sums are integers below 2^53) and stored
+// to an Int32Array (ToInt32 wrap).  w_layout 0: W is [N,K] (contract dim 1);
+// 1: W is [K,N] (contract dim 0).  threads <= 0 means all cores.
+void orc_qdot_i32(const int8_t* A, const int8_t* W, int64_t M, int64_t N, int64_t K, int w_layout,
+                  int zpA, int zpB, int32_t* C, int threads) {
+#ifdef _OPENMP
+  int nt = threads > 0 ? threads : omp_get_max_threads();
+#else
+  int nt = 1;
+#endif
+  (void)nt;
+  std::vector<int8_t> wt;
+  const int8_t* Wnk = W;
+  if (w_layout == 1) {  // make K contiguous once; the arithmetic does not change
+    wt.resize((size_t)N * K);
+    for (int64_t k = 0; k < K; k++)
+      for (int64_t n = 0; n < N; n++) wt[(size_t)n * K + k] = W[(size_t)k * N + n];
+    Wnk = wt.data();
+  }
+#pragma omp parallel for schedule(static) num_threads(nt)
+  for (int64_t m = 0; m < M; m++) {
+    const int8_t* a = A + m * K;
+    for (int64_t n = 0; n < N; n++) {
+      const int8_t* w = Wnk + n * K;
+      int64_t acc = 0;
+      if (zpA == 0 && zpB == 0) {
+        int32_t acc32 = 0;  // exact while K*128*128 < 2^31 (K < 131072); chunked to be safe
+        for (int64_t k0 = 0; k0 < K; k0 += 65536) {
+          int64_t k1 = k0 + 65536 < K ? k0 + 65536 : K;
+          acc32 = 0;
+          for (int64_t k = k0; k < k1; k++) acc32 += (int32_t)a[k] * (int32_t)w[k];
+          acc += acc32;
+        }
+      } else {
+        for (int64_t k = 0; k < K; k++) acc += (int64_t)((int)a[k] - zpA) * (int64_t)((int)w[k] - zpB);
+      }
+      C[m * N + n] = (int32_t)(uint32_t)(uint64_t)acc;  // ToInt32 wrap
+    }
+  }
+}
+
+// Per-channel tail (quantization_pass.ts:427-456) + bias (nn/functional/linear.ts:13-15)
+// + activation, in the fused-region form the CPU target evaluates:
+//   sv   = fround(aScale * wScale[n])          (binary64 product stored as an f32 constant)
+//   t    = fround((+acc) * sv)                 (int->f32 cast is not rounded)
+//   y    = fround(t + bias[n])
+//   out  = act(y)
+// a_scales has M entries when per_token != 0 (the per-token extension: the same
+// expression with aScale varying per row), else one entry.
+void orc_epilogue(const int32_t* acc, int64_t M, int64_t N, const float* a_scales, int per_token,
+                  const float* w_scales, const float* bias, int act, float* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; m++) {
+    double as = (double)a_scales[per_token ? m : 0];
+    for (int64_t n = 0; n < N; n++) {
+      float sv = (float)(as * (double)w_scales[n]);
+      float t = (float)((double)acc[m * N + n] * (double)sv);
+      float y = bias ? (float)((double)t + (double)bias[n]) : t;
+      out[m * N + n] = activation_ref(y, act);
+    }
+  }
+}
+
+// Same tail when the scale vector is given directly (static activation scale:
+// sv[n] = fround(aScale64 * wScale64[n]) is formed by the caller in binary64).
+void orc_epilogue_sv(const int32_t* acc, int64_t M, int64_t N, const float* sv, const float* bias, int act,
+                     float* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; m++)
+    for (int64_t n = 0; n < N; n++) {
+      float t = (float)((double)acc[m * N + n] * (double)sv[n]);
+      float y = bias ? (float)((double)t + (double)bias[n]) : t;
+      out[m * N + n] = activation_ref(y, act);
+    }
+}
+
+void orc_activation(const float* y, int64_t n, int act, float* out) {
+  for (int64_t i = 0; i < n; i++) out[i] = activation_ref(y[i], act);
+}
+
+// calibration.ts:11-39 min/max observer (NaN never wins a strict comparison).
+void orc_minmax_observe(const float* x, int64_t n, double* mn, double* mx) {
+  double a = *mn, b = *mx;
+  for (int64_t i = 0; i < n; i++) {
+    double v = (double)x[i];
+    if (v < a) a = v;
+    if (v > b) b = v;
+  }
+  *mn = a; *mx = b;
+}
+
+double orc_js_round(double x) { return js_round(x); }
+int orc_num_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+}  // extern "C"
