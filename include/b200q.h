@@ -1,0 +1,145 @@
+/* b200q — C ABI of the B200 backend for mlfw's int8 quantized-inference path.
+ *
+ * The library is what the TypeScript host of mlfw binds through koffi (the way
+ * src/runtime/node/terac.ts:88-101 binds the terac C API).  Conventions follow
+ * terac/include/Tera/CAPI/Execution.h:40-81: opaque handle, functions return
+ * int (0 = ok) and leave a message for b200q_last_error() otherwise, no
+ * exceptions or callbacks cross the boundary, the caller frees what it
+ * allocated.
+ *
+ * Unless a function says "host", every data pointer is a DEVICE pointer obtained
+ * from b200q_alloc (or any CUDA allocation on the context's device).  Work is
+ * enqueued on the context's stream; b200q_sync waits for it.  A context belongs
+ * to one GPU and is not thread safe; distinct contexts may be used concurrently.
+ * There is no CPU fallback: without a usable CUDA device b200q_create fails.
+ *
+ * Paths cited below are inside the reference project (slexisvn/mlfw v0.1.6).
+ */
+#ifndef B200Q_H
+#define B200Q_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200q_ctx b200q_ctx;
+
+/* Activations of the fused tail (src/compiler/passes/decompose/decomposition_pass.ts:197-230;
+ * relu: src/compiler/ir/graph/builder.ts:561-565).  GELU_TANH has no counterpart
+ * in the reference (its gelu is the sigmoid form). */
+enum { B200Q_ACT_NONE = 0, B200Q_ACT_RELU = 1, B200Q_ACT_GELU_SIGMOID = 2, B200Q_ACT_GELU_TANH = 3, B200Q_ACT_SILU = 4 };
+/* Weight layouts: quantized_dot contracts rhs dim 1 ([N,K], a traced Linear) or
+ * dim 0 ([K,N]) (src/compiler/ir/graph/ops/quantization.ts:103-154). */
+enum { B200Q_W_NK = 0, B200Q_W_KN = 1 };
+/* Element kinds of the compiled quantize / dequantize ops (src/compiler/passes/lowering/quant_math.ts:7-14). */
+enum { B200Q_I8 = 0, B200Q_UI8 = 1, B200Q_I32 = 2 };
+
+/* ------------------------------------------------------------------ lifetime
+ * Replaces device bring-up of the reference CUDA runtime
+ * (src/runtime/node/cuda/device.ts:21-32, runtime_api.ts:16-18). */
+int b200q_device_count(void);
+int b200q_create(int device, b200q_ctx** out);
+void b200q_destroy(b200q_ctx* ctx);
+const char* b200q_last_error(void);           /* teraLastError, Execution.h:58 */
+int b200q_sync(b200q_ctx* ctx);
+/* Bits set by kernels that gave up a bounded wait (0 = healthy); reading clears nothing. */
+int b200q_status_word(b200q_ctx* ctx, uint32_t* out);
+int b200q_clear_status(b200q_ctx* ctx);
+/* Bound, in seconds, of every device-side wait of the tensor-core kernel (default 2). */
+int b200q_set_wait_limit(b200q_ctx* ctx, double seconds);
+/* 0: tensor-core GEMM whenever the shape allows (default); 1: CUDA-core kernel only. */
+int b200q_set_gemm_variant(b200q_ctx* ctx, int variant);
+/* Kernels launched through this context since it was created. */
+uint64_t b200q_launch_count(b200q_ctx* ctx);
+int b200q_sm_count(b200q_ctx* ctx);
+
+/* -------------------------------------------------------------------- memory
+ * teraDeviceAlloc / Free / Upload / Download (Execution.h:62-81); the reference
+ * CUDA runtime's pool (src/runtime/node/cuda/memory.ts). */
+int b200q_alloc(b200q_ctx* ctx, size_t bytes, void** dev);
+int b200q_free(b200q_ctx* ctx, void* dev);
+int b200q_memset(b200q_ctx* ctx, void* dev, int byte_value, size_t bytes);
+int b200q_upload(b200q_ctx* ctx, void* dev, const void* host, size_t bytes);     /* synchronous */
+int b200q_download(b200q_ctx* ctx, void* host, const void* dev, size_t bytes);   /* synchronous */
+int b200q_host_alloc(b200q_ctx* ctx, size_t bytes, void** host);                 /* page-locked host memory */
+int b200q_host_free(b200q_ctx* ctx, void* host);
+
+/* -------------------------------------------------------------------- timing
+ * CUDA events on the context's stream (the reference times with a host clock:
+ * measureCudaKernel, src/runtime/node/cuda_runtime.ts:46-76). */
+int b200q_timer_start(b200q_ctx* ctx);
+int b200q_timer_stop(b200q_ctx* ctx, float* elapsed_ms);                         /* synchronises */
+
+/* ------------------------------------------------- per-token (dynamic) ops
+ * QuantizationParams.fromConstantArrayPerChannel(x, [M,K], axis 0) +
+ * quantizeArrayPerChannel (src/compiler/ir/graph/quantization_types.ts:299-317,118-130):
+ * one symmetric scale per row, scale = absMax/127 (row range widened by +-0.5
+ * when all entries are equal, non-finite ends replaced by -+1), codes
+ * clamp(round_half_up(x / scale)) computed in binary64; NaN stores as 0.
+ * scales[m] receives the scale rounded to binary32. */
+int b200q_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t K, int8_t* q, float* scales, int qmin,
+                             int qmax);
+/* dequantizeArrayPerChannel (quantization_types.ts:132-141) with the binary32 scales: y = fround(q * scale[m]). */
+int b200q_dequantize_per_token(b200q_ctx* ctx, const int8_t* q, const float* scales, int64_t M, int64_t K, float* y);
+
+/* ------------------------------------------------- static (compiled) ops
+ * The `quantize` / `dequantize` graph ops (src/compiler/ir/graph/ops/quantization.ts:12-101,
+ * lowering src/compiler/passes/lowering/rules/quantization.ts:6-21, leaf math quant_math.ts:16-34)
+ * exactly as the CPU target evaluates them: fround(x / scale) [+ zero_point], Math.round,
+ * clamp to the dtype range, (v|0).  dst_kind: B200Q_I8 or B200Q_UI8. */
+int b200q_quantize_static(b200q_ctx* ctx, const float* x, int64_t n, double scale, int zero_point, int dst_kind, void* q);
+/* src_kind: B200Q_I8, B200Q_UI8 or B200Q_I32 (the result of quantized_dot). */
+int b200q_dequantize_static(b200q_ctx* ctx, const void* q, int src_kind, int64_t n, double scale, int zero_point, float* y);
+
+/* ------------------------------------------------- weights (once per model)
+ * QuantizationPass._replacePerChannelDot (src/compiler/passes/quantization/quantization_pass.ts:390-400):
+ * per-output-channel symmetric scales and codes of an f32 weight given as [N,K]
+ * (B200Q_W_NK) or [K,N] (B200Q_W_KN).  Codes are written K-major, qw[N,K].
+ * w_scales64 (binary64, as the pass keeps them) may be null. */
+int b200q_quantize_weights_per_channel(b200q_ctx* ctx, const float* w, int64_t N, int64_t K, int layout, int8_t* qw,
+                                       float* w_scales32, double* w_scales64);
+/* Re-lay int8 weights [K,N] as [N,K] (the layout the tensor-core kernel reads). */
+int b200q_transpose_i8(b200q_ctx* ctx, const int8_t* w_kn, int64_t K, int64_t N, int8_t* w_nk);
+
+/* ------------------------------------------------- contraction and tail
+ * quantized_dot (ops/quantization.ts:103-154; lowering rules/quantization.ts:23-42):
+ * C[m,n] = sum_k (A[m,k]-zpA) * (W[n,k]-zpW), int32.  W is [N,K]. */
+int b200q_int8_gemm_i32(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA,
+                        int zpW, int32_t* C);
+/* The per-channel tail as separate ops (quantization_pass.ts:427-456, nn/functional/linear.ts:13-15):
+ * out = act(fround(fround(acc * sv) + bias[n])) with sv = fround(a_scales[m] * w_scales[n]),
+ * or sv = w_scales[n] when a_scales is null (static activation scale folded by the host). */
+int b200q_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
+                   const float* bias, int act, float* out);
+/* quantized_dot + tail in one kernel.  A int8 [M,K], W int8 [N,K]. */
+int b200q_int8_linear(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk, const float* w_scales,
+                      const float* bias, int act, int64_t M, int64_t N, int64_t K, float* out);
+/* Same, followed by the next layer's static `quantize` (scale out_scale, zero-point 0, int8) inside the epilogue. */
+int b200q_int8_linear_requant_static(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk,
+                                     const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K,
+                                     double out_scale, int8_t* out_q);
+/* Same, followed by the next layer's per-token quantize (two kernels: the f32 result
+ * goes through a context-owned workspace). */
+int b200q_int8_linear_requant_token(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk,
+                                    const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K,
+                                    int8_t* out_q, float* out_scales);
+/* The whole hot path from f32 activations: per-token quantize (into a context-owned
+ * workspace), contraction, tail. */
+int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const float* w_scales, const float* bias, int act,
+                     int64_t M, int64_t N, int64_t K, float* out);
+/* Same call with HOST activations and HOST result (what RuntimeModule.run hands a
+ * backend: typed arrays, src/runtime/runtime.ts:239-268); weights stay on the device.
+ * Copies both ways and synchronises. */
+int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_nk, const float* w_scales, const float* bias,
+                          int act, int64_t M, int64_t N, int64_t K, float* out_host);
+/* Host-buffer round trip of the standalone ops: quantize_per_token then dequantize_per_token. */
+int b200q_quant_roundtrip_host(b200q_ctx* ctx, const float* x_host, int64_t M, int64_t K, int8_t* q_host, float* scales_host,
+                               float* y_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H */

@@ -1,0 +1,85 @@
+"""ctypes binding of ``libb200q.so`` — one prototype per declaration in ``include/b200q.h``.
+
+There is no fallback: if the library is missing or fails to load the import of the
+package raises, and every call that returns non-zero raises :class:`B200QError`
+with the library's own message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200q.so")
+
+c_i64, c_int, c_dbl, c_vp, c_sz = C.c_int64, C.c_int, C.c_double, C.c_void_p, C.c_size_t
+
+# name -> (restype, argtypes); kept in the order of the header
+PROTOTYPES = {
+    "b200q_device_count": (c_int, []),
+    "b200q_create": (c_int, [c_int, C.POINTER(c_vp)]),
+    "b200q_destroy": (None, [c_vp]),
+    "b200q_last_error": (C.c_char_p, []),
+    "b200q_sync": (c_int, [c_vp]),
+    "b200q_status_word": (c_int, [c_vp, C.POINTER(C.c_uint32)]),
+    "b200q_clear_status": (c_int, [c_vp]),
+    "b200q_set_wait_limit": (c_int, [c_vp, c_dbl]),
+    "b200q_set_gemm_variant": (c_int, [c_vp, c_int]),
+    "b200q_launch_count": (C.c_uint64, [c_vp]),
+    "b200q_sm_count": (c_int, [c_vp]),
+    "b200q_alloc": (c_int, [c_vp, c_sz, C.POINTER(c_vp)]),
+    "b200q_free": (c_int, [c_vp, c_vp]),
+    "b200q_memset": (c_int, [c_vp, c_vp, c_int, c_sz]),
+    "b200q_upload": (c_int, [c_vp, c_vp, c_vp, c_sz]),
+    "b200q_download": (c_int, [c_vp, c_vp, c_vp, c_sz]),
+    "b200q_host_alloc": (c_int, [c_vp, c_sz, C.POINTER(c_vp)]),
+    "b200q_host_free": (c_int, [c_vp, c_vp]),
+    "b200q_timer_start": (c_int, [c_vp]),
+    "b200q_timer_stop": (c_int, [c_vp, C.POINTER(C.c_float)]),
+    "b200q_quantize_per_token": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_int]),
+    "b200q_dequantize_per_token": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
+    "b200q_quantize_static": (c_int, [c_vp, c_vp, c_i64, c_dbl, c_int, c_int, c_vp]),
+    "b200q_dequantize_static": (c_int, [c_vp, c_vp, c_int, c_i64, c_dbl, c_int, c_vp]),
+    "b200q_quantize_weights_per_channel": (c_int, [c_vp, c_vp, c_i64, c_i64, c_int, c_vp, c_vp, c_vp]),
+    "b200q_transpose_i8": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp]),
+    "b200q_int8_gemm_i32": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_int, c_vp]),
+    "b200q_epilogue": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_int, c_vp]),
+    "b200q_int8_linear": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
+    "b200q_int8_linear_requant_static": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_dbl, c_vp]),
+    "b200q_int8_linear_requant_token": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp]),
+    "b200q_linear_f32": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
+    "b200q_linear_f32_host": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
+    "b200q_quant_roundtrip_host": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+}
+
+
+class B200QError(RuntimeError):
+    pass
+
+
+def load(path: str = LIB_PATH) -> C.CDLL:
+    if not os.path.exists(path):
+        raise B200QError(f"{path} is missing: build it with `python -m mlfw_b200.build` (nvcc, sm_100a). "
+                         "This backend has no CPU fallback.")
+    lib = C.CDLL(path)
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)  # AttributeError here means the header and the library disagree
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+_LIB = None
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        _LIB = load()
+    return _LIB
+
+
+def check(code: int, what: str = "") -> None:
+    if code != 0:
+        msg = lib().b200q_last_error()
+        raise B200QError(f"{what}: {msg.decode() if msg else 'error'} (code {code})")

@@ -1,0 +1,415 @@
+// The C ABI of libb200q.so (declared in include/b200q.h): argument checks on the
+// host before any launch, CUDA errors turned into return codes and a
+// thread-local message, no exceptions or aborts across the boundary.
+#include <cstdarg>
+#include <cstring>
+#include <new>
+
+#include "../../include/b200q.h"
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace b200q {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int ws_reserve(b200q_ctx* ctx, Workspace& ws, size_t bytes) {
+  if (bytes <= ws.bytes) return 0;
+  // Stream-ordered, so a buffer still read by queued kernels is released after them.
+  if (ws.ptr) B200Q_CHECK_CUDA(cudaFreeAsync(ws.ptr, ctx->stream));
+  ws.ptr = nullptr;
+  ws.bytes = 0;
+  size_t want = bytes + bytes / 8;
+  want = (want + 255) & ~size_t(255);
+  B200Q_CHECK_CUDA(cudaMallocAsync(&ws.ptr, want, ctx->stream));
+  ws.bytes = want;
+  return 0;
+}
+
+static int use_device(b200q_ctx* ctx) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_CHECK_CUDA(cudaSetDevice(ctx->device));
+  return 0;
+}
+
+static bool use_umma(b200q_ctx* ctx, const void* A, const void* W, int64_t M, int64_t N, int64_t K) {
+  return ctx->gemm_variant == 0 && gemm_umma_supported(A, W, M, N, K);
+}
+
+#define B200Q_DIMS_OK(M, N, K)                                                                              \
+  B200Q_REQUIRE((M) >= 0 && (N) >= 0 && (K) >= 0, "negative dimension (M=%lld N=%lld K=%lld)", (long long)(M), \
+                (long long)(N), (long long)(K))
+
+// quantized_dot + tail, any shape: tensor cores when possible, otherwise the CUDA-core
+// kernel into a workspace followed by the tail kernel.
+static int linear_core(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W, const float* w_scales,
+                       const float* bias, int act, int64_t M, int64_t N, int64_t K, float* out_f32, int8_t* out_q,
+                       double q_scale) {
+  if (M == 0 || N == 0) return 0;
+  if (K > 0 && use_umma(ctx, A, W, M, N, K))
+    return launch_gemm_i8_umma(ctx, A, W, M, N, K, a_scales, w_scales, bias, act, out_f32, nullptr, out_q, q_scale);
+  if (ws_reserve(ctx, ctx->ws_acc, (size_t)M * N * sizeof(int32_t))) return 1;
+  int32_t* acc = (int32_t*)ctx->ws_acc.ptr;
+  if (int e = launch_gemm_i8_simt(ctx, A, W, M, N, K, 0, 0, acc)) return e;
+  return launch_epilogue(ctx, acc, M, N, a_scales, w_scales, bias, act, out_f32, out_q, q_scale);
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    set_error("cudaGetDeviceCount failed: no usable CUDA driver or device");
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+const char* b200q_last_error(void) { return g_error; }
+
+int b200q_create(int device, b200q_ctx** out) {
+  B200Q_REQUIRE(out != nullptr, "b200q_create: null out pointer");
+  *out = nullptr;
+  int n = b200q_device_count();
+  B200Q_REQUIRE(n > 0, "b200q_create: no CUDA device is available (this backend has no CPU fallback)");
+  B200Q_REQUIRE(device >= 0 && device < n, "b200q_create: device %d out of range (0..%d)", device, n - 1);
+  B200Q_CHECK_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  B200Q_CHECK_CUDA(cudaGetDeviceProperties(&prop, device));
+  B200Q_REQUIRE(prop.major == 10, "b200q_create: device %d is sm_%d%d; this library is built for sm_100a only", device,
+                prop.major, prop.minor);
+  b200q_ctx* ctx = new (std::nothrow) b200q_ctx();
+  B200Q_REQUIRE(ctx != nullptr, "b200q_create: out of host memory");
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->l2_bytes = prop.l2CacheSize;
+  cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_start);
+  if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_stop);
+  if (e == cudaSuccess) e = cudaMalloc(&ctx->status_dev, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(ctx->status_dev, 0, sizeof(uint32_t));
+  if (e != cudaSuccess) {
+    set_error("b200q_create: %s", cudaGetErrorString(e));
+    b200q_destroy(ctx);
+    return 1;
+  }
+  *out = ctx;
+  return 0;
+}
+
+void b200q_destroy(b200q_ctx* ctx) {
+  if (!ctx) return;
+  cudaSetDevice(ctx->device);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  Workspace* all[] = {&ctx->ws_q, &ctx->ws_scales, &ctx->ws_acc, &ctx->ws_stage_in, &ctx->ws_stage_out};
+  for (Workspace* w : all)
+    if (w->ptr) cudaFree(w->ptr);
+  if (ctx->status_dev) cudaFree(ctx->status_dev);
+  if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+  if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
+  if (ctx->stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+}
+
+int b200q_sync(b200q_ctx* ctx) {
+  if (use_device(ctx)) return 1;
+  B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  return 0;
+}
+
+int b200q_status_word(b200q_ctx* ctx, uint32_t* out) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(out != nullptr, "b200q_status_word: null out pointer");
+  B200Q_CHECK_CUDA(cudaMemcpyAsync(out, ctx->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  return 0;
+}
+
+int b200q_clear_status(b200q_ctx* ctx) {
+  if (use_device(ctx)) return 1;
+  B200Q_CHECK_CUDA(cudaMemsetAsync(ctx->status_dev, 0, sizeof(uint32_t), ctx->stream));
+  return 0;
+}
+
+int b200q_set_wait_limit(b200q_ctx* ctx, double seconds) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_REQUIRE(seconds > 0 && seconds <= 60, "b200q_set_wait_limit: %g s is outside (0, 60]", seconds);
+  ctx->wait_limit_s = seconds;
+  return 0;
+}
+
+int b200q_set_gemm_variant(b200q_ctx* ctx, int variant) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_REQUIRE(variant == 0 || variant == 1, "b200q_set_gemm_variant: unknown variant %d", variant);
+  ctx->gemm_variant = variant;
+  return 0;
+}
+
+uint64_t b200q_launch_count(b200q_ctx* ctx) { return ctx ? ctx->launches : 0; }
+int b200q_sm_count(b200q_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+
+// ---------------------------------------------------------------- memory
+int b200q_alloc(b200q_ctx* ctx, size_t bytes, void** dev) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(dev != nullptr, "b200q_alloc: null out pointer");
+  *dev = nullptr;
+  if (bytes == 0) bytes = 16;
+  B200Q_CHECK_CUDA(cudaMalloc(dev, bytes));
+  return 0;
+}
+
+int b200q_free(b200q_ctx* ctx, void* dev) {
+  if (use_device(ctx)) return 1;
+  if (!dev) return 0;
+  B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  B200Q_CHECK_CUDA(cudaFree(dev));
+  return 0;
+}
+
+int b200q_memset(b200q_ctx* ctx, void* dev, int byte_value, size_t bytes) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(dev != nullptr || bytes == 0, "b200q_memset: null pointer");
+  if (bytes) B200Q_CHECK_CUDA(cudaMemsetAsync(dev, byte_value, bytes, ctx->stream));
+  return 0;
+}
+
+int b200q_upload(b200q_ctx* ctx, void* dev, const void* host, size_t bytes) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE((dev && host) || bytes == 0, "b200q_upload: null pointer");
+  if (bytes) {
+    B200Q_CHECK_CUDA(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
+  return 0;
+}
+
+int b200q_download(b200q_ctx* ctx, void* host, const void* dev, size_t bytes) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE((dev && host) || bytes == 0, "b200q_download: null pointer");
+  if (bytes) {
+    B200Q_CHECK_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
+  return 0;
+}
+
+int b200q_host_alloc(b200q_ctx* ctx, size_t bytes, void** host) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(host != nullptr, "b200q_host_alloc: null out pointer");
+  *host = nullptr;
+  if (bytes == 0) bytes = 16;
+  B200Q_CHECK_CUDA(cudaMallocHost(host, bytes));
+  return 0;
+}
+
+int b200q_host_free(b200q_ctx* ctx, void* host) {
+  if (use_device(ctx)) return 1;
+  if (host) B200Q_CHECK_CUDA(cudaFreeHost(host));
+  return 0;
+}
+
+// ---------------------------------------------------------------- timing
+int b200q_timer_start(b200q_ctx* ctx) {
+  if (use_device(ctx)) return 1;
+  B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_start, ctx->stream));
+  return 0;
+}
+
+int b200q_timer_stop(b200q_ctx* ctx, float* elapsed_ms) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(elapsed_ms != nullptr, "b200q_timer_stop: null out pointer");
+  B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_stop, ctx->stream));
+  B200Q_CHECK_CUDA(cudaEventSynchronize(ctx->ev_stop));
+  B200Q_CHECK_CUDA(cudaEventElapsedTime(elapsed_ms, ctx->ev_start, ctx->ev_stop));
+  return 0;
+}
+
+// ---------------------------------------------------------------- ops
+int b200q_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t K, int8_t* q, float* scales, int qmin,
+                             int qmax) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(M, 0, K);
+  B200Q_REQUIRE(M == 0 || K == 0 || (x && q), "b200q_quantize_per_token: null data pointer");
+  B200Q_REQUIRE(M == 0 || scales, "b200q_quantize_per_token: null scales pointer");
+  B200Q_REQUIRE(qmin >= -128 && qmax <= 127 && qmin < qmax, "b200q_quantize_per_token: clamp [%d,%d] is not an int8 range", qmin,
+                qmax);
+  B200Q_REQUIRE(K > 0 || M == 0, "b200q_quantize_per_token: rows of zero length have no range");
+  return launch_quantize_per_token(ctx, x, M, K, q, scales, qmin, qmax);
+}
+
+int b200q_dequantize_per_token(b200q_ctx* ctx, const int8_t* q, const float* scales, int64_t M, int64_t K, float* y) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(M, 0, K);
+  B200Q_REQUIRE(M == 0 || K == 0 || (q && scales && y), "b200q_dequantize_per_token: null pointer");
+  return launch_dequantize_per_token(ctx, q, scales, M, K, y);
+}
+
+int b200q_quantize_static(b200q_ctx* ctx, const float* x, int64_t n, double scale, int zero_point, int dst_kind, void* q) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(n >= 0, "b200q_quantize_static: negative length");
+  B200Q_REQUIRE(n == 0 || (x && q), "b200q_quantize_static: null pointer");
+  B200Q_REQUIRE(dst_kind == B200Q_I8 || dst_kind == B200Q_UI8, "b200q_quantize_static: target must be int8 or uint8");
+  B200Q_REQUIRE(scale == scale && scale != 0.0, "b200q_quantize_static: scale must be a non-zero number");
+  B200Q_REQUIRE(zero_point >= -128 && zero_point <= 255, "b200q_quantize_static: zero point %d outside 8-bit range", zero_point);
+  return launch_quantize_static(ctx, x, n, scale, zero_point, dst_kind, q);
+}
+
+int b200q_dequantize_static(b200q_ctx* ctx, const void* q, int src_kind, int64_t n, double scale, int zero_point, float* y) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(n >= 0, "b200q_dequantize_static: negative length");
+  B200Q_REQUIRE(n == 0 || (q && y), "b200q_dequantize_static: null pointer");
+  B200Q_REQUIRE(src_kind == B200Q_I8 || src_kind == B200Q_UI8 || src_kind == B200Q_I32,
+                "b200q_dequantize_static: source must be int8, uint8 or int32");
+  return launch_dequantize_static(ctx, q, src_kind, n, scale, zero_point, y);
+}
+
+int b200q_quantize_weights_per_channel(b200q_ctx* ctx, const float* w, int64_t N, int64_t K, int layout, int8_t* qw,
+                                       float* w_scales32, double* w_scales64) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(0, N, K);
+  B200Q_REQUIRE(layout == B200Q_W_NK || layout == B200Q_W_KN, "b200q_quantize_weights_per_channel: unknown layout %d", layout);
+  B200Q_REQUIRE(N == 0 || K == 0 || (w && qw), "b200q_quantize_weights_per_channel: null pointer");
+  // per_channel scheme: clampRange() is [-128,127] (quantization_types.ts:62-73)
+  return launch_quantize_weights(ctx, w, N, K, layout, -128, 127, qw, w_scales32, w_scales64);
+}
+
+int b200q_transpose_i8(b200q_ctx* ctx, const int8_t* w_kn, int64_t K, int64_t N, int8_t* w_nk) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(0, N, K);
+  B200Q_REQUIRE(N == 0 || K == 0 || (w_kn && w_nk), "b200q_transpose_i8: null pointer");
+  return launch_transpose_i8(ctx, w_kn, K, N, w_nk);
+}
+
+int b200q_int8_gemm_i32(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpW,
+                        int32_t* C) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(M, N, K);
+  B200Q_REQUIRE(M == 0 || N == 0 || C, "b200q_int8_gemm_i32: null output");
+  B200Q_REQUIRE(M == 0 || N == 0 || K == 0 || (A && W_nk), "b200q_int8_gemm_i32: null operand");
+  B200Q_REQUIRE(zpA >= -128 && zpA <= 127 && zpW >= -128 && zpW <= 127, "b200q_int8_gemm_i32: zero point outside int8");
+  if (M == 0 || N == 0) return 0;
+  if (K == 0) {
+    B200Q_CHECK_CUDA(cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(int32_t), ctx->stream));
+    return 0;
+  }
+  if (zpA == 0 && zpW == 0 && use_umma(ctx, A, W_nk, M, N, K))
+    return launch_gemm_i8_umma(ctx, A, W_nk, M, N, K, nullptr, nullptr, nullptr, 0, nullptr, C, nullptr, 1.0);
+  return launch_gemm_i8_simt(ctx, A, W_nk, M, N, K, zpA, zpW, C);
+}
+
+int b200q_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
+                   const float* bias, int act, float* out) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(M, N, 0);
+  B200Q_REQUIRE(M == 0 || N == 0 || (acc && w_scales && out), "b200q_epilogue: null pointer");
+  B200Q_REQUIRE(act >= 0 && act <= 4, "b200q_epilogue: unknown activation %d", act);
+  return launch_epilogue(ctx, acc, M, N, a_scales, w_scales, bias, act, out, nullptr, 1.0);
+}
+
+static int check_linear(const char* who, const void* A, const void* W, const float* w_scales, int act, int64_t M, int64_t N,
+                        int64_t K, const void* out) {
+  B200Q_DIMS_OK(M, N, K);
+  B200Q_REQUIRE(act >= 0 && act <= 4, "%s: unknown activation %d", who, act);
+  B200Q_REQUIRE(M == 0 || N == 0 || (out && w_scales), "%s: null output or weight scales", who);
+  B200Q_REQUIRE(M == 0 || N == 0 || K == 0 || (A && W), "%s: null operand", who);
+  return 0;
+}
+
+int b200q_int8_linear(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk, const float* w_scales,
+                      const float* bias, int act, int64_t M, int64_t N, int64_t K, float* out) {
+  if (use_device(ctx)) return 1;
+  if (int e = check_linear("b200q_int8_linear", A, W_nk, w_scales, act, M, N, K, out)) return e;
+  return linear_core(ctx, A, a_scales, W_nk, w_scales, bias, act, M, N, K, out, nullptr, 1.0);
+}
+
+int b200q_int8_linear_requant_static(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk,
+                                     const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K,
+                                     double out_scale, int8_t* out_q) {
+  if (use_device(ctx)) return 1;
+  if (int e = check_linear("b200q_int8_linear_requant_static", A, W_nk, w_scales, act, M, N, K, out_q)) return e;
+  B200Q_REQUIRE(out_scale == out_scale && out_scale != 0.0, "b200q_int8_linear_requant_static: scale must be a non-zero number");
+  return linear_core(ctx, A, a_scales, W_nk, w_scales, bias, act, M, N, K, nullptr, out_q, out_scale);
+}
+
+int b200q_int8_linear_requant_token(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk,
+                                    const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K,
+                                    int8_t* out_q, float* out_scales) {
+  if (use_device(ctx)) return 1;
+  if (int e = check_linear("b200q_int8_linear_requant_token", A, W_nk, w_scales, act, M, N, K, out_q)) return e;
+  B200Q_REQUIRE(M == 0 || out_scales, "b200q_int8_linear_requant_token: null scales output");
+  if (M == 0 || N == 0) return 0;
+  // The f32 result lives in its own workspace: ws_acc may be in use by the CUDA-core path.
+  if (ws_reserve(ctx, ctx->ws_stage_out, (size_t)M * N * sizeof(float))) return 1;
+  float* y = (float*)ctx->ws_stage_out.ptr;
+  if (int e = linear_core(ctx, A, a_scales, W_nk, w_scales, bias, act, M, N, K, y, nullptr, 1.0)) return e;
+  return launch_quantize_per_token(ctx, y, M, N, out_q, out_scales, -127, 127);
+}
+
+int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const float* w_scales, const float* bias, int act,
+                     int64_t M, int64_t N, int64_t K, float* out) {
+  if (use_device(ctx)) return 1;
+  if (int e = check_linear("b200q_linear_f32", x, W_nk, w_scales, act, M, N, K, out)) return e;
+  B200Q_REQUIRE(K > 0 || M == 0, "b200q_linear_f32: rows of zero length have no range");
+  if (M == 0 || N == 0) return 0;
+  if (ws_reserve(ctx, ctx->ws_q, (size_t)M * K)) return 1;
+  if (ws_reserve(ctx, ctx->ws_scales, (size_t)M * sizeof(float))) return 1;
+  int8_t* q = (int8_t*)ctx->ws_q.ptr;
+  float* s = (float*)ctx->ws_scales.ptr;
+  if (int e = launch_quantize_per_token(ctx, x, M, K, q, s, -127, 127)) return e;
+  return linear_core(ctx, q, s, W_nk, w_scales, bias, act, M, N, K, out, nullptr, 1.0);
+}
+
+int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_nk, const float* w_scales, const float* bias,
+                          int act, int64_t M, int64_t N, int64_t K, float* out_host) {
+  if (use_device(ctx)) return 1;
+  if (int e = check_linear("b200q_linear_f32_host", x_host, W_nk, w_scales, act, M, N, K, out_host)) return e;
+  if (M == 0 || N == 0) return 0;
+  if (ws_reserve(ctx, ctx->ws_stage_in, (size_t)M * K * sizeof(float))) return 1;
+  if (ws_reserve(ctx, ctx->ws_stage_out, (size_t)M * N * sizeof(float))) return 1;
+  float* x = (float*)ctx->ws_stage_in.ptr;
+  float* y = (float*)ctx->ws_stage_out.ptr;
+  B200Q_CHECK_CUDA(cudaMemcpyAsync(x, x_host, (size_t)M * K * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  if (int e = b200q_linear_f32(ctx, x, W_nk, w_scales, bias, act, M, N, K, y)) return e;
+  B200Q_CHECK_CUDA(cudaMemcpyAsync(out_host, y, (size_t)M * N * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  return 0;
+}
+
+int b200q_quant_roundtrip_host(b200q_ctx* ctx, const float* x_host, int64_t M, int64_t K, int8_t* q_host, float* scales_host,
+                               float* y_host) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(M, 0, K);
+  B200Q_REQUIRE(M == 0 || K == 0 || (x_host && y_host), "b200q_quant_roundtrip_host: null pointer");
+  if (M == 0 || K == 0) return 0;
+  const size_t n = (size_t)M * K;
+  if (ws_reserve(ctx, ctx->ws_stage_in, n * sizeof(float))) return 1;
+  if (ws_reserve(ctx, ctx->ws_stage_out, n * sizeof(float))) return 1;
+  if (ws_reserve(ctx, ctx->ws_q, n)) return 1;
+  if (ws_reserve(ctx, ctx->ws_scales, (size_t)M * sizeof(float))) return 1;
+  float* x = (float*)ctx->ws_stage_in.ptr;
+  float* y = (float*)ctx->ws_stage_out.ptr;
+  int8_t* q = (int8_t*)ctx->ws_q.ptr;
+  float* s = (float*)ctx->ws_scales.ptr;
+  B200Q_CHECK_CUDA(cudaMemcpyAsync(x, x_host, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  if (int e = launch_quantize_per_token(ctx, x, M, K, q, s, -127, 127)) return e;
+  if (int e = launch_dequantize_per_token(ctx, q, s, M, K, y)) return e;
+  if (q_host) B200Q_CHECK_CUDA(cudaMemcpyAsync(q_host, q, n, cudaMemcpyDeviceToHost, ctx->stream));
+  if (scales_host) B200Q_CHECK_CUDA(cudaMemcpyAsync(scales_host, s, (size_t)M * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  B200Q_CHECK_CUDA(cudaMemcpyAsync(y_host, y, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  return 0;
+}
+
+}  // extern "C"

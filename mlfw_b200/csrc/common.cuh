@@ -1,0 +1,67 @@
+// Host-side plumbing shared by the translation units of libb200q.so.
+#pragma once
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cuda_runtime.h>
+
+namespace b200q {
+
+// Thread-local error text returned by b200q_last_error().
+void set_error(const char* fmt, ...);
+
+#define B200Q_CHECK_CUDA(expr)                                                              \
+  do {                                                                                      \
+    cudaError_t _e = (expr);                                                                \
+    if (_e != cudaSuccess) {                                                                \
+      ::b200q::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+      return 1;                                                                             \
+    }                                                                                       \
+  } while (0)
+
+#define B200Q_REQUIRE(cond, ...)        \
+  do {                                  \
+    if (!(cond)) {                      \
+      ::b200q::set_error(__VA_ARGS__);  \
+      return 2;                         \
+    }                                   \
+  } while (0)
+
+// Bits of the device status word (b200q_status_word).  A kernel sets a bit and
+// returns instead of trapping or spinning for ever; the host reads the word
+// after synchronising.
+enum StatusBits : uint32_t {
+  STATUS_TMA_WAIT_TIMEOUT = 1u << 0,   // producer gave up waiting for a free pipeline slot
+  STATUS_MMA_WAIT_TIMEOUT = 1u << 1,   // MMA issuer gave up waiting for operands or a free accumulator
+  STATUS_EPI_WAIT_TIMEOUT = 1u << 2,   // epilogue gave up waiting for an accumulator
+  STATUS_BAD_TMEM_ALLOC = 1u << 3,     // tensor-memory allocation returned an unexpected address
+};
+
+struct Workspace {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+}  // namespace b200q
+
+// The context behind the opaque handle of the C ABI: one per GPU, not thread safe.
+struct b200q_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int l2_bytes = 0;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+  uint32_t* status_dev = nullptr;        // device status word
+  b200q::Workspace ws_q;                 // int8 activations of the fused linear
+  b200q::Workspace ws_scales;            // their per-token scales
+  b200q::Workspace ws_acc;               // int32 / f32 intermediates of the unfused paths
+  b200q::Workspace ws_stage_in, ws_stage_out;  // device staging of the host-buffer entry points
+  double wait_limit_s = 2.0;             // bound of every device-side wait
+  int gemm_variant = 0;                  // 0 = auto (tensor cores when the shape allows), 1 = CUDA-core kernel only
+  bool umma_ready = false;               // shared-memory attribute of the tensor-core kernel set on this device
+  uint64_t launches = 0;                 // kernels launched through this context
+};
+
+namespace b200q {
+int ws_reserve(b200q_ctx* ctx, Workspace& ws, size_t bytes);
+}

@@ -1,0 +1,440 @@
+// int8 x int8 -> int32 GEMM on the 5th-generation tensor cores with the whole
+// quantized-linear tail fused into the epilogue.
+//
+//   C[m,n] = sum_k A[m,k] * W[n,k]                    (tcgen05.mma.kind::i8, int32 in tensor memory)
+//   y      = act( C * (aScale[m] * wScale[n]) + bias[n] )     -> f32, or
+//   q      = static requantization of y                        -> int8, or
+//   C                                                           -> int32
+//
+// Reference semantics: quantized_dot (src/compiler/passes/lowering/rules/
+// quantization.ts:23-42) followed by the per-channel tail the quantization pass
+// emits (src/compiler/passes/quantization/quantization_pass.ts:427-456), bias
+// (src/nn/functional/linear.ts:13-15) and the decomposed activation.  Fusing is a
+// performance change only: the arithmetic is the same chain, rounded at the
+// same points (see quant_math.cuh).
+//
+// Structure (one CTA per SM, persistent over 128x256 output tiles):
+//   warp 0     TMA producer: A tile 128x128 B and W tile 256x128 B per stage, 128-byte swizzle
+//   warp 1     allocates tensor memory, one lane issues tcgen05.mma (4 per stage, K = 32 each)
+//   warps 2-5  epilogue: tcgen05.ld of a finished accumulator, tail arithmetic, global stores
+// The accumulator is double buffered in tensor memory (2 x 256 columns), so the
+// epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Every wait is bounded: a role that waits longer than the context's limit sets a
+// bit in the status word, raises a CTA-wide abort flag and all roles leave their
+// loops; the CTA then lets copies in flight land, frees tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.cuh"
+#include "quant_math.cuh"
+
+namespace b200q {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 128;  // int8: bytes == elements
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 32;
+constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int EPI_WARPS = 4;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
+constexpr int TMEM_COLS = 512;
+constexpr int MISC_BYTES = 1024;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + MISC_BYTES + 1024;  // + slack to align the tiles to 1024 B
+
+struct GemmParams {
+  int64_t M, N, K;
+  const float* a_scales;  // [M] or null
+  const float* w_scales;  // [N]; null when the raw accumulator is the output
+  const float* bias;      // [N] or null
+  int act;
+  float* out_f32;
+  int32_t* out_i32;
+  int8_t* out_q;
+  double q_scale;
+  float q_inv;
+  int q_exact;
+  uint32_t* status;
+  unsigned long long wait_limit_ns;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false means "give up" (either this wait ran out or another role raised the abort flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned long long limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++it & 31u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 B,
+// groups of 8 rows 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;              // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset
+  d |= (uint64_t)1 << 46;              // version
+  d |= (uint64_t)2 << 61;              // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::i8: D = S32, A = B = signed 8-bit, both K-major, M = 128, N = 256.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct Misc {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  double exp_tbl[64];
+};
+static_assert(sizeof(Misc) <= MISC_BYTES, "misc region too small");
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(tiles + STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &misc->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + BM - 1) / BM;
+  const int64_t num_tiles = tiles_m * tiles_n;
+  const int num_kb = (int)((p.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(smem_u32(&misc->full[s]), 1);
+      mbar_init(smem_u32(&misc->empty[s]), 1);
+    }
+    for (int s = 0; s < 2; s++) {
+      mbar_init(smem_u32(&misc->tmem_full[s]), 1);
+      mbar_init(smem_u32(&misc->tmem_empty[s]), EPI_WARPS);
+    }
+    misc->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  fill_exp2_table(misc->exp_tbl, threadIdx.x, blockDim.x);
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&misc->tmem_base)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = misc->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (int)(tile / tiles_n) * BM, n0 = (int)(tile % tiles_n) * BN;
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&misc->empty[s]), ph ^ 1u, abort_flag, p.wait_limit_ns)) {
+            atomicOr(p.status, STATUS_TMA_WAIT_TIMEOUT);
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&misc->full[s]);
+          mbar_expect_tx(bar, STAGE_BYTES);
+          uint8_t* st = tiles + s * STAGE_BYTES;
+          tma_load_2d(smem_u32(st), &tmA, bar, kb * BK, m0);
+          tma_load_2d(smem_u32(st + A_BYTES), &tmB, bar, kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, tile_it++) {
+        const uint32_t slot = tile_it & 1u, tph = (tile_it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&misc->tmem_empty[slot]), tph ^ 1u, abort_flag, p.wait_limit_ns)) {
+          atomicOr(p.status, STATUS_MMA_WAIT_TIMEOUT);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + slot * BN;
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&misc->full[s]), ph, abort_flag, p.wait_limit_ns)) {
+            atomicOr(p.status, STATUS_MMA_WAIT_TIMEOUT);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
+          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++) {
+            // advancing K inside the 128-byte swizzle atom = advancing the start address by 32 B
+            umma_i8(tmem_d, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc, (kb | k) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&misc->empty[s]));  // frees the stage when these MMAs have read it
+        }
+        if (ok) umma_commit(smem_u32(&misc->tmem_full[slot]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // tensor-memory lanes this warp may read: [32*quarter, 32*quarter+32)
+    const double* tbl = misc->exp_tbl;
+    const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out_f32) & 15u) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.out_i32) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(p.out_q) & 3u) == 0);
+    uint32_t tile_it = 0;
+    for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tile_it++) {
+      const uint32_t slot = tile_it & 1u, tph = (tile_it >> 1) & 1u;
+      const int64_t m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      bool ok = true;
+      if (lane == 0) {
+        ok = mbar_wait(smem_u32(&misc->tmem_full[slot]), tph, abort_flag, p.wait_limit_ns);
+        if (!ok) atomicOr(p.status, STATUS_EPI_WAIT_TIMEOUT);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t m = m0 + quarter * 32 + lane;
+      const bool row_ok = m < p.M;
+      const float a_scale = (p.a_scales && row_ok) ? __ldg(p.a_scales + m) : 1.0f;
+      const uint32_t taddr_row = tmem_base + slot * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        const int64_t nb = n0 + c * 32;
+        if (nb >= p.N) break;  // uniform across the CTA
+        int acc[32];
+        tmem_ld32(taddr_row + (uint32_t)(c * 32), acc);
+        if (!row_ok) continue;
+        const bool full = vec_ok && (nb + 32 <= p.N);
+        if (p.out_i32) {
+          int32_t* o = p.out_i32 + m * p.N + nb;
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(o + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (nb + j < p.N) o[j] = acc[j];
+          }
+          continue;
+        }
+        float y[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          const int64_t n = nb + j;
+          const bool col_ok = full || n < p.N;
+          const float ws = col_ok ? __ldg(p.w_scales + n) : 0.0f;
+          const float sv = p.a_scales ? __fmul_rn(a_scale, ws) : ws;
+          float v = scale_acc(acc[j], sv);
+          if (p.bias) v = __fadd_rn(v, col_ok ? __ldg(p.bias + n) : 0.0f);
+          y[j] = apply_act(v, p.act, tbl);
+        }
+        if (p.out_f32) {
+          float* o = p.out_f32 + m * p.N + nb;
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (nb + j < p.N) o[j] = y[j];
+          }
+        }
+        if (p.out_q) {
+          int8_t* o = p.out_q + m * p.N + nb;
+          int code[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) code[j] = quantize_code_c(y[j], p.q_scale, p.q_inv, 0.0f, p.q_exact != 0, -128.0f, 127.0f);
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<uint32_t*>(o + j) = (uint32_t)(code[j] & 0xff) | ((uint32_t)(code[j + 1] & 0xff) << 8) |
+                                                    ((uint32_t)(code[j + 2] & 0xff) << 16) | ((uint32_t)(code[j + 3] & 0xff) << 24);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (nb + j < p.N) o[j] = (int8_t)code[j];
+          }
+        }
+      }
+      // this warp is done reading the accumulator: hand the slot back to the MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&misc->tmem_empty[slot]));
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*abort_flag) {
+    // Something gave up.  Let bulk copies and MMAs that are still in flight finish
+    // before shared and tensor memory are released (bounded: 2 ms).
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Row-major int8 matrix [rows, K]; box = 128 bytes of K by box_rows rows, 128-byte swizzle, zero fill outside.
+int make_tensor_map(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t K, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  B200Q_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200Q_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (rows=%lld K=%lld)", (int)r, (long long)rows,
+                (long long)K);
+  return 0;
+}
+
+}  // namespace
+
+bool gemm_umma_supported(const void* A, const void* W, int64_t M, int64_t N, int64_t K) {
+  return M > 0 && N > 0 && K > 0 && (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) &&
+         ((reinterpret_cast<uintptr_t>(W) & 15u) == 0) && M < (1ll << 31) - BM && N < (1ll << 31) - BN && K < (1ll << 31) - BK;
+}
+
+int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K,
+                        const float* a_scales, const float* w_scales, const float* bias, int act, float* out_f32,
+                        int32_t* out_i32, int8_t* out_q, double q_scale) {
+  B200Q_REQUIRE(gemm_umma_supported(A, W_nk, M, N, K), "tensor-core int8 gemm needs K %% 16 == 0 and 16-byte aligned operands");
+  if (!ctx->umma_ready) {
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(gemm_i8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    ctx->umma_ready = true;
+  }
+  CUtensorMap tmA, tmB;
+  if (int e = make_tensor_map(&tmA, A, M, K, BM)) return e;
+  if (int e = make_tensor_map(&tmB, W_nk, N, K, BN)) return e;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_scales = a_scales; p.w_scales = w_scales; p.bias = bias; p.act = act;
+  p.out_f32 = out_f32; p.out_i32 = out_i32; p.out_q = out_q;
+  p.q_scale = q_scale;
+  p.q_inv = 0.0f; p.q_exact = 0;
+  if (out_q) {
+    p.q_inv = (float)(1.0 / q_scale);
+    float a = p.q_inv < 0 ? -p.q_inv : p.q_inv;
+    p.q_exact = !(a >= 1.17549435e-38f && a <= 3.402823466e38f);
+  }
+  p.status = ctx->status_dev;
+  p.wait_limit_ns = (unsigned long long)(ctx->wait_limit_s * 1e9);
+  const int64_t num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const unsigned grid = (unsigned)(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);
+  gemm_i8_umma_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace b200q

@@ -1,0 +1,32 @@
+// Launchers implemented by the kernel translation units; called by the C ABI (api.cu).
+// All of them enqueue on ctx->stream and return 0 or a non-zero code after set_error().
+#pragma once
+#include <cstdint>
+
+struct b200q_ctx;
+
+namespace b200q {
+
+int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t K, int8_t* q, float* scales, int qmin, int qmax);
+int launch_dequantize_per_token(b200q_ctx* ctx, const int8_t* q, const float* scales, int64_t M, int64_t K, float* y);
+// dst_kind / src_kind: 0 = int8, 1 = uint8, 2 = int32 (source of dequantize only)
+int launch_quantize_static(b200q_ctx* ctx, const float* x, int64_t n, double scale, int zp, int dst_kind, void* q);
+int launch_dequantize_static(b200q_ctx* ctx, const void* q, int src_kind, int64_t n, double scale, int zp, float* y);
+// layout 0: w is [N,K]; 1: w is [K,N].  Codes are always written [N,K].
+int launch_quantize_weights(b200q_ctx* ctx, const float* w, int64_t N, int64_t K, int layout, int qmin, int qmax, int8_t* qw,
+                            float* scales32, double* scales64);
+int launch_transpose_i8(b200q_ctx* ctx, const int8_t* src_kn, int64_t K, int64_t N, int8_t* dst_nk);
+
+int launch_gemm_i8_simt(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,
+                        int32_t* C);
+// Exactly one of out_f32 / out_q is written (both may be given); out_q uses the static scale q_scale.
+int launch_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
+                    const float* bias, int act, float* out_f32, int8_t* out_q, double q_scale);
+
+bool gemm_umma_supported(const void* A, const void* W, int64_t M, int64_t N, int64_t K);
+// Tensor-core GEMM with the fused tail.  out_i32 != null: raw accumulators (tail arguments ignored).
+int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K,
+                        const float* a_scales, const float* w_scales, const float* bias, int act, float* out_f32,
+                        int32_t* out_i32, int8_t* out_q, double q_scale);
+
+}  // namespace b200q

@@ -1,0 +1,447 @@
+// Quantize / dequantize kernels: HBM-streaming, 128-bit loads and stores where
+// the layout allows, warp-shuffle reductions for the per-token range.
+//
+// What they compute (reference, paths inside the reference project):
+//   per token   src/compiler/ir/graph/quantization_types.ts:299-317 (range per row),
+//               :266-281 (scale = absMax/127 || 1e-10), :118-130 (codes), :132-141 (dequantize)
+//   static      src/compiler/passes/lowering/quant_math.ts:16-34 as emitted by
+//               src/backend/cpu/codegen.ts:474-545
+//   weights     src/compiler/passes/quantization/quantization_pass.ts:390-400
+#include "common.cuh"
+#include "kernels.cuh"
+#include "quant_math.cuh"
+
+namespace b200q {
+
+namespace {
+
+__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
+
+// Scale of one row from its NaN-ignoring min and max (quantization_types.ts:308-316, 271-275).
+__device__ __forceinline__ double row_scale(float mn_f, float mx_f) {
+  double mn = (double)mn_f, mx = (double)mx_f;
+  if (!isfinite(mn)) mn = -1.0;
+  if (!isfinite(mx)) mx = 1.0;
+  if (mn == mx) { mn -= 0.5; mx += 0.5; }
+  double absmax = fmax(fabs(mn), fabs(mx));
+  double s = absmax / 127.0;
+  return (s == 0.0 || s != s) ? 1e-10 : s;
+}
+
+__device__ __forceinline__ bool is_normal_f32(float v) {
+  float a = fabsf(v);
+  return a >= 1.17549435e-38f && a <= 3.402823466e38f;
+}
+
+// ---------------------------------------------------------------------------
+// Per-token quantize, row resident in registers.
+// A group of G threads owns one row of K = 4*K4 floats; each thread holds VPT
+// float4 vectors (coalesced: vector i of a thread is G vectors after vector i-1).
+// One read of x, one write of q: 5 bytes per element of HBM traffic.
+// ---------------------------------------------------------------------------
+template <int VPT>
+__global__ void __launch_bounds__(1024) quantize_per_token_vec_kernel(const float* __restrict__ x, int64_t M, int K4, int G,
+                                                                       int8_t* __restrict__ q, float* __restrict__ scales,
+                                                                       float qmin, float qmax) {
+  __shared__ float s_mn[32], s_mx[32];
+  const int rows_per_block = blockDim.x / G;
+  const int grp = threadIdx.x / G;
+  const int t = threadIdx.x - grp * G;
+  const int64_t row = (int64_t)blockIdx.x * rows_per_block + grp;
+  const bool live = row < M;
+  const float4* xr = reinterpret_cast<const float4*>(x) + row * K4;
+
+  const float qnan = __int_as_float(0x7fc00000);
+  float4 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {
+    int c = t + i * G;
+    v[i] = (live && c < K4) ? ld_stream(xr + c) : make_float4(qnan, qnan, qnan, qnan);
+  }
+  float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {  // fminf/fmaxf drop NaN operands, as the strict < and > of the reference do
+    mn = fminf(fminf(mn, v[i].x), fminf(fminf(v[i].y, v[i].z), v[i].w));
+    mx = fmaxf(fmaxf(mx, v[i].x), fmaxf(fmaxf(v[i].y, v[i].z), v[i].w));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (G > 32) {
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) { s_mn[warp] = mn; s_mx[warp] = mx; }
+    __syncthreads();
+    const int w0 = (grp * G) >> 5, nw = G >> 5;
+    float a = s_mn[w0], b = s_mx[w0];
+    for (int w = 1; w < nw; w++) { a = fminf(a, s_mn[w0 + w]); b = fmaxf(b, s_mx[w0 + w]); }
+    mn = a; mx = b;
+  }
+  if (!live) return;
+
+  // One lane per warp does the binary64 divisions, the others receive the result.
+  double s = 0.0;
+  float inv = 0.0f;
+  if ((threadIdx.x & 31) == 0) {
+    s = row_scale(mn, mx);
+    inv = (float)(1.0 / s);
+  }
+  s = __hiloint2double(__shfl_sync(0xffffffffu, __double2hiint(s), 0), __shfl_sync(0xffffffffu, __double2loint(s), 0));
+  inv = __shfl_sync(0xffffffffu, inv, 0);
+  const bool exact_only = !is_normal_f32(inv);
+
+  uint32_t* qr = reinterpret_cast<uint32_t*>(q) + row * K4;
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {
+    int c = t + i * G;
+    if (c < K4) {
+      int c0 = quantize_code_p(v[i].x, s, inv, exact_only, qmin, qmax);
+      int c1 = quantize_code_p(v[i].y, s, inv, exact_only, qmin, qmax);
+      int c2 = quantize_code_p(v[i].z, s, inv, exact_only, qmin, qmax);
+      int c3 = quantize_code_p(v[i].w, s, inv, exact_only, qmin, qmax);
+      uint32_t packed = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) |
+                        ((uint32_t)(c3 & 0xff) << 24);
+      __stcs(qr + c, packed);
+    }
+  }
+  if (t == 0) scales[row] = (float)s;
+}
+
+// Any K, any alignment: one block per row, the row is read twice (the second
+// read is served by L2 for rows up to tens of megabytes).
+__global__ void __launch_bounds__(256) quantize_per_token_generic_kernel(const float* __restrict__ x, int64_t M, int64_t K,
+                                                                         int8_t* __restrict__ q, float* __restrict__ scales,
+                                                                         float qmin, float qmax) {
+  __shared__ float s_mn[8], s_mx[8];
+  __shared__ double s_scale;
+  __shared__ float s_inv;
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float* xr = x + row * K;
+    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x) {
+      float vv = xr[k];
+      mn = fminf(mn, vv);
+      mx = fmaxf(mx, vv);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) { s_mn[threadIdx.x >> 5] = mn; s_mx[threadIdx.x >> 5] = mx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < (int)(blockDim.x >> 5); w++) { mn = fminf(mn, s_mn[w]); mx = fmaxf(mx, s_mx[w]); }
+      double s = row_scale(mn, mx);
+      s_scale = s;
+      s_inv = (float)(1.0 / s);
+      scales[row] = (float)s;
+    }
+    __syncthreads();
+    const double s = s_scale;
+    const float inv = s_inv;
+    const bool exact_only = !is_normal_f32(inv);
+    int8_t* qr = q + row * K;
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x)
+      qr[k] = (int8_t)quantize_code_p(xr[k], s, inv, exact_only, qmin, qmax);
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Per-token dequantize: y[m,k] = fround(q[m,k] * scale[m]).  A thread turns VPT
+// packed words (4 codes each) into VPT float4 stores.
+// ---------------------------------------------------------------------------
+template <int VPT>
+__global__ void __launch_bounds__(256) dequantize_per_token_vec_kernel(const int8_t* __restrict__ q,
+                                                                       const float* __restrict__ scales, int64_t M, int K4,
+                                                                       float* __restrict__ y) {
+  const int64_t row = blockIdx.x;
+  const float s = __ldg(scales + row);
+  const uint32_t* qr = reinterpret_cast<const uint32_t*>(q) + row * K4;
+  float4* yr = reinterpret_cast<float4*>(y) + row * K4;
+  const int base = blockIdx.y * (blockDim.x * VPT) + threadIdx.x;
+  uint32_t w[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {
+    int c = base + i * blockDim.x;
+    w[i] = (c < K4) ? __ldcs(qr + c) : 0u;
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {
+    int c = base + i * blockDim.x;
+    if (c < K4) {
+      float4 o;
+      o.x = __fmul_rn((float)(int8_t)(w[i] & 0xff), s);
+      o.y = __fmul_rn((float)(int8_t)((w[i] >> 8) & 0xff), s);
+      o.z = __fmul_rn((float)(int8_t)((w[i] >> 16) & 0xff), s);
+      o.w = __fmul_rn((float)(int8_t)(w[i] >> 24), s);
+      __stcs(yr + c, o);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) dequantize_per_token_generic_kernel(const int8_t* __restrict__ q,
+                                                                           const float* __restrict__ scales, int64_t M,
+                                                                           int64_t K, float* __restrict__ y) {
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float s = scales[row];
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x) y[row * K + k] = __fmul_rn((float)q[row * K + k], s);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Static-scale (compiled-op) quantize / dequantize over a flat tensor.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) quantize_static_kernel(const float* __restrict__ x, int64_t n, double s, float inv,
+                                                              float zp, int exact_only, float qmin, float qmax,
+                                                              int8_t* __restrict__ q, int vec_ok) {
+  const bool exact = exact_only != 0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t n4 = vec_ok ? (n >> 2) : 0;
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  uint32_t* q4 = reinterpret_cast<uint32_t*>(q);
+  for (int64_t i = tid; i < n4; i += stride) {
+    float4 v = ld_stream(x4 + i);
+    int c0 = quantize_code_c(v.x, s, inv, zp, exact, qmin, qmax);
+    int c1 = quantize_code_c(v.y, s, inv, zp, exact, qmin, qmax);
+    int c2 = quantize_code_c(v.z, s, inv, zp, exact, qmin, qmax);
+    int c3 = quantize_code_c(v.w, s, inv, zp, exact, qmin, qmax);
+    __stcs(q4 + i, (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) |
+                       ((uint32_t)(c3 & 0xff) << 24));
+  }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += stride)
+    q[i] = (int8_t)quantize_code_c(x[i], s, inv, zp, exact, qmin, qmax);
+}
+
+// (+q) [fround(- zp)] then fround(* s): the int -> f32 cast is not rounded (cpu/codegen.ts:521).
+__device__ __forceinline__ float dequant_c(int qv, double s, float zp) {
+  if (zp != 0.0f) return __double2float_rn((double)__double2float_rn((double)qv - (double)zp) * s);
+  return __double2float_rn((double)qv * s);
+}
+
+// 8-bit sources have 256 possible codes: a shared-memory table of the exact
+// results keeps binary64 off the streaming path.  src_kind 0 = i8, 1 = ui8.
+__global__ void __launch_bounds__(256) dequantize_static_8_kernel(const uint8_t* __restrict__ q, int64_t n, double s, float zp,
+                                                                  int src_kind, float* __restrict__ y, int vec_ok) {
+  __shared__ float lut[256];
+  {
+    int b = threadIdx.x;  // blockDim.x == 256
+    int code = src_kind == 0 ? (int)(int8_t)b : b;
+    lut[b] = dequant_c(code, s, zp);
+  }
+  __syncthreads();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t n4 = vec_ok ? (n >> 2) : 0;
+  const uint32_t* q4 = reinterpret_cast<const uint32_t*>(q);
+  float4* y4 = reinterpret_cast<float4*>(y);
+  for (int64_t i = tid; i < n4; i += stride) {
+    uint32_t w = __ldcs(q4 + i);
+    float4 o = make_float4(lut[w & 0xff], lut[(w >> 8) & 0xff], lut[(w >> 16) & 0xff], lut[w >> 24]);
+    __stcs(y4 + i, o);
+  }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += stride) y[i] = lut[q[i]];
+}
+
+__global__ void __launch_bounds__(256) dequantize_static_i32_kernel(const int32_t* __restrict__ q, int64_t n, double s, float zp,
+                                                                    float* __restrict__ y) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = dequant_c(q[i], s, zp);
+}
+
+// ---------------------------------------------------------------------------
+// Weight preparation (once per model): per-output-channel symmetric scales and
+// int8 codes, written K-major ([N,K]) whatever the source layout.
+// ---------------------------------------------------------------------------
+// layout 0: w is [N,K] (channel = row); layout 1: w is [K,N] (channel = column).
+__global__ void __launch_bounds__(256) weight_range_kernel(const float* __restrict__ w, int64_t N, int64_t K, int layout,
+                                                           double* __restrict__ scales64, float* __restrict__ scales32) {
+  __shared__ float s_mn[8], s_mx[8];
+  for (int64_t n = blockIdx.x; n < N; n += gridDim.x) {
+    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x) {
+      float v = layout == 0 ? w[n * K + k] : w[k * N + n];
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) { s_mn[threadIdx.x >> 5] = mn; s_mx[threadIdx.x >> 5] = mx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int wi = 1; wi < (int)(blockDim.x >> 5); wi++) { mn = fminf(mn, s_mn[wi]); mx = fmaxf(mx, s_mx[wi]); }
+      double s = row_scale(mn, mx);
+      if (scales64) scales64[n] = s;
+      if (scales32) scales32[n] = (float)s;
+    }
+    __syncthreads();
+  }
+}
+
+// 32x32 tile through shared memory so that both the read (source layout) and
+// the write ([N,K]) are coalesced.  Every code takes the exact binary64 path:
+// this runs once per weight.
+__global__ void __launch_bounds__(256) weight_quantize_kernel(const float* __restrict__ w, int64_t N, int64_t K, int layout,
+                                                              const double* __restrict__ scales64, float qmin, float qmax,
+                                                              int8_t* __restrict__ qw) {
+  __shared__ float tile[32][33];
+  const int64_t n0 = (int64_t)blockIdx.y * 32, k0 = (int64_t)blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int j = ty; j < 32; j += 8) {
+    if (layout == 0) {
+      int64_t n = n0 + j, k = k0 + tx;
+      tile[j][tx] = (n < N && k < K) ? w[n * K + k] : 0.0f;  // tile[n][k]
+    } else {
+      int64_t k = k0 + j, n = n0 + tx;
+      tile[tx][j] = (n < N && k < K) ? w[k * N + n] : 0.0f;  // tile[n][k]
+    }
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    int64_t n = n0 + j, k = k0 + tx;
+    if (n < N && k < K) qw[n * K + k] = (int8_t)quantize_code_p(tile[j][tx], scales64[n], 0.0f, true, qmin, qmax);
+  }
+}
+
+// int8 [K,N] -> [N,K]
+__global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* __restrict__ src, int64_t K, int64_t N,
+                                                           int8_t* __restrict__ dst) {
+  __shared__ int8_t tile[32][33];
+  const int64_t n0 = (int64_t)blockIdx.y * 32, k0 = (int64_t)blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int j = ty; j < 32; j += 8) {
+    int64_t k = k0 + j, n = n0 + tx;
+    tile[j][tx] = (k < K && n < N) ? src[k * N + n] : (int8_t)0;
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    int64_t n = n0 + j, k = k0 + tx;
+    if (n < N && k < K) dst[n * K + k] = tile[tx][j];
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+// ----------------------------------------------------------------------------
+// Launchers
+// ----------------------------------------------------------------------------
+int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t K, int8_t* q, float* scales, int qmin,
+                              int qmax) {
+  if (M == 0 || K == 0) {
+    return 0;
+  }
+  const bool vec = (K % 4 == 0) && aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 3u) == 0) && (K / 4 <= 8 * 1024);
+  if (vec) {
+    const int K4 = (int)(K / 4);
+    int G = 32;
+    while (G < 1024 && (K4 + G - 1) / G > 4) G <<= 1;
+    const int vpt_needed = (K4 + G - 1) / G;
+    const int threads = G < 256 ? 256 : G;
+    const int rows_per_block = threads / G;
+    const unsigned blocks = (unsigned)((M + rows_per_block - 1) / rows_per_block);
+    if (vpt_needed <= 1)
+      quantize_per_token_vec_kernel<1><<<blocks, threads, 0, ctx->stream>>>(x, M, K4, G, q, scales, (float)qmin, (float)qmax);
+    else if (vpt_needed <= 2)
+      quantize_per_token_vec_kernel<2><<<blocks, threads, 0, ctx->stream>>>(x, M, K4, G, q, scales, (float)qmin, (float)qmax);
+    else if (vpt_needed <= 4)
+      quantize_per_token_vec_kernel<4><<<blocks, threads, 0, ctx->stream>>>(x, M, K4, G, q, scales, (float)qmin, (float)qmax);
+    else
+      quantize_per_token_vec_kernel<8><<<blocks, threads, 0, ctx->stream>>>(x, M, K4, G, q, scales, (float)qmin, (float)qmax);
+  } else {
+    const unsigned blocks = (unsigned)(M < (int64_t)ctx->sm_count * 8 ? M : (int64_t)ctx->sm_count * 8);
+    quantize_per_token_generic_kernel<<<blocks, 256, 0, ctx->stream>>>(x, M, K, q, scales, (float)qmin, (float)qmax);
+  }
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_dequantize_per_token(b200q_ctx* ctx, const int8_t* q, const float* scales, int64_t M, int64_t K, float* y) {
+  if (M == 0 || K == 0) return 0;
+  const bool vec = (K % 4 == 0) && aligned16(y) && ((reinterpret_cast<uintptr_t>(q) & 3u) == 0) && M < (1ll << 31);
+  if (vec) {
+    const int K4 = (int)(K / 4);
+    constexpr int VPT = 4;
+    const int per_block = 256 * VPT;
+    dim3 grid((unsigned)M, (unsigned)((K4 + per_block - 1) / per_block));
+    dequantize_per_token_vec_kernel<VPT><<<grid, 256, 0, ctx->stream>>>(q, scales, M, K4, y);
+  } else {
+    const unsigned blocks = (unsigned)(M < (int64_t)ctx->sm_count * 8 ? M : (int64_t)ctx->sm_count * 8);
+    dequantize_per_token_generic_kernel<<<blocks, 256, 0, ctx->stream>>>(q, scales, M, K, y);
+  }
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static unsigned flat_blocks(b200q_ctx* ctx, int64_t work_items) {
+  int64_t b = (work_items + 255) / 256;
+  int64_t cap = (int64_t)ctx->sm_count * 16;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (unsigned)b;
+}
+
+int launch_quantize_static(b200q_ctx* ctx, const float* x, int64_t n, double scale, int zp, int dst_kind, void* q) {
+  if (n == 0) return 0;
+  const float inv = (float)(1.0 / scale);
+  const float a = inv < 0 ? -inv : inv;
+  const int exact_only = !(a >= 1.17549435e-38f && a <= 3.402823466e38f) || zp != 0;
+  const float qmin = dst_kind == 1 ? 0.0f : -128.0f, qmax = dst_kind == 1 ? 255.0f : 127.0f;
+  const int vec_ok = aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 3u) == 0);
+  quantize_static_kernel<<<flat_blocks(ctx, (n + 3) / 4), 256, 0, ctx->stream>>>(x, n, scale, inv, (float)zp, exact_only, qmin,
+                                                                                   qmax, (int8_t*)q, vec_ok);
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_dequantize_static(b200q_ctx* ctx, const void* q, int src_kind, int64_t n, double scale, int zp, float* y) {
+  if (n == 0) return 0;
+  if (src_kind == 2) {
+    dequantize_static_i32_kernel<<<flat_blocks(ctx, n), 256, 0, ctx->stream>>>((const int32_t*)q, n, scale, (float)zp, y);
+  } else {
+    const int vec_ok = aligned16(y) && ((reinterpret_cast<uintptr_t>(q) & 3u) == 0);
+    dequantize_static_8_kernel<<<flat_blocks(ctx, (n + 3) / 4), 256, 0, ctx->stream>>>((const uint8_t*)q, n, scale, (float)zp,
+                                                                                         src_kind, y, vec_ok);
+  }
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_quantize_weights(b200q_ctx* ctx, const float* w, int64_t N, int64_t K, int layout, int qmin, int qmax, int8_t* qw,
+                            float* scales32, double* scales64) {
+  if (N == 0 || K == 0) return 0;
+  double* s64 = scales64;
+  if (!s64) {
+    if (ws_reserve(ctx, ctx->ws_acc, (size_t)N * sizeof(double))) return 1;
+    s64 = (double*)ctx->ws_acc.ptr;
+  }
+  const unsigned rb = (unsigned)(N < (int64_t)ctx->sm_count * 8 ? N : (int64_t)ctx->sm_count * 8);
+  weight_range_kernel<<<rb, 256, 0, ctx->stream>>>(w, N, K, layout, s64, scales32);
+  dim3 grid((unsigned)((K + 31) / 32), (unsigned)((N + 31) / 32));
+  weight_quantize_kernel<<<grid, 256, 0, ctx->stream>>>(w, N, K, layout, s64, (float)qmin, (float)qmax, qw);
+  ctx->launches += 2;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_transpose_i8(b200q_ctx* ctx, const int8_t* src_kn, int64_t K, int64_t N, int8_t* dst_nk) {
+  if (N == 0 || K == 0) return 0;
+  dim3 grid((unsigned)((K + 31) / 32), (unsigned)((N + 31) / 32));
+  transpose_i8_kernel<<<grid, 256, 0, ctx->stream>>>(src_kn, K, N, dst_nk);
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace b200q

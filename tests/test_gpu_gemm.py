@@ -1,0 +1,254 @@
+"""GPU parity of the int8 contraction and its fused tail against the CPU oracle (through the C ABI).
+
+int32 accumulators and int8 codes must be bit-exact.  f32 outputs of the relu / none /
+sigmoid-GELU / SiLU tails are expected bit-exact as well (the device follows the same
+rounding chain); the stated bar is 1e-5 of the output absmax, which is what gelu_tanh
+(no reference counterpart) is held to.
+"""
+import numpy as np
+import pytest
+
+from gpu_util import Guarded, activations, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import mlfw_b200
+    c = mlfw_b200.Context(0)
+    yield c
+    c.check_status()
+    c.close()
+
+
+def gemm_inputs(rng, M, N, K):
+    A = rng.integers(-127, 128, size=(M, K)).astype(np.int8)
+    W = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    return A, W
+
+
+# (M, N, K): ragged around the 64-wide tiles of the CUDA-core kernel and the 128x256x128 tiles of the tensor-core kernel
+SIMT_SHAPES = [(1, 1, 1), (4, 6, 8), (64, 32, 128), (3, 5, 7), (65, 130, 67), (128, 256, 100), (200, 70, 333)]
+UMMA_SHAPES = [(128, 256, 128), (1, 8, 16), (4, 6, 16), (64, 32, 128), (130, 260, 144), (256, 512, 1024), (128, 256, 4096),
+               (300, 768, 768), (129, 257, 272), (512, 1024, 512), (127, 255, 112), (1024, 256, 2048)]
+
+
+@pytest.mark.parametrize("M,N,K", SIMT_SHAPES + UMMA_SHAPES)
+def test_gemm_i32_cuda_cores(ctx, orc, M, N, K):
+    rng = np.random.default_rng(M * 1009 + N * 31 + K)
+    A, W = gemm_inputs(rng, M, N, K)
+    ctx.set_gemm_variant(1)
+    try:
+        dA, dW = Guarded(ctx, A.shape, np.int8, A), Guarded(ctx, W.shape, np.int8, W)
+        dC = Guarded(ctx, (M, N), np.int32)
+        ctx.int8_gemm_i32(dA.ptr, dW.ptr, M, N, K, dC.ptr)
+        ctx.sync()
+        assert (dC.download() == orc.qdot_i32(A, W)).all()
+    finally:
+        ctx.set_gemm_variant(0)
+
+
+@pytest.mark.parametrize("zpA,zpW", [(3, 0), (0, -5), (-128, 127), (7, 9)])
+def test_gemm_i32_zero_points(ctx, orc, zpA, zpW):
+    rng = np.random.default_rng(3)
+    M, N, K = 37, 45, 150
+    A = rng.integers(-128, 128, size=(M, K)).astype(np.int8)
+    W = rng.integers(-128, 128, size=(N, K)).astype(np.int8)
+    dA, dW = Guarded(ctx, A.shape, np.int8, A), Guarded(ctx, W.shape, np.int8, W)
+    dC = Guarded(ctx, (M, N), np.int32)
+    ctx.int8_gemm_i32(dA.ptr, dW.ptr, M, N, K, dC.ptr, zpA, zpW)
+    ctx.sync()
+    assert (dC.download() == orc.qdot_i32(A, W, "NK", zpA, zpW)).all()
+
+
+@pytest.mark.parametrize("M,N,K", UMMA_SHAPES)
+def test_gemm_i32_tensor_cores(ctx, orc, M, N, K):
+    rng = np.random.default_rng(M * 1009 + N * 31 + K + 1)
+    A, W = gemm_inputs(rng, M, N, K)
+    dA, dW = ctx.to_device(A), ctx.to_device(W)      # cudaMalloc alignment: the TMA path is taken
+    dC = Guarded(ctx, (M, N), np.int32)
+    ctx.int8_gemm_i32(dA.ptr, dW.ptr, M, N, K, dC.ptr)
+    ctx.sync()
+    ctx.check_status()
+    C = dC.download()
+    ref = orc.qdot_i32(A, W)
+    assert (C == ref).all(), f"{int((C != ref).sum())} of {C.size} accumulators differ"
+
+
+def test_gemm_i32_extreme_values(ctx, orc):
+    """All -128 x -128 over K = 4096 reaches 2^26: far above 2^24, still exact in int32."""
+    M, N, K = 128, 256, 4096
+    A = np.full((M, K), -128, np.int8)
+    W = np.full((N, K), -128, np.int8)
+    W[::2] = 127
+    dA, dW = ctx.to_device(A), ctx.to_device(W)
+    dC = Guarded(ctx, (M, N), np.int32)
+    ctx.int8_gemm_i32(dA.ptr, dW.ptr, M, N, K, dC.ptr)
+    ctx.sync()
+    assert (dC.download() == orc.qdot_i32(A, W)).all()
+
+
+def linear_case(rng, M, N, K, big_acc=False):
+    x = activations(rng, M, K)
+    W = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    ws = rng.uniform(1e-3, 1e-2, size=N).astype(np.float32) / np.float32(np.sqrt(K) / 8)
+    bias = (rng.standard_normal(N) * 0.01).astype(np.float32)
+    if big_acc:
+        W[: N // 2] = 127          # correlated weights: accumulators beyond 2^24
+        x = np.abs(x)
+    return x, W, ws, bias
+
+
+ACTS = ["none", "relu", "gelu_sigmoid", "silu", "gelu_tanh"]
+EXACT_ACTS = {"none", "relu", "gelu_sigmoid", "silu"}
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("act", ACTS)
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (130, 260, 144), (64, 1000, 768), (5, 7, 16)])
+def test_int8_linear_fused_tail(ctx, orc, M, N, K, act, variant):
+    rng = np.random.default_rng(M + N + K + len(act))
+    x, W, ws, bias = linear_case(rng, M, N, K)
+    q, _, s32 = orc.quantize_per_token(x)
+    acc = orc.qdot_i32(q, W)
+    ref = orc.epilogue(acc, s32, ws, bias, act)
+    ctx.set_gemm_variant(variant)
+    try:
+        dq, dW = ctx.to_device(q), ctx.to_device(W)
+        ds, dws, db = ctx.to_device(s32), ctx.to_device(ws), ctx.to_device(bias)
+        dout = Guarded(ctx, (M, N), np.float32)
+        ctx.int8_linear(dq.ptr, ds.ptr, dW.ptr, dws.ptr, db.ptr, act, M, N, K, dout.ptr)
+        ctx.sync()
+        ctx.check_status()
+    finally:
+        ctx.set_gemm_variant(0)
+    out = dout.download()
+    assert rel_err(out, ref) <= TOL
+    if act in EXACT_ACTS:
+        nd = int((out.view(np.uint32) != ref.view(np.uint32)).sum())
+        assert nd == 0, f"{nd} of {out.size} f32 outputs are not bit-identical to the oracle"
+
+
+def test_int8_linear_large_accumulators(ctx, orc):
+    """|acc| >= 2^24: the int -> f32 conversion of the reference is NOT rounded before the multiply."""
+    rng = np.random.default_rng(99)
+    M, N, K = 128, 256, 4096
+    x, W, ws, bias = linear_case(rng, M, N, K, big_acc=True)
+    q, _, s32 = orc.quantize_per_token(x)
+    acc = orc.qdot_i32(q, W)
+    assert np.abs(acc).max() >= 2 ** 24
+    ref = orc.epilogue(acc, s32, ws, bias, "none")
+    dq, dW = ctx.to_device(q), ctx.to_device(W)
+    ds, dws, db = ctx.to_device(s32), ctx.to_device(ws), ctx.to_device(bias)
+    dout = Guarded(ctx, (M, N), np.float32)
+    ctx.int8_linear(dq.ptr, ds.ptr, dW.ptr, dws.ptr, db.ptr, "none", M, N, K, dout.ptr)
+    ctx.sync()
+    assert (dout.download().view(np.uint32) == ref.view(np.uint32)).all()
+
+
+def test_int8_linear_static_scale_no_bias(ctx, orc):
+    """Reference scheme: static activation scale folded into sv[n] by the host (quantization_pass.ts:427-437)."""
+    rng = np.random.default_rng(5)
+    M, N, K = 64, 128, 256
+    x = activations(rng, M, K, outliers=False)
+    a_scale = 6 / 127
+    q = orc.quantize_static(x, a_scale, 0)
+    W = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    wsc = rng.uniform(1e-3, 1e-2, size=N)
+    sv = (a_scale * wsc).astype(np.float32)
+    ref = orc.epilogue_sv(orc.qdot_i32(q, W), sv, None, "relu")
+    dx = ctx.to_device(x)
+    dq = ctx.empty((M, K), np.int8)
+    ctx.quantize_static(dx.ptr, M * K, a_scale, 0, 0, dq.ptr)
+    dW, dsv = ctx.to_device(W), ctx.to_device(sv)
+    dout = Guarded(ctx, (M, N), np.float32)
+    ctx.int8_linear(dq.ptr, None, dW.ptr, dsv.ptr, None, "relu", M, N, K, dout.ptr)
+    ctx.sync()
+    assert (dq.download() == q).all()
+    assert (dout.download().view(np.uint32) == ref.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+def test_int8_linear_requant_static(ctx, orc, variant):
+    rng = np.random.default_rng(17)
+    M, N, K = 200, 520, 256
+    x, W, ws, bias = linear_case(rng, M, N, K)
+    q, _, s32 = orc.quantize_per_token(x)
+    y = orc.epilogue(orc.qdot_i32(q, W), s32, ws, bias, "relu")
+    out_scale = float(np.abs(y).max()) / 127
+    ref = orc.quantize_static(y, out_scale, 0)
+    ctx.set_gemm_variant(variant)
+    try:
+        dq, dW = ctx.to_device(q), ctx.to_device(W)
+        ds, dws, db = ctx.to_device(s32), ctx.to_device(ws), ctx.to_device(bias)
+        dout = Guarded(ctx, (M, N), np.int8)
+        ctx.int8_linear_requant_static(dq.ptr, ds.ptr, dW.ptr, dws.ptr, db.ptr, "relu", M, N, K, out_scale, dout.ptr)
+        ctx.sync()
+    finally:
+        ctx.set_gemm_variant(0)
+    assert (dout.download() == ref).all()
+
+
+def test_int8_linear_requant_token(ctx, orc):
+    rng = np.random.default_rng(18)
+    M, N, K = 130, 512, 256
+    x, W, ws, bias = linear_case(rng, M, N, K)
+    q, _, s32 = orc.quantize_per_token(x)
+    y = orc.epilogue(orc.qdot_i32(q, W), s32, ws, bias, "silu")
+    rq, _, rs = orc.quantize_per_token(y)
+    dq, dW = ctx.to_device(q), ctx.to_device(W)
+    ds, dws, db = ctx.to_device(s32), ctx.to_device(ws), ctx.to_device(bias)
+    doq = Guarded(ctx, (M, N), np.int8)
+    dos = Guarded(ctx, (M,), np.float32)
+    ctx.int8_linear_requant_token(dq.ptr, ds.ptr, dW.ptr, dws.ptr, db.ptr, "silu", M, N, K, doq.ptr, dos.ptr)
+    ctx.sync()
+    assert (dos.download().view(np.uint32) == rs.view(np.uint32)).all()
+    assert (doq.download() == rq).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 1024, 512), (33, 100, 48), (7, 9, 10)])
+def test_linear_f32_whole_path(ctx, orc, M, N, K):
+    """f32 activations -> per-token quantize -> contraction -> tail, device and host-buffer entry points."""
+    rng = np.random.default_rng(M * N + K)
+    x, W, ws, bias = linear_case(rng, M, N, K)
+    ref, _, _, _ = orc.linear(x, W, ws, bias, "relu")
+    dx, dW, dws, db = ctx.to_device(x), ctx.to_device(W), ctx.to_device(ws), ctx.to_device(bias)
+    dout = Guarded(ctx, (M, N), np.float32)
+    ctx.linear_f32(dx.ptr, dW.ptr, dws.ptr, db.ptr, "relu", M, N, K, dout.ptr)
+    ctx.sync()
+    assert (dout.download().view(np.uint32) == ref.view(np.uint32)).all()
+    out_host = np.zeros((M, N), np.float32)
+    ctx.linear_f32_host(x, dW.ptr, dws.ptr, db.ptr, "relu", M, N, K, out_host)
+    assert (out_host.view(np.uint32) == ref.view(np.uint32)).all()
+
+
+def test_epilogue_separate_op(ctx, orc):
+    """convert -> mul(scale vector) -> add(bias) -> activation as its own kernel (the reference's unfused chain)."""
+    rng = np.random.default_rng(23)
+    M, N = 70, 130
+    acc = rng.integers(-2 ** 27, 2 ** 27, size=(M, N)).astype(np.int32)
+    a = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    w = rng.uniform(1e-5, 1e-4, N).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    for act in ["none", "relu", "gelu_sigmoid", "silu"]:
+        ref = orc.epilogue(acc, a, w, b, act)
+        dacc, da, dw, db = ctx.to_device(acc), ctx.to_device(a), ctx.to_device(w), ctx.to_device(b)
+        dout = Guarded(ctx, (M, N), np.float32)
+        ctx.epilogue(dacc.ptr, M, N, da.ptr, dw.ptr, db.ptr, act, dout.ptr)
+        ctx.sync()
+        assert (dout.download().view(np.uint32) == ref.view(np.uint32)).all(), act
+
+
+def test_quant_roundtrip_host(ctx, orc):
+    rng = np.random.default_rng(29)
+    M, K = 64, 512
+    x = activations(rng, M, K)
+    q = np.zeros((M, K), np.int8)
+    s = np.zeros(M, np.float32)
+    y = np.zeros((M, K), np.float32)
+    ctx.quant_roundtrip_host(x, M, K, q, s, y)
+    rq, _, rs = orc.quantize_per_token(x)
+    assert (q == rq).all() and (s == rs).all()
+    assert (y == orc.dequantize_per_token_f32(rq, rs)).all()
