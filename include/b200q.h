@@ -73,6 +73,15 @@ int b200q_host_free(b200q_ctx* ctx, void* host);
 int b200q_timer_start(b200q_ctx* ctx);
 int b200q_timer_stop(b200q_ctx* ctx, float* elapsed_ms);                         /* synchronises */
 
+/* Per-kernel timing: while enabled, every kernel launch is bracketed by CUDA events
+ * and its duration added to the sum of its family.  Families (the `kind` argument):
+ * 0 quantize_per_token, 1 dequantize_per_token, 2 quantize_static, 3 dequantize_static,
+ * 4 weight preparation, 5 tensor-core GEMM (+ fused tail), 6 CUDA-core GEMM, 7 separate tail.
+ * (No counterpart in the reference, whose runtime only offers measureCudaKernel.) */
+int b200q_profile_enable(b200q_ctx* ctx, int on);
+int b200q_profile_reset(b200q_ctx* ctx);
+int b200q_profile_read(b200q_ctx* ctx, int kind, double* total_ms, uint64_t* launches);   /* synchronises */
+
 /* ------------------------------------------------- per-token (dynamic) ops
  * QuantizationParams.fromConstantArrayPerChannel(x, [M,K], axis 0) +
  * quantizeArrayPerChannel (src/compiler/ir/graph/quantization_types.ts:299-317,118-130):

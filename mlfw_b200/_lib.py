@@ -36,6 +36,9 @@ PROTOTYPES = {
     "b200q_host_free": (c_int, [c_vp, c_vp]),
     "b200q_timer_start": (c_int, [c_vp]),
     "b200q_timer_stop": (c_int, [c_vp, C.POINTER(C.c_float)]),
+    "b200q_profile_enable": (c_int, [c_vp, c_int]),
+    "b200q_profile_reset": (c_int, [c_vp]),
+    "b200q_profile_read": (c_int, [c_vp, c_int, C.POINTER(c_dbl), C.POINTER(C.c_uint64)]),
     "b200q_quantize_per_token": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_int]),
     "b200q_dequantize_per_token": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
     "b200q_quantize_static": (c_int, [c_vp, c_vp, c_i64, c_dbl, c_int, c_int, c_vp]),

@@ -37,7 +37,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
     cmd = [
-        _nvcc(), "-shared", "-o", LIB,
+        _nvcc(), "-shared", "-o", LIB + ".tmp",
         "-gencode", "arch=compute_100a,code=sm_100a",
         "-O3", "-lineinfo", "-std=c++17",
         "-Xcompiler", "-fPIC,-O2,-Wall",
@@ -50,6 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    os.replace(LIB + ".tmp", LIB)  # a failed build leaves the previous library in place
     if verbose:
         print(res.stdout + res.stderr)
     return LIB

@@ -33,6 +33,18 @@ int ws_reserve(b200q_ctx* ctx, Workspace& ws, size_t bytes) {
   return 0;
 }
 
+int prof_fold(b200q_ctx* ctx) {
+  for (int i = 0; i < ctx->prof_used; i++) {
+    float ms = 0.0f;
+    B200Q_CHECK_CUDA(cudaEventSynchronize(ctx->prof_ev[i][1]));
+    B200Q_CHECK_CUDA(cudaEventElapsedTime(&ms, ctx->prof_ev[i][0], ctx->prof_ev[i][1]));
+    ctx->prof_ms[ctx->prof_kind[i]] += ms;
+    ctx->prof_n[ctx->prof_kind[i]] += 1;
+  }
+  ctx->prof_used = 0;
+  return 0;
+}
+
 static int use_device(b200q_ctx* ctx) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
   B200Q_CHECK_CUDA(cudaSetDevice(ctx->device));
@@ -117,6 +129,9 @@ void b200q_destroy(b200q_ctx* ctx) {
   for (Workspace* w : all)
     if (w->ptr) cudaFree(w->ptr);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
+  for (int i = 0; i < PROFILE_RING; i++)
+    for (int j = 0; j < 2; j++)
+      if (ctx->prof_ev[i][j]) cudaEventDestroy(ctx->prof_ev[i][j]);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -154,6 +169,34 @@ int b200q_set_gemm_variant(b200q_ctx* ctx, int variant) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
   B200Q_REQUIRE(variant == 0 || variant == 1, "b200q_set_gemm_variant: unknown variant %d", variant);
   ctx->gemm_variant = variant;
+  return 0;
+}
+
+int b200q_profile_enable(b200q_ctx* ctx, int on) {
+  if (use_device(ctx)) return 1;
+  if (on && !ctx->prof_ev[0][0]) {
+    for (int i = 0; i < PROFILE_RING; i++)
+      for (int j = 0; j < 2; j++) B200Q_CHECK_CUDA(cudaEventCreate(&ctx->prof_ev[i][j]));
+  }
+  if (!on && ctx->profiling) prof_fold(ctx);
+  ctx->profiling = on != 0;
+  return 0;
+}
+
+int b200q_profile_reset(b200q_ctx* ctx) {
+  if (use_device(ctx)) return 1;
+  if (prof_fold(ctx)) return 1;
+  for (int k = 0; k < KK_COUNT; k++) { ctx->prof_ms[k] = 0.0; ctx->prof_n[k] = 0; }
+  return 0;
+}
+
+int b200q_profile_read(b200q_ctx* ctx, int kind, double* total_ms, uint64_t* launches) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(kind >= 0 && kind < KK_COUNT, "b200q_profile_read: unknown kernel family %d", kind);
+  B200Q_REQUIRE(total_ms && launches, "b200q_profile_read: null out pointer");
+  if (prof_fold(ctx)) return 1;
+  *total_ms = ctx->prof_ms[kind];
+  *launches = ctx->prof_n[kind];
   return 0;
 }
 

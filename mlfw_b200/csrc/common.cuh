@@ -37,6 +37,11 @@ enum StatusBits : uint32_t {
   STATUS_BAD_TMEM_ALLOC = 1u << 3,     // tensor-memory allocation returned an unexpected address
 };
 
+// Kernel families timed separately when profiling is on (b200q_profile_*).
+enum KernelKind : int { KK_QUANT_TOKEN = 0, KK_DEQUANT_TOKEN, KK_QUANT_STATIC, KK_DEQUANT_STATIC, KK_WEIGHTS, KK_GEMM_UMMA,
+                        KK_GEMM_SIMT, KK_EPILOGUE, KK_COUNT };
+constexpr int PROFILE_RING = 256;
+
 struct Workspace {
   void* ptr = nullptr;
   size_t bytes = 0;
@@ -58,10 +63,34 @@ struct b200q_ctx {
   b200q::Workspace ws_stage_in, ws_stage_out;  // device staging of the host-buffer entry points
   double wait_limit_s = 2.0;             // bound of every device-side wait
   int gemm_variant = 0;                  // 0 = auto (tensor cores when the shape allows), 1 = CUDA-core kernel only
-  bool umma_ready = false;               // shared-memory attribute of the tensor-core kernel set on this device
+  uint32_t umma_ready_mask = 0;          // tensor-core kernel variants whose shared-memory attribute is set on this device
   uint64_t launches = 0;                 // kernels launched through this context
+  // per-kernel CUDA-event timing (off by default): a ring of event pairs, folded into the sums when it wraps or is read
+  bool profiling = false;
+  cudaEvent_t prof_ev[b200q::PROFILE_RING][2] = {};
+  int prof_kind[b200q::PROFILE_RING] = {};
+  int prof_used = 0;
+  double prof_ms[b200q::KK_COUNT] = {};
+  uint64_t prof_n[b200q::KK_COUNT] = {};
 };
 
 namespace b200q {
 int ws_reserve(b200q_ctx* ctx, Workspace& ws, size_t bytes);
+int prof_fold(b200q_ctx* ctx);
+
+// Brackets the kernel launches of one launcher with an event pair when profiling is on.
+struct ProfScope {
+  b200q_ctx* ctx;
+  int idx = -1;
+  ProfScope(b200q_ctx* c, int kind) : ctx(c) {
+    if (!c->profiling) return;
+    if (c->prof_used == PROFILE_RING) prof_fold(c);
+    idx = c->prof_used++;
+    c->prof_kind[idx] = kind;
+    cudaEventRecord(c->prof_ev[idx][0], c->stream);
+  }
+  ~ProfScope() {
+    if (idx >= 0) cudaEventRecord(ctx->prof_ev[idx][1], ctx->stream);
+  }
+};
 }

@@ -89,7 +89,12 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const int32_t* __restrict
     if (bias) y = __fadd_rn(y, bias[n]);
     y = apply_act(y, act, tbl);
     if (out_f32) out_f32[i] = y;
-    if (out_q) out_q[i] = (int8_t)quantize_code_c(y, q_scale, q_inv, 0.0f, q_exact != 0, -128.0f, 127.0f);
+    if (out_q) {
+      bool redo;
+      int c = quantize_fast(y, q_inv, -128.0f, 127.0f, redo);
+      if (redo || q_exact) c = quantize_exact_c(y, q_scale, 0.0f, -128.0f, 127.0f);
+      out_q[i] = (int8_t)c;
+    }
   }
 }
 
@@ -97,6 +102,7 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const int32_t* __restrict
 
 int launch_gemm_i8_simt(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,
                         int32_t* C) {
+  ProfScope prof(ctx, KK_GEMM_SIMT);
   if (M == 0 || N == 0) return 0;
   dim3 grid((unsigned)((N + TN - 1) / TN), (unsigned)((M + TM - 1) / TM));
   B200Q_REQUIRE(grid.y <= 65535, "int8 gemm (simt): M too large for one launch (%lld rows)", (long long)M);
@@ -111,6 +117,7 @@ int launch_gemm_i8_simt(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
 
 int launch_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
                     const float* bias, int act, float* out_f32, int8_t* out_q, double q_scale) {
+  ProfScope prof(ctx, KK_EPILOGUE);
   if (M == 0 || N == 0) return 0;
   float q_inv = 0.0f;
   int q_exact = 0;

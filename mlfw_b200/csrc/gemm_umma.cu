@@ -16,7 +16,8 @@
 // Structure (one CTA per SM, persistent over 128x256 output tiles):
 //   warp 0     TMA producer: A tile 128x128 B and W tile 256x128 B per stage, 128-byte swizzle
 //   warp 1     allocates tensor memory, one lane issues tcgen05.mma (4 per stage, K = 32 each)
-//   warps 2-5  epilogue: tcgen05.ld of a finished accumulator, tail arithmetic, global stores
+//   warps 2-9  epilogue: tcgen05.ld of a finished accumulator, tail arithmetic, global stores
+//              (warp w reads tensor-memory lanes 32*(w%4).., i.e. 32 rows, and half of the columns)
 // The accumulator is double buffered in tensor memory (2 x 256 columns), so the
 // epilogue of tile i overlaps the main loop of tile i+1.
 //
@@ -24,6 +25,8 @@
 // bit in the status word, raises a CTA-wide abort flag and all roles leave their
 // loops; the CTA then lets copies in flight land, frees tensor memory and returns.
 #include <cuda.h>
+
+#include <cstddef>
 
 #include "common.cuh"
 #include "kernels.cuh"
@@ -37,10 +40,11 @@ constexpr int BM = 128, BN = 256, BK = 128;  // int8: bytes == elements
 constexpr int STAGES = 4;
 constexpr int UMMA_K = 32;
 constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int EPI_WARPS = 4;
+constexpr int EPI_WARPS = 8;                   // two warps per tensor-memory lane quarter, 128 columns each
+constexpr int EPI_COLS = BN / (EPI_WARPS / 4); // columns of a tile one epilogue warp handles
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr int MISC_BYTES = 1024;
+constexpr int MISC_BYTES = 1024 + EPI_WARPS * EPI_COLS * 8;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + MISC_BYTES + 1024;  // + slack to align the tiles to 1024 B
 
 struct GemmParams {
@@ -151,10 +155,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
         "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-struct Misc {
+struct alignas(16) Misc {
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
@@ -162,9 +166,15 @@ struct Misc {
   uint32_t tmem_base;
   int abort_flag;
   double exp_tbl[64];
+  alignas(16) float col_scale[EPI_WARPS][EPI_COLS];   // per-warp copy of w_scales for the tile's columns (read as float4)
+  alignas(16) float col_bias[EPI_WARPS][EPI_COLS];
 };
 static_assert(sizeof(Misc) <= MISC_BYTES, "misc region too small");
+static_assert(offsetof(Misc, col_scale) % 16 == 0 && offsetof(Misc, col_bias) % 16 == 0, "float4 reads need 16-byte alignment");
 
+enum OutMode : int { OUT_F32 = 0, OUT_I32 = 1, OUT_Q8 = 2 };
+
+template <int ACT_T, int OUT_T>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -261,14 +271,32 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int quarter = warp & 3;  // tensor-memory lanes this warp may read: [32*quarter, 32*quarter+32)
+    const int ew = warp - 2;             // 0..7
+    const int quarter = warp & 3;        // tensor-memory lanes this warp may read: [32*quarter, 32*quarter+32)
+    const int col0 = (ew >> 2) * EPI_COLS;  // first tile column of this warp
     const double* tbl = misc->exp_tbl;
-    const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out_f32) & 15u) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.out_i32) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(p.out_q) & 3u) == 0);
+    float* cs = misc->col_scale[ew];
+    float* cb = misc->col_bias[ew];
+    const bool has_bias = p.bias != nullptr;
+    // 16-byte stores need every row segment 16-byte aligned: N a multiple of 4 elements (f32, i32) or of 16 (int8).
+    const bool vec_ok = OUT_T == OUT_Q8 ? ((p.N % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out_q) & 15u) == 0))
+                        : OUT_T == OUT_I32 ? ((p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out_i32) & 15u) == 0))
+                                           : ((p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out_f32) & 15u) == 0));
     uint32_t tile_it = 0;
     for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tile_it++) {
       const uint32_t slot = tile_it & 1u, tph = (tile_it >> 1) & 1u;
-      const int64_t m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const int64_t m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN + col0;
+      if (OUT_T != OUT_I32) {
+        // Stage this warp's column scales and biases while the main loop of the tile still runs.
+        __syncwarp();
+#pragma unroll
+        for (int j = lane; j < EPI_COLS; j += 32) {
+          const int64_t n = n0 + j;
+          cs[j] = (n < p.N) ? __ldg(p.w_scales + n) : 0.0f;
+          cb[j] = (has_bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+        }
+        __syncwarp();
+      }
       bool ok = true;
       if (lane == 0) {
         ok = mbar_wait(smem_u32(&misc->tmem_full[slot]), tph, abort_flag, p.wait_limit_ns);
@@ -279,42 +307,59 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const int64_t m = m0 + quarter * 32 + lane;
       const bool row_ok = m < p.M;
-      const float a_scale = (p.a_scales && row_ok) ? __ldg(p.a_scales + m) : 1.0f;
-      const uint32_t taddr_row = tmem_base + slot * BN + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        const int64_t nb = n0 + c * 32;
-        if (nb >= p.N) break;  // uniform across the CTA
-        int acc[32];
-        tmem_ld32(taddr_row + (uint32_t)(c * 32), acc);
-        if (!row_ok) continue;
-        const bool full = vec_ok && (nb + 32 <= p.N);
-        if (p.out_i32) {
-          int32_t* o = p.out_i32 + m * p.N + nb;
-          if (full) {
+      const float a_scale = (p.a_scales && row_ok) ? __ldg(p.a_scales + m) : 1.0f;  // fround(1 * ws) == ws
+      const uint32_t taddr = tmem_base + slot * BN + (uint32_t)col0 + ((uint32_t)(quarter * 32) << 16);
+      constexpr int NCH = EPI_COLS / 32;
+      int acc[2][32];
+      if (n0 < p.N) tmem_ld32(taddr, acc[0]);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(o + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      for (int c = 0; c < NCH; c++) {
+        const int64_t nb = n0 + c * 32;
+        if (nb >= p.N) break;  // uniform across the warp
+        tmem_ld_wait();
+        if (c + 1 < NCH && nb + 32 < p.N) tmem_ld32(taddr + (uint32_t)((c + 1) * 32), acc[(c + 1) & 1]);
+        const int(&a)[32] = acc[c & 1];
+        // No lane may leave this iteration early: the tensor-memory loads and the vote below are
+        // warp-collective.  Rows past M compute on whatever the accumulator holds and store nothing.
+        const bool full = vec_ok && (nb + 32 <= p.N);
+        if (OUT_T == OUT_I32) {
+          int32_t* o = p.out_i32 + m * p.N + nb;
+          if (!row_ok) {
+          } else if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(o + j) = make_int4(a[j], a[j + 1], a[j + 2], a[j + 3]);
           } else {
 #pragma unroll
             for (int j = 0; j < 32; j++)
-              if (nb + j < p.N) o[j] = acc[j];
+              if (nb + j < p.N) o[j] = a[j];
           }
           continue;
         }
-        float y[32];
+        // |acc| >= 2^24 anywhere in this warp's chunk: the whole chunk takes the binary64 product.
+        int big = 0;
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
-          const int64_t n = nb + j;
-          const bool col_ok = full || n < p.N;
-          const float ws = col_ok ? __ldg(p.w_scales + n) : 0.0f;
-          const float sv = p.a_scales ? __fmul_rn(a_scale, ws) : ws;
-          float v = scale_acc(acc[j], sv);
-          if (p.bias) v = __fadd_rn(v, col_ok ? __ldg(p.bias + n) : 0.0f);
-          y[j] = apply_act(v, p.act, tbl);
+        for (int j = 0; j < 32; j++) big |= (abs(a[j]) >> 24);
+        const bool wide = __any_sync(0xffffffffu, big != 0);
+        float y[32];
+        const float4* cs4 = reinterpret_cast<const float4*>(cs + c * 32);
+        const float4* cb4 = reinterpret_cast<const float4*>(cb + c * 32);
+#pragma unroll
+        for (int j4 = 0; j4 < 8; j4++) {
+          const float4 w4 = cs4[j4], b4 = cb4[j4];
+          const float wsv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const int j = j4 * 4 + e;
+            const float sv = __fmul_rn(a_scale, wsv[e]);
+            float v = wide ? scale_acc_wide(a[j], sv) : scale_acc_small(a[j], sv);
+            if (has_bias) v = __fadd_rn(v, bv[e]);
+            y[j] = apply_act_t<ACT_T>(v, tbl);
+          }
         }
-        if (p.out_f32) {
+        if (OUT_T == OUT_F32) {
           float* o = p.out_f32 + m * p.N + nb;
-          if (full) {
+          if (!row_ok) {
+          } else if (full) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
           } else {
@@ -322,21 +367,39 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int j = 0; j < 32; j++)
               if (nb + j < p.N) o[j] = y[j];
           }
-        }
-        if (p.out_q) {
+        } else {
           int8_t* o = p.out_q + m * p.N + nb;
-          int code[32];
+          uint32_t words[8];
+          uint32_t redo = 0;
 #pragma unroll
-          for (int j = 0; j < 32; j++) code[j] = quantize_code_c(y[j], p.q_scale, p.q_inv, 0.0f, p.q_exact != 0, -128.0f, 127.0f);
-          if (full) {
+          for (int j4 = 0; j4 < 8; j4++) {
+            bool r0, r1, r2, r3;
+            const int c0 = quantize_fast(y[j4 * 4 + 0], p.q_inv, -128.0f, 127.0f, r0);
+            const int c1 = quantize_fast(y[j4 * 4 + 1], p.q_inv, -128.0f, 127.0f, r1);
+            const int c2 = quantize_fast(y[j4 * 4 + 2], p.q_inv, -128.0f, 127.0f, r2);
+            const int c3 = quantize_fast(y[j4 * 4 + 3], p.q_inv, -128.0f, 127.0f, r3);
+            words[j4] = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) |
+                        ((uint32_t)(c3 & 0xff) << 24);
+            redo |= ((uint32_t)r0 | ((uint32_t)r1 << 1) | ((uint32_t)r2 << 2) | ((uint32_t)r3 << 3)) << (4 * j4);
+          }
+          if (p.q_exact) redo = 0xffffffffu;
+          if (redo) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<uint32_t*>(o + j) = (uint32_t)(code[j] & 0xff) | ((uint32_t)(code[j + 1] & 0xff) << 8) |
-                                                    ((uint32_t)(code[j + 2] & 0xff) << 16) | ((uint32_t)(code[j + 3] & 0xff) << 24);
+            for (int j = 0; j < 32; j++)
+              if ((redo >> j) & 1u) {
+                const int cx = quantize_exact_c(y[j], p.q_scale, 0.0f, -128.0f, 127.0f);
+                words[j >> 2] = (words[j >> 2] & ~(0xffu << (8 * (j & 3)))) | ((uint32_t)(cx & 0xff) << (8 * (j & 3)));
+              }
+          }
+          if (!row_ok) {
+          } else if (full) {
+#pragma unroll
+            for (int j4 = 0; j4 < 8; j4 += 4)
+              *reinterpret_cast<uint4*>(o + j4 * 4) = make_uint4(words[j4], words[j4 + 1], words[j4 + 2], words[j4 + 3]);
           } else {
 #pragma unroll
             for (int j = 0; j < 32; j++)
-              if (nb + j < p.N) o[j] = (int8_t)code[j];
+              if (nb + j < p.N) o[j] = (int8_t)((words[j >> 2] >> (8 * (j & 3))) & 0xff);
           }
         }
       }
@@ -408,11 +471,8 @@ bool gemm_umma_supported(const void* A, const void* W, int64_t M, int64_t N, int
 int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K,
                         const float* a_scales, const float* w_scales, const float* bias, int act, float* out_f32,
                         int32_t* out_i32, int8_t* out_q, double q_scale) {
+  ProfScope prof(ctx, KK_GEMM_UMMA);
   B200Q_REQUIRE(gemm_umma_supported(A, W_nk, M, N, K), "tensor-core int8 gemm needs K %% 16 == 0 and 16-byte aligned operands");
-  if (!ctx->umma_ready) {
-    B200Q_CHECK_CUDA(cudaFuncSetAttribute(gemm_i8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    ctx->umma_ready = true;
-  }
   CUtensorMap tmA, tmB;
   if (int e = make_tensor_map(&tmA, A, M, K, BM)) return e;
   if (int e = make_tensor_map(&tmB, W_nk, N, K, BN)) return e;
@@ -431,7 +491,24 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   p.wait_limit_ns = (unsigned long long)(ctx->wait_limit_s * 1e9);
   const int64_t num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const unsigned grid = (unsigned)(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);
-  gemm_i8_umma_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
+  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const GemmParams);
+  static const KernelFn table[5][2] = {
+      {gemm_i8_umma_kernel<ACT_NONE, OUT_F32>, gemm_i8_umma_kernel<ACT_NONE, OUT_Q8>},
+      {gemm_i8_umma_kernel<ACT_RELU, OUT_F32>, gemm_i8_umma_kernel<ACT_RELU, OUT_Q8>},
+      {gemm_i8_umma_kernel<ACT_GELU_SIGMOID, OUT_F32>, gemm_i8_umma_kernel<ACT_GELU_SIGMOID, OUT_Q8>},
+      {gemm_i8_umma_kernel<ACT_GELU_TANH, OUT_F32>, gemm_i8_umma_kernel<ACT_GELU_TANH, OUT_Q8>},
+      {gemm_i8_umma_kernel<ACT_SILU, OUT_F32>, gemm_i8_umma_kernel<ACT_SILU, OUT_Q8>},
+  };
+  B200Q_REQUIRE(act >= 0 && act <= 4, "unknown activation %d", act);
+  B200Q_REQUIRE((out_i32 != nullptr) + (out_f32 != nullptr) + (out_q != nullptr) == 1,
+                "tensor-core int8 gemm writes exactly one output");
+  KernelFn fn = out_i32 ? gemm_i8_umma_kernel<ACT_NONE, OUT_I32> : table[act][out_q ? 1 : 0];
+  const int slot_idx = out_i32 ? 10 : act * 2 + (out_q ? 1 : 0);
+  if (!(ctx->umma_ready_mask & (1u << slot_idx))) {
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    ctx->umma_ready_mask |= 1u << slot_idx;
+  }
+  fn<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;

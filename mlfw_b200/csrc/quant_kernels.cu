@@ -28,6 +28,22 @@ __device__ __forceinline__ double row_scale(float mn_f, float mx_f) {
   return (s == 0.0 || s != s) ? 1e-10 : s;
 }
 
+
+// Four codes from one float4 on the fast path; bit e of `redo` is set when element e needs the exact path.
+__device__ __forceinline__ uint32_t pack4_fast(const float4& v, float inv, float qmin, float qmax, uint32_t& redo) {
+  bool r0, r1, r2, r3;
+  const int c0 = quantize_fast(v.x, inv, qmin, qmax, r0);
+  const int c1 = quantize_fast(v.y, inv, qmin, qmax, r1);
+  const int c2 = quantize_fast(v.z, inv, qmin, qmax, r2);
+  const int c3 = quantize_fast(v.w, inv, qmin, qmax, r3);
+  redo = (uint32_t)r0 | ((uint32_t)r1 << 1) | ((uint32_t)r2 << 2) | ((uint32_t)r3 << 3);
+  return (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) | ((uint32_t)(c3 & 0xff) << 24);
+}
+__device__ __forceinline__ float elem4(const float4& v, int e) { return e == 0 ? v.x : e == 1 ? v.y : e == 2 ? v.z : v.w; }
+__device__ __forceinline__ uint32_t put_byte(uint32_t w, int e, int code) {
+  return (w & ~(0xffu << (8 * e))) | ((uint32_t)(code & 0xff) << (8 * e));
+}
+
 __device__ __forceinline__ bool is_normal_f32(float v) {
   float a = fabsf(v);
   return a >= 1.17549435e-38f && a <= 3.402823466e38f;
@@ -91,19 +107,27 @@ __global__ void __launch_bounds__(1024) quantize_per_token_vec_kernel(const floa
   inv = __shfl_sync(0xffffffffu, inv, 0);
   const bool exact_only = !is_normal_f32(inv);
 
+  uint32_t words[VPT];
+  uint32_t redo = 0;
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {
+    uint32_t r;
+    words[i] = pack4_fast(v[i], inv, qmin, qmax, r);
+    redo |= r << (4 * i);
+  }
+  if (exact_only) redo = 0xffffffffu;
+  if (redo) {  // rare: elements too close to a tie for the binary32 quotient
+#pragma unroll
+    for (int i = 0; i < VPT; i++)
+#pragma unroll
+      for (int e = 0; e < 4; e++)
+        if ((redo >> (4 * i + e)) & 1u) words[i] = put_byte(words[i], e, quantize_exact_p(elem4(v[i], e), s, qmin, qmax));
+  }
   uint32_t* qr = reinterpret_cast<uint32_t*>(q) + row * K4;
 #pragma unroll
   for (int i = 0; i < VPT; i++) {
     int c = t + i * G;
-    if (c < K4) {
-      int c0 = quantize_code_p(v[i].x, s, inv, exact_only, qmin, qmax);
-      int c1 = quantize_code_p(v[i].y, s, inv, exact_only, qmin, qmax);
-      int c2 = quantize_code_p(v[i].z, s, inv, exact_only, qmin, qmax);
-      int c3 = quantize_code_p(v[i].w, s, inv, exact_only, qmin, qmax);
-      uint32_t packed = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) |
-                        ((uint32_t)(c3 & 0xff) << 24);
-      __stcs(qr + c, packed);
-    }
+    if (c < K4) __stcs(qr + c, words[i]);
   }
   if (t == 0) scales[row] = (float)s;
 }
@@ -143,8 +167,13 @@ __global__ void __launch_bounds__(256) quantize_per_token_generic_kernel(const f
     const float inv = s_inv;
     const bool exact_only = !is_normal_f32(inv);
     int8_t* qr = q + row * K;
-    for (int64_t k = threadIdx.x; k < K; k += blockDim.x)
-      qr[k] = (int8_t)quantize_code_p(xr[k], s, inv, exact_only, qmin, qmax);
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x) {
+      bool redo;
+      const float xv = xr[k];
+      int c = quantize_fast(xv, inv, qmin, qmax, redo);
+      if (redo || exact_only) c = quantize_exact_p(xv, s, qmin, qmax);
+      qr[k] = (int8_t)c;
+    }
     __syncthreads();
   }
 }
@@ -204,16 +233,23 @@ __global__ void __launch_bounds__(256) quantize_static_kernel(const float* __res
   const float4* x4 = reinterpret_cast<const float4*>(x);
   uint32_t* q4 = reinterpret_cast<uint32_t*>(q);
   for (int64_t i = tid; i < n4; i += stride) {
-    float4 v = ld_stream(x4 + i);
-    int c0 = quantize_code_c(v.x, s, inv, zp, exact, qmin, qmax);
-    int c1 = quantize_code_c(v.y, s, inv, zp, exact, qmin, qmax);
-    int c2 = quantize_code_c(v.z, s, inv, zp, exact, qmin, qmax);
-    int c3 = quantize_code_c(v.w, s, inv, zp, exact, qmin, qmax);
-    __stcs(q4 + i, (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) |
-                       ((uint32_t)(c3 & 0xff) << 24));
+    const float4 v = ld_stream(x4 + i);
+    uint32_t redo;
+    uint32_t w = pack4_fast(v, inv, qmin, qmax, redo);
+    if (exact) redo = 0xfu;
+    if (redo) {
+#pragma unroll
+      for (int e = 0; e < 4; e++)
+        if ((redo >> e) & 1u) w = put_byte(w, e, quantize_exact_c(elem4(v, e), s, zp, qmin, qmax));
+    }
+    __stcs(q4 + i, w);
   }
-  for (int64_t i = (n4 << 2) + tid; i < n; i += stride)
-    q[i] = (int8_t)quantize_code_c(x[i], s, inv, zp, exact, qmin, qmax);
+  for (int64_t i = (n4 << 2) + tid; i < n; i += stride) {
+    bool redo;
+    int c = quantize_fast(x[i], inv, qmin, qmax, redo);
+    if (redo || exact) c = quantize_exact_c(x[i], s, zp, qmin, qmax);
+    q[i] = (int8_t)c;
+  }
 }
 
 // (+q) [fround(- zp)] then fround(* s): the int -> f32 cast is not rounded (cpu/codegen.ts:521).
@@ -305,7 +341,7 @@ __global__ void __launch_bounds__(256) weight_quantize_kernel(const float* __res
   __syncthreads();
   for (int j = ty; j < 32; j += 8) {
     int64_t n = n0 + j, k = k0 + tx;
-    if (n < N && k < K) qw[n * K + k] = (int8_t)quantize_code_p(tile[j][tx], scales64[n], 0.0f, true, qmin, qmax);
+    if (n < N && k < K) qw[n * K + k] = (int8_t)quantize_exact_p(tile[j][tx], scales64[n], qmin, qmax);
   }
 }
 
@@ -335,6 +371,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // ----------------------------------------------------------------------------
 int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t K, int8_t* q, float* scales, int qmin,
                               int qmax) {
+  ProfScope prof(ctx, KK_QUANT_TOKEN);
   if (M == 0 || K == 0) {
     return 0;
   }
@@ -365,6 +402,7 @@ int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t
 }
 
 int launch_dequantize_per_token(b200q_ctx* ctx, const int8_t* q, const float* scales, int64_t M, int64_t K, float* y) {
+  ProfScope prof(ctx, KK_DEQUANT_TOKEN);
   if (M == 0 || K == 0) return 0;
   const bool vec = (K % 4 == 0) && aligned16(y) && ((reinterpret_cast<uintptr_t>(q) & 3u) == 0) && M < (1ll << 31);
   if (vec) {
@@ -391,6 +429,7 @@ static unsigned flat_blocks(b200q_ctx* ctx, int64_t work_items) {
 }
 
 int launch_quantize_static(b200q_ctx* ctx, const float* x, int64_t n, double scale, int zp, int dst_kind, void* q) {
+  ProfScope prof(ctx, KK_QUANT_STATIC);
   if (n == 0) return 0;
   const float inv = (float)(1.0 / scale);
   const float a = inv < 0 ? -inv : inv;
@@ -405,6 +444,7 @@ int launch_quantize_static(b200q_ctx* ctx, const float* x, int64_t n, double sca
 }
 
 int launch_dequantize_static(b200q_ctx* ctx, const void* q, int src_kind, int64_t n, double scale, int zp, float* y) {
+  ProfScope prof(ctx, KK_DEQUANT_STATIC);
   if (n == 0) return 0;
   if (src_kind == 2) {
     dequantize_static_i32_kernel<<<flat_blocks(ctx, n), 256, 0, ctx->stream>>>((const int32_t*)q, n, scale, (float)zp, y);
@@ -420,6 +460,7 @@ int launch_dequantize_static(b200q_ctx* ctx, const void* q, int src_kind, int64_
 
 int launch_quantize_weights(b200q_ctx* ctx, const float* w, int64_t N, int64_t K, int layout, int qmin, int qmax, int8_t* qw,
                             float* scales32, double* scales64) {
+  ProfScope prof(ctx, KK_WEIGHTS);
   if (N == 0 || K == 0) return 0;
   double* s64 = scales64;
   if (!s64) {
@@ -436,6 +477,7 @@ int launch_quantize_weights(b200q_ctx* ctx, const float* w, int64_t N, int64_t K
 }
 
 int launch_transpose_i8(b200q_ctx* ctx, const int8_t* src_kn, int64_t K, int64_t N, int8_t* dst_nk) {
+  ProfScope prof(ctx, KK_WEIGHTS);
   if (N == 0 || K == 0) return 0;
   dim3 grid((unsigned)((K + 31) / 32), (unsigned)((N + 31) / 32));
   transpose_i8_kernel<<<grid, 256, 0, ctx->stream>>>(src_kn, K, N, dst_nk);

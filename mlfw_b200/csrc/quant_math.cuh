@@ -17,13 +17,19 @@ namespace b200q {
 
 enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU_SIGMOID = 2, ACT_GELU_TANH = 3, ACT_SILU = 4 };
 
-// A quotient whose fractional part is closer than this to .5 is re-evaluated
-// exactly.  The fast quotient x * fl32(1/s) carries a relative error below
-// 2^-23 (one rounding of the reciprocal to binary32, one of the product), i.e.
-// below 2^-15 in absolute terms while |x/s| < 256; rounding the true quotient
-// to binary32 (static ops) adds at most 2^-17 more.  2^-13 leaves a factor of
-// three of slack, and sends about one element in 4000 to the exact path.
-#define B200Q_TIE_EPS 1.220703125e-4f
+// ---------------------------------------------------------------------------
+// Rounding a quotient x / s to the nearest integer, ties toward +infinity.
+//
+// The streaming kernels evaluate the quotient as t = x * fl32(1/s): two binary32
+// roundings, so |t - x/s| <= |x/s| * 2^-23.  Rounding the TRUE quotient to
+// binary32 first (the static ops do: fround(x / s)) moves it by at most another
+// |x/s| * 2^-24.  An element is therefore safe on the fast path unless the
+// fractional part of t lies within |t| * 2^-21 of .5 (a margin of 2.6x); the few
+// that do not (about one in 10^5 for unit-variance data) are flagged and redone
+// exactly in binary64.  Everything on the fast path is branch-free, so the
+// compiler can interleave the independent elements a thread holds; the exact
+// path is a separate, rarely taken loop.
+// ---------------------------------------------------------------------------
 
 // Math.round for a binary64 value (ties toward +infinity; NaN/Inf pass through:
 // for Inf the difference is NaN, the comparison false and floor(Inf) = Inf).
@@ -36,44 +42,37 @@ __device__ __forceinline__ float js_round_f32(float t) {
   return (__fsub_rn(t, r) >= 0.5f) ? r + 1.0f : r;  // t - floor(t) is exact
 }
 
-// Nearest-integer decision for an APPROXIMATE quotient `t` whose exact value is
-// produced on demand by `exact()` (returning the already rounded integer as a
-// float).  Finite |t| >= 512 is beyond every 8-bit clamp and needs no care.
-template <class ExactFn>
-__device__ __forceinline__ float round_quotient(float t, ExactFn exact) {
-  float r = floorf(t);
-  float f = __fsub_rn(t, r);
-  if (fabsf(t) < 512.0f && fabsf(f - 0.5f) < B200Q_TIE_EPS) return exact();
-  return (f > 0.5f) ? r + 1.0f : r;  // Inf: f is NaN, keeps r = +-Inf
+// Fast path shared by both modes.  Returns the int8/uint8 code for x and sets
+// `redo` when the element must take the exact path.  NaN gives code 0 (typed-array
+// store of NaN) and never asks for a redo.  |t| >= 512 is beyond every 8-bit clamp.
+__device__ __forceinline__ int quantize_fast(float x, float inv, float qmin, float qmax, bool& redo) {
+  const float t = __fmul_rn(x, inv);
+  const float r = floorf(t);
+  const float f = __fsub_rn(t, r);                       // exact; NaN when t is +-Inf
+  const float at = fabsf(t);
+  redo = (fabsf(f - 0.5f) < at * 4.76837158203125e-7f) && (at < 512.0f);
+  float q = (f > 0.5f) ? r + 1.0f : r;                   // Inf keeps r = +-Inf
+  q = fminf(fmaxf(q, qmin), qmax);
+  const int c = (int)q;
+  return (x != x) ? 0 : c;
 }
 
 // QuantizationParams.quantize (src/compiler/ir/graph/quantization_types.ts:75-79,118-130):
-// max(cMin, min(cMax, Math.round(x / s))) in binary64, then an Int8Array store
-// (NaN -> 0).  `inv` is fl32(1 / s); `exact_only` is set per row when that
-// reciprocal is not a normal binary32 number.
-__device__ __forceinline__ int quantize_code_p(float x, double s, float inv, bool exact_only, float qmin,
-                                               float qmax) {
+// max(cMin, min(cMax, Math.round(x / s))) in binary64, then an Int8Array store (NaN -> 0).
+static __device__ __noinline__ int quantize_exact_p(float x, double s, float qmin, float qmax) {
   if (x != x) return 0;
-  auto exact = [&]() -> float { return (float)js_round_f64((double)x / s); };
-  float r = exact_only ? exact() : round_quotient(__fmul_rn(x, inv), exact);
-  r = fminf(fmaxf(r, qmin), qmax);
-  return (int)r;
+  float r = (float)js_round_f64((double)x / s);
+  return (int)fminf(fmaxf(r, qmin), qmax);
 }
 
-// Compiled `quantize` (src/compiler/passes/lowering/quant_math.ts:16-27 as emitted
-// by src/backend/cpu/codegen.ts): t = fround(x / s); [t = fround(t + zp);]
-// Math.round; clamp; (v|0); typed-array store.
-__device__ __forceinline__ int quantize_code_c(float x, double s, float inv, float zp, bool exact_only, float qmin,
-                                               float qmax) {
+// Compiled `quantize` (src/compiler/passes/lowering/quant_math.ts:16-27 as emitted by
+// src/backend/cpu/codegen.ts): t = fround(x / s); [t = fround(t + zp);] Math.round; clamp; (v|0).
+static __device__ __noinline__ int quantize_exact_c(float x, double s, float zp, float qmin, float qmax) {
   if (x != x) return 0;
-  auto exact = [&]() -> float {
-    float t = __double2float_rn((double)x / s);
-    if (zp != 0.0f) t = __fadd_rn(t, zp);
-    return js_round_f32(t);
-  };
-  float r = exact_only ? exact() : round_quotient(__fmul_rn(x, inv), exact);
-  r = fminf(fmaxf(r, qmin), qmax);
-  return (int)r;
+  float t = __double2float_rn((double)x / s);
+  if (zp != 0.0f) t = __fadd_rn(t, zp);
+  float r = js_round_f32(t);
+  return (int)fminf(fmaxf(r, qmin), qmax);
 }
 
 // fround((double)acc * sv): exact product in binary64 whenever |acc| < 2^24,
@@ -82,6 +81,9 @@ __device__ __forceinline__ float scale_acc(int acc, float sv) {
   if (abs(acc) < (1 << 24)) return __fmul_rn((float)acc, sv);
   return __double2float_rn((double)acc * (double)sv);
 }
+// The two halves of scale_acc for callers that pick one per group of elements.
+__device__ __forceinline__ float scale_acc_small(int acc, float sv) { return __fmul_rn((float)acc, sv); }
+__device__ __forceinline__ float scale_acc_wide(int acc, float sv) { return __double2float_rn((double)acc * (double)sv); }
 
 // ---------------------------------------------------------------------------
 // exp for a binary32 argument, evaluated in binary64 (error < 2 ulp of
@@ -118,10 +120,12 @@ __device__ __forceinline__ double exp_f64(double xd, const double* tbl) {
   return m * __hiloint2double((e + 1023) << 20, 0);
 }
 
+// Branch-free: the argument is clamped to [-160, 128] (exp(128) rounds to +Inf in
+// binary32, exp(-160) to 0), NaN is restored by a select.
 __device__ __forceinline__ float exp_fround(float x, const double* tbl) {
-  if (!(x < 128.0f)) return (x != x) ? x : __int_as_float(0x7f800000);
-  if (x < -160.0f) return 0.0f;
-  return __double2float_rn(exp_f64((double)x, tbl));
+  const float xc = fminf(fmaxf(x, -160.0f), 128.0f);
+  const float r = __double2float_rn(exp_f64((double)xc, tbl));
+  return (x != x) ? x : r;
 }
 
 // sigmoid as the reference decomposes it (src/compiler/passes/decompose/
@@ -133,6 +137,9 @@ __device__ __forceinline__ float sigmoid_ref(float z, const double* tbl) {
 }
 
 // Bias add has happened; `y` is the pre-activation value.
+template <int ACT_T>
+__device__ __forceinline__ float apply_act_t(float y, const double* tbl);
+
 __device__ __forceinline__ float apply_act(float y, int act, const double* tbl) {
   switch (act) {
     case ACT_RELU:  // Math.max(y, 0): NaN stays NaN, -0 becomes +0
@@ -157,6 +164,11 @@ __device__ __forceinline__ float apply_act(float y, int act, const double* tbl) 
     default:
       return y;
   }
+}
+
+template <int ACT_T>
+__device__ __forceinline__ float apply_act_t(float y, const double* tbl) {
+  return apply_act(y, ACT_T, tbl);  // the switch folds away: ACT_T is a compile-time constant
 }
 
 }  // namespace b200q

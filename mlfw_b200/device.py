@@ -163,6 +163,25 @@ class Context:
         check(self.lib.b200q_timer_stop(self.handle, C.byref(ms)), "b200q_timer_stop")
         return ms.value
 
+    KERNEL_KINDS = ("quantize_per_token", "dequantize_per_token", "quantize_static", "dequantize_static", "weights",
+                    "gemm_tensor_core", "gemm_cuda_core", "tail")
+
+    def profile_enable(self, on: bool = True):
+        check(self.lib.b200q_profile_enable(self.handle, int(on)), "b200q_profile_enable")
+
+    def profile_reset(self):
+        check(self.lib.b200q_profile_reset(self.handle), "b200q_profile_reset")
+
+    def profile_read(self) -> dict:
+        """{kernel family: (total ms, launches)} since the last reset (synchronises)."""
+        out = {}
+        for k, name in enumerate(self.KERNEL_KINDS):
+            ms, n = C.c_double(), C.c_uint64()
+            check(self.lib.b200q_profile_read(self.handle, k, C.byref(ms), C.byref(n)), "b200q_profile_read")
+            if n.value:
+                out[name] = (ms.value, int(n.value))
+        return out
+
     # ---- ops (device pointers)
     def quantize_per_token(self, x, M, K, q, scales, qmin=-127, qmax=127):
         check(self.lib.b200q_quantize_per_token(self.handle, _ptr(x), M, K, _ptr(q), _ptr(scales), qmin, qmax),

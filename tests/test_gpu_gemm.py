@@ -96,8 +96,8 @@ def linear_case(rng, M, N, K, big_acc=False):
     ws = rng.uniform(1e-3, 1e-2, size=N).astype(np.float32) / np.float32(np.sqrt(K) / 8)
     bias = (rng.standard_normal(N) * 0.01).astype(np.float32)
     if big_acc:
-        W[: N // 2] = 127          # correlated weights: accumulators beyond 2^24
-        x = np.abs(x)
+        W[: N // 2] = 127          # correlated weights and codes in [64,127]: accumulators beyond 2^24
+        x = rng.uniform(0.5, 1.0, size=(M, K)).astype(np.float32)
     return x, W, ws, bias
 
 
