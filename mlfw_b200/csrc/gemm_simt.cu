@@ -90,9 +90,9 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const int32_t* __restrict
     y = apply_act(y, act, tbl);
     if (out_f32) out_f32[i] = y;
     if (out_q) {
-      bool redo;
-      int c = quantize_fast(y, q_inv, -128.0f, 127.0f, redo);
-      if (redo || q_exact) c = quantize_exact_c(y, q_scale, 0.0f, -128.0f, 127.0f);
+      QuantGuard guard;
+      int c = quantize_fast(y, q_inv, guard);
+      if (q_exact || guard.unsafe(127.49f)) c = quantize_exact_c(y, q_scale, 0.0f, -128.0f, 127.0f);
       out_q[i] = (int8_t)c;
     }
   }

@@ -310,15 +310,13 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const float a_scale = (p.a_scales && row_ok) ? __ldg(p.a_scales + m) : 1.0f;  // fround(1 * ws) == ws
       const uint32_t taddr = tmem_base + slot * BN + (uint32_t)col0 + ((uint32_t)(quarter * 32) << 16);
       constexpr int NCH = EPI_COLS / 32;
-      int acc[2][32];
-      if (n0 < p.N) tmem_ld32(taddr, acc[0]);
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < NCH; c++) {
         const int64_t nb = n0 + c * 32;
         if (nb >= p.N) break;  // uniform across the warp
+        int a[32];
+        tmem_ld32(taddr + (uint32_t)(c * 32), a);
         tmem_ld_wait();
-        if (c + 1 < NCH && nb + 32 < p.N) tmem_ld32(taddr + (uint32_t)((c + 1) * 32), acc[(c + 1) & 1]);
-        const int(&a)[32] = acc[c & 1];
         // No lane may leave this iteration early: the tensor-memory loads and the vote below are
         // warp-collective.  Rows past M compute on whatever the accumulator holds and store nothing.
         const bool full = vec_ok && (nb + 32 <= p.N);
@@ -335,14 +333,17 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           continue;
         }
-        // |acc| >= 2^24 anywhere in this warp's chunk: the whole chunk takes the binary64 product.
+        // An accumulator of 2^22 or more anywhere in the warp's chunk sends the whole chunk through the binary64
+        // product (the cheap int -> float conversion and the binary32 product are only exact below that).
         int big = 0;
 #pragma unroll
-        for (int j = 0; j < 32; j++) big |= (abs(a[j]) >> 24);
+        for (int j = 0; j < 32; j++) big |= (abs(a[j]) >> 22);
         const bool wide = __any_sync(0xffffffffu, big != 0);
         float y[32];
+        unsigned vkey = 0;
         const float4* cs4 = reinterpret_cast<const float4*>(cs + c * 32);
         const float4* cb4 = reinterpret_cast<const float4*>(cb + c * 32);
+        constexpr unsigned kGeneral = act_general_threshold<ACT_T>();
 #pragma unroll
         for (int j4 = 0; j4 < 8; j4++) {
           const float4 w4 = cs4[j4], b4 = cb4[j4];
@@ -353,7 +354,18 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const float sv = __fmul_rn(a_scale, wsv[e]);
             float v = wide ? scale_acc_wide(a[j], sv) : scale_acc_small(a[j], sv);
             if (has_bias) v = __fadd_rn(v, bv[e]);
-            y[j] = apply_act_t<ACT_T>(v, tbl);
+            if (kGeneral != 0xFFFFFFFFu) vkey = max(vkey, __float_as_uint(v));
+            y[j] = apply_act_fast<ACT_T>(v, tbl);
+            // Where the fast form is not valid (large negative argument, -Inf) keep the argument itself: no valid
+            // result of these activations is below -0.3, so the bit test below recognises such an element again.
+            if (kGeneral != 0xFFFFFFFFu && __float_as_uint(v) > kGeneral) y[j] = v;
+          }
+        }
+        if (kGeneral != 0xFFFFFFFFu) {
+          if (__any_sync(0xffffffffu, vkey > kGeneral)) {  // rare
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (__float_as_uint(y[j]) > kGeneral) y[j] = apply_act_general(y[j], ACT_T, tbl);
           }
         }
         if (OUT_T == OUT_F32) {
@@ -370,26 +382,18 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         } else {
           int8_t* o = p.out_q + m * p.N + nb;
           uint32_t words[8];
-          uint32_t redo = 0;
+          QuantGuard guard;
 #pragma unroll
-          for (int j4 = 0; j4 < 8; j4++) {
-            bool r0, r1, r2, r3;
-            const int c0 = quantize_fast(y[j4 * 4 + 0], p.q_inv, -128.0f, 127.0f, r0);
-            const int c1 = quantize_fast(y[j4 * 4 + 1], p.q_inv, -128.0f, 127.0f, r1);
-            const int c2 = quantize_fast(y[j4 * 4 + 2], p.q_inv, -128.0f, 127.0f, r2);
-            const int c3 = quantize_fast(y[j4 * 4 + 3], p.q_inv, -128.0f, 127.0f, r3);
-            words[j4] = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) |
-                        ((uint32_t)(c3 & 0xff) << 24);
-            redo |= ((uint32_t)r0 | ((uint32_t)r1 << 1) | ((uint32_t)r2 << 2) | ((uint32_t)r3 << 3)) << (4 * j4);
-          }
-          if (p.q_exact) redo = 0xffffffffu;
-          if (redo) {
+          for (int j4 = 0; j4 < 8; j4++)
+            words[j4] = pack_codes(quantize_fast(y[j4 * 4 + 0], p.q_inv, guard), quantize_fast(y[j4 * 4 + 1], p.q_inv, guard),
+                                   quantize_fast(y[j4 * 4 + 2], p.q_inv, guard), quantize_fast(y[j4 * 4 + 3], p.q_inv, guard));
+          if (p.q_exact || guard.unsafe(127.49f)) {  // rare: a tie, a value beyond the clamp, NaN
 #pragma unroll
-            for (int j = 0; j < 32; j++)
-              if ((redo >> j) & 1u) {
-                const int cx = quantize_exact_c(y[j], p.q_scale, 0.0f, -128.0f, 127.0f);
-                words[j >> 2] = (words[j >> 2] & ~(0xffu << (8 * (j & 3)))) | ((uint32_t)(cx & 0xff) << (8 * (j & 3)));
-              }
+            for (int j4 = 0; j4 < 8; j4++)
+              words[j4] = pack_codes(quantize_exact_c(y[j4 * 4 + 0], p.q_scale, 0.0f, -128.0f, 127.0f),
+                                     quantize_exact_c(y[j4 * 4 + 1], p.q_scale, 0.0f, -128.0f, 127.0f),
+                                     quantize_exact_c(y[j4 * 4 + 2], p.q_scale, 0.0f, -128.0f, 127.0f),
+                                     quantize_exact_c(y[j4 * 4 + 3], p.q_scale, 0.0f, -128.0f, 127.0f));
           }
           if (!row_ok) {
           } else if (full) {

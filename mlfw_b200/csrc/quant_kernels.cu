@@ -29,20 +29,23 @@ __device__ __forceinline__ double row_scale(float mn_f, float mx_f) {
 }
 
 
-// Four codes from one float4 on the fast path; bit e of `redo` is set when element e needs the exact path.
-__device__ __forceinline__ uint32_t pack4_fast(const float4& v, float inv, float qmin, float qmax, uint32_t& redo) {
-  bool r0, r1, r2, r3;
-  const int c0 = quantize_fast(v.x, inv, qmin, qmax, r0);
-  const int c1 = quantize_fast(v.y, inv, qmin, qmax, r1);
-  const int c2 = quantize_fast(v.z, inv, qmin, qmax, r2);
-  const int c3 = quantize_fast(v.w, inv, qmin, qmax, r3);
-  redo = (uint32_t)r0 | ((uint32_t)r1 << 1) | ((uint32_t)r2 << 2) | ((uint32_t)r3 << 3);
-  return (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) | ((uint32_t)(c3 & 0xff) << 24);
+// Four codes from one float4 on the fast path (valid while the guard stays safe).
+__device__ __forceinline__ uint32_t pack4_fast(const float4& v, float inv, QuantGuard& g) {
+  const int c0 = quantize_fast(v.x, inv, g);
+  const int c1 = quantize_fast(v.y, inv, g);
+  const int c2 = quantize_fast(v.z, inv, g);
+  const int c3 = quantize_fast(v.w, inv, g);
+  return pack_codes(c0, c1, c2, c3);
 }
-__device__ __forceinline__ float elem4(const float4& v, int e) { return e == 0 ? v.x : e == 1 ? v.y : e == 2 ? v.z : v.w; }
-__device__ __forceinline__ uint32_t put_byte(uint32_t w, int e, int code) {
-  return (w & ~(0xffu << (8 * e))) | ((uint32_t)(code & 0xff) << (8 * e));
+__device__ __forceinline__ uint32_t pack4_exact_p(const float4& v, double s, float qmin, float qmax) {
+  return pack_codes(quantize_exact_p(v.x, s, qmin, qmax), quantize_exact_p(v.y, s, qmin, qmax),
+                    quantize_exact_p(v.z, s, qmin, qmax), quantize_exact_p(v.w, s, qmin, qmax));
 }
+__device__ __forceinline__ uint32_t pack4_exact_c(const float4& v, double s, float zp, float qmin, float qmax) {
+  return pack_codes(quantize_exact_c(v.x, s, zp, qmin, qmax), quantize_exact_c(v.y, s, zp, qmin, qmax),
+                    quantize_exact_c(v.z, s, zp, qmin, qmax), quantize_exact_c(v.w, s, zp, qmin, qmax));
+}
+__device__ __forceinline__ float guard_limit(float qmin, float qmax) { return fminf(-qmin, qmax) + 0.49f; }
 
 __device__ __forceinline__ bool is_normal_f32(float v) {
   float a = fabsf(v);
@@ -108,20 +111,12 @@ __global__ void __launch_bounds__(1024) quantize_per_token_vec_kernel(const floa
   const bool exact_only = !is_normal_f32(inv);
 
   uint32_t words[VPT];
-  uint32_t redo = 0;
+  QuantGuard guard;
 #pragma unroll
-  for (int i = 0; i < VPT; i++) {
-    uint32_t r;
-    words[i] = pack4_fast(v[i], inv, qmin, qmax, r);
-    redo |= r << (4 * i);
-  }
-  if (exact_only) redo = 0xffffffffu;
-  if (redo) {  // rare: elements too close to a tie for the binary32 quotient
+  for (int i = 0; i < VPT; i++) words[i] = pack4_fast(v[i], inv, guard);   // NaN padding of dead vectors only trips the guard
+  if (exact_only || guard.unsafe(guard_limit(qmin, qmax))) {  // rare: a tie, an out-of-range or a non-finite element
 #pragma unroll
-    for (int i = 0; i < VPT; i++)
-#pragma unroll
-      for (int e = 0; e < 4; e++)
-        if ((redo >> (4 * i + e)) & 1u) words[i] = put_byte(words[i], e, quantize_exact_p(elem4(v[i], e), s, qmin, qmax));
+    for (int i = 0; i < VPT; i++) words[i] = pack4_exact_p(v[i], s, qmin, qmax);
   }
   uint32_t* qr = reinterpret_cast<uint32_t*>(q) + row * K4;
 #pragma unroll
@@ -168,10 +163,10 @@ __global__ void __launch_bounds__(256) quantize_per_token_generic_kernel(const f
     const bool exact_only = !is_normal_f32(inv);
     int8_t* qr = q + row * K;
     for (int64_t k = threadIdx.x; k < K; k += blockDim.x) {
-      bool redo;
+      QuantGuard guard;
       const float xv = xr[k];
-      int c = quantize_fast(xv, inv, qmin, qmax, redo);
-      if (redo || exact_only) c = quantize_exact_p(xv, s, qmin, qmax);
+      int c = quantize_fast(xv, inv, guard);
+      if (exact_only || guard.unsafe(guard_limit(qmin, qmax))) c = quantize_exact_p(xv, s, qmin, qmax);
       qr[k] = (int8_t)c;
     }
     __syncthreads();
@@ -227,6 +222,8 @@ __global__ void __launch_bounds__(256) quantize_static_kernel(const float* __res
                                                               float zp, int exact_only, float qmin, float qmax,
                                                               int8_t* __restrict__ q, int vec_ok) {
   const bool exact = exact_only != 0;
+  // Unsigned targets clamp at 0: the guard (symmetric in |t|) then sends every negative quotient to the exact path.
+  const float limit = guard_limit(qmin, qmax);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t n4 = vec_ok ? (n >> 2) : 0;
@@ -234,20 +231,15 @@ __global__ void __launch_bounds__(256) quantize_static_kernel(const float* __res
   uint32_t* q4 = reinterpret_cast<uint32_t*>(q);
   for (int64_t i = tid; i < n4; i += stride) {
     const float4 v = ld_stream(x4 + i);
-    uint32_t redo;
-    uint32_t w = pack4_fast(v, inv, qmin, qmax, redo);
-    if (exact) redo = 0xfu;
-    if (redo) {
-#pragma unroll
-      for (int e = 0; e < 4; e++)
-        if ((redo >> e) & 1u) w = put_byte(w, e, quantize_exact_c(elem4(v, e), s, zp, qmin, qmax));
-    }
+    QuantGuard guard;
+    uint32_t w = pack4_fast(v, inv, guard);
+    if (exact || guard.unsafe(limit)) w = pack4_exact_c(v, s, zp, qmin, qmax);
     __stcs(q4 + i, w);
   }
   for (int64_t i = (n4 << 2) + tid; i < n; i += stride) {
-    bool redo;
-    int c = quantize_fast(x[i], inv, qmin, qmax, redo);
-    if (redo || exact) c = quantize_exact_c(x[i], s, zp, qmin, qmax);
+    QuantGuard guard;
+    int c = quantize_fast(x[i], inv, guard);
+    if (exact || guard.unsafe(limit)) c = quantize_exact_c(x[i], s, zp, qmin, qmax);
     q[i] = (int8_t)c;
   }
 }

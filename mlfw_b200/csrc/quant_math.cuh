@@ -23,12 +23,17 @@ enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU_SIGMOID = 2, ACT_GELU_TANH
 // The streaming kernels evaluate the quotient as t = x * fl32(1/s): two binary32
 // roundings, so |t - x/s| <= |x/s| * 2^-23.  Rounding the TRUE quotient to
 // binary32 first (the static ops do: fround(x / s)) moves it by at most another
-// |x/s| * 2^-24.  An element is therefore safe on the fast path unless the
-// fractional part of t lies within |t| * 2^-21 of .5 (a margin of 2.6x); the few
-// that do not (about one in 10^5 for unit-variance data) are flagged and redone
-// exactly in binary64.  Everything on the fast path is branch-free, so the
-// compiler can interleave the independent elements a thread holds; the exact
-// path is a separate, rarely taken loop.
+// |x/s| * 2^-24.  Away from a tie every rounding rule gives the same integer, so
+// the fast path rounds with the 1.5*2^23 trick (no conversion instruction) and
+// only KEEPS TRACK of whether any element of the thread was unsafe:
+//   - closer to a tie than |t| * 2^-21 (a margin of 2.6x over the error above),
+//   - outside the clamp range (the fast path does not clamp) or beyond 2^22,
+//   - NaN or infinite.
+// All of these are folded into two running maxima kept as integers (the bit
+// pattern of a non-negative float orders like the float, NaN sorts above all),
+// which costs two instructions per element and no branch.  A thread that saw an
+// unsafe element (about one element in 10^5 for unit-variance data) recomputes
+// its codes with the exact binary64 routines below.
 // ---------------------------------------------------------------------------
 
 // Math.round for a binary64 value (ties toward +infinity; NaN/Inf pass through:
@@ -42,19 +47,28 @@ __device__ __forceinline__ float js_round_f32(float t) {
   return (__fsub_rn(t, r) >= 0.5f) ? r + 1.0f : r;  // t - floor(t) is exact
 }
 
-// Fast path shared by both modes.  Returns the int8/uint8 code for x and sets
-// `redo` when the element must take the exact path.  NaN gives code 0 (typed-array
-// store of NaN) and never asks for a redo.  |t| >= 512 is beyond every 8-bit clamp.
-__device__ __forceinline__ int quantize_fast(float x, float inv, float qmin, float qmax, bool& redo) {
+struct QuantGuard {
+  int tie = 0;  // max of bits(|t - rint(t)| + |t| * 2^-21)
+  int mag = 0;  // max of bits(|t|)
+  // limit = min(-qmin, qmax) + 0.49: beyond it the unclamped fast code may be wrong
+  __device__ __forceinline__ bool unsafe(float limit) const { return tie >= 0x3f000000 || mag > __float_as_int(limit); }
+};
+
+// Code of x on the fast path (valid only if the guard stays safe).
+__device__ __forceinline__ int quantize_fast(float x, float inv, QuantGuard& g) {
   const float t = __fmul_rn(x, inv);
-  const float r = floorf(t);
-  const float f = __fsub_rn(t, r);                       // exact; NaN when t is +-Inf
-  const float at = fabsf(t);
-  redo = (fabsf(f - 0.5f) < at * 4.76837158203125e-7f) && (at < 512.0f);
-  float q = (f > 0.5f) ? r + 1.0f : r;                   // Inf keeps r = +-Inf
-  q = fminf(fmaxf(q, qmin), qmax);
-  const int c = (int)q;
-  return (x != x) ? 0 : c;
+  const float u = __fadd_rn(t, 12582912.0f);            // 1.5 * 2^23: the sum is rounded to an integer
+  const int c = __float_as_int(u) - 0x4B400000;
+  const float d = __fsub_rn(t, __fsub_rn(u, 12582912.0f));
+  const float e = __fmaf_rn(fabsf(t), 4.76837158203125e-7f, fabsf(d));
+  g.tie = max(g.tie, __float_as_int(e));                // NaN has the bit pattern 0x7fffffff
+  g.mag = max(g.mag, __float_as_int(fabsf(t)));
+  return c;
+}
+
+// Four int codes -> one word of four bytes (low byte first).
+__device__ __forceinline__ uint32_t pack_codes(int c0, int c1, int c2, int c3) {
+  return __byte_perm(__byte_perm((uint32_t)c0, (uint32_t)c1, 0x0040), __byte_perm((uint32_t)c2, (uint32_t)c3, 0x0040), 0x5410);
 }
 
 // QuantizationParams.quantize (src/compiler/ir/graph/quantization_types.ts:75-79,118-130):
@@ -82,7 +96,10 @@ __device__ __forceinline__ float scale_acc(int acc, float sv) {
   return __double2float_rn((double)acc * (double)sv);
 }
 // The two halves of scale_acc for callers that pick one per group of elements.
-__device__ __forceinline__ float scale_acc_small(int acc, float sv) { return __fmul_rn((float)acc, sv); }
+// Small: |acc| < 2^22, converted without a conversion instruction (1.5 * 2^23 trick).
+__device__ __forceinline__ float scale_acc_small(int acc, float sv) {
+  return __fmul_rn(__fsub_rn(__int_as_float(0x4B400000 + acc), 12582912.0f), sv);
+}
 __device__ __forceinline__ float scale_acc_wide(int acc, float sv) { return __double2float_rn((double)acc * (double)sv); }
 
 // ---------------------------------------------------------------------------
@@ -128,6 +145,79 @@ __device__ __forceinline__ float exp_fround(float x, const double* tbl) {
   return (x != x) ? x : r;
 }
 
+// ---------------------------------------------------------------------------
+// Branch-free activations for the fused epilogue.  A thread evaluates 32 of
+// them back to back; anything with a call or a data-dependent branch in it
+// (the IEEE division, range checks) would stop the compiler from interleaving
+// those 32 independent chains.  The sigmoid-based ones are exact (same value as
+// sigmoid_ref) for every argument except z < -87 (exp(-z) overflows towards the
+// binary32 range limit) and -Inf, where they return an unspecified finite value or
+// NaN: callers test `needs_general_act` and redo those elements with apply_act.
+// NaN and +Inf arguments give the reference's result without help.
+// ---------------------------------------------------------------------------
+
+// Correctly rounded 1/d for finite d in [1, 2^126], branch-free: hardware approximation, one
+// Newton step (faithful result), then the better of the result and its neighbour on the side the
+// exact residual 1 - d*y points to (the residual of a faithful y is exactly representable).
+__device__ __forceinline__ float rcp_rn_ge1(float d) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(d));
+  const float e = __fmaf_rn(-d, y, 1.0f);
+  y = __fmaf_rn(y, e, y);
+  const float r = __fmaf_rn(-d, y, 1.0f);
+  const float yc = __int_as_float(__float_as_int(y) + (r > 0.0f ? 1 : -1));
+  const float rc = __fmaf_rn(-d, yc, 1.0f);
+  return (fabsf(rc) < fabsf(r)) ? yc : y;
+}
+
+// sigmoid(z) for z >= -87 (exact), NaN (NaN) and +Inf (1).
+__device__ __forceinline__ float sigmoid_fast(float z, const double* tbl) {
+  float zc;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(zc) : "f"(z), "f"(100.0f));  // exp(-100) already vanishes against 1; NaN is kept
+  const float e = __double2float_rn(exp_f64((double)(-zc), tbl));
+  return rcp_rn_ge1(__fadd_rn(1.0f, e));
+}
+
+// fround(1.702 * y) with 1.702 a binary64 constant, in binary32 arithmetic: 1.702 = CH + CL + (< 2^-53),
+// y*CH is expanded exactly with an FMA.  Differs from the binary64 product only when that product lies
+// within 2^-48 (relative) of a rounding boundary, about one argument in 10^7.
+__device__ __forceinline__ float mul_1702(float y) {
+  const float CH = 1.70200002193450927734375f;             // fl32(1.702)
+  const float CL = -2.1934509319976314e-08f;               // fl32(1.702 - CH)
+  const float p = __fmul_rn(y, CH);
+  const float ep = __fmaf_rn(y, CH, -p);                   // NaN when p overflowed to +-Inf
+  const float z = __fadd_rn(p, __fmaf_rn(y, CL, ep));
+  return (fabsf(p) == __int_as_float(0x7f800000)) ? p : z;
+}
+
+template <int ACT_T>
+__device__ __forceinline__ float apply_act_fast(float y, const double* tbl) {
+  if (ACT_T == ACT_RELU) return (y > 0.0f) ? y : ((y != y) ? y : 0.0f);
+  if (ACT_T == ACT_GELU_SIGMOID) return __fmul_rn(y, sigmoid_fast(mul_1702(y), tbl));
+  if (ACT_T == ACT_SILU) return __fmul_rn(y, sigmoid_fast(y, tbl));
+  if (ACT_T == ACT_GELU_TANH) {
+    // 0.5*(1+tanh(u)) = 1/(1+exp(-2u)), u = sqrt(2/pi)*(y + 0.044715 y^3); binary32, tolerance only
+    // (the reference has no tanh form).  Saturates correctly for large |y|.
+    const float y2 = y * y;
+    const float w = y * fmaf(y2, -0.10294324f, -2.3022082f);   // -2u*log2(e)
+    float e, s;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(w));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(1.0f + e));
+    return y * s;
+  }
+  return y;
+}
+
+// True when apply_act_fast<ACT_T>(y) may differ from apply_act(y): compares the bit pattern as an
+// unsigned number, which orders the negative floats by magnitude and puts them (and -Inf, -NaN)
+// above every positive one.
+template <int ACT_T>
+__device__ __forceinline__ constexpr unsigned act_general_threshold() {
+  return ACT_T == ACT_GELU_SIGMOID ? 0xC24C0000u /* -51.0f: 1.702 * 51 < 87 */
+         : ACT_T == ACT_SILU       ? 0xC2AE0000u /* -87.0f */
+                                   : 0xFFFFFFFFu;
+}
+
 // sigmoid as the reference decomposes it (src/compiler/passes/decompose/
 // decomposition_pass.ts:197-203): 1 / (1 + exp(-z)), one rounding per op.
 __device__ __forceinline__ float sigmoid_ref(float z, const double* tbl) {
@@ -165,6 +255,9 @@ __device__ __forceinline__ float apply_act(float y, int act, const double* tbl) 
       return y;
   }
 }
+
+// Out-of-line copy for rarely taken paths (keeps the hot loops small).
+static __device__ __noinline__ float apply_act_general(float y, int act, const double* tbl) { return apply_act(y, act, tbl); }
 
 template <int ACT_T>
 __device__ __forceinline__ float apply_act_t(float y, const double* tbl) {

@@ -252,3 +252,32 @@ def test_quant_roundtrip_host(ctx, orc):
     rq, _, rs = orc.quantize_per_token(x)
     assert (q == rq).all() and (s == rs).all()
     assert (y == orc.dequantize_per_token_f32(rq, rs)).all()
+
+
+@pytest.mark.parametrize("act", ["gelu_sigmoid", "silu", "relu", "gelu_tanh"])
+def test_fused_tail_extreme_arguments(ctx, orc, act):
+    """Pre-activations far outside the tame range (exp overflow side, NaN, +-Inf) take the general path."""
+    rng = np.random.default_rng(41)
+    M, N, K = 128, 256, 64
+    x = activations(rng, M, K, outliers=False)
+    W = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    ws = np.full(N, 1e-4, np.float32)
+    specials = np.array([-200.0, -90.0, -87.5, -60.0, -51.5, -50.5, -30.0, 0.0, 30.0, 100.0, 1e30, -1e30, np.nan, np.inf,
+                         -np.inf, 3.0], np.float32)
+    bias = np.tile(specials, N // specials.size)
+    q, _, s32 = orc.quantize_per_token(x)
+    ref = orc.epilogue(orc.qdot_i32(q, W), s32, ws, bias, act)
+    dq, dW = ctx.to_device(q), ctx.to_device(W)
+    ds, dws, db = ctx.to_device(s32), ctx.to_device(ws), ctx.to_device(bias)
+    dout = Guarded(ctx, (M, N), np.float32)
+    ctx.int8_linear(dq.ptr, ds.ptr, dW.ptr, dws.ptr, db.ptr, act, M, N, K, dout.ptr)
+    ctx.sync()
+    out = dout.download()
+    assert (np.isnan(out) == np.isnan(ref)).all()
+    ok = ~np.isnan(ref)
+    if act in EXACT_ACTS:
+        assert (out[ok].view(np.uint32) == ref[ok].view(np.uint32)).all()
+    else:
+        fin = np.isfinite(ref)
+        assert (out[ok & ~fin] == ref[ok & ~fin]).all()
+        assert np.abs(out[fin].astype(np.float64) - ref[fin]).max() <= TOL * np.abs(ref[fin]).max()
