@@ -39,6 +39,7 @@ WORKLOADS = {
     "c3_gemm_8192x4096x4096_gelu_sigmoid": (8192, 4096, 4096, "gelu_sigmoid"),
     "small_2048x4096x4096_gelu_tanh": (2048, 4096, 4096, "gelu_tanh"),       # profiler-sized case
     "small_2048x4096x4096_gelu_sigmoid": (2048, 4096, 4096, "gelu_sigmoid"),
+    "small_2048x4096x4096_none": (2048, 4096, 4096, "none"),
 }
 DEFAULT_WORKLOAD = "c3_gemm_8192x4096x4096_gelu_tanh"
 C2_SHAPE = (16384, 4096)          # standalone quantize -> dequantize round trip

@@ -50,7 +50,8 @@ int b200q_status_word(b200q_ctx* ctx, uint32_t* out);
 int b200q_clear_status(b200q_ctx* ctx);
 /* Bound, in seconds, of every device-side wait of the tensor-core kernel (default 2). */
 int b200q_set_wait_limit(b200q_ctx* ctx, double seconds);
-/* 0: tensor-core GEMM whenever the shape allows (default); 1: CUDA-core kernel only. */
+/* 0: tensor-core GEMM whenever the shape allows, one CTA or a CTA pair per tile chosen by size (default);
+ * 1: CUDA-core kernel only; 2: tensor cores, one CTA per tile; 3: tensor cores, CTA pairs. */
 int b200q_set_gemm_variant(b200q_ctx* ctx, int variant);
 /* Kernels launched through this context since it was created. */
 uint64_t b200q_launch_count(b200q_ctx* ctx);

@@ -52,7 +52,7 @@ static int use_device(b200q_ctx* ctx) {
 }
 
 static bool use_umma(b200q_ctx* ctx, const void* A, const void* W, int64_t M, int64_t N, int64_t K) {
-  return ctx->gemm_variant == 0 && gemm_umma_supported(A, W, M, N, K);
+  return ctx->gemm_variant != 1 && gemm_umma_supported(A, W, M, N, K);
 }
 
 #define B200Q_DIMS_OK(M, N, K)                                                                              \
@@ -167,7 +167,7 @@ int b200q_set_wait_limit(b200q_ctx* ctx, double seconds) {
 
 int b200q_set_gemm_variant(b200q_ctx* ctx, int variant) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
-  B200Q_REQUIRE(variant == 0 || variant == 1, "b200q_set_gemm_variant: unknown variant %d", variant);
+  B200Q_REQUIRE(variant >= 0 && variant <= 3, "b200q_set_gemm_variant: unknown variant %d", variant);
   ctx->gemm_variant = variant;
   return 0;
 }

@@ -62,7 +62,7 @@ struct b200q_ctx {
   b200q::Workspace ws_acc;               // int32 / f32 intermediates of the unfused paths
   b200q::Workspace ws_stage_in, ws_stage_out;  // device staging of the host-buffer entry points
   double wait_limit_s = 2.0;             // bound of every device-side wait
-  int gemm_variant = 0;                  // 0 = auto (tensor cores when the shape allows), 1 = CUDA-core kernel only
+  int gemm_variant = 0;                  // 0 auto, 1 CUDA-core kernel only, 2 tensor cores with one CTA per tile, 3 with CTA pairs
   uint32_t umma_ready_mask = 0;          // tensor-core kernel variants whose shared-memory attribute is set on this device
   uint64_t launches = 0;                 // kernels launched through this context
   // per-kernel CUDA-event timing (off by default): a ring of event pairs, folded into the sums when it wraps or is read

@@ -13,7 +13,13 @@
 // performance change only: the arithmetic is the same chain, rounded at the
 // same points (see quant_math.cuh).
 //
-// Structure (one CTA per SM, persistent over 128x256 output tiles):
+// Two variants share the code: one CTA per 128x256 tile (cta_group::1), and a pair of CTAs on
+// neighbouring SMs per 256x256 tile (cta_group::2: each CTA stages its own 128 rows of A and its own
+// half of the W tile, one thread of the even CTA issues MMAs that span both SMs; this cuts the L2 ->
+// shared-memory traffic per output by a third and halves the W reads of each SM's tensor core).
+// No load is multicast: every CTA fetches its own operands.
+//
+// Structure (one CTA per SM, persistent over its tiles):
 //   warp 0     TMA producer: A tile 128x128 B and W tile 256x128 B per stage, 128-byte swizzle
 //   warp 1     allocates tensor memory, one lane issues tcgen05.mma (4 per stage, K = 32 each)
 //   warps 2-9  epilogue: tcgen05.ld of a finished accumulator, tail arithmetic, global stores
@@ -36,16 +42,22 @@ namespace b200q {
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 128;  // int8: bytes == elements
-constexpr int STAGES = 4;
+constexpr int BM = 128, BN = 256, BK = 128;  // per-CTA tile; int8: bytes == elements
 constexpr int UMMA_K = 32;
-constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int MAX_STAGES = 6;
+template <int NCTA>
+struct Cfg {
+  static constexpr int B_ROWS = BN / NCTA;  // rows of the W tile one CTA stages
+  static constexpr int A_BYTES = BM * BK, B_BYTES = B_ROWS * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = NCTA == 1 ? 4 : 6;
+};
 constexpr int EPI_WARPS = 8;                   // two warps per tensor-memory lane quarter, 128 columns each
 constexpr int EPI_COLS = BN / (EPI_WARPS / 4); // columns of a tile one epilogue warp handles
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int MISC_BYTES = 1024 + EPI_WARPS * EPI_COLS * 8;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + MISC_BYTES + 1024;  // + slack to align the tiles to 1024 B
+template <int NCTA>
+constexpr int smem_bytes() { return Cfg<NCTA>::STAGES * Cfg<NCTA>::STAGE_BYTES + MISC_BYTES + 1024; }  // + slack to align the tiles to 1024 B
 
 struct GemmParams {
   int64_t M, N, K;
@@ -113,6 +125,31 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
       : "memory");
 }
 
+// The same copy issued by a CTA of a pair: the mbarrier may live in the other CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar_cluster, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+// Address of `local` (a shared::cta address) in the shared memory of CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 B,
 // groups of 8 rows 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
@@ -138,6 +175,20 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"((uint16_t)3)
+               : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -159,8 +210,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct alignas(16) Misc {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -174,17 +225,23 @@ static_assert(offsetof(Misc, col_scale) % 16 == 0 && offsetof(Misc, col_bias) % 
 
 enum OutMode : int { OUT_F32 = 0, OUT_I32 = 1, OUT_Q8 = 2 };
 
-template <int ACT_T, int OUT_T>
+template <int ACT_T, int OUT_T, int NCTA>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using C = Cfg<NCTA>;
+  constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, A_BYTES = C::A_BYTES;
   extern __shared__ uint8_t smem_raw[];
+  // The pair variant needs the same shared-memory offsets in both CTAs: the dynamic region starts at the
+  // same window offset in every CTA of a kernel, so rounding it up to 1024 B gives the same result in both.
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Misc* misc = reinterpret_cast<Misc*>(tiles + STAGES * STAGE_BYTES);
   volatile int* abort_flag = &misc->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + BM - 1) / BM;
+  const uint32_t cta_rank = NCTA == 2 ? cluster_cta_rank() : 0u;   // 0 = the CTA that issues the MMAs
+  const int64_t tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + BM * NCTA - 1) / (BM * NCTA);
   const int64_t num_tiles = tiles_m * tiles_n;
+  const int64_t tile_first = blockIdx.x / NCTA, tile_step = gridDim.x / NCTA;
   const int num_kb = (int)((p.K + BK - 1) / BK);
 
   if (threadIdx.x == 0) {
@@ -194,20 +251,28 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(smem_u32(&misc->tmem_full[s]), 1);
-      mbar_init(smem_u32(&misc->tmem_empty[s]), EPI_WARPS);
+      mbar_init(smem_u32(&misc->tmem_empty[s]), EPI_WARPS * NCTA);  // the epilogue warps of both CTAs of a pair
     }
     misc->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   fill_exp2_table(misc->exp_tbl, threadIdx.x, blockDim.x);
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&misc->tmem_base)),
-                 "r"((uint32_t)TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (NCTA == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&misc->tmem_base)),
+                   "r"((uint32_t)TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else {  // the same warp of both CTAs allocates, with the same destination offset
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&misc->tmem_base)),
+                   "r"((uint32_t)TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
     tc_fence_before();
   }
   __syncthreads();
+  if (NCTA == 2) cluster_sync_all();  // the partner's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = misc->tmem_base;
 
@@ -216,8 +281,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (int)(tile / tiles_n) * BM, n0 = (int)(tile % tiles_n) * BN;
+      for (int64_t tile = tile_first; ok && tile < num_tiles; tile += tile_step) {
+        const int m0 = (int)(tile / tiles_n) * (BM * NCTA) + (int)cta_rank * BM;
+        const int n0 = (int)(tile % tiles_n) * BN + (int)cta_rank * C::B_ROWS;
         for (int kb = 0; kb < num_kb; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -227,20 +293,29 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             break;
           }
           const uint32_t bar = smem_u32(&misc->full[s]);
-          mbar_expect_tx(bar, STAGE_BYTES);
           uint8_t* st = tiles + s * STAGE_BYTES;
-          tma_load_2d(smem_u32(st), &tmA, bar, kb * BK, m0);
-          tma_load_2d(smem_u32(st + A_BYTES), &tmB, bar, kb * BK, n0);
+          if (NCTA == 1) {
+            mbar_expect_tx(bar, STAGE_BYTES);
+            tma_load_2d(smem_u32(st), &tmA, bar, kb * BK, m0);
+            tma_load_2d(smem_u32(st + A_BYTES), &tmB, bar, kb * BK, n0);
+          } else {
+            // Both CTAs' copies complete on the barrier of the MMA-issuing CTA, which expects the bytes of both.
+            // (A partner's bytes may land before the expectation is posted; the count is signed.)
+            if (cta_rank == 0) mbar_expect_tx(bar, 2 * STAGE_BYTES);
+            const uint32_t bar0 = map_to_cta(bar, 0);
+            tma_load_2d_pair(smem_u32(st), &tmA, bar0, kb * BK, m0);
+            tma_load_2d_pair(smem_u32(st + A_BYTES), &tmB, bar0, kb * BK, n0);
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc(BM * NCTA, BN);
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, tile_it++) {
+      for (int64_t tile = tile_first; ok && tile < num_tiles; tile += tile_step, tile_it++) {
         const uint32_t slot = tile_it & 1u, tph = (tile_it >> 1) & 1u;
         if (!mbar_wait(smem_u32(&misc->tmem_empty[slot]), tph ^ 1u, abort_flag, p.wait_limit_ns)) {
           atomicOr(p.status, STATUS_MMA_WAIT_TIMEOUT);
@@ -262,11 +337,18 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; k++) {
             // advancing K inside the 128-byte swizzle atom = advancing the start address by 32 B
-            umma_i8(tmem_d, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc, (kb | k) ? 1u : 0u);
+            const uint64_t dak = da + (uint64_t)(k * (UMMA_K >> 4)), dbk = db + (uint64_t)(k * (UMMA_K >> 4));
+            if (NCTA == 1) umma_i8(tmem_d, dak, dbk, idesc, (kb | k) ? 1u : 0u);
+            else umma_i8_pair(tmem_d, dak, dbk, idesc, (kb | k) ? 1u : 0u);
           }
-          umma_commit(smem_u32(&misc->empty[s]));  // frees the stage when these MMAs have read it
+          // frees the stage (in both CTAs of a pair) when these MMAs have read it
+          if (NCTA == 1) umma_commit(smem_u32(&misc->empty[s]));
+          else umma_commit_pair(smem_u32(&misc->empty[s]));
         }
-        if (ok) umma_commit(smem_u32(&misc->tmem_full[slot]));
+        if (ok) {
+          if (NCTA == 1) umma_commit(smem_u32(&misc->tmem_full[slot]));
+          else umma_commit_pair(smem_u32(&misc->tmem_full[slot]));
+        }
       }
     }
   } else {
@@ -283,9 +365,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         : OUT_T == OUT_I32 ? ((p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out_i32) & 15u) == 0))
                                            : ((p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out_f32) & 15u) == 0));
     uint32_t tile_it = 0;
-    for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tile_it++) {
+    for (int64_t tile = tile_first; tile < num_tiles; tile += tile_step, tile_it++) {
       const uint32_t slot = tile_it & 1u, tph = (tile_it >> 1) & 1u;
-      const int64_t m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN + col0;
+      const int64_t m0 = (tile / tiles_n) * (BM * NCTA) + cta_rank * BM, n0 = (tile % tiles_n) * BN + col0;
       if (OUT_T != OUT_I32) {
         // Stage this warp's column scales and biases while the main loop of the tile still runs.
         __syncwarp();
@@ -293,10 +375,13 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int j = lane; j < EPI_COLS; j += 32) {
           const int64_t n = n0 + j;
           cs[j] = (n < p.N) ? __ldg(p.w_scales + n) : 0.0f;
-          cb[j] = (has_bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+          cb[j] = (has_bias && n < p.N) ? __ldg(p.bias + n) : -0.0f;  // x + (-0) == x for every x, -0 included
         }
         __syncwarp();
       }
+      const int64_t m = m0 + quarter * 32 + lane;
+      const bool row_ok = m < p.M;
+      const float a_scale = (p.a_scales && row_ok) ? __ldg(p.a_scales + m) : 1.0f;  // fround(1 * ws) == ws
       bool ok = true;
       if (lane == 0) {
         ok = mbar_wait(smem_u32(&misc->tmem_full[slot]), tph, abort_flag, p.wait_limit_ns);
@@ -305,9 +390,6 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
-      const int64_t m = m0 + quarter * 32 + lane;
-      const bool row_ok = m < p.M;
-      const float a_scale = (p.a_scales && row_ok) ? __ldg(p.a_scales + m) : 1.0f;  // fround(1 * ws) == ws
       const uint32_t taddr = tmem_base + slot * BN + (uint32_t)col0 + ((uint32_t)(quarter * 32) << 16);
       constexpr int NCH = EPI_COLS / 32;
 #pragma unroll 1
@@ -344,21 +426,35 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const float4* cs4 = reinterpret_cast<const float4*>(cs + c * 32);
         const float4* cb4 = reinterpret_cast<const float4*>(cb + c * 32);
         constexpr unsigned kGeneral = act_general_threshold<ACT_T>();
+        // The loops below contain no branch at all (the choice between the two conversions is made once per
+        // chunk, a missing bias was staged as -0.0, which is the identity of the rounded addition), so the 32
+        // independent element chains of a thread can be interleaved freely.
+        if (!wide) {
 #pragma unroll
-        for (int j4 = 0; j4 < 8; j4++) {
-          const float4 w4 = cs4[j4], b4 = cb4[j4];
-          const float wsv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+          for (int j4 = 0; j4 < 8; j4++) {
+            const float4 w4 = cs4[j4], b4 = cb4[j4];
+            const float wsv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const int j = j4 * 4 + e;
-            const float sv = __fmul_rn(a_scale, wsv[e]);
-            float v = wide ? scale_acc_wide(a[j], sv) : scale_acc_small(a[j], sv);
-            if (has_bias) v = __fadd_rn(v, bv[e]);
+            for (int e = 0; e < 4; e++) y[j4 * 4 + e] = __fadd_rn(scale_acc_small(a[j4 * 4 + e], __fmul_rn(a_scale, wsv[e])), bv[e]);
+          }
+        } else {
+#pragma unroll
+          for (int j4 = 0; j4 < 8; j4++) {
+            const float4 w4 = cs4[j4], b4 = cb4[j4];
+            const float wsv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) y[j4 * 4 + e] = __fadd_rn(scale_acc_wide(a[j4 * 4 + e], __fmul_rn(a_scale, wsv[e])), bv[e]);
+          }
+        }
+        if (ACT_T != ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const float v = y[j];
             if (kGeneral != 0xFFFFFFFFu) vkey = max(vkey, __float_as_uint(v));
-            y[j] = apply_act_fast<ACT_T>(v, tbl);
+            const float r = apply_act_fast<ACT_T>(v, tbl);
             // Where the fast form is not valid (large negative argument, -Inf) keep the argument itself: no valid
             // result of these activations is below -0.3, so the bit test below recognises such an element again.
-            if (kGeneral != 0xFFFFFFFFu && __float_as_uint(v) > kGeneral) y[j] = v;
+            y[j] = (kGeneral != 0xFFFFFFFFu && __float_as_uint(v) > kGeneral) ? v : r;
           }
         }
         if (kGeneral != 0xFFFFFFFFu) {
@@ -410,7 +506,10 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // this warp is done reading the accumulator: hand the slot back to the MMA issuer
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&misc->tmem_empty[slot]));
+      if (lane == 0) {
+        if (NCTA == 1) mbar_arrive(smem_u32(&misc->tmem_empty[slot]));
+        else mbar_arrive_cluster(map_to_cta(smem_u32(&misc->tmem_empty[slot]), 0));
+      }
     }
   }
 
@@ -423,10 +522,14 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
+  if (NCTA == 2) cluster_sync_all();  // neither CTA leaves while its partner may still signal its barriers or read its tiles
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    if (NCTA == 1)
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
   }
 }
 
@@ -477,9 +580,11 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
                         int32_t* out_i32, int8_t* out_q, double q_scale) {
   ProfScope prof(ctx, KK_GEMM_UMMA);
   B200Q_REQUIRE(gemm_umma_supported(A, W_nk, M, N, K), "tensor-core int8 gemm needs K %% 16 == 0 and 16-byte aligned operands");
+  // CTA pairs pay off once there are enough 256-row tiles to go round; small or forced cases use single CTAs.
+  const int ncta = ctx->gemm_variant == 2 ? 1 : ctx->gemm_variant == 3 ? 2 : (M >= 1024 ? 2 : 1);
   CUtensorMap tmA, tmB;
   if (int e = make_tensor_map(&tmA, A, M, K, BM)) return e;
-  if (int e = make_tensor_map(&tmB, W_nk, N, K, BN)) return e;
+  if (int e = make_tensor_map(&tmB, W_nk, N, K, BN / ncta)) return e;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.a_scales = a_scales; p.w_scales = w_scales; p.bias = bias; p.act = act;
@@ -493,26 +598,39 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   }
   p.status = ctx->status_dev;
   p.wait_limit_ns = (unsigned long long)(ctx->wait_limit_s * 1e9);
-  const int64_t num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const unsigned grid = (unsigned)(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);
+  const int64_t num_tiles = ((M + BM * ncta - 1) / (BM * ncta)) * ((N + BN - 1) / BN);
+  const int64_t units = ctx->sm_count / ncta;   // CTAs (or CTA pairs) that can be resident at once
+  const unsigned grid = (unsigned)((num_tiles < units ? num_tiles : units) * ncta);
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const GemmParams);
-  static const KernelFn table[5][2] = {
-      {gemm_i8_umma_kernel<ACT_NONE, OUT_F32>, gemm_i8_umma_kernel<ACT_NONE, OUT_Q8>},
-      {gemm_i8_umma_kernel<ACT_RELU, OUT_F32>, gemm_i8_umma_kernel<ACT_RELU, OUT_Q8>},
-      {gemm_i8_umma_kernel<ACT_GELU_SIGMOID, OUT_F32>, gemm_i8_umma_kernel<ACT_GELU_SIGMOID, OUT_Q8>},
-      {gemm_i8_umma_kernel<ACT_GELU_TANH, OUT_F32>, gemm_i8_umma_kernel<ACT_GELU_TANH, OUT_Q8>},
-      {gemm_i8_umma_kernel<ACT_SILU, OUT_F32>, gemm_i8_umma_kernel<ACT_SILU, OUT_Q8>},
-  };
+#define B200Q_ROW(A) \
+  {{gemm_i8_umma_kernel<A, OUT_F32, 1>, gemm_i8_umma_kernel<A, OUT_F32, 2>}, {gemm_i8_umma_kernel<A, OUT_Q8, 1>, gemm_i8_umma_kernel<A, OUT_Q8, 2>}}
+  static const KernelFn table[5][2][2] = {B200Q_ROW(ACT_NONE), B200Q_ROW(ACT_RELU), B200Q_ROW(ACT_GELU_SIGMOID),
+                                          B200Q_ROW(ACT_GELU_TANH), B200Q_ROW(ACT_SILU)};
+#undef B200Q_ROW
+  static const KernelFn raw[2] = {gemm_i8_umma_kernel<ACT_NONE, OUT_I32, 1>, gemm_i8_umma_kernel<ACT_NONE, OUT_I32, 2>};
   B200Q_REQUIRE(act >= 0 && act <= 4, "unknown activation %d", act);
   B200Q_REQUIRE((out_i32 != nullptr) + (out_f32 != nullptr) + (out_q != nullptr) == 1,
                 "tensor-core int8 gemm writes exactly one output");
-  KernelFn fn = out_i32 ? gemm_i8_umma_kernel<ACT_NONE, OUT_I32> : table[act][out_q ? 1 : 0];
-  const int slot_idx = out_i32 ? 10 : act * 2 + (out_q ? 1 : 0);
+  KernelFn fn = out_i32 ? raw[ncta - 1] : table[act][out_q ? 1 : 0][ncta - 1];
+  const int smem = ncta == 1 ? smem_bytes<1>() : smem_bytes<2>();
+  const int slot_idx = (out_i32 ? 10 : act * 2 + (out_q ? 1 : 0)) * 2 + (ncta - 1);
   if (!(ctx->umma_ready_mask & (1u << slot_idx))) {
-    B200Q_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     ctx->umma_ready_mask |= 1u << slot_idx;
   }
-  fn<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)ncta;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B200Q_CHECK_CUDA(cudaLaunchKernelEx(&cfg, fn, tmA, tmB, p));
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;

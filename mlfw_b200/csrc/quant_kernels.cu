@@ -57,74 +57,104 @@ __device__ __forceinline__ bool is_normal_f32(float v) {
 // A group of G threads owns one row of K = 4*K4 floats; each thread holds VPT
 // float4 vectors (coalesced: vector i of a thread is G vectors after vector i-1).
 // One read of x, one write of q: 5 bytes per element of HBM traffic.
+// Blocks are persistent and software pipelined: the loads of a thread's next row
+// are issued before the current row is reduced and encoded, so a block keeps a
+// whole row of reads in flight through every phase of its work.
 // ---------------------------------------------------------------------------
 template <int VPT>
-__global__ void __launch_bounds__(1024) quantize_per_token_vec_kernel(const float* __restrict__ x, int64_t M, int K4, int G,
+__device__ __forceinline__ void load_row(float4 (&v)[VPT], const float* __restrict__ x, int64_t row, int64_t M, int K4, int G, int t) {
+  const float qnan = __int_as_float(0x7fc00000);  // neutral for fminf / fmaxf
+  const float4* xr = reinterpret_cast<const float4*>(x) + row * K4;
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {
+    const int c = t + i * G;
+    v[i] = (row < M && c < K4) ? ld_stream(xr + c) : make_float4(qnan, qnan, qnan, qnan);
+  }
+}
+
+// MAXT: largest block the instance is launched with (256 or 1024); the 1024-thread instances have only 64
+// registers per thread and do not prefetch.
+template <int VPT, int MAXT>
+__global__ void __launch_bounds__(MAXT) quantize_per_token_vec_kernel(const float* __restrict__ x, int64_t M, int K4, int G,
                                                                        int8_t* __restrict__ q, float* __restrict__ scales,
                                                                        float qmin, float qmax) {
-  __shared__ float s_mn[32], s_mx[32];
+  __shared__ float s_mn[2][32], s_mx[2][32];
   const int rows_per_block = blockDim.x / G;
   const int grp = threadIdx.x / G;
   const int t = threadIdx.x - grp * G;
-  const int64_t row = (int64_t)blockIdx.x * rows_per_block + grp;
-  const bool live = row < M;
-  const float4* xr = reinterpret_cast<const float4*>(x) + row * K4;
+  const int64_t row_stride = (int64_t)gridDim.x * rows_per_block;
+  const float limit = guard_limit(qmin, qmax);
 
-  const float qnan = __int_as_float(0x7fc00000);
-  float4 v[VPT];
-#pragma unroll
-  for (int i = 0; i < VPT; i++) {
-    int c = t + i * G;
-    v[i] = (live && c < K4) ? ld_stream(xr + c) : make_float4(qnan, qnan, qnan, qnan);
-  }
-  float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
-#pragma unroll
-  for (int i = 0; i < VPT; i++) {  // fminf/fmaxf drop NaN operands, as the strict < and > of the reference do
-    mn = fminf(fminf(mn, v[i].x), fminf(fminf(v[i].y, v[i].z), v[i].w));
-    mx = fmaxf(fmaxf(mx, v[i].x), fmaxf(fmaxf(v[i].y, v[i].z), v[i].w));
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  }
-  if (G > 32) {
-    const int warp = threadIdx.x >> 5;
-    if ((threadIdx.x & 31) == 0) { s_mn[warp] = mn; s_mx[warp] = mx; }
-    __syncthreads();
-    const int w0 = (grp * G) >> 5, nw = G >> 5;
-    float a = s_mn[w0], b = s_mx[w0];
-    for (int w = 1; w < nw; w++) { a = fminf(a, s_mn[w0 + w]); b = fmaxf(b, s_mx[w0 + w]); }
-    mn = a; mx = b;
-  }
-  if (!live) return;
+  constexpr bool PREFETCH = MAXT <= 256;
+  float4 nxt[PREFETCH ? VPT : 1];
+  if (PREFETCH) load_row<VPT>(reinterpret_cast<float4(&)[VPT]>(nxt), x, (int64_t)blockIdx.x * rows_per_block + grp, M, K4, G, t);
 
-  // One lane per warp does the binary64 divisions, the others receive the result.
-  double s = 0.0;
-  float inv = 0.0f;
-  if ((threadIdx.x & 31) == 0) {
-    s = row_scale(mn, mx);
-    inv = (float)(1.0 / s);
-  }
-  s = __hiloint2double(__shfl_sync(0xffffffffu, __double2hiint(s), 0), __shfl_sync(0xffffffffu, __double2loint(s), 0));
-  inv = __shfl_sync(0xffffffffu, inv, 0);
-  const bool exact_only = !is_normal_f32(inv);
+  int it = 0;
+  for (int64_t row0 = (int64_t)blockIdx.x * rows_per_block; row0 < M; row0 += row_stride, it++) {  // row0: uniform per block
+    const int64_t row = row0 + grp;
+    const bool live = row < M;
+    float4 v[VPT];
+    if (PREFETCH) {
+#pragma unroll
+      for (int i = 0; i < VPT; i++) v[i] = nxt[PREFETCH ? i : 0];
+      load_row<VPT>(reinterpret_cast<float4(&)[VPT]>(nxt), x, row + row_stride, M, K4, G, t);
+    } else {
+      load_row<VPT>(v, x, row, M, K4, G, t);
+    }
 
-  uint32_t words[VPT];
-  QuantGuard guard;
+    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
 #pragma unroll
-  for (int i = 0; i < VPT; i++) words[i] = pack4_fast(v[i], inv, guard);   // NaN padding of dead vectors only trips the guard
-  if (exact_only || guard.unsafe(guard_limit(qmin, qmax))) {  // rare: a tie, an out-of-range or a non-finite element
+    for (int i = 0; i < VPT; i++) {  // fminf/fmaxf drop NaN operands, as the strict < and > of the reference do
+      mn = fminf(fminf(mn, v[i].x), fminf(fminf(v[i].y, v[i].z), v[i].w));
+      mx = fmaxf(fmaxf(mx, v[i].x), fmaxf(fmaxf(v[i].y, v[i].z), v[i].w));
+    }
 #pragma unroll
-    for (int i = 0; i < VPT; i++) words[i] = pack4_exact_p(v[i], s, qmin, qmax);
+    for (int o = 16; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if (G > 32) {
+      // Two buffers alternate, so one barrier per row is enough: a buffer is rewritten two rows later,
+      // after every thread has passed the barrier of the row in between.
+      const int warp = threadIdx.x >> 5, b = it & 1;
+      if ((threadIdx.x & 31) == 0) { s_mn[b][warp] = mn; s_mx[b][warp] = mx; }
+      __syncthreads();
+      const int w0 = (grp * G) >> 5, nw = G >> 5;
+      float lo = s_mn[b][w0], hi = s_mx[b][w0];
+      for (int w = 1; w < nw; w++) { lo = fminf(lo, s_mn[b][w0 + w]); hi = fmaxf(hi, s_mx[b][w0 + w]); }
+      mn = lo; mx = hi;
+    }
+    if (!live) continue;
+
+    // Ordinary row (finite, not constant): the reciprocal scale 127/absmax is needed in binary32 only.
+    // Everything else (a constant row, whose range is widened in binary64; non-finite ends; a reciprocal
+    // that is not a normal binary32 number) encodes through the exact binary64 path.
+    const float absmax = fmaxf(fabsf(mn), fabsf(mx));
+    const float inv = __fdiv_rn(127.0f, absmax);
+    const bool exact_only = !((mn < mx) && absmax <= 3.402823466e38f && is_normal_f32(inv));
+#pragma unroll
+    for (int i = 0; i < VPT; i++)
+      if (t + i * G >= K4) v[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // dead vectors must not trip the guard
+
+    uint32_t words[VPT];
+    QuantGuard guard;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) words[i] = pack4_fast(v[i], inv, guard);
+    if (exact_only || guard.unsafe(limit)) {  // rare: a tie, an out-of-range or a non-finite element
+      const double s = row_scale(mn, mx);
+#pragma unroll
+      for (int i = 0; i < VPT; i++) words[i] = pack4_exact_p(v[i], s, qmin, qmax);
+    }
+    uint32_t* qr = reinterpret_cast<uint32_t*>(q) + row * K4;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int c = t + i * G;
+      if (c < K4) __stcs(qr + c, words[i]);
+    }
+    // fround(absmax / 127) of two binary32 numbers is the correctly rounded binary32 quotient
+    // (rounding the binary64 quotient again is innocuous for a division), so ordinary rows need no binary64.
+    if (t == 0) scales[row] = exact_only ? (float)row_scale(mn, mx) : __fdiv_rn(absmax, 127.0f);
   }
-  uint32_t* qr = reinterpret_cast<uint32_t*>(q) + row * K4;
-#pragma unroll
-  for (int i = 0; i < VPT; i++) {
-    int c = t + i * G;
-    if (c < K4) __stcs(qr + c, words[i]);
-  }
-  if (t == 0) scales[row] = (float)s;
 }
 
 // Any K, any alignment: one block per row, the row is read twice (the second
@@ -375,15 +405,19 @@ int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t
     const int vpt_needed = (K4 + G - 1) / G;
     const int threads = G < 256 ? 256 : G;
     const int rows_per_block = threads / G;
-    const unsigned blocks = (unsigned)((M + rows_per_block - 1) / rows_per_block);
-    if (vpt_needed <= 1)
-      quantize_per_token_vec_kernel<1><<<blocks, threads, 0, ctx->stream>>>(x, M, K4, G, q, scales, (float)qmin, (float)qmax);
-    else if (vpt_needed <= 2)
-      quantize_per_token_vec_kernel<2><<<blocks, threads, 0, ctx->stream>>>(x, M, K4, G, q, scales, (float)qmin, (float)qmax);
-    else if (vpt_needed <= 4)
-      quantize_per_token_vec_kernel<4><<<blocks, threads, 0, ctx->stream>>>(x, M, K4, G, q, scales, (float)qmin, (float)qmax);
-    else
-      quantize_per_token_vec_kernel<8><<<blocks, threads, 0, ctx->stream>>>(x, M, K4, G, q, scales, (float)qmin, (float)qmax);
+    typedef void (*Kern)(const float*, int64_t, int, int, int8_t*, float*, float, float);
+    const bool small = threads <= 256;
+    const Kern kern = vpt_needed <= 1   ? (small ? quantize_per_token_vec_kernel<1, 256> : quantize_per_token_vec_kernel<1, 1024>)
+                      : vpt_needed <= 2 ? (small ? quantize_per_token_vec_kernel<2, 256> : quantize_per_token_vec_kernel<2, 1024>)
+                      : vpt_needed <= 4 ? (small ? quantize_per_token_vec_kernel<4, 256> : quantize_per_token_vec_kernel<4, 1024>)
+                                        : (small ? quantize_per_token_vec_kernel<8, 256> : quantize_per_token_vec_kernel<8, 1024>);
+    int per_sm = 1;
+    B200Q_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0));
+    if (per_sm < 1) per_sm = 1;
+    int64_t blocks = (M + rows_per_block - 1) / rows_per_block;
+    const int64_t resident = (int64_t)ctx->sm_count * per_sm;
+    if (blocks > resident) blocks = resident;
+    kern<<<(unsigned)blocks, threads, 0, ctx->stream>>>(x, M, K4, G, q, scales, (float)qmin, (float)qmax);
   } else {
     const unsigned blocks = (unsigned)(M < (int64_t)ctx->sm_count * 8 ? M : (int64_t)ctx->sm_count * 8);
     quantize_per_token_generic_kernel<<<blocks, 256, 0, ctx->stream>>>(x, M, K, q, scales, (float)qmin, (float)qmax);

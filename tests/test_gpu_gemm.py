@@ -63,14 +63,20 @@ def test_gemm_i32_zero_points(ctx, orc, zpA, zpW):
     assert (dC.download() == orc.qdot_i32(A, W, "NK", zpA, zpW)).all()
 
 
-@pytest.mark.parametrize("M,N,K", UMMA_SHAPES)
-def test_gemm_i32_tensor_cores(ctx, orc, M, N, K):
+# gemm variants: 1 = CUDA cores, 2 = tensor cores with one CTA per 128x256 tile, 3 = CTA pairs on 256x256 tiles
+@pytest.mark.parametrize("variant", [2, 3])
+@pytest.mark.parametrize("M,N,K", UMMA_SHAPES + [(2048, 512, 256), (1300, 300, 160)])
+def test_gemm_i32_tensor_cores(ctx, orc, M, N, K, variant):
     rng = np.random.default_rng(M * 1009 + N * 31 + K + 1)
     A, W = gemm_inputs(rng, M, N, K)
     dA, dW = ctx.to_device(A), ctx.to_device(W)      # cudaMalloc alignment: the TMA path is taken
     dC = Guarded(ctx, (M, N), np.int32)
-    ctx.int8_gemm_i32(dA.ptr, dW.ptr, M, N, K, dC.ptr)
-    ctx.sync()
+    ctx.set_gemm_variant(variant)
+    try:
+        ctx.int8_gemm_i32(dA.ptr, dW.ptr, M, N, K, dC.ptr)
+        ctx.sync()
+    finally:
+        ctx.set_gemm_variant(0)
     ctx.check_status()
     C = dC.download()
     ref = orc.qdot_i32(A, W)
@@ -105,7 +111,7 @@ ACTS = ["none", "relu", "gelu_sigmoid", "silu", "gelu_tanh"]
 EXACT_ACTS = {"none", "relu", "gelu_sigmoid", "silu"}
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 @pytest.mark.parametrize("act", ACTS)
 @pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (130, 260, 144), (64, 1000, 768), (5, 7, 16)])
 def test_int8_linear_fused_tail(ctx, orc, M, N, K, act, variant):
@@ -170,7 +176,7 @@ def test_int8_linear_static_scale_no_bias(ctx, orc):
     assert (dout.download().view(np.uint32) == ref.view(np.uint32)).all()
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 def test_int8_linear_requant_static(ctx, orc, variant):
     rng = np.random.default_rng(17)
     M, N, K = 200, 520, 256
