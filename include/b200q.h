@@ -140,6 +140,17 @@ int b200q_int8_linear_requant_token(b200q_ctx* ctx, const int8_t* A, const float
  * workspace), contraction, tail. */
 int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const float* w_scales, const float* bias, int act,
                      int64_t M, int64_t N, int64_t K, float* out);
+/* b200q_linear_f32 for callers that must not allocate device memory inside the call (a host whose own pool
+ * owns the device, a latency-bound serving loop, a phase in which the CUDA allocation calls are not allowed).
+ * This entry point has no counterpart in the reference.  Same arguments and result as b200q_linear_f32; the
+ * int8 codes and per-token scales of the activations go to a fixed array inside the library image instead of
+ * a workspace, so: M * K <= 4 Mi elements and M <= 16384 rows, and the shape must be one the tensor-core
+ * kernel takes (K a multiple of 16, 16-byte aligned weights) - anything else is rejected with an error.
+ * The array costs 4 MiB + 64 KiB on every GPU that loads the library, until the process exits.  It is shared by
+ * all calls on a GPU: calls that overlap on one GPU (two contexts) race on it.  The first call on each device
+ * looks the array's device address up (no allocation); make that call before beginning any stream capture. */
+int b200q_linear_f32_noalloc(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const float* w_scales, const float* bias,
+                             int act, int64_t M, int64_t N, int64_t K, float* out);
 /* Same call with HOST activations and HOST result (what RuntimeModule.run hands a
  * backend: typed arrays, src/runtime/runtime.ts:239-268); weights stay on the device.
  * Copies both ways and synchronises. */

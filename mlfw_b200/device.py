@@ -232,6 +232,12 @@ class Context:
         check(self.lib.b200q_linear_f32(self.handle, _ptr(x), _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act], M, N, K,
                                         _ptr(out)), "b200q_linear_f32")
 
+    def linear_f32_noalloc(self, x, W_nk, w_scales, bias, act, M, N, K, out):
+        """b200q_linear_f32 without any allocation inside the call: scratch is a fixed array in the library
+        (M*K <= 4 Mi, M <= 16384, tensor-core shapes only); overlapping calls on one GPU race on it."""
+        check(self.lib.b200q_linear_f32_noalloc(self.handle, _ptr(x), _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act], M, N, K,
+                                                _ptr(out)), "b200q_linear_f32_noalloc")
+
     # ---- ops (host buffers in and out; weights on the device)
     def linear_f32_host(self, x_host, W_nk, w_scales, bias, act, M, N, K, out_host):
         check(self.lib.b200q_linear_f32_host(self.handle, _ptr(x_host), _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act], M, N,
