@@ -132,6 +132,13 @@ void b200q_destroy(b200q_ctx* ctx) {
   for (int i = 0; i < PROFILE_RING; i++)
     for (int j = 0; j < 2; j++)
       if (ctx->prof_ev[i][j]) cudaEventDestroy(ctx->prof_ev[i][j]);
+  for (int i = 0; i < HOST_CHUNKS; i++) {
+    if (ctx->ev_in[i]) cudaEventDestroy(ctx->ev_in[i]);
+    if (ctx->ev_done[i]) cudaEventDestroy(ctx->ev_done[i]);
+  }
+  if (ctx->ev_free) cudaEventDestroy(ctx->ev_free);
+  if (ctx->stream_h2d) cudaStreamDestroy(ctx->stream_h2d);
+  if (ctx->stream_d2h) cudaStreamDestroy(ctx->stream_d2h);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -414,18 +421,58 @@ int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const f
   return linear_core(ctx, q, s, W_nk, w_scales, bias, act, M, N, K, out, nullptr, 1.0);
 }
 
+static int host_pipeline_ready(b200q_ctx* ctx) {
+  if (ctx->stream_h2d) return 0;
+  B200Q_CHECK_CUDA(cudaStreamCreateWithFlags(&ctx->stream_h2d, cudaStreamNonBlocking));
+  B200Q_CHECK_CUDA(cudaStreamCreateWithFlags(&ctx->stream_d2h, cudaStreamNonBlocking));
+  for (int i = 0; i < HOST_CHUNKS; i++) {
+    B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming));
+    B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_done[i], cudaEventDisableTiming));
+  }
+  B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_free, cudaEventDisableTiming));
+  return 0;
+}
+
+// Rows are independent, so the call is cut into row blocks and pipelined over three streams: while block i is
+// computed, block i+1 is on its way in and block i-1 on its way out (PCIe is full duplex).  With page-locked host
+// buffers the call then costs about one direction of the transfer instead of both plus the compute.
 int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_nk, const float* w_scales, const float* bias,
                           int act, int64_t M, int64_t N, int64_t K, float* out_host) {
   if (use_device(ctx)) return 1;
   if (int e = check_linear("b200q_linear_f32_host", x_host, W_nk, w_scales, act, M, N, K, out_host)) return e;
+  B200Q_REQUIRE(K > 0 || M == 0, "b200q_linear_f32_host: rows of zero length have no range");
   if (M == 0 || N == 0) return 0;
+  if (host_pipeline_ready(ctx)) return 1;
   if (ws_reserve(ctx, ctx->ws_stage_in, (size_t)M * K * sizeof(float))) return 1;
   if (ws_reserve(ctx, ctx->ws_stage_out, (size_t)M * N * sizeof(float))) return 1;
+  if (ws_reserve(ctx, ctx->ws_q, (size_t)M * K)) return 1;
+  if (ws_reserve(ctx, ctx->ws_scales, (size_t)M * sizeof(float))) return 1;
   float* x = (float*)ctx->ws_stage_in.ptr;
   float* y = (float*)ctx->ws_stage_out.ptr;
-  B200Q_CHECK_CUDA(cudaMemcpyAsync(x, x_host, (size_t)M * K * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
-  if (int e = b200q_linear_f32(ctx, x, W_nk, w_scales, bias, act, M, N, K, y)) return e;
-  B200Q_CHECK_CUDA(cudaMemcpyAsync(out_host, y, (size_t)M * N * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  int8_t* q = (int8_t*)ctx->ws_q.ptr;
+  float* sc = (float*)ctx->ws_scales.ptr;
+  // Row blocks of a multiple of 256 rows (one tile of the CTA-pair kernel), at most HOST_CHUNKS of them.
+  int64_t rows = ((M + HOST_CHUNKS - 1) / HOST_CHUNKS + 255) / 256 * 256;
+  if (rows < 1024) rows = 1024;
+  // The workspaces may just have been (re)allocated on the compute stream: the copy streams start after that.
+  B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_free, ctx->stream));
+  B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream_h2d, ctx->ev_free, 0));
+  B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream_d2h, ctx->ev_free, 0));
+  int c = 0;
+  for (int64_t m0 = 0; m0 < M; m0 += rows, c++) {
+    const int64_t mc = (M - m0 < rows) ? (M - m0) : rows;
+    B200Q_CHECK_CUDA(cudaMemcpyAsync(x + m0 * K, x_host + m0 * K, (size_t)mc * K * sizeof(float), cudaMemcpyHostToDevice,
+                                     ctx->stream_h2d));
+    B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_in[c], ctx->stream_h2d));
+    B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_in[c], 0));
+    if (int e = launch_quantize_per_token(ctx, x + m0 * K, mc, K, q + m0 * K, sc + m0, -127, 127)) return e;
+    if (int e = linear_core(ctx, q + m0 * K, sc + m0, W_nk, w_scales, bias, act, mc, N, K, y + m0 * N, nullptr, 1.0)) return e;
+    B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_done[c], ctx->stream));
+    B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream_d2h, ctx->ev_done[c], 0));
+    B200Q_CHECK_CUDA(cudaMemcpyAsync(out_host + m0 * N, y + m0 * N, (size_t)mc * N * sizeof(float), cudaMemcpyDeviceToHost,
+                                     ctx->stream_d2h));
+  }
+  B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream_d2h));
   B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
   return 0;
 }

@@ -41,6 +41,7 @@ enum StatusBits : uint32_t {
 enum KernelKind : int { KK_QUANT_TOKEN = 0, KK_DEQUANT_TOKEN, KK_QUANT_STATIC, KK_DEQUANT_STATIC, KK_WEIGHTS, KK_GEMM_UMMA,
                         KK_GEMM_SIMT, KK_EPILOGUE, KK_COUNT };
 constexpr int PROFILE_RING = 256;
+constexpr int HOST_CHUNKS = 16;   // most pieces a host-buffer call is split into
 
 struct Workspace {
   void* ptr = nullptr;
@@ -55,6 +56,9 @@ struct b200q_ctx {
   int sm_count = 0;
   int l2_bytes = 0;
   cudaStream_t stream = nullptr;
+  // copy streams and events of the pipelined host-buffer entry points (created on first use)
+  cudaStream_t stream_h2d = nullptr, stream_d2h = nullptr;
+  cudaEvent_t ev_in[b200q::HOST_CHUNKS] = {}, ev_done[b200q::HOST_CHUNKS] = {}, ev_free = nullptr;
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
   uint32_t* status_dev = nullptr;        // device status word
   b200q::Workspace ws_q;                 // int8 activations of the fused linear
