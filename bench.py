@@ -113,6 +113,36 @@ def make_case(workload: str, rank: int):
     return M, K, N, act, xs, W, ws, bias
 
 
+def run_roundtrip(ctx, pk, iters, warmup):
+    """Standalone quantize -> dequantize of f32 [16384,4096] with 0.1% outliers (HBM bound); per-kernel GB/s."""
+    from mlfw_b200 import synth
+    M2, K2 = C2_SHAPE
+    x2 = synth.with_outliers(synth.normal(synth.tensor_seed(0, 20), (M2, K2)), synth.tensor_seed(0, 21), synth.tensor_seed(0, 22))
+    d2 = [ctx.to_device(x2), ctx.to_device(x2[::-1].copy())]      # two sets alternate: 671 MB per set pair, > L2
+    q2 = [ctx.empty((M2, K2), np.int8) for _ in range(2)]
+    s2 = [ctx.empty((M2,), np.float32) for _ in range(2)]
+    y2 = [ctx.empty((M2, K2), np.float32) for _ in range(2)]
+    for i in range(warmup):
+        ctx.quantize_per_token(d2[i % 2], M2, K2, q2[i % 2], s2[i % 2])
+        ctx.dequantize_per_token(q2[i % 2], s2[i % 2], M2, K2, y2[i % 2])
+    ctx.profile_enable(True)
+    ctx.profile_reset()
+    for i in range(iters):
+        ctx.quantize_per_token(d2[i % 2], M2, K2, q2[i % 2], s2[i % 2])
+        ctx.dequantize_per_token(q2[i % 2], s2[i % 2], M2, K2, y2[i % 2])
+    p2 = ctx.profile_read()
+    ctx.profile_enable(False)
+    ctx.check_status()
+    bytes_each = 5.0 * M2 * K2 + 4.0 * M2
+    rt = {}
+    for name in ("quantize_per_token", "dequantize_per_token"):
+        t, n = p2[name]
+        gbs = bytes_each / (t / n * 1e-3) / 1e9
+        rt[name] = {"achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                    "frac_of_nominal_8000": gbs / 8000.0, "avg_launch_ms": t / n}
+    return {"workload": "quantize -> dequantize, f32 [16384,4096], 0.1% outliers", "algorithmic_bytes": bytes_each, **rt}
+
+
 def run_reference_arm(args, rank, world):
     """The reference's CPU path (its C++ restatement: no JavaScript engine exists here) on all host cores."""
     if rank != 0:
@@ -153,6 +183,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
+    ap.add_argument("--roundtrip-only", action="store_true", help="only the standalone quantize -> dequantize round trip (profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" and not args.no_extras else args.warmup
 
@@ -184,6 +215,10 @@ def main():
         return float(t.item())
 
     ctx = mlfw_b200.Context(local_rank)
+    if args.roundtrip_only:
+        print(json.dumps({"metric": "quantize_dequantize_GBps", "roundtrip_c2": run_roundtrip(ctx, peaks(), args.steps, args.warmup)}))
+        ctx.close()
+        return
     M, K, N, act, xs, W, ws, bias = make_case(args.workload, rank)
     dxs = [ctx.to_device(x) for x in xs]
     douts = [ctx.empty((M, N), np.float32) for _ in xs]
@@ -271,32 +306,7 @@ def main():
                        "api": "b200q_linear_f32_host (pinned host input, host output, synchronous)"}
 
         if rank == 0 and world == 1:
-            # ---------------------------------------------------- standalone quantize / dequantize (HBM bound)
-            from mlfw_b200 import synth
-            M2, K2 = C2_SHAPE
-            x2 = synth.with_outliers(synth.normal(synth.tensor_seed(0, 20), (M2, K2)), synth.tensor_seed(0, 21), synth.tensor_seed(0, 22))
-            d2 = [ctx.to_device(x2), ctx.to_device(x2[::-1].copy())]
-            q2 = [ctx.empty((M2, K2), np.int8) for _ in range(2)]
-            s2 = [ctx.empty((M2,), np.float32) for _ in range(2)]
-            y2 = [ctx.empty((M2, K2), np.float32) for _ in range(2)]
-            for i in range(4):
-                ctx.quantize_per_token(d2[i % 2], M2, K2, q2[i % 2], s2[i % 2])
-                ctx.dequantize_per_token(q2[i % 2], s2[i % 2], M2, K2, y2[i % 2])
-            ctx.profile_enable(True)
-            ctx.profile_reset()
-            for i in range(20):
-                ctx.quantize_per_token(d2[i % 2], M2, K2, q2[i % 2], s2[i % 2])
-                ctx.dequantize_per_token(q2[i % 2], s2[i % 2], M2, K2, y2[i % 2])
-            p2 = ctx.profile_read()
-            ctx.profile_enable(False)
-            bytes_each = 5.0 * M2 * K2 + 4.0 * M2
-            rt = {}
-            for name in ("quantize_per_token", "dequantize_per_token"):
-                t, n = p2[name]
-                gbs = bytes_each / (t / n * 1e-3) / 1e9
-                rt[name] = {"achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
-                            "frac_of_nominal_8000": gbs / 8000.0, "avg_launch_ms": t / n}
-            line["roundtrip_c2"] = {"workload": "quantize -> dequantize, f32 [16384,4096], 0.1% outliers", "algorithmic_bytes": bytes_each, **rt}
+            line["roundtrip_c2"] = run_roundtrip(ctx, pk, iters=20, warmup=4)
 
             # ---------------------------------------------------- CPU baseline (bounded sample)
             import oracle

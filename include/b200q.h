@@ -53,6 +53,9 @@ int b200q_set_wait_limit(b200q_ctx* ctx, double seconds);
 /* 0: tensor-core GEMM whenever the shape allows, one CTA or a CTA pair per tile chosen by size (default);
  * 1: CUDA-core kernel only; 2: tensor cores, one CTA per tile; 3: tensor cores, CTA pairs. */
 int b200q_set_gemm_variant(b200q_ctx* ctx, int variant);
+/* Per-token quantize: 0 = rows staged through shared memory by bulk copies when they fit (default);
+ * 1 = register-resident kernel only. */
+int b200q_set_quant_variant(b200q_ctx* ctx, int variant);
 /* Kernels launched through this context since it was created. */
 uint64_t b200q_launch_count(b200q_ctx* ctx);
 int b200q_sm_count(b200q_ctx* ctx);

@@ -1,0 +1,443 @@
+"""Host-side mirror of the reference's backend interface for this path.
+
+The reference is TypeScript; the image has no JavaScript engine, so the logic a maintainer would add to the
+reference (``mlfw_b200/ts/``) is kept here in runnable form with the same names and behaviour:
+
+* :func:`B200Target` — a target description carrying ``EXTERNAL_COMPILER`` (the seam ``TeracTarget`` uses,
+  src/backend/terac/target.ts:16-38; consumed at src/compiler/pipeline/compiler.ts:297-329);
+* :func:`compile_with_b200` — receives the graph AFTER the reference's graph passes (``QuantizationPass``
+  included) and returns a :class:`B200RuntimeModule`;
+* :class:`B200RuntimeModule` — ``RuntimeModuleLike`` (src/compiler/support/config_types.ts:58-66): ``run``,
+  ``runAsync``, ``isAsync``, ``getKernelSource``, ``getKernelMetadata``, ``listKernels``.
+
+The graph is the reference's graph IR reduced to what matters here: a flat list of ops with the reference's op
+names and attributes (fusion is disabled on the target, so no ``fusion`` regions arrive).  Anything outside the
+contract raises :class:`B200CompileError` — there is no CPU fallback inside the backend.  This module only plans
+and marshals; all arithmetic on tensors happens in ``libb200q.so``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence
+
+import numpy as np
+
+from .device import ACT, Context, KIND, W_KN, W_NK  # noqa: F401
+
+
+class B200CompileError(RuntimeError):
+    pass
+
+
+# ----------------------------------------------------------------------------- the graph contract
+@dataclass(eq=False)
+class Value:
+    shape: tuple
+    dtype: str                      # 'f32', 'i8', 'ui8', 'i32'
+    producer: Optional["Op"] = None
+    name: str = ""
+
+
+@dataclass(eq=False)
+class Op:
+    name: str                       # reference op name: 'quantize', 'quantized_dot', 'convert', 'mul', ...
+    operands: List[Value]
+    attrs: Dict[str, Any]
+    result: Value
+
+
+@dataclass
+class GraphFunction:
+    name: str
+    args: List[Value]
+    ops: List[Op] = field(default_factory=list)
+    returns: List[Value] = field(default_factory=list)
+
+    def users(self, v: Value) -> List[Op]:
+        return [o for o in self.ops if any(x is v for x in o.operands)]
+
+
+class GraphBuilder:
+    """Builds a :class:`GraphFunction` op by op (the role IRBuilder plays in the reference's tests,
+    tests/_utils/ir_fixture.js:10-29)."""
+
+    def __init__(self, name: str):
+        self.func = GraphFunction(name, [])
+
+    def arg(self, shape, dtype="f32") -> Value:
+        v = Value(tuple(shape), dtype, None, f"arg{len(self.func.args)}")
+        self.func.args.append(v)
+        return v
+
+    def op(self, name: str, operands: Sequence[Value], shape, dtype: str, **attrs) -> Value:
+        res = Value(tuple(shape), dtype)
+        o = Op(name, list(operands), dict(attrs), res)
+        res.producer = o
+        self.func.ops.append(o)
+        return res
+
+    def constant(self, value, shape, dtype) -> Value:
+        return self.op("constant", [], shape, dtype, value=value)
+
+    def ret(self, *values: Value) -> GraphFunction:
+        self.func.returns = list(values)
+        return self.func
+
+
+NP_DTYPE = {"f32": np.float32, "i8": np.int8, "ui8": np.uint8, "i32": np.int32}
+
+TARGET_ATTR_FUSION = "fusion"
+TARGET_ATTR_EXTERNAL_COMPILER = "externalCompiler"
+B200_OPTIONS = "b200Options"
+
+
+def B200Target(library: Optional[str] = None, device: int = 0, activationQuant: str = "static") -> dict:
+    """The target object a user passes to ``compile(model, inputs, {target: B200Target()})``.
+
+    ``activationQuant='static'`` reproduces the reference's scales (the activation scale the pass baked into the
+    graph); ``'per_token_dynamic'`` ignores it, computes one scale per row on the device and recovers the weight
+    scales as ``scaleVec[n] / lhs_scale``."""
+    if activationQuant not in ("static", "per_token_dynamic"):
+        raise ValueError("activationQuant must be 'static' or 'per_token_dynamic'")
+    return {
+        "kind": "accelerator", "name": "b200_int8", "supportsInt8": True, "supportsConstBuffers": True,
+        "attrs": {TARGET_ATTR_FUSION: {"enabled": False}, TARGET_ATTR_EXTERNAL_COMPILER: compile_with_b200,
+                  B200_OPTIONS: {"library": library, "device": device, "activationQuant": activationQuant}},
+    }
+
+
+def compile_with_b200(module: Dict[str, GraphFunction], config: dict) -> "B200RuntimeModule":
+    """``TargetAttr.EXTERNAL_COMPILER`` hook: ``(GraphModule, CompilerConfig) -> RuntimeModuleLike``."""
+    options = config["target"]["attrs"].get(B200_OPTIONS, {})
+    return B200RuntimeModule(module, options)
+
+
+# ----------------------------------------------------------------------------- planning
+@dataclass
+class Step:
+    kind: str                       # 'quantize_static' | 'quantize_token' | 'dequantize_static' | 'linear'
+    ins: List[Value]
+    out: Value
+    params: Dict[str, Any]
+
+
+def _const_array(v: Value) -> Optional[np.ndarray]:
+    if v.producer is not None and v.producer.name == "constant":
+        val = v.producer.attrs["value"]
+        return np.asarray(val, dtype=np.float64).reshape(v.shape if v.shape else ())
+    return None
+
+
+def _broadcast_source(v: Value) -> Optional[Value]:
+    """The operand of a broadcast_in_dim / broadcast producing ``v`` (or ``v`` itself if it is a constant)."""
+    if v.producer is None:
+        return None
+    if v.producer.name in ("broadcast_in_dim", "broadcast"):
+        return v.producer.operands[0]
+    if v.producer.name == "constant":
+        return v
+    return None
+
+
+def _scalar_const(v: Value) -> Optional[float]:
+    src = _broadcast_source(v)
+    if src is None:
+        return None
+    arr = _const_array(src)
+    if arr is None or arr.size != 1:
+        return None
+    return float(arr.reshape(-1)[0])
+
+
+class _Planner:
+    def __init__(self, func: GraphFunction, dynamic: bool):
+        self.f = func
+        self.dynamic = dynamic
+        self.steps: List[Step] = []
+        self.done: set = set()      # ids of ops absorbed into a step
+
+    def other(self, op: Op, v: Value) -> Value:
+        a, b = op.operands
+        return b if a is v else a
+
+    def single_user(self, v: Value, name: str) -> Optional[Op]:
+        us = [u for u in self.f.users(v) if id(u) not in self.done]
+        return us[0] if len(us) == 1 and us[0].name == name else None
+
+    # ---- activation chains as the decomposition pass emits them (decomposition_pass.ts:197-230, builder.ts:561-565)
+    def match_sigmoid(self, z: Value):
+        """neg(z) -> exp -> add(1, .) -> div(1, .); returns (result, ops) or None."""
+        neg = next((u for u in self.f.users(z) if u.name == "neg"), None)
+        if neg is None:
+            return None
+        exp = self.single_user(neg.result, "exp")
+        if exp is None:
+            return None
+        add = self.single_user(exp.result, "add")
+        if add is None or _scalar_const(self.other(add, exp.result)) != 1.0:
+            return None
+        div = self.single_user(add.result, "div")
+        if div is None or div.operands[1] is not add.result or _scalar_const(div.operands[0]) != 1.0:
+            return None
+        return div.result, [neg, exp, add, div]
+
+    def match_activation(self, y: Value):
+        """Returns (act, result value, absorbed ops) for the chain hanging off ``y``; ('none', y, []) if none."""
+        users = [u for u in self.f.users(y) if id(u) not in self.done]
+        for u in users:
+            if u.name == "maximum" and _scalar_const(self.other(u, y)) == 0.0 and len(users) == 1:
+                return "relu", u.result, [u]
+        # silu: y * sigmoid(y)
+        sig = self.match_sigmoid(y)
+        if sig is not None:
+            res, ops = sig
+            mul = next((u for u in self.f.users(res) if u.name == "mul" and any(o is y for o in u.operands)), None)
+            if mul is not None:
+                return "silu", mul.result, ops + [mul]
+        # gelu: y * sigmoid(1.702 * y)
+        for u in users:
+            if u.name == "mul":
+                c = _scalar_const(self.other(u, y))
+                if c is not None and abs(c - 1.702) < 1e-12:
+                    sig = self.match_sigmoid(u.result)
+                    if sig is not None:
+                        res, ops = sig
+                        mul = next((m for m in self.f.users(res) if m.name == "mul" and any(o is y for o in m.operands)), None)
+                        if mul is not None:
+                            return "gelu_sigmoid", mul.result, [u] + ops + [mul]
+        for u in users:
+            if u.name == "gelu_tanh":      # not a reference op: offered for callers that build the graph themselves
+                return "gelu_tanh", u.result, [u]
+        return "none", y, []
+
+    def plan_dot(self, op: Op):
+        lhs, rhs = op.operands
+        w = _const_array(rhs)
+        if w is None or rhs.dtype != "i8" or len(rhs.shape) != 2:
+            raise B200CompileError("quantized_dot needs a constant rank-2 int8 rhs (weights cross the boundary as buffers)")
+        if op.attrs.get("lhs_zero_point", 0) or op.attrs.get("rhs_zero_point", 0):
+            raise B200CompileError("quantized_dot with zero-points is outside the symmetric north-star path")
+        if op.attrs.get("lhs_batch") or op.attrs.get("rhs_batch"):
+            raise B200CompileError("batched quantized_dot is not supported: flatten leading dimensions to M")
+        rc = list(op.attrs.get("rhs_contracting", [0]))
+        lc = list(op.attrs.get("lhs_contracting", [len(lhs.shape) - 1]))
+        if lc != [len(lhs.shape) - 1] or len(rc) != 1:
+            raise B200CompileError("quantized_dot must contract the last lhs dimension with one rhs dimension")
+        w_layout = W_KN if rc[0] == 0 else W_NK
+        K = rhs.shape[rc[0]]
+        N = rhs.shape[1 - rc[0]]
+        M = int(np.prod(lhs.shape[:-1]))      # leading dimensions flatten to rows (cublas_split.ts:84-90 does the same)
+        lhs_scale = float(op.attrs.get("lhs_scale", 1.0))
+        absorbed = [op]
+        y = op.result
+        sv = None
+        # per-channel tail: convert -> mul(broadcast(constant f32[N]))
+        conv = self.single_user(y, "convert")
+        deq = self.single_user(y, "dequantize")
+        if conv is not None:
+            mul = self.single_user(conv.result, "mul")
+            src = _broadcast_source(self.other(mul, conv.result)) if mul is not None else None
+            arr = _const_array(src) if src is not None else None
+            if mul is None or arr is None or arr.size != N:
+                raise B200CompileError("quantized_dot -> convert must be followed by mul with a per-channel scale vector")
+            sv = arr.reshape(-1)
+            absorbed += [conv, mul]
+            y = mul.result
+        elif deq is not None:                 # per-tensor path: dequantize(scale = lhs_scale * rhs_scale)
+            if deq.attrs.get("zero_point", 0):
+                raise B200CompileError("dequantize with a zero-point after quantized_dot is not supported")
+            sv = np.full(N, float(deq.attrs["scale"]), np.float64)
+            absorbed += [deq]
+            y = deq.result
+        else:
+            raise B200CompileError("quantized_dot must be followed by its dequantizing tail")
+        bias = None
+        add = self.single_user(y, "add")
+        if add is not None:
+            src = _broadcast_source(self.other(add, y))
+            arr = _const_array(src) if src is not None else None
+            if arr is not None and arr.size == N:
+                bias = arr.reshape(-1).astype(np.float32)
+                absorbed.append(add)
+                y = add.result
+        for o in absorbed:
+            self.done.add(id(o))
+        act, y, act_ops = self.match_activation(y)
+        for o in act_ops:
+            self.done.add(id(o))
+        params = {"M": M, "N": N, "K": K, "w": w.astype(np.int8), "w_layout": w_layout, "bias": bias, "act": act,
+                  "requant_scale": None, "a_dynamic": False}
+        if self.dynamic:
+            # recover the weight scales from the baked product (both are still binary64 here), rounded to f32 once
+            params["w_scales"] = (sv / lhs_scale).astype(np.float32)
+            params["a_dynamic"] = True
+        else:
+            params["w_scales"] = sv.astype(np.float32)          # fround(aScale * wScale[n]): the f32 constant of the graph
+        # a following static quantize of the result fuses into the epilogue
+        nq = self.single_user(y, "quantize")
+        if nq is not None and not self.dynamic and not nq.attrs.get("zero_point", 0) and nq.attrs.get("target_dtype", "i8") == "i8" \
+                and not any(r is y for r in self.f.returns):
+            params["requant_scale"] = float(nq.attrs["scale"])
+            self.done.add(id(nq))
+            y = nq.result
+        self.steps.append(Step("linear", [lhs], y, params))
+
+    def plan(self) -> List[Step]:
+        for op in self.f.ops:
+            if id(op) in self.done:
+                continue
+            n = op.name
+            if n in ("constant", "broadcast_in_dim", "broadcast"):
+                continue                       # consumed through their users
+            if n == "quantize":
+                x = op.operands[0]
+                users = self.f.users(op.result)
+                feeds_dot = bool(users) and all(u.name == "quantized_dot" and u.operands[0] is op.result for u in users)
+                if self.dynamic and feeds_dot and len(x.shape) >= 2:
+                    self.steps.append(Step("quantize_token", [x], op.result, {"K": x.shape[-1], "M": int(np.prod(x.shape[:-1]))}))
+                else:
+                    self.steps.append(Step("quantize_static", [x], op.result, {
+                        "scale": float(op.attrs["scale"]), "zero_point": int(op.attrs.get("zero_point", 0)),
+                        "kind": 1 if op.attrs.get("target_dtype", "i8") == "ui8" else 0}))
+            elif n == "dequantize":
+                self.steps.append(Step("dequantize_static", [op.operands[0]], op.result, {
+                    "scale": float(op.attrs["scale"]), "zero_point": int(op.attrs.get("zero_point", 0)),
+                    "kind": {"i8": 0, "ui8": 1, "i32": 2}[op.operands[0].dtype]}))
+            elif n == "quantized_dot":
+                self.plan_dot(op)
+            elif n == "return":
+                continue
+            else:
+                raise B200CompileError(f"op '{n}' is outside the graph contract of the B200 backend "
+                                       "(quantize, dequantize, quantized_dot and its per-channel tail); "
+                                       "compile with quantizableOps = {'dot'} and keep other ops on another target")
+        return self.steps
+
+
+def plan_function(func: GraphFunction, dynamic: bool) -> List[Step]:
+    return _Planner(func, dynamic).plan()
+
+
+# ----------------------------------------------------------------------------- execution
+class _FunctionPlan:
+    def __init__(self, ctx: Context, func: GraphFunction, dynamic: bool):
+        self.func = func
+        self.steps = plan_function(func, dynamic)
+        self.inputs = len(func.args)
+        self.outputs = len(func.returns)
+        self.ctx = ctx
+        self.buf: Dict[int, Any] = {}           # id(Value) -> DeviceBuffer
+        self.scales: Dict[int, Any] = {}        # id(Value of per-token codes) -> DeviceBuffer of scales
+        for v in func.args:
+            self._alloc(v)
+        for st in self.steps:
+            self._alloc(st.out)
+            if st.kind == "quantize_token":
+                self.scales[id(st.out)] = ctx.empty((st.params["M"],), np.float32)
+            if st.kind == "linear":
+                p = st.params
+                w = p["w"]
+                if p["w_layout"] == W_KN:       # re-lay [K,N] constants as [N,K] once, on the device
+                    src = ctx.to_device(w)
+                    dst = ctx.empty((p["N"], p["K"]), np.int8)
+                    ctx.transpose_i8(src, p["K"], p["N"], dst)
+                    ctx.sync()
+                    src.free()
+                    p["dW"] = dst
+                else:
+                    p["dW"] = ctx.to_device(w)
+                p["dws"] = ctx.to_device(p["w_scales"])
+                p["db"] = ctx.to_device(p["bias"]) if p["bias"] is not None else None
+        missing = [r for r in func.returns if id(r) not in self.buf]
+        if missing:
+            raise B200CompileError("a returned value is not produced by any native step")
+
+    def _alloc(self, v: Value):
+        if id(v) not in self.buf:
+            self.buf[id(v)] = self.ctx.empty(v.shape if v.shape else (1,), NP_DTYPE[v.dtype])
+
+    def describe(self) -> str:
+        lines = []
+        for st in self.steps:
+            p = {k: v for k, v in st.params.items() if k in ("M", "N", "K", "act", "scale", "zero_point", "requant_scale", "a_dynamic")}
+            lines.append(f"{st.kind} {p}")
+        return "\n".join(lines)
+
+    def execute(self, arrays: Sequence[np.ndarray]):
+        ctx = self.ctx
+        for v, a in zip(self.func.args, arrays[: self.inputs]):
+            self.buf[id(v)].upload(np.ascontiguousarray(a, NP_DTYPE[v.dtype]).reshape(v.shape))
+        for st in self.steps:
+            x = self.buf[id(st.ins[0])]
+            out = self.buf[id(st.out)]
+            p = st.params
+            if st.kind == "quantize_static":
+                ctx.quantize_static(x, int(np.prod(st.ins[0].shape)), p["scale"], p["zero_point"], p["kind"], out)
+            elif st.kind == "quantize_token":
+                ctx.quantize_per_token(x, p["M"], p["K"], out, self.scales[id(st.out)])
+            elif st.kind == "dequantize_static":
+                ctx.dequantize_static(x, p["kind"], int(np.prod(st.ins[0].shape)), p["scale"], p["zero_point"], out)
+            elif st.kind == "linear":
+                a_scales = self.scales.get(id(st.ins[0])) if p["a_dynamic"] else None
+                if p["a_dynamic"] and a_scales is None:
+                    raise B200CompileError("dynamic activation scales are missing for a quantized_dot operand")
+                if p["requant_scale"] is not None:
+                    ctx.int8_linear_requant_static(x, a_scales, p["dW"], p["dws"], p["db"], p["act"], p["M"], p["N"], p["K"],
+                                                   p["requant_scale"], out)
+                else:
+                    ctx.int8_linear(x, a_scales, p["dW"], p["dws"], p["db"], p["act"], p["M"], p["N"], p["K"], out)
+        ctx.sync()
+        ctx.check_status()
+        for v, a in zip(self.func.returns, arrays[self.inputs:]):
+            res = self.buf[id(v)].download()
+            np.copyto(a.reshape(res.shape), res)
+
+
+def _as_array(arg) -> np.ndarray:
+    """Both argument forms of the reference (src/runtime/runtime.ts:242-250): a typed array or {data, shape, dtype}."""
+    if isinstance(arg, np.ndarray):
+        return arg
+    if isinstance(arg, dict) and "data" in arg:
+        return np.asarray(arg["data"]).reshape(arg.get("shape", np.asarray(arg["data"]).shape))
+    raise TypeError("arguments must be numpy arrays or {data, shape, dtype} tensors")
+
+
+class B200RuntimeModule:
+    """RuntimeModuleLike over libb200q.so: one native plan per function of the module."""
+
+    def __init__(self, module: Dict[str, GraphFunction], options: Optional[dict] = None):
+        options = options or {}
+        self.ctx = Context(int(options.get("device", 0) or 0))      # raises without a GPU: no fallback
+        dynamic = options.get("activationQuant", "static") == "per_token_dynamic"
+        self.plans = {name: _FunctionPlan(self.ctx, f, dynamic) for name, f in module.items()}
+
+    def run(self, funcName: str, *args):
+        plan = self.plans.get(funcName)
+        if plan is None:
+            raise KeyError(f"b200: no function named {funcName}")
+        if len(args) != plan.inputs + plan.outputs:
+            raise ValueError(f"b200: {funcName} takes {plan.inputs} tensors and returns {plan.outputs}, "
+                             f"but the call passes {len(args)} buffers")
+        plan.execute([_as_array(a) for a in args])
+
+    def runAsync(self, funcName: str, *args):
+        return self.run(funcName, *args)
+
+    def isAsync(self, funcName: str = "") -> bool:
+        return False
+
+    def getKernelSource(self, funcName: str) -> Optional[str]:
+        p = self.plans.get(funcName)
+        return p.describe() if p else None
+
+    def getKernelMetadata(self, funcName: str) -> Optional[dict]:
+        p = self.plans.get(funcName)
+        return {"kind": "b200", "inputs": p.inputs, "outputs": p.outputs, "steps": len(p.steps)} if p else None
+
+    def listKernels(self) -> List[str]:
+        return list(self.plans)
+
+    def release(self):
+        if self.ctx is not None:
+            self.ctx.close()
+            self.ctx = None

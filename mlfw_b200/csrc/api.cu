@@ -179,6 +179,13 @@ int b200q_set_gemm_variant(b200q_ctx* ctx, int variant) {
   return 0;
 }
 
+int b200q_set_quant_variant(b200q_ctx* ctx, int variant) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_REQUIRE(variant == 0 || variant == 1, "b200q_set_quant_variant: unknown variant %d", variant);
+  ctx->quant_variant = variant;
+  return 0;
+}
+
 int b200q_profile_enable(b200q_ctx* ctx, int on) {
   if (use_device(ctx)) return 1;
   if (on && !ctx->prof_ev[0][0]) {

@@ -35,6 +35,7 @@ enum StatusBits : uint32_t {
   STATUS_MMA_WAIT_TIMEOUT = 1u << 1,   // MMA issuer gave up waiting for operands or a free accumulator
   STATUS_EPI_WAIT_TIMEOUT = 1u << 2,   // epilogue gave up waiting for an accumulator
   STATUS_BAD_TMEM_ALLOC = 1u << 3,     // tensor-memory allocation returned an unexpected address
+  STATUS_QUANT_WAIT_TIMEOUT = 1u << 4, // the staged quantize kernel gave up waiting for a row chunk or a free slot
 };
 
 // Kernel families timed separately when profiling is on (b200q_profile_*).
@@ -67,6 +68,8 @@ struct b200q_ctx {
   b200q::Workspace ws_stage_in, ws_stage_out;  // device staging of the host-buffer entry points
   double wait_limit_s = 2.0;             // bound of every device-side wait
   int gemm_variant = 0;                  // 0 auto, 1 CUDA-core kernel only, 2 tensor cores with one CTA per tile, 3 with CTA pairs
+  int quant_variant = 0;                 // 0 auto (rows staged in shared memory when they fit), 1 register-resident kernel only
+  bool quant_staged_ready = false;
   uint32_t umma_ready_mask = 0;          // tensor-core kernel variants whose shared-memory attribute is set on this device
   uint64_t launches = 0;                 // kernels launched through this context
   // per-kernel CUDA-event timing (off by default): a ring of event pairs, folded into the sums when it wraps or is read

@@ -157,6 +157,219 @@ __global__ void __launch_bounds__(MAXT) quantize_per_token_vec_kernel(const floa
   }
 }
 
+// ---------------------------------------------------------------------------
+// Per-token quantize, rows staged in shared memory by bulk copies.
+//
+// One persistent block per SM.  A producer lane streams row chunks (R consecutive rows = one contiguous
+// range of global memory) into a ring of shared-memory slots with cp.async.bulk; the copy engine keeps the
+// whole ring (~190 KB per SM) in flight whatever the warps are doing, which is what saturates HBM.  Each of the
+// 16 consumer warps takes every 16th chunk: it reads a row twice from shared memory (min/max, then encode), so
+// global memory is read exactly once, reductions never leave the warp (shuffles only, no block barrier), and the
+// codes go out as coalesced 128-byte stores.
+// A slot is consumed by different warps on successive turns, and a parity wait must never look at a barrier that is
+// a whole phase behind (it would pass at once).  Each slot therefore carries a turn counter: the warp that takes
+// turn t of a slot first waits until the warp of turn t-1 has released it, and only then waits for the copy.
+// Waits are bounded like those of the GEMM: a wait that runs out sets STATUS_QUANT_WAIT_TIMEOUT and the block leaves.
+// ---------------------------------------------------------------------------
+constexpr int QT_CONSUMER_WARPS = 16;
+constexpr int QT_THREADS = 32 * (QT_CONSUMER_WARPS + 1);
+constexpr int QT_MAX_SLOTS = 24;
+
+__device__ __forceinline__ uint32_t q_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool q_mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool q_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned long long limit_ns) {
+  if (q_mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0, t1;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  uint32_t it = 0;
+  while (!q_mbar_try_wait(bar, parity)) {
+    if ((++it & 31u) == 0u) {
+      if (*abort_flag) return false;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// tie tracking only: in a per-token row |x * (127/absmax)| <= 127 (1 + 2^-23) by construction, so the magnitude
+// needs no watching; a NaN element still trips the guard through `e`.
+__device__ __forceinline__ int quantize_fast_bounded(float x, float inv, int& tie) {
+  const float t = __fmul_rn(x, inv);
+  const float u = __fadd_rn(t, 12582912.0f);
+  const int c = __float_as_int(u) - 0x4B400000;
+  const float d = __fsub_rn(t, __fsub_rn(u, 12582912.0f));
+  const float e = __fmaf_rn(fabsf(t), 4.76837158203125e-7f, fabsf(d));
+  tie = max(tie, __float_as_int(e));
+  return c;
+}
+
+__global__ void __launch_bounds__(QT_THREADS, 1)
+quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4, int rows_per_chunk, int slots,
+                                 int8_t* __restrict__ q, float* __restrict__ scales, float qmin, float qmax, uint32_t* status,
+                                 unsigned long long limit_ns) {
+  extern __shared__ __align__(128) uint8_t qt_smem[];
+  __shared__ uint64_t full[QT_MAX_SLOTS], empty[QT_MAX_SLOTS];
+  __shared__ int turn_done[QT_MAX_SLOTS];   // turns of each slot that have been consumed and released
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  volatile int* turns = turn_done;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row_bytes = (int64_t)K4 * 16;
+  const int64_t chunk_bytes = row_bytes * rows_per_chunk;
+  const int64_t num_chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < slots; s++) {
+      turn_done[s] = 0;
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(q_smem_u32(&full[s])), "r"(1) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(q_smem_u32(&empty[s])), "r"(1) : "memory");
+    }
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == QT_CONSUMER_WARPS) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t i = 0;
+      for (int64_t chunk = blockIdx.x; chunk < num_chunks; chunk += gridDim.x, i++) {
+        const int s = i % slots;
+        const uint32_t ph = (i / slots) & 1u;
+        if (!q_mbar_wait(q_smem_u32(&empty[s]), ph ^ 1u, abort_flag, limit_ns)) {
+          atomicOr(status, STATUS_QUANT_WAIT_TIMEOUT);
+          break;
+        }
+        const int64_t row0 = chunk * rows_per_chunk;
+        const int64_t rows = (M - row0 < rows_per_chunk) ? (M - row0) : rows_per_chunk;
+        const uint32_t bytes = (uint32_t)(rows * row_bytes);
+        const uint32_t bar = q_smem_u32(&full[s]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         q_smem_u32(qt_smem + (int64_t)s * chunk_bytes)),
+                     "l"(reinterpret_cast<const uint8_t*>(x) + row0 * row_bytes), "r"(bytes), "r"(bar)
+                     : "memory");
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ consumers
+    const float limit = guard_limit(qmin, qmax);
+    uint32_t i = 0;
+    for (int64_t chunk = blockIdx.x; chunk < num_chunks; chunk += gridDim.x, i++) {
+      if ((int)(i % QT_CONSUMER_WARPS) != warp) continue;   // uniform per warp
+      const int s = i % slots;
+      const int turn = (int)(i / slots);
+      const uint32_t ph = (uint32_t)turn & 1u;
+      bool ok = true;
+      if (lane == 0) {
+        // wait for the previous turn of this slot to be released (bounded), then for this turn's copy
+        unsigned long long t0, t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        uint32_t spins = 0;
+        while (turns[s] != turn) {
+          if ((++spins & 31u) == 0u) {
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (*abort_flag || t1 - t0 > limit_ns) { *abort_flag = 1; ok = false; break; }
+          }
+        }
+        ok = ok && q_mbar_wait(q_smem_u32(&full[s]), ph, abort_flag, limit_ns);
+        if (!ok) atomicOr(status, STATUS_QUANT_WAIT_TIMEOUT);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      const int64_t row0 = chunk * rows_per_chunk;
+      const int rows = (int)((M - row0 < rows_per_chunk) ? (M - row0) : rows_per_chunk);
+      const float4* slot = reinterpret_cast<const float4*>(qt_smem + (int64_t)s * chunk_bytes);
+      for (int r = 0; r < rows; r++) {
+        const float4* xr = slot + (int64_t)r * K4;
+        // pass 1: range of the row (fminf/fmaxf drop NaN operands, as the strict comparisons of the reference do)
+        float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+        int c = lane;
+#pragma unroll 4
+        for (; c + 96 < K4; c += 128) {
+          const float4 v0 = xr[c], v1 = xr[c + 32], v2 = xr[c + 64], v3 = xr[c + 96];
+          mn = fminf(fminf(fminf(mn, v0.x), fminf(v0.y, v0.z)), fminf(fminf(v0.w, v1.x), fminf(v1.y, v1.z)));
+          mn = fminf(fminf(fminf(mn, v1.w), fminf(v2.x, v2.y)), fminf(fminf(v2.z, v2.w), fminf(v3.x, v3.y)));
+          mn = fminf(mn, fminf(v3.z, v3.w));
+          mx = fmaxf(fmaxf(fmaxf(mx, v0.x), fmaxf(v0.y, v0.z)), fmaxf(fmaxf(v0.w, v1.x), fmaxf(v1.y, v1.z)));
+          mx = fmaxf(fmaxf(fmaxf(mx, v1.w), fmaxf(v2.x, v2.y)), fmaxf(fmaxf(v2.z, v2.w), fmaxf(v3.x, v3.y)));
+          mx = fmaxf(mx, fmaxf(v3.z, v3.w));
+        }
+        for (; c < K4; c += 32) {
+          const float4 v = xr[c];
+          mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));
+          mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        const float absmax = fmaxf(fabsf(mn), fabsf(mx));
+        const float inv = __fdiv_rn(127.0f, absmax);
+        const bool exact_only = !((mn < mx) && absmax <= 3.402823466e38f && is_normal_f32(inv));
+        // pass 2: encode, four vectors (16 elements) per lane at a time
+        uint32_t* qr = reinterpret_cast<uint32_t*>(q) + (row0 + r) * K4;
+        for (int c0 = lane; c0 < K4; c0 += 128) {
+          float4 v[4];
+          uint32_t w[4];
+          int tie = 0;
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int cc = c0 + 32 * j;
+            v[j] = (cc < K4) ? xr[cc] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; j++)
+            w[j] = pack_codes(quantize_fast_bounded(v[j].x, inv, tie), quantize_fast_bounded(v[j].y, inv, tie),
+                              quantize_fast_bounded(v[j].z, inv, tie), quantize_fast_bounded(v[j].w, inv, tie));
+          if (exact_only || tie >= 0x3f000000 || limit < 127.0f) {  // rare: a tie, NaN, an odd row, a narrow clamp
+            const double sd = row_scale(mn, mx);
+#pragma unroll
+            for (int j = 0; j < 4; j++) w[j] = pack4_exact_p(v[j], sd, qmin, qmax);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int cc = c0 + 32 * j;
+            if (cc < K4) __stcs(qr + cc, w[j]);
+          }
+        }
+        if (lane == 0) scales[row0 + r] = exact_only ? (float)row_scale(mn, mx) : __fdiv_rn(absmax, 127.0f);
+      }
+      // every lane has finished reading the slot: hand it back to the producer
+      __syncwarp();
+      if (lane == 0) {
+        turns[s] = turn + 1;
+        __threadfence_block();
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(q_smem_u32(&empty[s])) : "memory");
+      }
+    }
+  }
+  if (*abort_flag) {  // give copies in flight time to land before the shared memory is released (bounded: 2 ms)
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    do {
+      __nanosleep(1000);
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    } while (t1 - t0 < 2000000ull);
+  }
+  __syncthreads();
+}
+
 // Any K, any alignment: one block per row, the row is read twice (the second
 // read is served by L2 for rows up to tens of megabytes).
 __global__ void __launch_bounds__(256) quantize_per_token_generic_kernel(const float* __restrict__ x, int64_t M, int64_t K,
@@ -398,7 +611,27 @@ int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t
     return 0;
   }
   const bool vec = (K % 4 == 0) && aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 3u) == 0) && (K / 4 <= 8 * 1024);
-  if (vec) {
+  // Rows of up to 16 KB are staged through shared memory by bulk copies; longer rows stay in registers.
+  const bool staged = vec && ctx->quant_variant != 1 && K * 4 <= 16384 && M >= 64;
+  if (staged) {
+    const int K4 = (int)(K / 4);
+    const int64_t row_bytes = K * 4;
+    int rows_per_chunk = (int)(8192 / row_bytes);
+    if (rows_per_chunk < 1) rows_per_chunk = 1;
+    const int64_t chunk_bytes = row_bytes * rows_per_chunk;
+    int slots = (int)((196 * 1024) / chunk_bytes);
+    if (slots > QT_MAX_SLOTS) slots = QT_MAX_SLOTS;
+    const size_t smem = (size_t)slots * chunk_bytes;
+    if (!ctx->quant_staged_ready) {
+      B200Q_CHECK_CUDA(cudaFuncSetAttribute(quantize_per_token_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      ctx->quant_staged_ready = true;
+    }
+    const int64_t num_chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
+    const unsigned blocks = (unsigned)(num_chunks < ctx->sm_count ? num_chunks : ctx->sm_count);
+    quantize_per_token_staged_kernel<<<blocks, QT_THREADS, smem, ctx->stream>>>(
+        x, M, K4, rows_per_chunk, slots, q, scales, (float)qmin, (float)qmax, ctx->status_dev,
+        (unsigned long long)(ctx->wait_limit_s * 1e9));
+  } else if (vec) {
     const int K4 = (int)(K / 4);
     int G = 32;
     while (G < 1024 && (K4 + G - 1) / G > 4) G <<= 1;

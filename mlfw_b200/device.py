@@ -18,7 +18,7 @@ W_NK, W_KN = 0, 1
 KIND = {np.dtype(np.int8): 0, np.dtype(np.uint8): 1, np.dtype(np.int32): 2}
 
 STATUS_BITS = {1: "TMA producer wait ran out", 2: "MMA issuer wait ran out", 4: "epilogue wait ran out",
-               8: "unexpected tensor-memory allocation"}
+               8: "unexpected tensor-memory allocation", 16: "staged quantize wait ran out"}
 
 
 class DeviceBuffer:
@@ -148,6 +148,9 @@ class Context:
 
     def set_gemm_variant(self, variant: int):
         check(self.lib.b200q_set_gemm_variant(self.handle, variant), "b200q_set_gemm_variant")
+
+    def set_quant_variant(self, variant: int):
+        check(self.lib.b200q_set_quant_variant(self.handle, variant), "b200q_set_quant_variant")
 
     def launch_count(self) -> int:
         return int(self.lib.b200q_launch_count(self.handle))

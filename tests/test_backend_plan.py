@@ -1,0 +1,107 @@
+"""CPU tests of the host-side mirror: the planner recognises the graph contract and rejects everything else."""
+import numpy as np
+import pytest
+
+from graph_util import activation, quantized_linear
+from mlfw_b200.backend import (B200CompileError, B200Target, GraphBuilder, TARGET_ATTR_EXTERNAL_COMPILER,
+                               TARGET_ATTR_FUSION, compile_with_b200, plan_function)
+
+
+def mlp_graph(orc, act="relu", w_is_kn=True, M=8, K=32, H=64, N=16):
+    rng = np.random.default_rng(0)
+    w1 = rng.standard_normal((K, H) if w_is_kn else (H, K)).astype(np.float32) * 0.1
+    w2 = rng.standard_normal((H, N) if w_is_kn else (N, H)).astype(np.float32) * 0.1
+    b1 = rng.uniform(-0.1, 0.1, H).astype(np.float32)
+    b2 = rng.uniform(-0.1, 0.1, N).astype(np.float32)
+    b = GraphBuilder("mlp")
+    x = b.arg((M, K))
+    h, f1 = quantized_linear(b, orc, x, w1, b1, 6 / 127, act, w_is_kn)
+    y, f2 = quantized_linear(b, orc, h, w2, b2, 4 / 127, "none", w_is_kn)
+    return b.ret(y), (f1, f2, b1, b2)
+
+
+def test_target_object():
+    t = B200Target()
+    assert t["kind"] == "accelerator" and t["supportsInt8"] and t["attrs"][TARGET_ATTR_FUSION] == {"enabled": False}
+    assert t["attrs"][TARGET_ATTR_EXTERNAL_COMPILER] is compile_with_b200
+    with pytest.raises(ValueError):
+        B200Target(activationQuant="bogus")
+
+
+@pytest.mark.parametrize("act", ["none", "relu", "silu", "gelu_sigmoid"])
+@pytest.mark.parametrize("w_is_kn", [True, False])
+def test_static_plan_fuses_tail_and_next_quantize(orc, act, w_is_kn):
+    func, (f1, f2, b1, b2) = mlp_graph(orc, act, w_is_kn)
+    steps = plan_function(func, dynamic=False)
+    assert [s.kind for s in steps] == ["quantize_static", "linear", "linear"]
+    l1, l2 = steps[1].params, steps[2].params
+    assert (l1["M"], l1["K"], l1["N"], l1["act"]) == (8, 32, 64, act)
+    assert l1["requant_scale"] == 4 / 127 and l2["requant_scale"] is None      # layer 2's quantize rides in layer 1's epilogue
+    assert (l1["w_scales"] == f1["scale_vec"].astype(np.float32)).all()         # the graph's f32 scale-vector constant
+    assert (l1["bias"] == b1).all() and (l2["bias"] == b2).all()
+    assert (l1["w"] == f1["wq"]).all() and l1["w_layout"] == (1 if w_is_kn else 0)
+    assert steps[2].out is func.returns[0]
+
+
+def test_dynamic_plan_recovers_weight_scales(orc):
+    func, (f1, f2, _, _) = mlp_graph(orc, "relu")
+    steps = plan_function(func, dynamic=True)
+    assert [s.kind for s in steps] == ["quantize_token", "linear", "quantize_token", "linear"]
+    assert steps[1].params["a_dynamic"] and steps[1].params["requant_scale"] is None
+    np.testing.assert_array_equal(steps[1].params["w_scales"], (f1["scale_vec"] / (6 / 127)).astype(np.float32))
+    assert np.abs(steps[1].params["w_scales"] / f1["wsc"] - 1).max() < 1e-6
+
+
+def test_standalone_quantize_dequantize(orc):
+    b = GraphBuilder("rt")
+    x = b.arg((6,))
+    q = b.op("quantize", [x], (6,), "i8", scale=6 / 127, zero_point=0, target_dtype="i8")
+    y = b.op("dequantize", [q], (6,), "f32", scale=6 / 127, zero_point=0)
+    steps = plan_function(b.ret(y), dynamic=False)
+    assert [s.kind for s in steps] == ["quantize_static", "dequantize_static"]
+
+
+def test_per_tensor_path(orc):
+    """quantize, quantize(const) folded, quantized_dot, dequantize(scale = lhs*rhs) (quantization_pass.ts:286-360)."""
+    b = GraphBuilder("pt")
+    x = b.arg((4, 8))
+    wq = np.arange(-24, 24, dtype=np.int8).reshape(8, 6)
+    xq = b.op("quantize", [x], (4, 8), "i8", scale=0.05, zero_point=0, target_dtype="i8")
+    wc = b.constant(wq.reshape(-1).tolist(), (8, 6), "i8")
+    qd = b.op("quantized_dot", [xq, wc], (4, 6), "i32", lhs_contracting=[1], rhs_contracting=[0], lhs_scale=0.05, rhs_scale=0.02,
+              output_scale=0.001)
+    y = b.op("dequantize", [qd], (4, 6), "f32", scale=0.05 * 0.02, zero_point=0)
+    steps = plan_function(b.ret(y), dynamic=False)
+    assert [s.kind for s in steps] == ["quantize_static", "linear"]
+    assert (steps[1].params["w_scales"] == np.float32(0.05 * 0.02)).all()
+
+
+def test_ops_outside_the_contract_are_refused(orc):
+    b = GraphBuilder("bad")
+    x = b.arg((4, 8))
+    y = b.op("softmax", [x], (4, 8), "f32")
+    with pytest.raises(B200CompileError, match="outside the graph contract"):
+        plan_function(b.ret(y), dynamic=False)
+    b = GraphBuilder("bad2")
+    x = b.arg((4, 8))
+    xq = b.op("quantize", [x], (4, 8), "i8", scale=0.05, zero_point=0)
+    w = b.arg((8, 6), "i8")                                  # non-constant weights
+    qd = b.op("quantized_dot", [xq, w], (4, 6), "i32", lhs_contracting=[1], rhs_contracting=[0])
+    with pytest.raises(B200CompileError, match="constant rank-2 int8"):
+        plan_function(b.ret(qd), dynamic=False)
+    b = GraphBuilder("bad3")                                 # fake-quant boundary around an elementwise op (D10)
+    x = b.arg((4,))
+    q = b.op("quantize", [x], (4,), "i8", scale=0.05, zero_point=0)
+    d = b.op("dequantize", [q], (4,), "f32", scale=0.05, zero_point=0)
+    a = b.op("add", [d, d], (4,), "f32")
+    with pytest.raises(B200CompileError, match="'add'"):
+        plan_function(b.ret(a), dynamic=False)
+
+
+def test_rank3_lhs_flattens_to_rows(orc):
+    rng = np.random.default_rng(1)
+    b = GraphBuilder("r3")
+    x = b.arg((2, 5, 16))
+    y, _ = quantized_linear(b, orc, x, rng.standard_normal((24, 16)).astype(np.float32), None, 0.03, "none", w_is_kn=False)
+    steps = plan_function(b.ret(y), dynamic=True)
+    assert steps[0].params["M"] == 10 and steps[1].params["M"] == 10 and steps[1].params["N"] == 24

@@ -1,0 +1,115 @@
+"""The reference-facing interface end to end on the GPU: graphs as the quantization pass emits them, compiled with
+compile_with_b200, run with typed arrays, checked against the CPU oracle's evaluation of the same graph.
+
+test_c1_mlp is BASELINE config 1: X f32 [256,512] ~ N(0,1), W1 [512,1024], W2 [1024,256] ~ N(0,0.02), biases
+~ U(-0.1,0.1), per-output-channel int8 weights, ReLU between the layers, f32 [256,256] out, seed 0."""
+import numpy as np
+import pytest
+
+from graph_util import quantized_linear
+from mlfw_b200 import synth
+from mlfw_b200.backend import B200Target, GraphBuilder, compile_with_b200
+
+pytestmark = pytest.mark.gpu
+
+
+def c1_tensors():
+    s = synth.tensor_seed
+    x = synth.normal(s(0, 0), (256, 512))
+    w1 = synth.normal(s(0, 1), (512, 1024), 0.0, 0.02)
+    b1 = synth.uniform(s(0, 2), (1024,), -0.1, 0.1)
+    w2 = synth.normal(s(0, 3), (1024, 256), 0.0, 0.02)
+    b2 = synth.uniform(s(0, 4), (256,), -0.1, 0.1)
+    return x, w1, b1, w2, b2
+
+
+def build_mlp(orc, x_shape, w1, b1, w2, b2, a1, a2, act="relu"):
+    b = GraphBuilder("mlp")
+    x = b.arg(x_shape)
+    h, f1 = quantized_linear(b, orc, x, w1, b1, a1, act, True)
+    y, f2 = quantized_linear(b, orc, h, w2, b2, a2, "none", True)
+    return b.ret(y), f1, f2
+
+
+def test_c1_mlp_static_scales_match_the_reference_chain(orc):
+    x, w1, b1, w2, b2 = c1_tensors()
+    a1 = orc.from_range(float(x.min()), float(x.max()))[0]          # min/max calibration (calibration.ts:246-268)
+    hf = np.maximum(x.astype(np.float64) @ w1 + b1, 0)
+    a2 = orc.from_range(float(hf.min()), float(hf.max()))[0]
+    func, f1, f2 = build_mlp(orc, x.shape, w1, b1, w2, b2, a1, a2)
+    mod = compile_with_b200({"mlp": func}, {"target": B200Target()})
+    out = np.zeros((256, 256), np.float32)
+    mod.run("mlp", x, out)
+    # the same graph as the reference's CPU target evaluates it
+    q1 = orc.quantize_static(x, a1)
+    h = orc.epilogue_sv(orc.qdot_i32(q1, f1["wq"], "KN"), f1["scale_vec"].astype(np.float32), b1, "relu")
+    q2 = orc.quantize_static(h, a2)
+    ref = orc.epilogue_sv(orc.qdot_i32(q2, f2["wq"], "KN"), f2["scale_vec"].astype(np.float32), b2, "none")
+    assert (out.view(np.uint32) == ref.view(np.uint32)).all()
+    # and it is a faithful int8 approximation of the float model (the reference asserts < 3 % for two layers + ReLU)
+    yf = hf @ w2 + b2
+    assert np.abs(out - yf).sum() / np.abs(yf).sum() < 0.03
+    assert mod.listKernels() == ["mlp"] and not mod.isAsync("mlp")
+    assert mod.getKernelMetadata("mlp")["steps"] == 3 and "linear" in mod.getKernelSource("mlp")
+    # {data, shape, dtype} tensors are accepted as well (tracing/compile.ts:84-95)
+    out2 = np.zeros((256, 256), np.float32)
+    mod.run("mlp", {"data": x.reshape(-1), "shape": [256, 512], "dtype": "f32"}, {"data": out2, "shape": [256, 256], "dtype": "f32"})
+    assert (out2 == out).all()
+    with pytest.raises(ValueError, match="takes 1 tensors"):
+        mod.run("mlp", x)
+    mod.release()
+
+
+def test_c1_mlp_per_token_dynamic(orc):
+    x, w1, b1, w2, b2 = c1_tensors()
+    func, f1, f2 = build_mlp(orc, x.shape, w1, b1, w2, b2, 6 / 127, 6 / 127)
+    mod = compile_with_b200({"mlp": func}, {"target": B200Target(activationQuant="per_token_dynamic")})
+    out = np.zeros((256, 256), np.float32)
+    mod.run("mlp", x, out)
+    ws1 = (f1["scale_vec"] / (6 / 127)).astype(np.float32)
+    ws2 = (f2["scale_vec"] / (6 / 127)).astype(np.float32)
+    h, q1, s1, acc1 = orc.linear(x, np.ascontiguousarray(f1["wq"].T), ws1, b1, "relu")
+    ref, q2, s2, acc2 = orc.linear(h, np.ascontiguousarray(f2["wq"].T), ws2, b2, "none")
+    assert (out.view(np.uint32) == ref.view(np.uint32)).all()
+    yf = np.maximum(x.astype(np.float64) @ w1 + b1, 0) @ w2 + b2
+    assert np.abs(out - yf).sum() / np.abs(yf).sum() < 0.02
+    mod.release()
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_sigmoid"])
+def test_rank3_linear_with_sigmoid_tails(orc, act):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((4, 33, 64)).astype(np.float32)
+    w = (rng.standard_normal((96, 64)) * 0.1).astype(np.float32)        # [N,K], a traced Linear
+    bias = rng.uniform(-0.1, 0.1, 96).astype(np.float32)
+    b = GraphBuilder("lin")
+    xv = b.arg(x.shape)
+    y, f = quantized_linear(b, orc, xv, w, bias, 0.03, act, w_is_kn=False)
+    mod = compile_with_b200({"lin": b.ret(y)}, {"target": B200Target(activationQuant="per_token_dynamic")})
+    out = np.zeros((4, 33, 96), np.float32)
+    mod.run("lin", x, out)
+    ws = (f["scale_vec"] / 0.03).astype(np.float32)
+    ref, _, _, _ = orc.linear(x.reshape(-1, 64), f["wq"], ws, bias, act)
+    assert (out.reshape(-1, 96).view(np.uint32) == ref.view(np.uint32)).all()
+    mod.release()
+
+
+def test_fake_quant_roundtrip_is_lossy(orc):
+    """tests/compiler/passes/quantization/pass.test.js:461-491 on this backend."""
+    s, z = orc.from_range(-6, 6)
+    data = np.array([3.5, -2.1, 5.9, 1.234, -5.9, 0.001], np.float32)
+    b = GraphBuilder("rt")
+    x = b.arg((6,))
+    q = b.op("quantize", [x], (6,), "i8", scale=s, zero_point=int(z), target_dtype="i8")
+    y = b.op("dequantize", [q], (6,), "f32", scale=s, zero_point=int(z))
+    mod = compile_with_b200({"rt": b.ret(y)}, {"target": B200Target()})
+    out = np.zeros(6, np.float32)
+    mod.run("rt", data, out)
+    cmin, cmax = orc.clamp_range()
+    applied = False
+    for i, v in enumerate([3.5, -2.1, 5.9, 1.234, -5.9, 0.001]):
+        ref = orc.qp_dequantize(orc.qp_quantize(v, s, z, cmin, cmax), s, z)
+        assert abs(out[i] - ref) < 1e-4 and abs(out[i] - v) <= s + 1e-6
+        applied |= abs(out[i] - v) > 1e-6
+    assert applied
+    mod.release()

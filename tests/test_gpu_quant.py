@@ -33,14 +33,24 @@ def run_quantize_per_token(ctx, x, qmin=-127, qmax=127):
 
 
 SHAPES = [(1, 1), (3, 5), (2, 6), (7, 64), (33, 128), (256, 512), (5, 768), (9, 3072), (4, 4096), (17, 4100),
-          (3, 8192), (2, 28672), (2, 32772), (1, 40000), (300, 4)]
+          (3, 8192), (2, 28672), (2, 32772), (1, 40000), (300, 4),
+          # 64 rows or more: the shared-memory staged kernel (variant 0) unless a row exceeds 32 KB
+          (100, 768), (65, 3072), (64, 8192), (70, 4096), (333, 512), (64, 4100), (1000, 16), (129, 2052),
+          # many chunks per block: every ring of slots wraps several times
+          (6000, 4096), (40000, 512), (20011, 768)]
 
 
+# variant 0: rows staged in shared memory when they fit; 1: register-resident kernel only
+@pytest.mark.parametrize("variant", [0, 1])
 @pytest.mark.parametrize("M,K", SHAPES)
-def test_quantize_per_token_bit_exact(ctx, orc, M, K):
+def test_quantize_per_token_bit_exact(ctx, orc, M, K, variant):
     rng = np.random.default_rng(M * 100003 + K)
     x = activations(rng, M, K)
-    q, s = run_quantize_per_token(ctx, x)
+    ctx.set_quant_variant(variant)
+    try:
+        q, s = run_quantize_per_token(ctx, x)
+    finally:
+        ctx.set_quant_variant(0)
     rq, _, rs32 = orc.quantize_per_token(x)
     assert (s.view(np.uint32) == rs32.view(np.uint32)).all()
     assert (q == rq).all(), f"{int((q != rq).sum())} codes differ"
@@ -60,7 +70,8 @@ def test_quantize_per_token_special_rows(ctx, orc):
     r = np.zeros(K, np.float32); r[3] = -0.0; r[4] = 1e-45; rows.append(r)
     r = np.full(K, -7.25, np.float32); rows.append(r)                      # all equal, negative
     x = np.stack(rows)
-    for qmin, qmax in [(-127, 127), (-128, 127)]:
+    x = np.concatenate([x] * 7)          # 70 rows: the staged kernel takes them too
+    for qmin, qmax in [(-127, 127), (-128, 127), (-100, 100)]:
         q, s = run_quantize_per_token(ctx, x, qmin, qmax)
         rq, _, rs32 = orc.quantize_per_token(x, qmin, qmax)
         assert (s.view(np.uint32) == rs32.view(np.uint32)).all()
@@ -80,6 +91,7 @@ def test_quantize_per_token_constructed_ties(ctx, orc):
         row = np.concatenate([[np.float32(absmax)], base, up, dn]).astype(np.float32)
         rows.append(row)
     x = np.stack(rows)
+    x = np.concatenate([x] * 7)          # 70 rows: the staged kernel
     x = np.clip(x, -np.abs(x[:, :1]), np.abs(x[:, :1]))  # keep the first entry the absmax
     q, s = run_quantize_per_token(ctx, x)
     rq, _, rs32 = orc.quantize_per_token(x)
