@@ -70,7 +70,7 @@ class ClockSampler:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=f, stderr=subprocess.DEVNULL)
+                                          "-lms", "20"], stdout=f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -146,7 +146,7 @@ def run_roundtrip(ctx, pk, iters, warmup):
 def run_reference_arm(args, rank, world):
     """The reference's CPU path (its C++ restatement: no JavaScript engine exists here) on all host cores."""
     if rank != 0:
-        return
+        return None
     import oracle
     oracle.build()
     M, K, N, act, xs, W, ws, bias = make_case(args.workload, 0)
@@ -172,14 +172,36 @@ def run_reference_arm(args, rank, world):
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    return line
+
+
+class _QuietStdout:
+    """Libraries (NCCL prints its version) must not add lines to stdout: fd 1 points at stderr until the JSON line."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
 
 
 def main():
+    with _QuietStdout():
+        line = _run()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def _run():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
@@ -216,9 +238,9 @@ def main():
 
     ctx = mlfw_b200.Context(local_rank)
     if args.roundtrip_only:
-        print(json.dumps({"metric": "quantize_dequantize_GBps", "roundtrip_c2": run_roundtrip(ctx, peaks(), args.steps, args.warmup)}))
+        line = {"metric": "quantize_dequantize_GBps", "roundtrip_c2": run_roundtrip(ctx, peaks(), args.steps, args.warmup)}
         ctx.close()
-        return
+        return line
     M, K, N, act, xs, W, ws, bias = make_case(args.workload, rank)
     dxs = [ctx.to_device(x) for x in xs]
     douts = [ctx.empty((M, N), np.float32) for _ in xs]
@@ -271,7 +293,7 @@ def main():
     }
     if quant_n:
         q_avg = quant_ms / quant_n
-        roofline_quant = {"kernel": "quantize_per_token_vec_kernel", "bound": "hbm", "achieved": 5.0 * M * K / (q_avg * 1e-3) / 1e9,
+        roofline_quant = {"kernel": "quantize_per_token_staged_kernel", "bound": "hbm", "achieved": 5.0 * M * K / (q_avg * 1e-3) / 1e9,
                           "peak": pk["hbm_gbs"], "unit": "GB/s", "avg_launch_ms": q_avg, "launches": quant_n}
         roofline_quant["frac"] = roofline_quant["achieved"] / pk["hbm_gbs"]
     else:
@@ -327,11 +349,10 @@ def main():
                                     "sample": f"first {rows} of {M} rows, all of N and K, {reps} repetitions; C++ restatement of the "
                                               "reference's CPU path with OpenMP", "gpu_vs_cpu_max_err_over_absmax": err}
 
-    if rank == 0:
-        print(json.dumps(line))
     ctx.close()
     if dist is not None:
         dist.destroy_process_group()
+    return line if rank == 0 else None
 
 
 if __name__ == "__main__":
