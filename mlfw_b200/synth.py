@@ -14,10 +14,11 @@ def tensor_seed(seed: int, index: int) -> int:
     return (seed * 1000003 + index) & 0xFFFFFFFF
 
 
-def mulberry32(seed: int, n: int) -> np.ndarray:
-    """The first ``n`` outputs of makeRng(seed) as float64 in [0, 1)."""
+def mulberry32(seed: int, n: int, start: int = 0) -> np.ndarray:
+    """Outputs ``start .. start+n-1`` of makeRng(seed) as float64 in [0, 1) (the state is a counter, so any
+    window of the stream can be produced directly)."""
     m = np.uint64(0xFFFFFFFF)
-    a = (np.uint64(seed & 0xFFFFFFFF) + np.uint64(0x6D2B79F5) * np.arange(1, n + 1, dtype=np.uint64)) & m
+    a = (np.uint64(seed & 0xFFFFFFFF) + np.uint64(0x6D2B79F5) * np.arange(start + 1, start + n + 1, dtype=np.uint64)) & m
     t = ((a ^ (a >> np.uint64(15))) * (np.uint64(1) | a)) & m
     t = ((t + (((t ^ (t >> np.uint64(7))) * (np.uint64(61) | t)) & m)) & m) ^ t
     return ((t ^ (t >> np.uint64(14))) & m).astype(np.float64) / 4294967296.0
@@ -42,9 +43,13 @@ def uniform(seed: int, shape, a: float = 0.0, b: float = 1.0) -> np.ndarray:
     return (a + mulberry32(seed, n) * (b - a)).astype(np.float32).reshape(shape)
 
 
-def randint_i8(seed: int, shape, lo: int = -127, hi: int = 127) -> np.ndarray:
+def randint_i8(seed: int, shape, lo: int = -127, hi: int = 127, chunk: int = 1 << 24) -> np.ndarray:
     n = int(np.prod(shape))
-    return (np.floor(mulberry32(seed, n) * (hi - lo + 1)).astype(np.int64) + lo).astype(np.int8).reshape(shape)
+    out = np.empty(n, np.int8)
+    for s0 in range(0, n, chunk):          # in pieces: the 64-bit temporaries of a 235 M-element weight would not fit comfortably
+        k = min(chunk, n - s0)
+        out[s0:s0 + k] = (np.floor(mulberry32(seed, k, s0) * (hi - lo + 1)).astype(np.int64) + lo).astype(np.int8)
+    return out.reshape(shape)
 
 
 def with_outliers(x: np.ndarray, seed_mask: int, seed_values: int, p: float = 0.001, std: float = 20.0) -> np.ndarray:

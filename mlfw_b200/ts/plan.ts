@@ -1,0 +1,186 @@
+// planGraph: matches the post-pass graph against the backend's graph contract and turns every function
+// into a list of native steps.  A transliteration of plan_function / _FunctionPlan in mlfw_b200/backend.py,
+// which is the tested form of the same rules (no JavaScript engine exists in the build image).
+//
+// Contract (what QuantizationPass emits with fusion disabled on the target,
+// src/compiler/passes/quantization/quantization_pass.ts:286-459):
+//   quantize · quantized_dot(constant i8 rhs) · convert · mul(broadcast_in_dim(constant f32[N]))
+//   [· add(broadcast(bias))] [· maximum(·,0) | x·sigmoid(1.702x) | x·sigmoid(x)] [· quantize]   -> one 'linear' step
+//   quantized_dot · dequantize{scale}                                                               -> 'linear' with a constant scale vector
+//   standalone quantize / dequantize                                                                 -> static steps
+// Anything else throws: the backend has no fallback.
+import { check } from './binding.js';
+
+import type { B200QBinding } from './binding.js';
+import type { GraphModule } from '../../compiler/ir/graph/module.js';
+import type { GraphFunction } from '../../compiler/ir/graph/function.js';
+import type { Operation } from '../../compiler/ir/graph/operation.js';
+import type { Value } from '../../compiler/ir/graph/value.js';
+import type { B200Options } from './target.js';
+
+const ACT = { none: 0, relu: 1, gelu_sigmoid: 2, gelu_tanh: 3, silu: 4 } as const;
+type Act = keyof typeof ACT;
+type Step =
+  | { kind: 'quantize_static'; in: Value; out: Value; scale: number; zeroPoint: number; dst: number }
+  | { kind: 'quantize_token'; in: Value; out: Value; M: number; K: number }
+  | { kind: 'dequantize_static'; in: Value; out: Value; scale: number; zeroPoint: number; src: number }
+  | { kind: 'linear'; in: Value; out: Value; M: number; N: number; K: number; act: Act; dynamic: boolean;
+      w: Int8Array; wIsKN: boolean; wScales: Float32Array; bias: Float32Array | null; requantScale: number | null;
+      dW?: unknown; dWs?: unknown; dBias?: unknown };
+
+const shapeOf = (v: Value): number[] => (v.type as { shape: number[] }).shape;
+const dtypeOf = (v: Value): string => (v.type as { dtype: string }).dtype;
+const numel = (s: readonly number[]) => s.reduce((a, b) => a * b, 1);
+
+function users(f: GraphFunction, v: Value, done: Set<Operation>): Operation[] {
+  const out: Operation[] = [];
+  for (const op of f.ops()) if (!done.has(op)) for (let i = 0; i < op.numOperands; i++) if (op.getOperand(i) === v) { out.push(op); break; }
+  return out;
+}
+function broadcastSource(v: Value): Value | null {
+  const d = v.definingOp;
+  if (!d) return null;
+  if (d.opName === 'broadcast_in_dim' || d.opName === 'broadcast') return d.getOperand(0);
+  return d.opName === 'constant' ? v : null;
+}
+function constArray(v: Value | null): number[] | null {
+  const d = v?.definingOp;
+  if (!d || d.opName !== 'constant') return null;
+  const val = d.getAttr<number | number[]>('value');
+  return typeof val === 'number' ? [val] : [...(val as number[])];
+}
+const scalarConst = (v: Value): number | null => { const a = constArray(broadcastSource(v)); return a && a.length === 1 ? a[0] : null; };
+const other = (op: Operation, v: Value): Value => (op.getOperand(0) === v ? op.getOperand(1) : op.getOperand(0));
+
+function matchSigmoid(f: GraphFunction, z: Value, done: Set<Operation>): { res: Value; ops: Operation[] } | null {
+  const neg = users(f, z, done).find((u) => u.opName === 'neg'); if (!neg) return null;
+  const exp = users(f, neg.getResult(0), done); if (exp.length !== 1 || exp[0].opName !== 'exp') return null;
+  const add = users(f, exp[0].getResult(0), done); if (add.length !== 1 || add[0].opName !== 'add' || scalarConst(other(add[0], exp[0].getResult(0))) !== 1) return null;
+  const div = users(f, add[0].getResult(0), done);
+  if (div.length !== 1 || div[0].opName !== 'div' || div[0].getOperand(1) !== add[0].getResult(0) || scalarConst(div[0].getOperand(0)) !== 1) return null;
+  return { res: div[0].getResult(0), ops: [neg, exp[0], add[0], div[0]] };
+}
+
+function matchActivation(f: GraphFunction, y: Value, done: Set<Operation>): { act: Act; res: Value; ops: Operation[] } {
+  const us = users(f, y, done);
+  if (us.length === 1 && us[0].opName === 'maximum' && scalarConst(other(us[0], y)) === 0) return { act: 'relu', res: us[0].getResult(0), ops: [us[0]] };
+  const silu = matchSigmoid(f, y, done);
+  if (silu) {
+    const mul = users(f, silu.res, done).find((u) => u.opName === 'mul' && (u.getOperand(0) === y || u.getOperand(1) === y));
+    if (mul) return { act: 'silu', res: mul.getResult(0), ops: [...silu.ops, mul] };
+  }
+  for (const u of us) {
+    if (u.opName !== 'mul') continue;
+    const c = scalarConst(other(u, y));
+    if (c === null || Math.abs(c - 1.702) > 1e-12) continue;
+    const sig = matchSigmoid(f, u.getResult(0), done);
+    const mul = sig && users(f, sig.res, done).find((m) => m.opName === 'mul' && (m.getOperand(0) === y || m.getOperand(1) === y));
+    if (sig && mul) return { act: 'gelu_sigmoid', res: mul.getResult(0), ops: [u, ...sig.ops, mul] };
+  }
+  return { act: 'none', res: y, ops: [] };
+}
+
+function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
+  const steps: Step[] = [];
+  const done = new Set<Operation>();
+  const returns = new Set<Value>(f.returnValues());
+  for (const op of f.ops()) {
+    if (done.has(op)) continue;
+    const n = op.opName;
+    if (n === 'constant' || n === 'broadcast_in_dim' || n === 'broadcast' || n === 'return') continue;
+    if (n === 'quantize') {
+      const x = op.getOperand(0), us = users(f, op.getResult(0), done);
+      const feedsDot = us.length > 0 && us.every((u) => u.opName === 'quantized_dot' && u.getOperand(0) === op.getResult(0));
+      const s = shapeOf(x);
+      if (dynamic && feedsDot && s.length >= 2) steps.push({ kind: 'quantize_token', in: x, out: op.getResult(0), M: numel(s.slice(0, -1)), K: s[s.length - 1] });
+      else steps.push({ kind: 'quantize_static', in: x, out: op.getResult(0), scale: op.getAttr<number>('scale')!, zeroPoint: op.getAttr<number>('zero_point') || 0,
+                        dst: op.getAttr<string>('target_dtype') === 'ui8' ? 1 : 0 });
+    } else if (n === 'dequantize') {
+      steps.push({ kind: 'dequantize_static', in: op.getOperand(0), out: op.getResult(0), scale: op.getAttr<number>('scale')!, zeroPoint: op.getAttr<number>('zero_point') || 0,
+                   src: { i8: 0, ui8: 1, i32: 2 }[dtypeOf(op.getOperand(0)) as 'i8' | 'ui8' | 'i32'] });
+    } else if (n === 'quantized_dot') {
+      const lhs = op.getOperand(0), rhs = op.getOperand(1);
+      const w = constArray(rhs), rs = shapeOf(rhs), ls = shapeOf(lhs);
+      if (!w || dtypeOf(rhs) !== 'i8' || rs.length !== 2) throw new Error('b200: quantized_dot needs a constant rank-2 int8 rhs');
+      if (op.getAttr<number>('lhs_zero_point') || op.getAttr<number>('rhs_zero_point')) throw new Error('b200: zero-points are outside the symmetric path');
+      const rc = op.getAttr<number[]>('rhs_contracting') || [0];
+      const K = rs[rc[0]], N = rs[1 - rc[0]], M = numel(ls.slice(0, -1));
+      const lhsScale = op.getAttr<number>('lhs_scale') || 1;
+      let y = op.getResult(0), sv: number[];
+      done.add(op);
+      const next = users(f, y, done);
+      if (next.length === 1 && next[0].opName === 'convert') {
+        const mul = users(f, next[0].getResult(0), done);
+        const arr = mul.length === 1 && mul[0].opName === 'mul' ? constArray(broadcastSource(other(mul[0], next[0].getResult(0)))) : null;
+        if (!arr || arr.length !== N) throw new Error('b200: quantized_dot -> convert must be followed by mul with a per-channel scale vector');
+        sv = arr; done.add(next[0]); done.add(mul[0]); y = mul[0].getResult(0);
+      } else if (next.length === 1 && next[0].opName === 'dequantize' && !next[0].getAttr<number>('zero_point')) {
+        sv = new Array(N).fill(next[0].getAttr<number>('scale')); done.add(next[0]); y = next[0].getResult(0);
+      } else throw new Error('b200: quantized_dot must be followed by its dequantizing tail');
+      let bias: Float32Array | null = null;
+      const add = users(f, y, done);
+      if (add.length === 1 && add[0].opName === 'add') {
+        const arr = constArray(broadcastSource(other(add[0], y)));
+        if (arr && arr.length === N) { bias = Float32Array.from(arr); done.add(add[0]); y = add[0].getResult(0); }
+      }
+      const a = matchActivation(f, y, done);
+      a.ops.forEach((o) => done.add(o)); y = a.res;
+      // dynamic per-token: recover wScale[n] = scaleVec[n] / lhs_scale (both binary64 here), rounded to f32 once
+      const wScales = Float32Array.from(dynamic ? sv.map((s) => s / lhsScale) : sv);
+      let requantScale: number | null = null;
+      const nq = users(f, y, done);
+      if (!dynamic && nq.length === 1 && nq[0].opName === 'quantize' && !nq[0].getAttr<number>('zero_point') && !returns.has(y)) {
+        requantScale = nq[0].getAttr<number>('scale')!; done.add(nq[0]); y = nq[0].getResult(0);
+      }
+      steps.push({ kind: 'linear', in: lhs, out: y, M, N, K, act: a.act, dynamic, w: Int8Array.from(w), wIsKN: rc[0] === 0, wScales, bias, requantScale });
+    } else {
+      throw new Error(`b200: op '${n}' is outside the graph contract (quantize, dequantize, quantized_dot and its tail)`);
+    }
+  }
+  return steps;
+}
+
+export type FunctionPlan = { inputs: number; outputs: number; steps: Step[]; describe(): string; execute(b: B200QBinding, ctx: unknown, args: ArrayBufferView[]): void };
+
+export function planGraph(module: GraphModule, options: B200Options, b: B200QBinding, ctx: unknown): Map<string, FunctionPlan> {
+  const dynamic = options.activationQuant === 'per_token_dynamic';
+  const plans = new Map<string, FunctionPlan>();
+  const alloc = (bytes: number): unknown => { const out: [unknown] = [null]; check(b, b.alloc(ctx, bytes, out), 'b200q_alloc'); return out[0]; };
+  const upload = (a: ArrayBufferView): unknown => { const d = alloc(a.byteLength); check(b, b.upload(ctx, d, a, a.byteLength), 'b200q_upload'); return d; };
+  const bytesOf = (v: Value) => numel(shapeOf(v)) * ({ f32: 4, i32: 4, i8: 1, ui8: 1 } as Record<string, number>)[dtypeOf(v)];
+  for (const f of module.functions()) {
+    const steps = planFunction(f, dynamic);
+    const buf = new Map<Value, unknown>(), tokScales = new Map<Value, unknown>();
+    for (const v of f.args) buf.set(v, alloc(bytesOf(v)));
+    for (const st of steps) {
+      buf.set(st.out, alloc(bytesOf(st.out)));
+      if (st.kind === 'quantize_token') tokScales.set(st.out, alloc(st.M * 4));
+      if (st.kind === 'linear') {                     // weights cross the boundary once, as buffers
+        const raw = upload(st.w);
+        if (st.wIsKN) { st.dW = alloc(st.w.byteLength); check(b, b.transposeI8(ctx, raw, st.K, st.N, st.dW), 'b200q_transpose_i8'); check(b, b.sync(ctx), 'b200q_sync'); check(b, b.free(ctx, raw), 'b200q_free'); }
+        else st.dW = raw;
+        st.dWs = upload(st.wScales);
+        st.dBias = st.bias ? upload(st.bias) : null;
+      }
+    }
+    const rets = f.returnValues();
+    plans.set(f.name, {
+      inputs: f.args.length, outputs: rets.length, steps,
+      describe: () => steps.map((s) => s.kind).join('\n'),
+      execute(bind, c, args) {
+        f.args.forEach((v, i) => check(bind, bind.upload(c, buf.get(v), args[i], args[i].byteLength), 'b200q_upload'));
+        for (const st of steps) {
+          const x = buf.get(st.in), y = buf.get(st.out);
+          if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, numel(shapeOf(st.in)), st.scale, st.zeroPoint, st.dst, y), 'b200q_quantize_static');
+          else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, st.M, st.K, y, tokScales.get(st.out), -127, 127), 'b200q_quantize_per_token');
+          else if (st.kind === 'dequantize_static') check(bind, bind.dequantizeStatic(c, x, st.src, numel(shapeOf(st.in)), st.scale, st.zeroPoint, y), 'b200q_dequantize_static');
+          else if (st.requantScale !== null) check(bind, bind.linearRequantStatic(c, x, null, st.dW, st.dWs, st.dBias, ACT[st.act], st.M, st.N, st.K, st.requantScale, y), 'b200q_int8_linear_requant_static');
+          else check(bind, bind.linear(c, x, st.dynamic ? tokScales.get(st.in) : null, st.dW, st.dWs, st.dBias, ACT[st.act], st.M, st.N, st.K, y), 'b200q_int8_linear');
+        }
+        check(bind, bind.sync(c), 'b200q_sync');
+        rets.forEach((v, i) => { const a = args[f.args.length + i]; check(bind, bind.download(c, a, buf.get(v), a.byteLength), 'b200q_download'); });
+      },
+    });
+  }
+  return plans;
+}
