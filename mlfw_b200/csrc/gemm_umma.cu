@@ -90,14 +90,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One probe of the barrier.  The hint lets the hardware park the thread for up to that many nanoseconds while the
+// phase is incomplete (it wakes as soon as the phase completes), so a waiting role does not burn the issue slots
+// the epilogue warps of its scheduler need.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(2000u)
       : "memory");
   return ok != 0;
 }
@@ -107,7 +110,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const uint64_t t0 = globaltimer_ns();
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++it & 31u) == 0u) {
+    if ((++it & 3u) == 0u) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
@@ -446,16 +449,21 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int e = 0; e < 4; e++) y[j4 * 4 + e] = __fadd_rn(scale_acc_wide(a[j4 * 4 + e], __fmul_rn(a_scale, wsv[e])), bv[e]);
           }
         }
-        if (ACT_T != ACT_NONE) {
+        if (ACT_T == ACT_GELU_SIGMOID || ACT_T == ACT_SILU) {
+          // Where the fast form is not valid (large negative argument, -Inf) the argument itself is kept: no valid
+          // result of these activations is below -0.3, so the bit test further down recognises such an element again.
 #pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const float v = y[j];
-            if (kGeneral != 0xFFFFFFFFu) vkey = max(vkey, __float_as_uint(v));
-            const float r = apply_act_fast<ACT_T>(v, tbl);
-            // Where the fast form is not valid (large negative argument, -Inf) keep the argument itself: no valid
-            // result of these activations is below -0.3, so the bit test below recognises such an element again.
-            y[j] = (kGeneral != 0xFFFFFFFFu && __float_as_uint(v) > kGeneral) ? v : r;
+          for (int j0 = 0; j0 < 32; j0 += 8) {
+            float v8[8], r8[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) { v8[e] = y[j0 + e]; r8[e] = v8[e]; vkey = max(vkey, __float_as_uint(v8[e])); }
+            apply_sigmoid_act_x8<ACT_T>(r8, tbl);
+#pragma unroll
+            for (int e = 0; e < 8; e++) y[j0 + e] = (__float_as_uint(v8[e]) > kGeneral) ? v8[e] : r8[e];
           }
+        } else if (ACT_T != ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) y[j] = apply_act_fast<ACT_T>(y[j], tbl);
         }
         if (kGeneral != 0xFFFFFFFFu) {
           if (__any_sync(0xffffffffu, vkey > kGeneral)) {  // rare

@@ -125,13 +125,15 @@ __device__ __forceinline__ double exp_f64(double xd, const double* tbl) {
   double kd = t - MAGIC;
   double r = fma(-kd, HI, xd);
   r = fma(-kd, LO, r);
-  double p = 1.0 / 720.0;
-  p = fma(p, r, 1.0 / 120.0);
-  p = fma(p, r, 1.0 / 24.0);
-  p = fma(p, r, 1.0 / 6.0);
-  p = fma(p, r, 0.5);
-  p = fma(p, r, 1.0);
-  p = fma(p, r, 1.0);
+  // exp(r) = 1 + r + r^2/2 + ... + r^6/720, evaluated in Estrin form: the dependent chain is 4 operations long
+  // instead of 6, which matters because the epilogue runs few warps.
+  const double r2 = r * r;
+  const double a = fma(r, 1.0, 1.0);                        // 1 + r
+  const double b = fma(r, 1.0 / 6.0, 0.5);                  // 1/2 + r/6
+  const double c = fma(r, 1.0 / 120.0, 1.0 / 24.0);         // 1/24 + r/120
+  const double d = fma(r2, 1.0 / 720.0, c);                 // 1/24 + r/120 + r^2/720
+  const double hi = fma(r2 * r2, d, 0.0);
+  const double p = fma(r2, b, a) + hi;
   double m = tbl[k & 63] * p;
   int e = k >> 6;                                      // |e| < 256: 2^e is a normal binary64
   return m * __hiloint2double((e + 1023) << 20, 0);
@@ -206,6 +208,61 @@ __device__ __forceinline__ float apply_act_fast(float y, const double* tbl) {
     return y * s;
   }
   return y;
+}
+
+// Eight sigmoid-based activations at once, written stage by stage: every loop below is one step of the
+// computation applied to eight independent elements, so the instruction stream itself is interleaved eight
+// ways (the per-element form leaves the compiler with one long dependent chain after another, and with two
+// epilogue warps per scheduler nothing else hides those latencies).  Same values as apply_act_fast.
+template <int ACT_T>
+__device__ __forceinline__ void apply_sigmoid_act_x8(float (&y)[8], const double* tbl) {
+  constexpr int W = 8;
+  float z[W];
+  double x[W], t[W], kd[W], r[W], r2[W], a[W], b[W], c[W], p[W], m[W];
+  int k[W];
+  float e[W], d[W], g[W], res[W], cand[W], rc[W];
+#pragma unroll
+  for (int i = 0; i < W; i++) z[i] = (ACT_T == ACT_GELU_SIGMOID) ? mul_1702(y[i]) : y[i];
+#pragma unroll
+  for (int i = 0; i < W; i++) {
+    float zc;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(zc) : "f"(z[i]), "f"(100.0f));
+    x[i] = (double)(-zc);
+  }
+  const double INV = 92.33248261689366, MAGIC = 6755399441055744.0;
+  const double HI = __longlong_as_double(0x3F862E42FEE00000LL), LO = __longlong_as_double(0x3D8A39EF35793C76LL);
+#pragma unroll
+  for (int i = 0; i < W; i++) t[i] = fma(x[i], INV, MAGIC);
+#pragma unroll
+  for (int i = 0; i < W; i++) { k[i] = __double2loint(t[i]); kd[i] = t[i] - MAGIC; }
+#pragma unroll
+  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], HI, x[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], LO, r[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++) { r2[i] = r[i] * r[i]; a[i] = fma(r[i], 1.0, 1.0); b[i] = fma(r[i], 1.0 / 6.0, 0.5); c[i] = fma(r[i], 1.0 / 120.0, 1.0 / 24.0); }
+#pragma unroll
+  for (int i = 0; i < W; i++) { c[i] = fma(r2[i], 1.0 / 720.0, c[i]); a[i] = fma(r2[i], b[i], a[i]); b[i] = r2[i] * r2[i]; }
+#pragma unroll
+  for (int i = 0; i < W; i++) p[i] = a[i] + fma(b[i], c[i], 0.0);
+#pragma unroll
+  for (int i = 0; i < W; i++) m[i] = tbl[k[i] & 63] * p[i];
+#pragma unroll
+  for (int i = 0; i < W; i++) e[i] = __double2float_rn(m[i] * __hiloint2double(((k[i] >> 6) + 1023) << 20, 0));
+#pragma unroll
+  for (int i = 0; i < W; i++) d[i] = __fadd_rn(1.0f, e[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g[i]) : "f"(d[i]));
+#pragma unroll
+  for (int i = 0; i < W; i++) g[i] = __fmaf_rn(g[i], __fmaf_rn(-d[i], g[i], 1.0f), g[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++) res[i] = __fmaf_rn(-d[i], g[i], 1.0f);
+#pragma unroll
+  for (int i = 0; i < W; i++) cand[i] = __int_as_float(__float_as_int(g[i]) + (res[i] > 0.0f ? 1 : -1));
+#pragma unroll
+  for (int i = 0; i < W; i++) rc[i] = __fmaf_rn(-d[i], cand[i], 1.0f);
+#pragma unroll
+  for (int i = 0; i < W; i++) y[i] = __fmul_rn(y[i], (fabsf(rc[i]) < fabsf(res[i])) ? cand[i] : g[i]);
 }
 
 // True when apply_act_fast<ACT_T>(y) may differ from apply_act(y): compares the bit pattern as an
