@@ -42,6 +42,7 @@ WORKLOADS = {
     "small_2048x4096x4096_none": (2048, 4096, 4096, "none"),
 }
 DEFAULT_WORKLOAD = "c3_gemm_8192x4096x4096_gelu_tanh"
+C5_WORKLOAD = "c5_stack_4096x8192x28672_silu"       # 4 linears 8192 -> 28672 -> 8192 -> 28672 -> 8192, M 4096 in total
 C2_SHAPE = (16384, 4096)          # standalone quantize -> dequantize round trip
 CPU_SAMPLE_ROWS = 64              # rows of M the CPU arm processes per step (rows are independent)
 
@@ -143,6 +144,84 @@ def run_roundtrip(ctx, pk, iters, warmup):
     return {"workload": "quantize -> dequantize, f32 [16384,4096], 0.1% outliers", "algorithmic_bytes": bytes_each, **rt}
 
 
+def run_c5(args, ctx, dist, rank, world, local_rank, barrier, max_over_ranks):
+    """Config 5: four int8 linears 8192 <-> 28672 with SiLU and a per-token requantize between them, M = 4096 rows in
+    total (strong scaling).  mshard: each rank takes M / world rows of every layer, weights replicated, no
+    collective.  nshard: each rank takes N / world output channels of every layer; per layer two [M]-float
+    all-reduces (row ranges) and one int8 all-gather of the column blocks over NVLink."""
+    import torch
+    from mlfw_b200 import sharding, synth
+    M, dims, acts = 4096, [8192, 28672, 8192, 28672, 8192], ["silu", "silu", "silu", "none"]
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    gen = np.random.default_rng(5)                               # same weights on every rank
+    x = synth.normal(synth.tensor_seed(5, 0), (M, dims[0]))
+    layers = []
+    for i in range(4):
+        K, N = dims[i], dims[i + 1]
+        w = gen.integers(-127, 128, size=(N, K), dtype=np.int8)
+        ws = (gen.uniform(1e-3, 1e-2, N) / np.sqrt(K)).astype(np.float32)
+        layers.append((w, ws, acts[i]))
+    ops_total = sum(2.0 * M * dims[i] * dims[i + 1] for i in range(4))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    if args.mode == "mshard":
+        r0, rows = sharding.row_block(M, world, rank)
+        dx = ctx.to_device(x[r0:r0 + rows])
+        dls = [(ctx.to_device(w), ctx.to_device(ws), a) for w, ws, a in layers]
+        q = [ctx.empty((rows, d), np.int8) for d in dims[:-1]]
+        sc = [ctx.empty((rows,), np.float32) for _ in dims[:-1]]
+        out = ctx.empty((rows, dims[-1]), np.float32)
+
+        def step():
+            ctx.quantize_per_token(dx, rows, dims[0], q[0], sc[0])
+            for i, (dw, dws, a) in enumerate(dls):
+                if i < 3:
+                    ctx.int8_linear_requant_token(q[i], sc[i], dw, dws, None, a, rows, dims[i + 1], dims[i], q[i + 1], sc[i + 1])
+                else:
+                    ctx.int8_linear(q[i], sc[i], dw, dws, None, a, rows, dims[i + 1], dims[i], out)
+            ctx.sync()
+    else:
+        shards = []
+        for i, (w, ws, a) in enumerate(layers):
+            c0, cols = sharding.column_block(dims[i + 1], world, rank)
+            shards.append(sharding.ShardedLayer(dims[i], dims[i + 1], c0, cols, torch.from_numpy(np.ascontiguousarray(w[c0:c0 + cols])).to(dev),
+                                                torch.from_numpy(ws[c0:c0 + cols].copy()).to(dev), None, a))
+        stack = sharding.ColumnShardedStack(sharding.DeviceOps(ctx, torch), dist, rank, world, shards)
+        tx = torch.from_numpy(x).to(dev)
+        tq = torch.empty((M, dims[0]), dtype=torch.int8, device=dev)
+        ts = torch.empty((M,), dtype=torch.float32, device=dev)
+
+        def step():
+            torch.cuda.current_stream(dev).synchronize()
+            ctx.quantize_per_token(tx.data_ptr(), M, dims[0], tq.data_ptr(), ts.data_ptr())
+            ctx.sync()
+            stack.forward(tq, ts, M, last_f32=True)
+            torch.cuda.current_stream(dev).synchronize()
+
+    del layers
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ctx.check_status()
+    launches0 = ctx.launch_count()
+    barrier()
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    ctx.check_status()
+    return {"metric": "int8_linear_tokens_per_s", "value": M / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 x int8 -> int32, f32 tail", "data": "synthetic (weights from numpy's PCG64, seed 5)",
+            "config": {"workload": C5_WORKLOAD, "M_total": M, "dims": dims, "activation": "silu", "mode": args.mode,
+                       "parallelism": (f"M-sharded x{world}, weights replicated, no collective" if args.mode == "mshard" else
+                                       f"N-sharded x{world}: per layer 2 all-reduces of [M] floats + 1 int8 all-gather (NCCL)")},
+            "tops": ops_total / (ms * 1e-3) / 1e12, "gpu_launches": ctx.launch_count() - launches0}
+
+
 def run_reference_arm(args, rank, world):
     """The reference's CPU path (its C++ restatement: no JavaScript engine exists here) on all host cores."""
     if rank != 0:
@@ -203,7 +282,9 @@ def _run():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [C5_WORKLOAD])
+    ap.add_argument("--mode", default="mshard", choices=["mshard", "nshard"],
+                    help="config 5 only: rows split over the GPUs (no collective) or output channels split (NCCL all-gather)")
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
     ap.add_argument("--roundtrip-only", action="store_true", help="only the standalone quantize -> dequantize round trip (profiler runs)")
     args = ap.parse_args()
@@ -241,6 +322,12 @@ def _run():
         line = {"metric": "quantize_dequantize_GBps", "roundtrip_c2": run_roundtrip(ctx, peaks(), args.steps, args.warmup)}
         ctx.close()
         return line
+    if args.workload == C5_WORKLOAD:
+        line = run_c5(args, ctx, dist, rank, world, local_rank, barrier, max_over_ranks)
+        ctx.close()
+        if dist is not None:
+            dist.destroy_process_group()
+        return line if rank == 0 else None
     M, K, N, act, xs, W, ws, bias = make_case(args.workload, rank)
     dxs = [ctx.to_device(x) for x in xs]
     douts = [ctx.empty((M, N), np.float32) for _ in xs]

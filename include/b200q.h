@@ -98,6 +98,15 @@ int b200q_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t 
 /* dequantizeArrayPerChannel (quantization_types.ts:132-141) with the binary32 scales: y = fround(q * scale[m]). */
 int b200q_dequantize_per_token(b200q_ctx* ctx, const int8_t* q, const float* scales, int64_t M, int64_t K, float* y);
 
+/* The same quantization in two steps, for rows whose columns are spread over several GPUs (column-sharded
+ * layers; the reference has no multi-device execution): the NaN-ignoring min and max of each row of the local
+ * columns, then - after the host has combined them over the GPUs (min of mins, max of maxes) - the codes
+ * and the scale from the agreed range.  ld* are row strides in elements.  The codes equal those of
+ * b200q_quantize_per_token on the whole row. */
+int b200q_row_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld, float* row_min, float* row_max);
+int b200q_quantize_rows_with_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld_in, const float* row_min,
+                                   const float* row_max, int8_t* q, int64_t ld_out, float* scales, int qmin, int qmax);
+
 /* ------------------------------------------------- static (compiled) ops
  * The `quantize` / `dequantize` graph ops (src/compiler/ir/graph/ops/quantization.ts:12-101,
  * lowering src/compiler/passes/lowering/rules/quantization.ts:6-21, leaf math quant_math.ts:16-34)

@@ -42,6 +42,8 @@ PROTOTYPES = {
     "b200q_profile_read": (c_int, [c_vp, c_int, C.POINTER(c_dbl), C.POINTER(C.c_uint64)]),
     "b200q_quantize_per_token": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_int]),
     "b200q_dequantize_per_token": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp]),
+    "b200q_row_range": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp]),
+    "b200q_quantize_rows_with_range": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_i64, c_vp, c_int, c_int]),
     "b200q_quantize_static": (c_int, [c_vp, c_vp, c_i64, c_dbl, c_int, c_int, c_vp]),
     "b200q_dequantize_static": (c_int, [c_vp, c_vp, c_int, c_i64, c_dbl, c_int, c_vp]),
     "b200q_quantize_weights_per_channel": (c_int, [c_vp, c_vp, c_i64, c_i64, c_int, c_vp, c_vp, c_vp]),

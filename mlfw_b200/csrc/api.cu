@@ -313,6 +313,24 @@ int b200q_dequantize_per_token(b200q_ctx* ctx, const int8_t* q, const float* sca
   return launch_dequantize_per_token(ctx, q, scales, M, K, y);
 }
 
+int b200q_row_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld, float* row_min, float* row_max) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(M, N, 0);
+  B200Q_REQUIRE(ld >= N, "b200q_row_range: row stride %lld is smaller than the row length %lld", (long long)ld, (long long)N);
+  B200Q_REQUIRE(M == 0 || (row_min && row_max && (y || N == 0)), "b200q_row_range: null pointer");
+  return launch_row_range(ctx, y, M, N, ld, row_min, row_max);
+}
+
+int b200q_quantize_rows_with_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld_in, const float* row_min,
+                                   const float* row_max, int8_t* q, int64_t ld_out, float* scales, int qmin, int qmax) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(M, N, 0);
+  B200Q_REQUIRE(ld_in >= N && ld_out >= N, "b200q_quantize_rows_with_range: a row stride is smaller than the row length");
+  B200Q_REQUIRE(M == 0 || N == 0 || (y && q && row_min && row_max), "b200q_quantize_rows_with_range: null pointer");
+  B200Q_REQUIRE(qmin >= -128 && qmax <= 127 && qmin < qmax, "b200q_quantize_rows_with_range: clamp [%d,%d] is not an int8 range", qmin, qmax);
+  return launch_quantize_rows_with_range(ctx, y, M, N, ld_in, row_min, row_max, q, ld_out, scales, qmin, qmax);
+}
+
 int b200q_quantize_static(b200q_ctx* ctx, const float* x, int64_t n, double scale, int zero_point, int dst_kind, void* q) {
   if (use_device(ctx)) return 1;
   B200Q_REQUIRE(n >= 0, "b200q_quantize_static: negative length");

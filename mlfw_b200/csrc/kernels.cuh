@@ -15,6 +15,11 @@ int launch_dequantize_static(b200q_ctx* ctx, const void* q, int src_kind, int64_
 // layout 0: w is [N,K]; 1: w is [K,N].  Codes are always written [N,K].
 int launch_quantize_weights(b200q_ctx* ctx, const float* w, int64_t N, int64_t K, int layout, int qmin, int qmax, int8_t* qw,
                             float* scales32, double* scales64);
+// Two-step per-token quantize for rows that are spread over several GPUs (column-sharded layers).
+// ld / ld_in / ld_out: row strides in elements (a shard may be a column block of a wider buffer).
+int launch_row_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld, float* mn, float* mx);
+int launch_quantize_rows_with_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld_in, const float* mn,
+                                    const float* mx, int8_t* q, int64_t ld_out, float* scales, int qmin, int qmax);
 int launch_transpose_i8(b200q_ctx* ctx, const int8_t* src_kn, int64_t K, int64_t N, int8_t* dst_nk);
 
 int launch_gemm_i8_simt(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,

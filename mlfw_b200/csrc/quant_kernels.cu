@@ -597,6 +597,62 @@ __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* __restr
   }
 }
 
+// ---------------------------------------------------------------------------
+// Column-sharded (N-sharded) layers: a row of the activation is spread over several GPUs, so its range is
+// found in two steps (range of the local columns here, min / max over the GPUs by the host's collective) and
+// the codes are then computed from the agreed range - bit for bit what quantizing the whole row would give.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) row_range_kernel(const float* __restrict__ y, int64_t M, int64_t N, int64_t ld,
+                                                        float* __restrict__ mn_out, float* __restrict__ mx_out) {
+  __shared__ float s_mn[8], s_mx[8];
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float* yr = y + row * ld;
+    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+    for (int64_t k = threadIdx.x; k < N; k += blockDim.x) {
+      const float v = yr[k];
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) { s_mn[threadIdx.x >> 5] = mn; s_mx[threadIdx.x >> 5] = mx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < (int)(blockDim.x >> 5); w++) { mn = fminf(mn, s_mn[w]); mx = fmaxf(mx, s_mx[w]); }
+      mn_out[row] = mn;
+      mx_out[row] = mx;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(256) quantize_rows_with_range_kernel(const float* __restrict__ y, int64_t M, int64_t N, int64_t ld_in,
+                                                                       const float* __restrict__ mn_in, const float* __restrict__ mx_in,
+                                                                       int8_t* __restrict__ q, int64_t ld_out, float* __restrict__ scales,
+                                                                       float qmin, float qmax) {
+  const float limit = guard_limit(qmin, qmax);
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float mn = mn_in[row], mx = mx_in[row];
+    const float absmax = fmaxf(fabsf(mn), fabsf(mx));
+    const float inv = __fdiv_rn(127.0f, absmax);
+    const bool exact_only = !((mn < mx) && absmax <= 3.402823466e38f && is_normal_f32(inv));
+    const double s = row_scale(mn, mx);
+    const float* yr = y + row * ld_in;
+    int8_t* qr = q + row * ld_out;
+    for (int64_t k = threadIdx.x; k < N; k += blockDim.x) {
+      QuantGuard guard;
+      const float xv = yr[k];
+      int c = quantize_fast(xv, inv, guard);
+      if (exact_only || guard.unsafe(limit)) c = quantize_exact_p(xv, s, qmin, qmax);
+      qr[k] = (int8_t)c;
+    }
+    if (threadIdx.x == 0 && scales) scales[row] = (float)s;
+  }
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -731,6 +787,27 @@ int launch_quantize_weights(b200q_ctx* ctx, const float* w, int64_t N, int64_t K
   dim3 grid((unsigned)((K + 31) / 32), (unsigned)((N + 31) / 32));
   weight_quantize_kernel<<<grid, 256, 0, ctx->stream>>>(w, N, K, layout, s64, (float)qmin, (float)qmax, qw);
   ctx->launches += 2;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_row_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld, float* mn, float* mx) {
+  ProfScope prof(ctx, KK_QUANT_TOKEN);
+  if (M == 0) return 0;
+  const unsigned blocks = (unsigned)(M < (int64_t)ctx->sm_count * 8 ? M : (int64_t)ctx->sm_count * 8);
+  row_range_kernel<<<blocks, 256, 0, ctx->stream>>>(y, M, N, ld, mn, mx);
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_quantize_rows_with_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld_in, const float* mn,
+                                    const float* mx, int8_t* q, int64_t ld_out, float* scales, int qmin, int qmax) {
+  ProfScope prof(ctx, KK_QUANT_TOKEN);
+  if (M == 0 || N == 0) return 0;
+  const unsigned blocks = (unsigned)(M < (int64_t)ctx->sm_count * 8 ? M : (int64_t)ctx->sm_count * 8);
+  quantize_rows_with_range_kernel<<<blocks, 256, 0, ctx->stream>>>(y, M, N, ld_in, mn, mx, q, ld_out, scales, (float)qmin, (float)qmax);
+  ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -194,6 +194,13 @@ class Context:
         check(self.lib.b200q_dequantize_per_token(self.handle, _ptr(q), _ptr(scales), M, K, _ptr(y)),
               "b200q_dequantize_per_token")
 
+    def row_range(self, y, M, N, ld, row_min, row_max):
+        check(self.lib.b200q_row_range(self.handle, _ptr(y), M, N, ld, _ptr(row_min), _ptr(row_max)), "b200q_row_range")
+
+    def quantize_rows_with_range(self, y, M, N, ld_in, row_min, row_max, q, ld_out, scales, qmin=-127, qmax=127):
+        check(self.lib.b200q_quantize_rows_with_range(self.handle, _ptr(y), M, N, ld_in, _ptr(row_min), _ptr(row_max), _ptr(q),
+                                                      ld_out, _ptr(scales), qmin, qmax), "b200q_quantize_rows_with_range")
+
     def quantize_static(self, x, n, scale, zero_point, dst_kind, q):
         check(self.lib.b200q_quantize_static(self.handle, _ptr(x), n, scale, zero_point, dst_kind, _ptr(q)),
               "b200q_quantize_static")
