@@ -205,6 +205,31 @@ __device__ __forceinline__ bool q_mbar_wait(uint32_t bar, uint32_t parity, volat
   return true;
 }
 
+// Three-input min / max that PROPAGATE NaN (one instruction on sm_100).
+__device__ __forceinline__ float fmin3n(float a, float b, float c) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float fmax3n(float a, float b, float c) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Leanest form of the fast code, for finite elements of an ordinary per-token row: the code, and the running maximum
+// of |t - rint t| (how close any element came to a tie).
+__device__ __forceinline__ uint32_t pack4_fast_lean(const float4& v, float inv, float& far) {
+  const float M = 12582912.0f;
+  const float t0 = __fmul_rn(v.x, inv), t1 = __fmul_rn(v.y, inv), t2 = __fmul_rn(v.z, inv), t3 = __fmul_rn(v.w, inv);
+  const float u0 = __fadd_rn(t0, M), u1 = __fadd_rn(t1, M), u2 = __fadd_rn(t2, M), u3 = __fadd_rn(t3, M);
+  const float d0 = __fsub_rn(t0, __fsub_rn(u0, M)), d1 = __fsub_rn(t1, __fsub_rn(u1, M));
+  const float d2 = __fsub_rn(t2, __fsub_rn(u2, M)), d3 = __fsub_rn(t3, __fsub_rn(u3, M));
+  far = fmaxf(fmaxf(fmaxf(far, fabsf(d0)), fmaxf(fabsf(d1), fabsf(d2))), fabsf(d3));
+  return pack_codes(__float_as_int(u0) - 0x4B400000, __float_as_int(u1) - 0x4B400000, __float_as_int(u2) - 0x4B400000,
+                    __float_as_int(u3) - 0x4B400000);
+}
+
 // tie tracking only: in a per-token row |x * (127/absmax)| <= 127 (1 + 2^-23) by construction, so the magnitude
 // needs no watching; a NaN element still trips the guard through `e`.
 __device__ __forceinline__ int quantize_fast_bounded(float x, float inv, int& tie) {
@@ -296,56 +321,107 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
       const float4* slot = reinterpret_cast<const float4*>(qt_smem + (int64_t)s * chunk_bytes);
       for (int r = 0; r < rows; r++) {
         const float4* xr = slot + (int64_t)r * K4;
-        // pass 1: range of the row (fminf/fmaxf drop NaN operands, as the strict comparisons of the reference do)
+        // pass 1: range of the row with NaN-PROPAGATING three-input min / max (one instruction per two elements and
+        // bound).  A row that contains a NaN shows up as a NaN range: it is rescanned with the NaN-dropping forms
+        // (the reference's strict comparisons ignore NaN) and encoded entirely on the exact path.
         float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
         int c = lane;
-#pragma unroll 4
+#pragma unroll 2
         for (; c + 96 < K4; c += 128) {
           const float4 v0 = xr[c], v1 = xr[c + 32], v2 = xr[c + 64], v3 = xr[c + 96];
-          mn = fminf(fminf(fminf(mn, v0.x), fminf(v0.y, v0.z)), fminf(fminf(v0.w, v1.x), fminf(v1.y, v1.z)));
-          mn = fminf(fminf(fminf(mn, v1.w), fminf(v2.x, v2.y)), fminf(fminf(v2.z, v2.w), fminf(v3.x, v3.y)));
-          mn = fminf(mn, fminf(v3.z, v3.w));
-          mx = fmaxf(fmaxf(fmaxf(mx, v0.x), fmaxf(v0.y, v0.z)), fmaxf(fmaxf(v0.w, v1.x), fmaxf(v1.y, v1.z)));
-          mx = fmaxf(fmaxf(fmaxf(mx, v1.w), fmaxf(v2.x, v2.y)), fmaxf(fmaxf(v2.z, v2.w), fmaxf(v3.x, v3.y)));
-          mx = fmaxf(mx, fmaxf(v3.z, v3.w));
+          float mn2 = fmin3n(v0.x, v0.y, v0.z), mx2 = fmax3n(v0.x, v0.y, v0.z);   // two independent chains per bound
+          mn = fmin3n(mn, v0.w, v1.x); mx = fmax3n(mx, v0.w, v1.x);
+          mn2 = fmin3n(mn2, v1.y, v1.z); mx2 = fmax3n(mx2, v1.y, v1.z);
+          mn = fmin3n(mn, v1.w, v2.x); mx = fmax3n(mx, v1.w, v2.x);
+          mn2 = fmin3n(mn2, v2.y, v2.z); mx2 = fmax3n(mx2, v2.y, v2.z);
+          mn = fmin3n(mn, v2.w, v3.x); mx = fmax3n(mx, v2.w, v3.x);
+          mn2 = fmin3n(mn2, v3.y, v3.z); mx2 = fmax3n(mx2, v3.y, v3.z);
+          mn = fmin3n(mn, v3.w, mn2); mx = fmax3n(mx, v3.w, mx2);
         }
         for (; c < K4; c += 32) {
           const float4 v = xr[c];
-          mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));
-          mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
+          mn = fmin3n(fmin3n(mn, v.x, v.y), v.z, v.w);
+          mx = fmax3n(fmax3n(mx, v.x, v.y), v.z, v.w);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
-          mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+          mn = fmin3n(mn, mn, __shfl_xor_sync(0xffffffffu, mn, o));
+          mx = fmax3n(mx, mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        const bool nan_row = (mn != mn) || (mx != mx);   // uniform over the warp after the reduction
+        if (nan_row) {
+          mn = __int_as_float(0x7f800000); mx = __int_as_float(0xff800000);
+          for (int cc = lane; cc < K4; cc += 32) {
+            const float4 v = xr[cc];
+            mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));
+            mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+          }
         }
         const float absmax = fmaxf(fabsf(mn), fabsf(mx));
         const float inv = __fdiv_rn(127.0f, absmax);
-        const bool exact_only = !((mn < mx) && absmax <= 3.402823466e38f && is_normal_f32(inv));
-        // pass 2: encode, four vectors (16 elements) per lane at a time
+        // odd rows (constant, non-finite ends, NaN inside, a reciprocal that is not a normal number) and narrow clamps
+        // encode through binary64 throughout
+        const bool exact_only = nan_row || limit < 127.0f || !((mn < mx) && absmax <= 3.402823466e38f && is_normal_f32(inv));
         uint32_t* qr = reinterpret_cast<uint32_t*>(q) + (row0 + r) * K4;
-        for (int c0 = lane; c0 < K4; c0 += 128) {
-          float4 v[4];
-          uint32_t w[4];
-          int tie = 0;
+        if (!exact_only && (K4 & 127) == 0) {
+          // pass 2, ordinary row whose length is a multiple of 512 elements: no bounds checks, five instructions per
+          // element for the code, one more to keep the largest |t - rint t| of the 16 elements a lane handles per turn.
+          // Every element is finite here and |t| <= 127 (1 + 2^-23), so a tie is the only thing that can go wrong:
+          // first a cheap test with the worst-case margin (|t| = 127.5), and only if that trips the per-element one.
+          for (int c0 = lane; c0 < K4; c0 += 128) {
+            float4 v[4];
+            uint32_t w[4];
+            float far = 0.0f;
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            const int cc = c0 + 32 * j;
-            v[j] = (cc < K4) ? xr[cc] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int j = 0; j < 4; j++) v[j] = xr[c0 + 32 * j];
+#pragma unroll
+            for (int j = 0; j < 4; j++) w[j] = pack4_fast_lean(v[j], inv, far);
+            if (far >= 0.49993920f) {                                   // 0.5 - 127.5 * 2^-21
+              int tie = 0;
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                (void)quantize_fast_bounded(v[j].x, inv, tie); (void)quantize_fast_bounded(v[j].y, inv, tie);
+                (void)quantize_fast_bounded(v[j].z, inv, tie); (void)quantize_fast_bounded(v[j].w, inv, tie);
+              }
+              if (tie >= 0x3f000000) {
+                const double sd = row_scale(mn, mx);
+#pragma unroll
+                for (int j = 0; j < 4; j++) w[j] = pack4_exact_p(v[j], sd, qmin, qmax);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) __stcs(qr + c0 + 32 * j, w[j]);
           }
+        } else {
+          // pass 2, general: ragged row length or the exact path
+          for (int c0 = lane; c0 < K4; c0 += 128) {
+            float4 v[4];
+            uint32_t w[4];
+            int tie = 0;
 #pragma unroll
-          for (int j = 0; j < 4; j++)
-            w[j] = pack_codes(quantize_fast_bounded(v[j].x, inv, tie), quantize_fast_bounded(v[j].y, inv, tie),
-                              quantize_fast_bounded(v[j].z, inv, tie), quantize_fast_bounded(v[j].w, inv, tie));
-          if (exact_only || tie >= 0x3f000000 || limit < 127.0f) {  // rare: a tie, NaN, an odd row, a narrow clamp
-            const double sd = row_scale(mn, mx);
+            for (int j = 0; j < 4; j++) {
+              const int cc = c0 + 32 * j;
+              v[j] = (cc < K4) ? xr[cc] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
 #pragma unroll
-            for (int j = 0; j < 4; j++) w[j] = pack4_exact_p(v[j], sd, qmin, qmax);
-          }
+            for (int j = 0; j < 4; j++)
+              w[j] = pack_codes(quantize_fast_bounded(v[j].x, inv, tie), quantize_fast_bounded(v[j].y, inv, tie),
+                                quantize_fast_bounded(v[j].z, inv, tie), quantize_fast_bounded(v[j].w, inv, tie));
+            if (exact_only || tie >= 0x3f000000) {  // rare: a tie, NaN, an odd row, a narrow clamp
+              const double sd = row_scale(mn, mx);
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            const int cc = c0 + 32 * j;
-            if (cc < K4) __stcs(qr + cc, w[j]);
+              for (int j = 0; j < 4; j++) w[j] = pack4_exact_p(v[j], sd, qmin, qmax);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int cc = c0 + 32 * j;
+              if (cc < K4) __stcs(qr + cc, w[j]);
+            }
           }
         }
         if (lane == 0) scales[row0 + r] = exact_only ? (float)row_scale(mn, mx) : __fdiv_rn(absmax, 127.0f);
