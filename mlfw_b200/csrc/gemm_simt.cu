@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const int32_t* __restrict
                                                        const float* __restrict__ a_scales, const float* __restrict__ w_scales,
                                                        const float* __restrict__ bias, int act, float* __restrict__ out_f32,
                                                        int8_t* __restrict__ out_q, double q_scale, float q_inv, int q_exact) {
-  __shared__ double tbl[64];
+  __shared__ double tbl[EXP2_TABLE_SIZE];
   fill_exp2_table(tbl, threadIdx.x, blockDim.x);
   __syncthreads();
   const int64_t total = M * N;

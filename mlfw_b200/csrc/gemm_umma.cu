@@ -55,9 +55,14 @@ constexpr int EPI_WARPS = 8;                   // two warps per tensor-memory la
 constexpr int EPI_COLS = BN / (EPI_WARPS / 4); // columns of a tile one epilogue warp handles
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr int MISC_BYTES = 1024 + EPI_WARPS * EPI_COLS * 8;
+constexpr int EPI_CH = 16;                     // columns an epilogue warp takes from tensor memory at a time
+// Staging tile of one epilogue warp for the bulk-tensor store of a chunk: 32 rows x EPI_CH 4-byte values.
+constexpr int OUT_STAGE_BYTES = 32 * EPI_CH * 4;
+constexpr int MISC_BYTES = 2560 + EPI_WARPS * EPI_COLS * 8;
 template <int NCTA>
-constexpr int smem_bytes() { return Cfg<NCTA>::STAGES * Cfg<NCTA>::STAGE_BYTES + MISC_BYTES + 1024; }  // + slack to align the tiles to 1024 B
+constexpr int smem_bytes() {  // + slack to align the tiles to 1024 B
+  return Cfg<NCTA>::STAGES * Cfg<NCTA>::STAGE_BYTES + EPI_WARPS * OUT_STAGE_BYTES + MISC_BYTES + 1024;
+}
 
 struct GemmParams {
   int64_t M, N, K;
@@ -71,6 +76,7 @@ struct GemmParams {
   double q_scale;
   float q_inv;
   int q_exact;
+  int tma_store;          // 4-byte outputs leave through bulk-tensor stores (needs N % 4 == 0 and a 16-byte aligned base)
   uint32_t* status;
   unsigned long long wait_limit_ns;
 };
@@ -198,19 +204,30 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
-        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr)
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Bulk-tensor store of one staging tile (shared -> global), tracked by the issuing thread's bulk async-group.
+// Rows and columns of the box that lie outside the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(tm)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Until every store this thread issued has finished READING its staging tile / has completed altogether.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Generic-proxy writes to shared memory become visible to the async proxy (the bulk copy engine).
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 struct alignas(16) Misc {
   uint64_t full[MAX_STAGES];
@@ -219,7 +236,7 @@ struct alignas(16) Misc {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  double exp_tbl[64];
+  double exp_tbl[EXP2_TABLE_SIZE];
   alignas(16) float col_scale[EPI_WARPS][EPI_COLS];   // per-warp copy of w_scales for the tile's columns (read as float4)
   alignas(16) float col_bias[EPI_WARPS][EPI_COLS];
 };
@@ -230,14 +247,16 @@ enum OutMode : int { OUT_F32 = 0, OUT_I32 = 1, OUT_Q8 = 2 };
 
 template <int ACT_T, int OUT_T, int NCTA>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   using C = Cfg<NCTA>;
   constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, A_BYTES = C::A_BYTES;
   extern __shared__ uint8_t smem_raw[];
   // The pair variant needs the same shared-memory offsets in both CTAs: the dynamic region starts at the
   // same window offset in every CTA of a kernel, so rounding it up to 1024 B gives the same result in both.
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  Misc* misc = reinterpret_cast<Misc*>(tiles + STAGES * STAGE_BYTES);
+  uint8_t* out_stage = tiles + STAGES * STAGE_BYTES;   // 1024-byte aligned: EPI_WARPS staging tiles of the epilogue
+  Misc* misc = reinterpret_cast<Misc*>(out_stage + EPI_WARPS * OUT_STAGE_BYTES);
   volatile int* abort_flag = &misc->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -367,6 +386,15 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const bool vec_ok = OUT_T == OUT_Q8 ? ((p.N % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out_q) & 15u) == 0))
                         : OUT_T == OUT_I32 ? ((p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out_i32) & 15u) == 0))
                                            : ((p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out_f32) & 15u) == 0));
+    // 4-byte outputs leave through this warp's staging tile and a bulk-tensor store: the copy engine writes whole
+    // 64-byte row segments and clips at M and N, where a lane writing its own row straight from registers issues
+    // 16-byte pieces of 32 different lines per instruction (measured: those stores, not the arithmetic, bounded
+    // the epilogue).  The tile is laid out for the tensor map's 64-byte swizzle: the 16-byte piece q of row r sits
+    // at piece q ^ ((r >> 1) & 3), which also keeps the eight lanes of a store phase on distinct banks.
+    const bool bulk_store = OUT_T != OUT_Q8 && p.tma_store != 0;
+    const uint32_t stage_addr = smem_u32(out_stage + ew * OUT_STAGE_BYTES);
+    const uint32_t stage_row = stage_addr + (uint32_t)lane * (EPI_CH * 4);
+    const uint32_t stage_xor = (uint32_t)((lane >> 1) & 3);
     uint32_t tile_it = 0;
     for (int64_t tile = tile_first; tile < num_tiles; tile += tile_step, tile_it++) {
       const uint32_t slot = tile_it & 1u, tph = (tile_it >> 1) & 1u;
@@ -382,7 +410,8 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         __syncwarp();
       }
-      const int64_t m = m0 + quarter * 32 + lane;
+      const int64_t mw = m0 + quarter * 32;   // first row of this warp
+      const int64_t m = mw + lane;
       const bool row_ok = m < p.M;
       const float a_scale = (p.a_scales && row_ok) ? __ldg(p.a_scales + m) : 1.0f;  // fround(1 * ws) == ws
       bool ok = true;
@@ -394,106 +423,106 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + slot * BN + (uint32_t)col0 + ((uint32_t)(quarter * 32) << 16);
-      constexpr int NCH = EPI_COLS / 32;
+      constexpr int NCH = EPI_COLS / EPI_CH;
 #pragma unroll 1
       for (int c = 0; c < NCH; c++) {
-        const int64_t nb = n0 + c * 32;
+        const int64_t nb = n0 + c * EPI_CH;
         if (nb >= p.N) break;  // uniform across the warp
-        int a[32];
-        tmem_ld32(taddr + (uint32_t)(c * 32), a);
+        int a[EPI_CH];
+        tmem_ld16(taddr + (uint32_t)(c * EPI_CH), a);
         tmem_ld_wait();
-        // No lane may leave this iteration early: the tensor-memory loads and the vote below are
-        // warp-collective.  Rows past M compute on whatever the accumulator holds and store nothing.
-        const bool full = vec_ok && (nb + 32 <= p.N);
+        // No lane may leave this iteration early: the tensor-memory loads, the votes and the staging protocol below
+        // are warp-collective.  Rows past M compute on whatever the accumulator holds and store nothing.
+        const bool full = vec_ok && (nb + EPI_CH <= p.N);
+        uint32_t v[EPI_CH];   // the chunk's 4-byte results as bit patterns (f32 or i32 output)
+        float y[EPI_CH];
         if (OUT_T == OUT_I32) {
-          int32_t* o = p.out_i32 + m * p.N + nb;
-          if (!row_ok) {
-          } else if (full) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(o + j) = make_int4(a[j], a[j + 1], a[j + 2], a[j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; j++)
-              if (nb + j < p.N) o[j] = a[j];
-          }
-          continue;
-        }
-        // An accumulator of 2^22 or more anywhere in the warp's chunk sends the whole chunk through the binary64
-        // product (the cheap int -> float conversion and the binary32 product are only exact below that).
-        int big = 0;
-#pragma unroll
-        for (int j = 0; j < 32; j++) big |= (abs(a[j]) >> 22);
-        const bool wide = __any_sync(0xffffffffu, big != 0);
-        float y[32];
-        unsigned vkey = 0;
-        const float4* cs4 = reinterpret_cast<const float4*>(cs + c * 32);
-        const float4* cb4 = reinterpret_cast<const float4*>(cb + c * 32);
-        constexpr unsigned kGeneral = act_general_threshold<ACT_T>();
-        // The loops below contain no branch at all (the choice between the two conversions is made once per
-        // chunk, a missing bias was staged as -0.0, which is the identity of the rounded addition), so the 32
-        // independent element chains of a thread can be interleaved freely.
-        if (!wide) {
-#pragma unroll
-          for (int j4 = 0; j4 < 8; j4++) {
-            const float4 w4 = cs4[j4], b4 = cb4[j4];
-            const float wsv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
-#pragma unroll
-            for (int e = 0; e < 4; e++) y[j4 * 4 + e] = __fadd_rn(scale_acc_small(a[j4 * 4 + e], __fmul_rn(a_scale, wsv[e])), bv[e]);
-          }
+          for (int j = 0; j < EPI_CH; j++) v[j] = (uint32_t)a[j];
         } else {
+          // An accumulator of 2^22 or more anywhere in the warp's chunk sends the whole chunk through the binary64
+          // product (the cheap int -> float conversion and the binary32 product are only exact below that).
+          int big = 0;
 #pragma unroll
-          for (int j4 = 0; j4 < 8; j4++) {
-            const float4 w4 = cs4[j4], b4 = cb4[j4];
-            const float wsv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+          for (int j = 0; j < EPI_CH; j++) big |= (abs(a[j]) >> 22);
+          const bool wide = __any_sync(0xffffffffu, big != 0);
+          const float4* cs4 = reinterpret_cast<const float4*>(cs + c * EPI_CH);
+          const float4* cb4 = reinterpret_cast<const float4*>(cb + c * EPI_CH);
+          // The loops below contain no branch at all (the choice between the two conversions is made once per
+          // chunk, a missing bias was staged as -0.0, which is the identity of the rounded addition), so the
+          // independent element chains of a thread can be interleaved freely.
+          if (!wide) {
 #pragma unroll
-            for (int e = 0; e < 4; e++) y[j4 * 4 + e] = __fadd_rn(scale_acc_wide(a[j4 * 4 + e], __fmul_rn(a_scale, wsv[e])), bv[e]);
-          }
-        }
-        if (ACT_T == ACT_GELU_SIGMOID || ACT_T == ACT_SILU) {
-          // Where the fast form is not valid (large negative argument, -Inf) the argument itself is kept: no valid
-          // result of these activations is below -0.3, so the bit test further down recognises such an element again.
+            for (int j4 = 0; j4 < EPI_CH / 4; j4++) {
+              const float4 w4 = cs4[j4], b4 = cb4[j4];
+              const float wsv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-          for (int j0 = 0; j0 < 32; j0 += 8) {
-            float v8[8], r8[8];
-#pragma unroll
-            for (int e = 0; e < 8; e++) { v8[e] = y[j0 + e]; r8[e] = v8[e]; vkey = max(vkey, __float_as_uint(v8[e])); }
-            apply_sigmoid_act_x8<ACT_T>(r8, tbl);
-#pragma unroll
-            for (int e = 0; e < 8; e++) y[j0 + e] = (__float_as_uint(v8[e]) > kGeneral) ? v8[e] : r8[e];
-          }
-        } else if (ACT_T != ACT_NONE) {
-#pragma unroll
-          for (int j = 0; j < 32; j++) y[j] = apply_act_fast<ACT_T>(y[j], tbl);
-        }
-        if (kGeneral != 0xFFFFFFFFu) {
-          if (__any_sync(0xffffffffu, vkey > kGeneral)) {  // rare
-#pragma unroll
-            for (int j = 0; j < 32; j++)
-              if (__float_as_uint(y[j]) > kGeneral) y[j] = apply_act_general(y[j], ACT_T, tbl);
-          }
-        }
-        if (OUT_T == OUT_F32) {
-          float* o = p.out_f32 + m * p.N + nb;
-          if (!row_ok) {
-          } else if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+              for (int e = 0; e < 4; e++) y[j4 * 4 + e] = __fadd_rn(scale_acc_small(a[j4 * 4 + e], __fmul_rn(a_scale, wsv[e])), bv[e]);
+            }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; j++)
-              if (nb + j < p.N) o[j] = y[j];
+            for (int j4 = 0; j4 < EPI_CH / 4; j4++) {
+              const float4 w4 = cs4[j4], b4 = cb4[j4];
+              const float wsv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+              for (int e = 0; e < 4; e++) y[j4 * 4 + e] = __fadd_rn(scale_acc_wide(a[j4 * 4 + e], __fmul_rn(a_scale, wsv[e])), bv[e]);
+            }
+          }
+          if (ACT_T == ACT_GELU_SIGMOID || ACT_T == ACT_SILU) {
+#pragma unroll
+            for (int j0 = 0; j0 < EPI_CH; j0 += 8) {
+              float r8[8];
+#pragma unroll
+              for (int e = 0; e < 8; e++) r8[e] = y[j0 + e];
+              apply_sigmoid_act_x8<ACT_T>(r8, tbl);
+#pragma unroll
+              for (int e = 0; e < 8; e++) y[j0 + e] = r8[e];
+            }
+          } else if (ACT_T != ACT_NONE) {
+#pragma unroll
+            for (int j = 0; j < EPI_CH; j++) y[j] = apply_act_fast<ACT_T>(y[j], tbl);
+          }
+#pragma unroll
+          for (int j = 0; j < EPI_CH; j++) v[j] = __float_as_uint(y[j]);
+        }
+        if (OUT_T != OUT_Q8) {
+          if (bulk_store) {
+            // The previous store of this warp must have finished reading the tile before it is overwritten.
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < EPI_CH / 4; q++) {
+              const uint32_t dst = stage_row + ((((uint32_t)q) ^ stage_xor) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[q * 4]), "r"(v[q * 4 + 1]), "r"(v[q * 4 + 2]),
+                           "r"(v[q * 4 + 3])
+                           : "memory");
+            }
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0 && mw < p.M) tma_store_2d(&tmC, stage_addr, (int)nb, (int)mw);
+          } else {
+            uint32_t* o = (OUT_T == OUT_I32 ? reinterpret_cast<uint32_t*>(p.out_i32) : reinterpret_cast<uint32_t*>(p.out_f32)) + m * p.N + nb;
+            if (!row_ok) {
+            } else if (full) {
+#pragma unroll
+              for (int j = 0; j < EPI_CH; j += 4) *reinterpret_cast<uint4*>(o + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < EPI_CH; j++)
+                if (nb + j < p.N) o[j] = v[j];
+            }
           }
         } else {
           int8_t* o = p.out_q + m * p.N + nb;
-          uint32_t words[8];
+          uint32_t words[EPI_CH / 4];
           QuantGuard guard;
 #pragma unroll
-          for (int j4 = 0; j4 < 8; j4++)
+          for (int j4 = 0; j4 < EPI_CH / 4; j4++)
             words[j4] = pack_codes(quantize_fast(y[j4 * 4 + 0], p.q_inv, guard), quantize_fast(y[j4 * 4 + 1], p.q_inv, guard),
                                    quantize_fast(y[j4 * 4 + 2], p.q_inv, guard), quantize_fast(y[j4 * 4 + 3], p.q_inv, guard));
           if (p.q_exact || guard.unsafe(127.49f)) {  // rare: a tie, a value beyond the clamp, NaN
 #pragma unroll
-            for (int j4 = 0; j4 < 8; j4++)
+            for (int j4 = 0; j4 < EPI_CH / 4; j4++)
               words[j4] = pack_codes(quantize_exact_c(y[j4 * 4 + 0], p.q_scale, 0.0f, -128.0f, 127.0f),
                                      quantize_exact_c(y[j4 * 4 + 1], p.q_scale, 0.0f, -128.0f, 127.0f),
                                      quantize_exact_c(y[j4 * 4 + 2], p.q_scale, 0.0f, -128.0f, 127.0f),
@@ -501,12 +530,11 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           if (!row_ok) {
           } else if (full) {
-#pragma unroll
-            for (int j4 = 0; j4 < 8; j4 += 4)
-              *reinterpret_cast<uint4*>(o + j4 * 4) = make_uint4(words[j4], words[j4 + 1], words[j4 + 2], words[j4 + 3]);
+            static_assert(EPI_CH == 16, "one 16-byte store per row and chunk");
+            *reinterpret_cast<uint4*>(o) = make_uint4(words[0], words[1], words[2], words[3]);
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; j++)
+            for (int j = 0; j < EPI_CH; j++)
               if (nb + j < p.N) o[j] = (int8_t)((words[j >> 2] >> (8 * (j & 3))) & 0xff);
           }
         }
@@ -519,6 +547,8 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         else mbar_arrive_cluster(map_to_cta(smem_u32(&misc->tmem_empty[slot]), 0));
       }
     }
+    // Bulk stores still in flight read this CTA's shared memory: they finish before the CTA may leave.
+    if (bulk_store && lane == 0) tma_store_wait_all();
   }
 
   // ---------------------------------------------------------------- teardown
@@ -576,6 +606,23 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t K, i
   return 0;
 }
 
+// Row-major output [M, N] of 4-byte values; box = EPI_CH columns by 32 rows (one epilogue warp's chunk), 64-byte swizzle.
+int make_output_map(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, bool is_float) {
+  EncodeTiledFn enc = get_encode_fn();
+  B200Q_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t gstride[1] = {(cuuint64_t)N * 4};
+  cuuint32_t box[2] = {(cuuint32_t)EPI_CH, 32};
+  cuuint32_t estr[2] = {1, 1};
+  static_assert(EPI_CH * 4 == 64, "the staging tile is laid out for the 64-byte swizzle");
+  CUresult r = enc(tm, is_float ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_INT32, 2, ptr, gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200Q_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (output M=%lld N=%lld)", (int)r, (long long)M,
+                (long long)N);
+  return 0;
+}
+
 }  // namespace
 
 bool gemm_umma_supported(const void* A, const void* W, int64_t M, int64_t N, int64_t K) {
@@ -590,10 +637,17 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   B200Q_REQUIRE(gemm_umma_supported(A, W_nk, M, N, K), "tensor-core int8 gemm needs K %% 16 == 0 and 16-byte aligned operands");
   // CTA pairs pay off once there are enough 256-row tiles to go round; small or forced cases use single CTAs.
   const int ncta = ctx->gemm_variant == 2 ? 1 : ctx->gemm_variant == 3 ? 2 : (M >= 1024 ? 2 : 1);
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
   if (int e = make_tensor_map(&tmA, A, M, K, BM)) return e;
   if (int e = make_tensor_map(&tmB, W_nk, N, K, BN / ncta)) return e;
   GemmParams p;
+  void* out4 = out_f32 ? static_cast<void*>(out_f32) : static_cast<void*>(out_i32);
+  p.tma_store = out4 != nullptr && N % 4 == 0 && (reinterpret_cast<uintptr_t>(out4) & 15u) == 0;
+  if (p.tma_store) {
+    if (int e = make_output_map(&tmC, out4, M, N, out_f32 != nullptr)) return e;
+  } else {
+    memset(&tmC, 0, sizeof(tmC));   // never dereferenced
+  }
   p.M = M; p.N = N; p.K = K;
   p.a_scales = a_scales; p.w_scales = w_scales; p.bias = bias; p.act = act;
   p.out_f32 = out_f32; p.out_i32 = out_i32; p.out_q = out_q;
@@ -609,7 +663,7 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   const int64_t num_tiles = ((M + BM * ncta - 1) / (BM * ncta)) * ((N + BN - 1) / BN);
   const int64_t units = ctx->sm_count / ncta;   // CTAs (or CTA pairs) that can be resident at once
   const unsigned grid = (unsigned)((num_tiles < units ? num_tiles : units) * ncta);
-  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const GemmParams);
+  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
 #define B200Q_ROW(A) \
   {{gemm_i8_umma_kernel<A, OUT_F32, 1>, gemm_i8_umma_kernel<A, OUT_F32, 2>}, {gemm_i8_umma_kernel<A, OUT_Q8, 1>, gemm_i8_umma_kernel<A, OUT_Q8, 2>}}
   static const KernelFn table[5][2][2] = {B200Q_ROW(ACT_NONE), B200Q_ROW(ACT_RELU), B200Q_ROW(ACT_GELU_SIGMOID),
@@ -638,7 +692,7 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B200Q_CHECK_CUDA(cudaLaunchKernelEx(&cfg, fn, tmA, tmB, p));
+  B200Q_CHECK_CUDA(cudaLaunchKernelEx(&cfg, fn, tmA, tmB, tmC, p));
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;

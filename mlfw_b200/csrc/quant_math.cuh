@@ -103,47 +103,60 @@ __device__ __forceinline__ float scale_acc_small(int acc, float sv) {
 __device__ __forceinline__ float scale_acc_wide(int acc, float sv) { return __double2float_rn((double)acc * (double)sv); }
 
 // ---------------------------------------------------------------------------
-// exp for a binary32 argument, evaluated in binary64 (error < 2 ulp of
+// exp for a binary32 argument, evaluated in binary64 (error about 1.2 ulp of
 // binary64) and rounded once to binary32 == Math.fround(Math.exp(x)) except
 // when the binary64 value lies within ~2^-52 of a binary32 rounding boundary
-// (probability about 1e-8 per evaluation).
-//   x = k*ln2/64 + r,  exp(x) = 2^(k>>6) * 2^((k&63)/64) * exp(r),  |r| <= ln2/128
-// `tbl` holds 2^(j/64), j = 0..63 (shared memory; see fill_exp2_table).
+// (probability of the order of 1e-9 per evaluation).
+//   x = k*ln2/256 + r,  exp(x) = 2^(k>>8) * 2^((k&255)/256) * exp(r),  |r| <= ln2/512 (1 + 2^-7)
+// Few binary64 operations on purpose (eight): they issue at a fraction of the binary32 rate.
+//  * k comes from a binary32 multiply-add (1.5*2^23 trick); it may be the second nearest integer when
+//    x*256/ln2 is within 0.002 of a half, which only widens |r| by that much;
+//  * k becomes a binary64 number through the bit pattern of 2^52 + 2^31 + k (exact);
+//  * exp(r) - 1 = r + r^2 (1/2 + r/6 + r^2/24) (truncation error < 4e-17), folded into the table
+//    product with one FMA: T + T*q;
+//  * 2^(k>>8) is added to the exponent field (the product is in [0.99, 2.01), |k>>8| < 160).
+// `tbl` holds 2^(j/256), j = 0..255, correctly rounded (shared memory; see fill_exp2_table).
 // ---------------------------------------------------------------------------
+constexpr int EXP2_TABLE_SIZE = 256;
+static __device__ const unsigned long long kExp2TableBits[EXP2_TABLE_SIZE] = {
+#include "exp2_table.inc"
+};
+
 __device__ __forceinline__ void fill_exp2_table(double* tbl, int tid, int nthreads) {
-  for (int j = tid; j < 64; j += nthreads) tbl[j] = exp2((double)j * (1.0 / 64.0));
+  for (int j = tid; j < EXP2_TABLE_SIZE; j += nthreads) tbl[j] = __longlong_as_double((long long)kExp2TableBits[j]);
 }
 
-__device__ __forceinline__ double exp_f64(double xd, const double* tbl) {
-  const double INV = 92.33248261689366;               // 64 / ln 2
-  const double MAGIC = 6755399441055744.0;            // 1.5 * 2^52: adding it rounds to an integer
-  // ln2/64 = HI + LO; HI keeps 32 significant bits so that kd * HI is exact for |kd| < 2^21.
-  const double HI = __longlong_as_double(0x3F862E42FEE00000LL);
-  const double LO = __longlong_as_double(0x3D8A39EF35793C76LL);
-  double t = fma(xd, INV, MAGIC);
-  int k = __double2loint(t);
-  double kd = t - MAGIC;
-  double r = fma(-kd, HI, xd);
-  r = fma(-kd, LO, r);
-  // exp(r) = 1 + r + r^2/2 + ... + r^6/720, evaluated in Estrin form: the dependent chain is 4 operations long
-  // instead of 6, which matters because the epilogue runs few warps.
+constexpr float EXP_INV_F = 369.329930467574632f;               // 256 / ln 2
+constexpr float EXP_MAGIC_F = 12582912.0f;                      // 1.5 * 2^23
+constexpr int EXP_MAGIC_BITS = 0x4B400000;
+constexpr double EXP_MAGIC_D = 4503601774854144.0;              // 2^52 + 2^31
+// ln2/256 = HI + LO; HI keeps 32 significant bits so that k * HI is exact for |k| < 2^21.
+#define B200Q_EXP_HI __longlong_as_double(0x3F662E42FEE00000LL)
+#define B200Q_EXP_LO __longlong_as_double(0x3D6A39EF35793C76LL)
+
+// exp(x) rounded to binary32 for x in [-160, 128] (any other finite x or NaN gives an unspecified value, no trap).
+__device__ __forceinline__ float exp_core(float x, const double* tbl) {
+  const float tf = __fmaf_rn(x, EXP_INV_F, EXP_MAGIC_F);
+  const int k = __float_as_int(tf) - EXP_MAGIC_BITS;
+  const double xd = (double)x;
+  const double kd = __hiloint2double(0x43300000, k ^ (int)0x80000000) - EXP_MAGIC_D;
+  double r = fma(-kd, B200Q_EXP_HI, xd);
+  r = fma(-kd, B200Q_EXP_LO, r);
   const double r2 = r * r;
-  const double a = fma(r, 1.0, 1.0);                        // 1 + r
-  const double b = fma(r, 1.0 / 6.0, 0.5);                  // 1/2 + r/6
-  const double c = fma(r, 1.0 / 120.0, 1.0 / 24.0);         // 1/24 + r/120
-  const double d = fma(r2, 1.0 / 720.0, c);                 // 1/24 + r/120 + r^2/720
-  const double hi = fma(r2 * r2, d, 0.0);
-  const double p = fma(r2, b, a) + hi;
-  double m = tbl[k & 63] * p;
-  int e = k >> 6;                                      // |e| < 256: 2^e is a normal binary64
-  return m * __hiloint2double((e + 1023) << 20, 0);
+  double b = fma(r, 1.0 / 6.0, 0.5);
+  b = fma(r2, 1.0 / 24.0, b);
+  const double q = fma(r2, b, r);
+  const double t = tbl[k & (EXP2_TABLE_SIZE - 1)];
+  const double m = fma(t, q, t);
+  const int hi = __double2hiint(m) + ((k >> 8) << 20);
+  return __double2float_rn(__hiloint2double(hi, __double2loint(m)));
 }
 
 // Branch-free: the argument is clamped to [-160, 128] (exp(128) rounds to +Inf in
 // binary32, exp(-160) to 0), NaN is restored by a select.
 __device__ __forceinline__ float exp_fround(float x, const double* tbl) {
   const float xc = fminf(fmaxf(x, -160.0f), 128.0f);
-  const float r = __double2float_rn(exp_f64((double)xc, tbl));
+  const float r = exp_core(xc, tbl);
   return (x != x) ? x : r;
 }
 
@@ -151,33 +164,37 @@ __device__ __forceinline__ float exp_fround(float x, const double* tbl) {
 // Branch-free activations for the fused epilogue.  A thread evaluates 32 of
 // them back to back; anything with a call or a data-dependent branch in it
 // (the IEEE division, range checks) would stop the compiler from interleaving
-// those 32 independent chains.  The sigmoid-based ones are exact (same value as
-// sigmoid_ref) for every argument except z < -87 (exp(-z) overflows towards the
-// binary32 range limit) and -Inf, where they return an unspecified finite value or
-// NaN: callers test `needs_general_act` and redo those elements with apply_act.
-// NaN and +Inf arguments give the reference's result without help.
+// those 32 independent chains.  The sigmoid-based ones give the same value as
+// sigmoid_ref for EVERY argument: large negative arguments (exp(-z) near or
+// beyond the binary32 range, where 1/(1+e) is subnormal or zero), +-Inf and NaN
+// go through the same instructions as ordinary ones.
 // ---------------------------------------------------------------------------
 
-// Correctly rounded 1/d for finite d in [1, 2^126], branch-free: hardware approximation, one
-// Newton step (faithful result), then the better of the result and its neighbour on the side the
-// exact residual 1 - d*y points to (the residual of a faithful y is exactly representable).
+// Correctly rounded 1/d for d in [1, +Inf], branch-free.  The hardware approximation and one Newton step
+// run on d * 2^-32 (so that neither d up to 2^128 nor its reciprocal leaves the normal range) and give a
+// faithful value; scaling back by 2^-32 is exact for a normal result and rounds onto the subnormal grid
+// otherwise, still within one grid step of 1/d.  The answer is then the better of that value and its
+// neighbour on the side the residual 1 - d*y points to (residuals come from one FMA, subnormal operands
+// included).  d = +Inf gives 0 by a final select.
 __device__ __forceinline__ float rcp_rn_ge1(float d) {
-  float y;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(d));
-  const float e = __fmaf_rn(-d, y, 1.0f);
-  y = __fmaf_rn(y, e, y);
+  const float ds = __fmul_rn(d, 2.3283064365386963e-10f);   // 2^-32
+  float g;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g) : "f"(ds));
+  g = __fmaf_rn(g, __fmaf_rn(-ds, g, 1.0f), g);
+  const float y = __fmul_rn(g, 2.3283064365386963e-10f);
   const float r = __fmaf_rn(-d, y, 1.0f);
   const float yc = __int_as_float(__float_as_int(y) + (r > 0.0f ? 1 : -1));
   const float rc = __fmaf_rn(-d, yc, 1.0f);
-  return (fabsf(rc) < fabsf(r)) ? yc : y;
+  const float best = (fabsf(rc) < fabsf(r)) ? yc : y;
+  return (d == __int_as_float(0x7f800000)) ? 0.0f : best;
 }
 
-// sigmoid(z) for z >= -87 (exact), NaN (NaN) and +Inf (1).
+// sigmoid(z) = 1 / (1 + exp(-z)) with one rounding per operation, any z.  -z is clamped to [-100, 128]:
+// exp(-100) already vanishes against 1, exp(128) is +Inf like exp of anything larger; a NaN argument
+// becomes -100 here and is restored by the caller's final product with the NaN pre-activation.
 __device__ __forceinline__ float sigmoid_fast(float z, const double* tbl) {
-  float zc;
-  asm("min.NaN.f32 %0, %1, %2;" : "=f"(zc) : "f"(z), "f"(100.0f));  // exp(-100) already vanishes against 1; NaN is kept
-  const float e = __double2float_rn(exp_f64((double)(-zc), tbl));
-  return rcp_rn_ge1(__fadd_rn(1.0f, e));
+  const float xc = fminf(fmaxf(-z, -100.0f), 128.0f);
+  return rcp_rn_ge1(__fadd_rn(1.0f, exp_core(xc, tbl)));
 }
 
 // fround(1.702 * y) with 1.702 a binary64 constant, in binary32 arithmetic: 1.702 = CH + CL + (< 2^-53),
@@ -217,44 +234,41 @@ __device__ __forceinline__ float apply_act_fast(float y, const double* tbl) {
 template <int ACT_T>
 __device__ __forceinline__ void apply_sigmoid_act_x8(float (&y)[8], const double* tbl) {
   constexpr int W = 8;
-  float z[W];
-  double x[W], t[W], kd[W], r[W], r2[W], a[W], b[W], c[W], p[W], m[W];
+  float z[W], xf[W];
+  double x[W], kd[W], r[W], r2[W], b[W], q[W], m[W];
   int k[W];
-  float e[W], d[W], g[W], res[W], cand[W], rc[W];
+  float e[W], d[W], ds[W], g[W], res[W], cand[W], rc[W];
 #pragma unroll
   for (int i = 0; i < W; i++) z[i] = (ACT_T == ACT_GELU_SIGMOID) ? mul_1702(y[i]) : y[i];
 #pragma unroll
-  for (int i = 0; i < W; i++) {
-    float zc;
-    asm("min.NaN.f32 %0, %1, %2;" : "=f"(zc) : "f"(z[i]), "f"(100.0f));
-    x[i] = (double)(-zc);
-  }
-  const double INV = 92.33248261689366, MAGIC = 6755399441055744.0;
-  const double HI = __longlong_as_double(0x3F862E42FEE00000LL), LO = __longlong_as_double(0x3D8A39EF35793C76LL);
+  for (int i = 0; i < W; i++) xf[i] = fminf(fmaxf(-z[i], -100.0f), 128.0f);
 #pragma unroll
-  for (int i = 0; i < W; i++) t[i] = fma(x[i], INV, MAGIC);
+  for (int i = 0; i < W; i++) k[i] = __float_as_int(__fmaf_rn(xf[i], EXP_INV_F, EXP_MAGIC_F)) - EXP_MAGIC_BITS;
 #pragma unroll
-  for (int i = 0; i < W; i++) { k[i] = __double2loint(t[i]); kd[i] = t[i] - MAGIC; }
+  for (int i = 0; i < W; i++) { x[i] = (double)xf[i]; kd[i] = __hiloint2double(0x43300000, k[i] ^ (int)0x80000000) - EXP_MAGIC_D; }
 #pragma unroll
-  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], HI, x[i]);
+  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], B200Q_EXP_HI, x[i]);
 #pragma unroll
-  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], LO, r[i]);
+  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], B200Q_EXP_LO, r[i]);
 #pragma unroll
-  for (int i = 0; i < W; i++) { r2[i] = r[i] * r[i]; a[i] = fma(r[i], 1.0, 1.0); b[i] = fma(r[i], 1.0 / 6.0, 0.5); c[i] = fma(r[i], 1.0 / 120.0, 1.0 / 24.0); }
+  for (int i = 0; i < W; i++) { r2[i] = r[i] * r[i]; b[i] = fma(r[i], 1.0 / 6.0, 0.5); }
 #pragma unroll
-  for (int i = 0; i < W; i++) { c[i] = fma(r2[i], 1.0 / 720.0, c[i]); a[i] = fma(r2[i], b[i], a[i]); b[i] = r2[i] * r2[i]; }
+  for (int i = 0; i < W; i++) b[i] = fma(r2[i], 1.0 / 24.0, b[i]);
 #pragma unroll
-  for (int i = 0; i < W; i++) p[i] = a[i] + fma(b[i], c[i], 0.0);
+  for (int i = 0; i < W; i++) { q[i] = fma(r2[i], b[i], r[i]); m[i] = tbl[k[i] & (EXP2_TABLE_SIZE - 1)]; }
 #pragma unroll
-  for (int i = 0; i < W; i++) m[i] = tbl[k[i] & 63] * p[i];
+  for (int i = 0; i < W; i++) m[i] = fma(m[i], q[i], m[i]);
 #pragma unroll
-  for (int i = 0; i < W; i++) e[i] = __double2float_rn(m[i] * __hiloint2double(((k[i] >> 6) + 1023) << 20, 0));
+  for (int i = 0; i < W; i++)
+    e[i] = __double2float_rn(__hiloint2double(__double2hiint(m[i]) + ((k[i] >> 8) << 20), __double2loint(m[i])));
 #pragma unroll
-  for (int i = 0; i < W; i++) d[i] = __fadd_rn(1.0f, e[i]);
+  for (int i = 0; i < W; i++) { d[i] = __fadd_rn(1.0f, e[i]); ds[i] = __fmul_rn(d[i], 2.3283064365386963e-10f); }
 #pragma unroll
-  for (int i = 0; i < W; i++) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g[i]) : "f"(d[i]));
+  for (int i = 0; i < W; i++) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g[i]) : "f"(ds[i]));
 #pragma unroll
-  for (int i = 0; i < W; i++) g[i] = __fmaf_rn(g[i], __fmaf_rn(-d[i], g[i], 1.0f), g[i]);
+  for (int i = 0; i < W; i++) g[i] = __fmaf_rn(g[i], __fmaf_rn(-ds[i], g[i], 1.0f), g[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++) g[i] = __fmul_rn(g[i], 2.3283064365386963e-10f);
 #pragma unroll
   for (int i = 0; i < W; i++) res[i] = __fmaf_rn(-d[i], g[i], 1.0f);
 #pragma unroll
@@ -262,17 +276,10 @@ __device__ __forceinline__ void apply_sigmoid_act_x8(float (&y)[8], const double
 #pragma unroll
   for (int i = 0; i < W; i++) rc[i] = __fmaf_rn(-d[i], cand[i], 1.0f);
 #pragma unroll
-  for (int i = 0; i < W; i++) y[i] = __fmul_rn(y[i], (fabsf(rc[i]) < fabsf(res[i])) ? cand[i] : g[i]);
-}
-
-// True when apply_act_fast<ACT_T>(y) may differ from apply_act(y): compares the bit pattern as an
-// unsigned number, which orders the negative floats by magnitude and puts them (and -Inf, -NaN)
-// above every positive one.
-template <int ACT_T>
-__device__ __forceinline__ constexpr unsigned act_general_threshold() {
-  return ACT_T == ACT_GELU_SIGMOID ? 0xC24C0000u /* -51.0f: 1.702 * 51 < 87 */
-         : ACT_T == ACT_SILU       ? 0xC2AE0000u /* -87.0f */
-                                   : 0xFFFFFFFFu;
+  for (int i = 0; i < W; i++) {
+    const float best = (fabsf(rc[i]) < fabsf(res[i])) ? cand[i] : g[i];
+    y[i] = __fmul_rn(y[i], (d[i] == __int_as_float(0x7f800000)) ? 0.0f : best);
+  }
 }
 
 // sigmoid as the reference decomposes it (src/compiler/passes/decompose/
@@ -312,9 +319,6 @@ __device__ __forceinline__ float apply_act(float y, int act, const double* tbl) 
       return y;
   }
 }
-
-// Out-of-line copy for rarely taken paths (keeps the hot loops small).
-static __device__ __noinline__ float apply_act_general(float y, int act, const double* tbl) { return apply_act(y, act, tbl); }
 
 template <int ACT_T>
 __device__ __forceinline__ float apply_act_t(float y, const double* tbl) {
