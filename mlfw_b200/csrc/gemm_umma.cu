@@ -76,7 +76,7 @@ struct GemmParams {
   double q_scale;
   float q_inv;
   int q_exact;
-  int tma_store;          // 4-byte outputs leave through bulk-tensor stores (needs N % 4 == 0 and a 16-byte aligned base)
+  int tma_store;          // results leave through bulk-tensor stores (needs a 16-byte aligned base and row pitch)
   uint32_t* status;
   unsigned long long wait_limit_ns;
 };
@@ -391,7 +391,10 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // 16-byte pieces of 32 different lines per instruction (measured: those stores, not the arithmetic, bounded
     // the epilogue).  The tile is laid out for the tensor map's 64-byte swizzle: the 16-byte piece q of row r sits
     // at piece q ^ ((r >> 1) & 3), which also keeps the eight lanes of a store phase on distinct banks.
-    const bool bulk_store = OUT_T != OUT_Q8 && p.tma_store != 0;
+    // int8 output uses the same tile as 32 rows x 64 codes: four chunks fill it, then one store writes 64-byte segments.
+    const bool bulk_store = p.tma_store != 0;
+    bool q8_pending = false;   // warp-uniform: the tile holds chunks that have not been stored yet
+    int64_t q8_col = 0;        // first column of the group of four chunks in the tile
     const uint32_t stage_addr = smem_u32(out_stage + ew * OUT_STAGE_BYTES);
     const uint32_t stage_row = stage_addr + (uint32_t)lane * (EPI_CH * 4);
     const uint32_t stage_xor = (uint32_t)((lane >> 1) & 3);
@@ -528,9 +531,26 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                      quantize_exact_c(y[j4 * 4 + 2], p.q_scale, 0.0f, -128.0f, 127.0f),
                                      quantize_exact_c(y[j4 * 4 + 3], p.q_scale, 0.0f, -128.0f, 127.0f));
           }
-          if (!row_ok) {
+          static_assert(EPI_CH == 16, "one 16-byte piece per row and chunk");
+          if (bulk_store) {
+            const uint32_t piece = (uint32_t)(c & 3);
+            if (piece == 0) {  // a new group: the store of the previous one must have read the tile
+              if (lane == 0) tma_store_wait_read();
+              __syncwarp();
+              q8_col = nb;
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + ((piece ^ stage_xor) << 4)), "r"(words[0]),
+                         "r"(words[1]), "r"(words[2]), "r"(words[3])
+                         : "memory");
+            q8_pending = true;
+            if (piece == 3) {
+              fence_async_shared();
+              __syncwarp();
+              if (lane == 0 && mw < p.M) tma_store_2d(&tmC, stage_addr, (int)q8_col, (int)mw);
+              q8_pending = false;
+            }
+          } else if (!row_ok) {
           } else if (full) {
-            static_assert(EPI_CH == 16, "one 16-byte store per row and chunk");
             *reinterpret_cast<uint4*>(o) = make_uint4(words[0], words[1], words[2], words[3]);
           } else {
 #pragma unroll
@@ -538,6 +558,12 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               if (nb + j < p.N) o[j] = (int8_t)((words[j >> 2] >> (8 * (j & 3))) & 0xff);
           }
         }
+      }
+      if (OUT_T == OUT_Q8 && q8_pending) {  // N ended inside a group of four chunks: columns past N are clipped
+        fence_async_shared();
+        __syncwarp();
+        if (lane == 0 && mw < p.M) tma_store_2d(&tmC, stage_addr, (int)q8_col, (int)mw);
+        q8_pending = false;
       }
       // this warp is done reading the accumulator: hand the slot back to the MMA issuer
       tc_fence_before();
@@ -606,18 +632,18 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t K, i
   return 0;
 }
 
-// Row-major output [M, N] of 4-byte values; box = EPI_CH columns by 32 rows (one epilogue warp's chunk), 64-byte swizzle.
-int make_output_map(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, bool is_float) {
+// Row-major output [M, N]; the box is what one epilogue warp stores at a time: 32 rows by 64 bytes (EPI_CH 4-byte
+// values, or 64 int8 codes), 64-byte swizzle.
+int make_output_map(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, CUtensorMapDataType dtype, int elem_bytes) {
   EncodeTiledFn enc = get_encode_fn();
   B200Q_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)M};
-  cuuint64_t gstride[1] = {(cuuint64_t)N * 4};
-  cuuint32_t box[2] = {(cuuint32_t)EPI_CH, 32};
+  cuuint64_t gstride[1] = {(cuuint64_t)N * (cuuint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(64 / elem_bytes), 32};
   cuuint32_t estr[2] = {1, 1};
   static_assert(EPI_CH * 4 == 64, "the staging tile is laid out for the 64-byte swizzle");
-  CUresult r = enc(tm, is_float ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_INT32, 2, ptr, gdim, gstride, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = enc(tm, dtype, 2, ptr, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   B200Q_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (output M=%lld N=%lld)", (int)r, (long long)M,
                 (long long)N);
   return 0;
@@ -641,10 +667,13 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   if (int e = make_tensor_map(&tmA, A, M, K, BM)) return e;
   if (int e = make_tensor_map(&tmB, W_nk, N, K, BN / ncta)) return e;
   GemmParams p;
-  void* out4 = out_f32 ? static_cast<void*>(out_f32) : static_cast<void*>(out_i32);
-  p.tma_store = out4 != nullptr && N % 4 == 0 && (reinterpret_cast<uintptr_t>(out4) & 15u) == 0;
+  // Bulk-tensor stores need a 16-byte aligned base and row pitch.
+  void* out_any = out_f32 ? static_cast<void*>(out_f32) : out_i32 ? static_cast<void*>(out_i32) : static_cast<void*>(out_q);
+  const int out_elem = out_q ? 1 : 4;
+  p.tma_store = out_any != nullptr && (N * out_elem) % 16 == 0 && (reinterpret_cast<uintptr_t>(out_any) & 15u) == 0;
   if (p.tma_store) {
-    if (int e = make_output_map(&tmC, out4, M, N, out_f32 != nullptr)) return e;
+    const CUtensorMapDataType dt = out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : out_i32 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    if (int e = make_output_map(&tmC, out_any, M, N, dt, out_elem)) return e;
   } else {
     memset(&tmC, 0, sizeof(tmC));   // never dereferenced
   }
