@@ -217,17 +217,48 @@ __device__ __forceinline__ float fmax3n(float a, float b, float c) {
   return r;
 }
 
-// Leanest form of the fast code, for finite elements of an ordinary per-token row: the code, and the running maximum
-// of |t - rint t| (how close any element came to a tie).
-__device__ __forceinline__ uint32_t pack4_fast_lean(const float4& v, float inv, float& far) {
-  const float M = 12582912.0f;
-  const float t0 = __fmul_rn(v.x, inv), t1 = __fmul_rn(v.y, inv), t2 = __fmul_rn(v.z, inv), t3 = __fmul_rn(v.w, inv);
-  const float u0 = __fadd_rn(t0, M), u1 = __fadd_rn(t1, M), u2 = __fadd_rn(t2, M), u3 = __fadd_rn(t3, M);
-  const float d0 = __fsub_rn(t0, __fsub_rn(u0, M)), d1 = __fsub_rn(t1, __fsub_rn(u1, M));
-  const float d2 = __fsub_rn(t2, __fsub_rn(u2, M)), d3 = __fsub_rn(t3, __fsub_rn(u3, M));
+// Packed binary32 arithmetic of sm_100: one instruction works on a pair of floats held in a 64-bit register
+// (round to nearest even per element, no flush to zero: the same values as the scalar instructions).
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_sub(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// Leanest form of the fast code, for finite elements of an ordinary per-token row: the four codes, and the running
+// maximum of |t - rint t| (how close any element came to a tie).  t = x * inv, u = t + 1.5*2^23 (the rounding), and
+// the code is the low byte of u's bit pattern (|t| <= 127.00002 here, so no clamp; 0x4B400000 + code keeps the code's
+// two's complement in its low byte).  Packed arithmetic: eight floating-point instructions per four elements.
+// `inv2` and `magic2` hold the reciprocal scale and 1.5*2^23 in both halves.
+__device__ __forceinline__ uint32_t pack4_fast_lean(const float4& v, uint64_t inv2, uint64_t magic2, float& far) {
+  const uint64_t t01 = f2_mul(f2_pack(v.x, v.y), inv2), t23 = f2_mul(f2_pack(v.z, v.w), inv2);
+  const uint64_t u01 = f2_add(t01, magic2), u23 = f2_add(t23, magic2);
+  const uint64_t d01 = f2_sub(t01, f2_sub(u01, magic2)), d23 = f2_sub(t23, f2_sub(u23, magic2));
+  float d0, d1, d2, d3, u0, u1, u2, u3;
+  f2_unpack(d01, d0, d1);
+  f2_unpack(d23, d2, d3);
+  f2_unpack(u01, u0, u1);
+  f2_unpack(u23, u2, u3);
   far = fmaxf(fmaxf(fmaxf(far, fabsf(d0)), fmaxf(fabsf(d1), fabsf(d2))), fabsf(d3));
-  return pack_codes(__float_as_int(u0) - 0x4B400000, __float_as_int(u1) - 0x4B400000, __float_as_int(u2) - 0x4B400000,
-                    __float_as_int(u3) - 0x4B400000);
+  const uint32_t lo = __byte_perm(__float_as_uint(u0), __float_as_uint(u1), 0x0040);   // bytes: u0.b0, u1.b0
+  const uint32_t hi = __byte_perm(__float_as_uint(u2), __float_as_uint(u3), 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
 }
 
 // tie tracking only: in a per-token row |x * (127/absmax)| <= 127 (1 + 2^-23) by construction, so the magnitude
@@ -306,6 +337,7 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
         uint32_t spins = 0;
         while (turns[s] != turn) {
+          __nanosleep(32);
           if ((++spins & 31u) == 0u) {
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
             if (*abort_flag || t1 - t0 > limit_ns) { *abort_flag = 1; ok = false; break; }
@@ -373,6 +405,7 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
           // element for the code, one more to keep the largest |t - rint t| of the 16 elements a lane handles per turn.
           // Every element is finite here and |t| <= 127 (1 + 2^-23), so a tie is the only thing that can go wrong:
           // first a cheap test with the worst-case margin (|t| = 127.5), and only if that trips the per-element one.
+          const uint64_t inv2 = f2_pack(inv, inv), magic2 = f2_pack(12582912.0f, 12582912.0f);
           for (int c0 = lane; c0 < K4; c0 += 128) {
             float4 v[4];
             uint32_t w[4];
@@ -380,7 +413,7 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
 #pragma unroll
             for (int j = 0; j < 4; j++) v[j] = xr[c0 + 32 * j];
 #pragma unroll
-            for (int j = 0; j < 4; j++) w[j] = pack4_fast_lean(v[j], inv, far);
+            for (int j = 0; j < 4; j++) w[j] = pack4_fast_lean(v[j], inv2, magic2, far);
             if (far >= 0.49993920f) {                                   // 0.5 - 127.5 * 2^-21
               int tie = 0;
 #pragma unroll
