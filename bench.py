@@ -42,6 +42,7 @@ WORKLOADS = {
     "small_2048x4096x4096_none": (2048, 4096, 4096, "none"),
 }
 DEFAULT_WORKLOAD = "c3_gemm_8192x4096x4096_gelu_tanh"
+C4_WORKLOAD = "c4_gpt_block_d768_h12_ff3072_32x512"
 C5_WORKLOAD = "c5_stack_4096x8192x28672_silu"       # 4 linears 8192 -> 28672 -> 8192 -> 28672 -> 8192, M 4096 in total
 C2_SHAPE = (16384, 4096)          # standalone quantize -> dequantize round trip
 CPU_SAMPLE_ROWS = 64              # rows of M the CPU arm processes per step (rows are independent)
@@ -222,6 +223,61 @@ def run_c5(args, ctx, dist, rank, world, local_rank, barrier, max_over_ranks):
             "tops": ops_total / (ms * 1e-3) / 1e12, "gpu_launches": ctx.launch_count() - launches0}
 
 
+def run_c4(args, ctx, rank, world, barrier, max_over_ranks):
+    """Config 4: one pre-norm GPT block (d 768, 12 heads, ff 3072) over 32 x 512 tokens per GPU, from token ids to the
+    block's output: embedding, LayerNorm + quantize, four int8 linears, causal attention, residual adds."""
+    from mlfw_b200.block import GPTBlock, random_block_params
+    D, H, FF, B, S, V = 768, 12, 3072, 32, 512, 50257
+    M = B * S
+    rng = np.random.default_rng(40 + rank)
+    blk = GPTBlock(ctx, D, H, FF, random_block_params(D, FF, seed=4))
+    table = ctx.to_device((rng.standard_normal((V, D)) * 0.02).astype(np.float32))
+    tokens = [ctx.to_device(rng.integers(0, V, size=M).astype(np.int32)) for _ in range(2)]
+    h, out = ctx.empty((M, D), np.float32), ctx.empty((M, D), np.float32)
+
+    def step(i):
+        ctx.embedding_f32(table, tokens[i % 2], None, M, D, V, S, h)
+        blk.forward(h, B, S, out)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    ctx.sync()
+    ctx.check_status()
+    ctx.profile_enable(True)
+    ctx.profile_reset()
+    launches0 = ctx.launch_count()
+    barrier()
+    ctx.sync()
+    ctx.timer_start()
+    for i in range(args.steps):
+        step(i)
+    ms = ctx.timer_stop()
+    ctx.sync()
+    barrier()
+    prof = ctx.profile_read()
+    ctx.profile_enable(False)
+    ctx.check_status()
+    ms = max_over_ranks(ms) / args.steps
+    gemm_ops = 2.0 * M * D * (3 * D + D + FF + FF)
+    attn_flops = 4.0 * B * H * S * (S + 64) / 2 * 64       # causal: about half of the S x S scores, QK^T and PV
+    per_kernel = {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps} for k, v in prof.items() if v[1]}
+    pk = peaks()
+    ln_ms = prof.get("layernorm_quantize", (0.0, 0))[0] / args.steps
+    sd_ms = prof.get("sdpa", (0.0, 0))[0] / args.steps
+    return {"metric": "int8_linear_tokens_per_s", "value": world * M / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x int8 -> int32 linears; f32 LayerNorm, attention, residuals", "data": "synthetic",
+            "config": {"workload": C4_WORKLOAD, "tokens_per_gpu": M, "d_model": D, "heads": H, "ff": FF, "batch": B, "seq": S,
+                       "activation": "gelu_sigmoid", "parallelism": f"batch-sharded x{world}, weights replicated, no collective"},
+            "tops": world * gemm_ops / (ms * 1e-3) / 1e12, "kernels": per_kernel,
+            "roofline_layernorm_quantize": {"bound": "hbm", "achieved": (2 * 5.0 + 8.0) * M * D / (ln_ms * 1e-3) / 1e9 if ln_ms else None,
+                                            "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                            "note": "two launches per step: 5 B/element (read x, write codes) and 13 B/element (read x and the residual, write their sum and the codes)"},
+            "roofline_sdpa": {"bound": "fp32 CUDA cores", "achieved": attn_flops / (sd_ms * 1e-3) / 1e12 if sd_ms else None, "unit": "TFLOP/s",
+                              "note": "binary32 FMA on CUDA cores (the 1e-5 bar rules out tf32 tensor-core products)"},
+            "gpu_launches": ctx.launch_count() - launches0}
+
+
 def run_reference_arm(args, rank, world):
     """The reference's CPU path (its C++ restatement: no JavaScript engine exists here) on all host cores."""
     if rank != 0:
@@ -282,7 +338,7 @@ def _run():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [C5_WORKLOAD])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [C4_WORKLOAD, C5_WORKLOAD])
     ap.add_argument("--mode", default="mshard", choices=["mshard", "nshard"],
                     help="config 5 only: rows split over the GPUs (no collective) or output channels split (NCCL all-gather)")
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
@@ -324,6 +380,12 @@ def _run():
         return line
     if args.workload == C5_WORKLOAD:
         line = run_c5(args, ctx, dist, rank, world, local_rank, barrier, max_over_ranks)
+        ctx.close()
+        if dist is not None:
+            dist.destroy_process_group()
+        return line if rank == 0 else None
+    if args.workload == C4_WORKLOAD:
+        line = run_c4(args, ctx, rank, world, barrier, max_over_ranks)
         ctx.close()
         if dist is not None:
             dist.destroy_process_group()
@@ -401,6 +463,16 @@ def _run():
     }
 
     if not args.no_extras:
+        # -------------------------------------------------------- spread of single steps (each one timed and synchronised by itself)
+        samples = []
+        for i in range(50):
+            ctx.timer_start()
+            step(i)
+            samples.append(ctx.timer_stop())
+        q1, med, q3 = (float(v) for v in np.percentile(samples, [25, 50, 75]))
+        line["step_samples_ms"] = {"n": len(samples), "median": med, "iqr": q3 - q1, "min": float(min(samples)), "max": float(max(samples)),
+                                   "note": "CUDA events around single synchronised steps; the headline times all steps back to back"}
+
         # -------------------------------------------------------- end to end (host buffers)
         hx = ctx.pinned((M, K), np.float32)
         hy = ctx.pinned((M, N), np.float32)
@@ -431,13 +503,18 @@ def _run():
             for _ in range(reps):
                 ref_out, _, _, _ = oracle.linear(xs[0][:rows], W, ws, bias, act)
             dt_cpu = (time.perf_counter() - t0) / reps
+            rows1 = min(8, M)      # the reference's own execution model is one thread
+            t0 = time.perf_counter()
+            oracle.linear(xs[0][:rows1], W, ws, bias, act, threads=1)
+            dt_cpu1 = time.perf_counter() - t0
             step(0)
             ctx.sync()
             got = douts[0].download()[:rows]
             err = float(np.abs(got.astype(np.float64) - ref_out).max() / np.abs(ref_out).max())
             line["cpu_baseline"] = {"value": rows / dt_cpu, "unit": "tokens/s", "cores": cores, "kind": "port",
                                     "sample": f"first {rows} of {M} rows, all of N and K, {reps} repetitions; C++ restatement of the "
-                                              "reference's CPU path with OpenMP", "gpu_vs_cpu_max_err_over_absmax": err}
+                                              "reference's CPU path with OpenMP", "gpu_vs_cpu_max_err_over_absmax": err,
+                                    "single_core": {"value": rows1 / dt_cpu1, "unit": "tokens/s", "sample": f"first {rows1} rows, one thread, one repetition"}}
 
     ctx.close()
     if dist is not None:

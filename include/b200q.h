@@ -172,6 +172,31 @@ int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_n
 int b200q_quant_roundtrip_host(b200q_ctx* ctx, const float* x_host, int64_t M, int64_t K, int8_t* q_host, float* scales_host,
                                float* y_host);
 
+/* ---- f32 pieces of a transformer block around the int8 linears ("next" components of the hot path) ----
+ * Floating-point kernels: results agree with the reference's CPU target to 1e-5 of the output's largest magnitude
+ * (its own summation order depends on which lowering runs); the int8 codes b200q_layernorm_quantize emits are the exact
+ * per-token quantization of the binary32 values it would store as y_out. */
+
+/* out[m, :] = table[tokens[m], :] (+ pos_table[m % S, :] when pos_table is not null).  table f32 [V, D], tokens int32 [M],
+ * pos_table f32 [S, D], out f32 [M, D]; D a multiple of 4.  src/nn/functional/embedding.ts:6-11; positions as in
+ * tests/_utils/gpt2_model.js:11-13.  A token outside [0, V) gives a zero row and sets a status bit. */
+int b200q_embedding_f32(b200q_ctx* ctx, const float* table, const int32_t* tokens, const float* pos_table, int64_t M, int64_t D,
+                        int64_t V, int64_t S, float* out);
+/* out = a + b elementwise (one rounding per element: ops.add), n a multiple of 4.  src/nn/modules/transformer.ts:144-152. */
+int b200q_add_f32(b200q_ctx* ctx, const float* a, const float* b, int64_t n, float* out);
+/* LayerNorm over the last axis of x [M, D] (+ residual [M, D] first, when given), then per-token int8 quantization of
+ * the result for the linear that follows.  gamma, beta f32 [D]; D a multiple of 4, at most 2048.  Outputs, each
+ * optional (null): sum_out = x + residual [M, D]; y_out = the normalised rows f32 [M, D]; q_out int8 [M, D] with
+ * scales_out f32 [M].  src/compiler/passes/decompose/decomposition_pass.ts:232-260 followed by
+ * src/compiler/ir/graph/quantization_types.ts:299-317, 118-130 along axis 0. */
+int b200q_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* residual, const float* gamma, const float* beta,
+                             float eps, int64_t M, int64_t D, float* sum_out, float* y_out, int8_t* q_out, float* scales_out);
+/* softmax(q k^T * scale + mask) v per (batch, head) in binary32; head dimension 64.  Row (b, s) of head h starts at
+ * base + (b*S + s)*ld + h*64 for q, k, v and out (so the projections are read where the linears wrote them);
+ * causal != 0 masks keys j > i.  src/nn/functional/attention.ts:42-74. */
+int b200q_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                   int64_t B, int64_t H, int64_t S, int64_t head_dim, float scale, int causal, float* out, int64_t ld_out);
+
 #ifdef __cplusplus
 }
 #endif

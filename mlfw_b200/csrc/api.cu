@@ -502,6 +502,38 @@ int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_n
   return 0;
 }
 
+int b200q_embedding_f32(b200q_ctx* ctx, const float* table, const int32_t* tokens, const float* pos_table, int64_t M, int64_t D,
+                        int64_t V, int64_t S, float* out) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(M >= 0 && D >= 0 && V >= 0 && S >= 0, "b200q_embedding_f32: negative dimension");
+  B200Q_REQUIRE(M == 0 || D == 0 || (table && tokens && out), "b200q_embedding_f32: null pointer");
+  return launch_embedding(ctx, table, tokens, pos_table, M, D, V, S, out);
+}
+
+int b200q_add_f32(b200q_ctx* ctx, const float* a, const float* b, int64_t n, float* out) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(n >= 0, "b200q_add_f32: negative length");
+  B200Q_REQUIRE(n == 0 || (a && b && out), "b200q_add_f32: null pointer");
+  return launch_add_f32(ctx, a, b, n, out);
+}
+
+int b200q_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* residual, const float* gamma, const float* beta,
+                             float eps, int64_t M, int64_t D, float* sum_out, float* y_out, int8_t* q_out, float* scales_out) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(M >= 0 && D >= 0, "b200q_layernorm_quantize: negative dimension");
+  B200Q_REQUIRE(M == 0 || (x && gamma && beta), "b200q_layernorm_quantize: null pointer");
+  B200Q_REQUIRE(sum_out == nullptr || residual != nullptr, "b200q_layernorm_quantize: sum_out needs a residual");
+  return launch_layernorm_quantize(ctx, x, residual, gamma, beta, eps, M, D, sum_out, y_out, q_out, scales_out);
+}
+
+int b200q_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                   int64_t B, int64_t H, int64_t S, int64_t head_dim, float scale, int causal, float* out, int64_t ld_out) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(B >= 0 && H >= 0 && S >= 0, "b200q_sdpa_f32: negative dimension");
+  B200Q_REQUIRE(B == 0 || H == 0 || S == 0 || (q && k && v && out), "b200q_sdpa_f32: null pointer");
+  return launch_sdpa_f32(ctx, q, k, v, ld_q, ld_k, ld_v, B, H, S, head_dim, scale, causal, out, ld_out);
+}
+
 int b200q_quant_roundtrip_host(b200q_ctx* ctx, const float* x_host, int64_t M, int64_t K, int8_t* q_host, float* scales_host,
                                float* y_host) {
   if (use_device(ctx)) return 1;

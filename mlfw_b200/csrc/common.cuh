@@ -36,11 +36,12 @@ enum StatusBits : uint32_t {
   STATUS_EPI_WAIT_TIMEOUT = 1u << 2,   // epilogue gave up waiting for an accumulator
   STATUS_BAD_TMEM_ALLOC = 1u << 3,     // tensor-memory allocation returned an unexpected address
   STATUS_QUANT_WAIT_TIMEOUT = 1u << 4, // the staged quantize kernel gave up waiting for a row chunk or a free slot
+  STATUS_BAD_INDEX = 1u << 5,          // an embedding lookup met a token outside its table (the row is zero)
 };
 
 // Kernel families timed separately when profiling is on (b200q_profile_*).
 enum KernelKind : int { KK_QUANT_TOKEN = 0, KK_DEQUANT_TOKEN, KK_QUANT_STATIC, KK_DEQUANT_STATIC, KK_WEIGHTS, KK_GEMM_UMMA,
-                        KK_GEMM_SIMT, KK_EPILOGUE, KK_COUNT };
+                        KK_GEMM_SIMT, KK_EPILOGUE, KK_EMBEDDING, KK_LAYERNORM, KK_SDPA, KK_ADD, KK_COUNT };
 constexpr int PROFILE_RING = 256;
 constexpr int HOST_CHUNKS = 16;   // most pieces a host-buffer call is split into
 
@@ -70,6 +71,7 @@ struct b200q_ctx {
   int gemm_variant = 0;                  // 0 auto, 1 CUDA-core kernel only, 2 tensor cores with one CTA per tile, 3 with CTA pairs
   int quant_variant = 0;                 // 0 auto (rows staged in shared memory when they fit), 1 register-resident kernel only
   bool quant_staged_ready = false;
+  bool sdpa_ready = false;               // the attention kernel's shared-memory size has been raised
   uint32_t umma_ready_mask = 0;          // tensor-core kernel variants whose shared-memory attribute is set on this device
   uint64_t launches = 0;                 // kernels launched through this context
   // per-kernel CUDA-event timing (off by default): a ring of event pairs, folded into the sums when it wraps or is read

@@ -34,4 +34,14 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
                         const float* a_scales, const float* w_scales, const float* bias, int act, float* out_f32,
                         int32_t* out_i32, int8_t* out_q, double q_scale);
 
+// f32 pieces of a transformer block (block_kernels.cu).
+int launch_embedding(b200q_ctx* ctx, const float* table, const int32_t* tokens, const float* pos_table, int64_t M, int64_t D,
+                     int64_t V, int64_t S, float* out);
+int launch_add_f32(b200q_ctx* ctx, const float* a, const float* b, int64_t n, float* out);
+// y = LayerNorm(x [+ residual]); any of sum_out (x + residual), y_out (f32 result), q_out + scales_out (per-token codes) may be null.
+int launch_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* residual, const float* gamma, const float* beta,
+                              float eps, int64_t M, int64_t D, float* sum_out, float* y_out, int8_t* q_out, float* scales_out);
+int launch_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                    int64_t B, int64_t H, int64_t S, int64_t Dh, float scale, int causal, float* out, int64_t ld_o);
+
 }  // namespace b200q

@@ -167,7 +167,7 @@ class Context:
         return ms.value
 
     KERNEL_KINDS = ("quantize_per_token", "dequantize_per_token", "quantize_static", "dequantize_static", "weights",
-                    "gemm_tensor_core", "gemm_cuda_core", "tail")
+                    "gemm_tensor_core", "gemm_cuda_core", "tail", "embedding", "layernorm_quantize", "sdpa", "add")
 
     def profile_enable(self, on: bool = True):
         check(self.lib.b200q_profile_enable(self.handle, int(on)), "b200q_profile_enable")
@@ -252,6 +252,23 @@ class Context:
     def linear_f32_host(self, x_host, W_nk, w_scales, bias, act, M, N, K, out_host):
         check(self.lib.b200q_linear_f32_host(self.handle, _ptr(x_host), _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act], M, N,
                                              K, _ptr(out_host)), "b200q_linear_f32_host")
+
+    # ---- f32 pieces of a transformer block
+    def embedding_f32(self, table, tokens, pos_table, M, D, V, S, out):
+        check(self.lib.b200q_embedding_f32(self.handle, _ptr(table), _ptr(tokens), _ptr(pos_table), M, D, V, S, _ptr(out)),
+              "b200q_embedding_f32")
+
+    def add_f32(self, a, b, n, out):
+        check(self.lib.b200q_add_f32(self.handle, _ptr(a), _ptr(b), n, _ptr(out)), "b200q_add_f32")
+
+    def layernorm_quantize(self, x, residual, gamma, beta, eps, M, D, sum_out=None, y_out=None, q_out=None, scales_out=None):
+        check(self.lib.b200q_layernorm_quantize(self.handle, _ptr(x), _ptr(residual), _ptr(gamma), _ptr(beta), float(eps), M, D,
+                                                _ptr(sum_out), _ptr(y_out), _ptr(q_out), _ptr(scales_out)),
+              "b200q_layernorm_quantize")
+
+    def sdpa_f32(self, q, k, v, ld_q, ld_k, ld_v, B, H, S, head_dim, scale, causal, out, ld_out):
+        check(self.lib.b200q_sdpa_f32(self.handle, _ptr(q), _ptr(k), _ptr(v), ld_q, ld_k, ld_v, B, H, S, head_dim, float(scale),
+                                      int(bool(causal)), _ptr(out), ld_out), "b200q_sdpa_f32")
 
     def quant_roundtrip_host(self, x_host, M, K, q_host, scales_host, y_host):
         check(self.lib.b200q_quant_roundtrip_host(self.handle, _ptr(x_host), M, K, _ptr(q_host), _ptr(scales_host),

@@ -242,6 +242,35 @@ def activation(y, act) -> np.ndarray:
     return out
 
 
+def layer_norm(x, gamma, beta, eps=1e-5, add=None, want_sum=False):
+    """LayerNorm over the last axis of x [M, D] (+ add first); returns y (and x + add when want_sum)."""
+    x = _f32(x)
+    M, D = x.shape
+    a = _f32(add) if add is not None else None
+    y = np.empty((M, D), np.float32)
+    s = np.empty((M, D), np.float32) if want_sum else None
+    lib().orc_layer_norm(_p(x), _p(a), _p(_f32(gamma)), _p(_f32(beta)), C.c_double(eps), C.c_int64(M), C.c_int64(D), _p(s), _p(y))
+    return (y, s) if want_sum else y
+
+
+def sdpa(q, k, v, B, H, S, Dh, scale, causal=True, rows=None):
+    """Attention over q, k, v given as [B*S, H*Dh] arrays (row (b, s), columns of head h at h*Dh).  Returns the same
+    layout, or, with ``rows`` (flattened (b*H + h)*S + i indices), a dense [len(rows), Dh] array of just those rows."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    ld = H * Dh
+    assert q.shape == (B * S, ld) and k.shape == q.shape and v.shape == q.shape
+    if rows is None:
+        out = np.zeros((B * S, ld), np.float32)
+        lib().orc_sdpa(_p(q), _p(k), _p(v), C.c_int64(ld), C.c_int64(ld), C.c_int64(ld), C.c_int64(B), C.c_int64(H), C.c_int64(S),
+                       C.c_int64(Dh), C.c_double(scale), C.c_int(int(causal)), None, C.c_int64(0), _p(out), C.c_int64(ld))
+        return out
+    r = np.ascontiguousarray(rows, np.int64)
+    out = np.zeros((r.size, Dh), np.float32)
+    lib().orc_sdpa(_p(q), _p(k), _p(v), C.c_int64(ld), C.c_int64(ld), C.c_int64(ld), C.c_int64(B), C.c_int64(H), C.c_int64(S),
+                   C.c_int64(Dh), C.c_double(scale), C.c_int(int(causal)), _p(r), C.c_int64(r.size), _p(out), C.c_int64(Dh))
+    return out
+
+
 def minmax_observe(batches):
     mn, mx = C.c_double(float("inf")), C.c_double(float("-inf"))
     for b in batches:

@@ -22,6 +22,8 @@
 //   src/compiler/passes/quantization/quantization_pass.ts:390-459  per-channel tail
 //   src/compiler/passes/decompose/decomposition_pass.ts:197-230    sigmoid, gelu(1.702), silu
 //   src/compiler/analysis/calibration.ts           min/max observer
+//   src/compiler/passes/decompose/decomposition_pass.ts:156-174, 232-260 and src/nn/functional/attention.ts:42-74
+//                                                   softmax, layer_norm, attention (tolerance only)
 //   src/util/random.ts, src/tensor/factory/creation_ops.ts, src/nn/init.ts  seeded data
 #include <cmath>
 #include <cstdint>
@@ -446,6 +448,94 @@ void orc_minmax_observe(const float* x, int64_t n, double* mn, double* mx) {
     if (v > b) b = v;
   }
   *mn = a; *mx = b;
+}
+
+// ---------------------------------------------------------------------------
+// f32 pieces of a transformer block (the "next" components around the int8 linears).
+// Each operation of the decomposed graph is a binary32 operation (binary64 then
+// Math.fround); reductions add the elements in index order.  The reference can lower
+// these through more than one path (fused or not, different loop nests), and its
+// tests only bound them by tolerances, so the device results are compared with this
+// restatement to a tolerance as well -- never bit for bit.
+// ---------------------------------------------------------------------------
+
+// layer_norm: src/compiler/passes/decompose/decomposition_pass.ts:232-260
+//   mean = reduce_mean(x); c = x - mean; var = reduce_mean(c * c); r = rsqrt(var + eps);
+//   y = c * r * gamma + beta.  `add` (optional) is summed to x first (ops.add of the residual stream).
+void orc_layer_norm(const float* x, const float* add, const float* gamma, const float* beta, double eps, int64_t M, int64_t D,
+                    float* sum_out, float* y) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; m++) {
+    std::vector<float> row((size_t)D);
+    for (int64_t d = 0; d < D; d++) {
+      float v = x[m * D + d];
+      if (add) v = (float)((double)v + (double)add[m * D + d]);
+      row[(size_t)d] = v;
+      if (sum_out) sum_out[m * D + d] = v;
+    }
+    float acc = 0.0f;
+    for (int64_t d = 0; d < D; d++) acc = (float)((double)acc + (double)row[(size_t)d]);
+    const float mean = (float)((double)acc / (double)D);
+    float acc2 = 0.0f;
+    for (int64_t d = 0; d < D; d++) {
+      const float c = (float)((double)row[(size_t)d] - (double)mean);
+      row[(size_t)d] = c;
+      acc2 = (float)((double)acc2 + (double)(float)((double)c * (double)c));
+    }
+    const float var = (float)((double)acc2 / (double)D);
+    const float ve = (float)((double)var + (double)(float)eps);
+    const float r = (float)(1.0 / std::sqrt((double)ve));
+    for (int64_t d = 0; d < D; d++) {
+      const float n = (float)((double)row[(size_t)d] * (double)r);
+      const float g = (float)((double)n * (double)gamma[d]);
+      y[m * D + d] = (float)((double)g + (double)beta[d]);
+    }
+  }
+}
+
+// scaled_dot_product_attention: src/nn/functional/attention.ts:42-74 with the softmax of
+// src/compiler/passes/decompose/decomposition_pass.ts:156-174.
+//   scores = matmul(q, k^T) * scale (+ mask: 0 where j <= i + S - L, else -Infinity);
+//   w = exp(scores - max) / sum(exp(scores - max)); out = matmul(w, v).
+// Row (b, s) of head h starts at base + (b*S + s)*ld + h*Dh.  `rows` (optional) lists the flattened
+// (b*H + h)*S + i query rows to compute, so that large cases can be spot checked.
+void orc_sdpa(const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t B, int64_t H,
+              int64_t S, int64_t Dh, double scale, int causal, const int64_t* rows, int64_t nrows, float* out, int64_t ld_o) {
+  const int64_t total = rows ? nrows : B * H * S;
+  const float scale32 = (float)scale;
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t t = 0; t < total; t++) {
+    const int64_t flat = rows ? rows[t] : t;
+    const int64_t i = flat % S, bh = flat / S, h = bh % H, b = bh / H;
+    const float* qi = q + (b * S + i) * ld_q + h * Dh;
+    std::vector<float> sc((size_t)S);
+    float mx = -std::numeric_limits<float>::infinity();
+    for (int64_t j = 0; j < S; j++) {
+      const float* kj = k + (b * S + j) * ld_k + h * Dh;
+      float acc = 0.0f;
+      for (int64_t d = 0; d < Dh; d++) acc = (float)((double)acc + (double)(float)((double)qi[d] * (double)kj[d]));
+      float sv = (float)((double)acc * (double)scale32);
+      if (causal) sv = (float)((double)sv + (j <= i ? 0.0 : -std::numeric_limits<double>::infinity()));
+      sc[(size_t)j] = sv;
+      if (sv > mx) mx = sv;
+    }
+    float sum = 0.0f;
+    for (int64_t j = 0; j < S; j++) {
+      const float e = (float)std::exp((double)(float)((double)sc[(size_t)j] - (double)mx));
+      sc[(size_t)j] = e;
+      sum = (float)((double)sum + (double)e);
+    }
+    // rows == null writes in place of the inputs' layout; a row list writes densely: row t of [nrows, Dh]
+    float* o = rows ? out + t * ld_o : out + (b * S + i) * ld_o + h * Dh;
+    for (int64_t d = 0; d < Dh; d++) {
+      float acc = 0.0f;
+      for (int64_t j = 0; j < S; j++) {
+        const float w = (float)((double)sc[(size_t)j] / (double)sum);
+        acc = (float)((double)acc + (double)(float)((double)w * (double)v[(b * S + j) * ld_v + h * Dh + d]));
+      }
+      o[d] = acc;
+    }
+  }
 }
 
 double orc_js_round(double x) { return js_round(x); }
