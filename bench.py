@@ -284,6 +284,8 @@ def run_reference_arm(args, rank, world):
         return None
     import oracle
     oracle.build()
+    if args.workload not in WORKLOADS:   # the block and stack workloads have no CPU arm of their own: time the headline linear
+        args.workload = DEFAULT_WORKLOAD
     M, K, N, act, xs, W, ws, bias = make_case(args.workload, 0)
     rows = min(CPU_SAMPLE_ROWS, M)
     x = xs[0][:rows]

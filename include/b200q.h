@@ -172,6 +172,14 @@ int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_n
 int b200q_quant_roundtrip_host(b200q_ctx* ctx, const float* x_host, int64_t M, int64_t K, int8_t* q_host, float* scales_host,
                                float* y_host);
 
+/* ---- calibration on the device (min/max mode) ----
+ * A calibration observer keeps the running minimum and maximum of every value of an observed tensor, NaN ignored
+ * (ValueObserver.update, src/compiler/analysis/calibration.ts:24-30).  `state` is two floats of device memory:
+ * state[0] = min, state[1] = max; b200q_observer_reset sets them to +Inf / -Inf ("nothing seen").  The quantization
+ * parameters follow on the host from QuantizationParams.fromRange (quantization_types.ts:248-263). */
+int b200q_observer_reset(b200q_ctx* ctx, float* state);
+int b200q_observe_minmax(b200q_ctx* ctx, const float* x, int64_t n, float* state);
+
 /* ---- f32 pieces of a transformer block around the int8 linears ("next" components of the hot path) ----
  * Floating-point kernels: results agree with the reference's CPU target to 1e-5 of the output's largest magnitude
  * (its own summation order depends on which lowering runs); the int8 codes b200q_layernorm_quantize emits are the exact
@@ -194,6 +202,9 @@ int b200q_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* residu
 /* softmax(q k^T * scale + mask) v per (batch, head) in binary32; head dimension 64.  Row (b, s) of head h starts at
  * base + (b*S + s)*ld + h*64 for q, k, v and out (so the projections are read where the linears wrote them);
  * causal != 0 masks keys j > i.  src/nn/functional/attention.ts:42-74. */
+/* 0 (default): b200q_sdpa_f32 runs on the CUDA cores with binary32 FMAs; 1: warp-level tensor-core instructions with
+ * three-way tf32 products (binary32 accuracy to ~2^-22; measured slightly slower on B200).  Both meet the 1e-5 bar. */
+int b200q_set_sdpa_variant(b200q_ctx* ctx, int variant);
 int b200q_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v,
                    int64_t B, int64_t H, int64_t S, int64_t head_dim, float scale, int causal, float* out, int64_t ld_out);
 

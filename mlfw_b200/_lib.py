@@ -57,9 +57,12 @@ PROTOTYPES = {
     "b200q_linear_f32_noalloc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_linear_f32_host": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_quant_roundtrip_host": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "b200q_observer_reset": (c_int, [c_vp, c_vp]),
+    "b200q_observe_minmax": (c_int, [c_vp, c_vp, c_i64, c_vp]),
     "b200q_embedding_f32": (c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp]),
     "b200q_add_f32": (c_int, [c_vp, c_vp, c_vp, c_i64, c_vp]),
     "b200q_layernorm_quantize": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, C.c_float, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
+    "b200q_set_sdpa_variant": (c_int, [c_vp, c_int]),
     "b200q_sdpa_f32": (c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_float, c_int, c_vp, c_i64]),
 }
 

@@ -6,6 +6,7 @@
 #include <new>
 
 #include "../../include/b200q.h"
+#include <limits>
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -169,6 +170,13 @@ int b200q_set_wait_limit(b200q_ctx* ctx, double seconds) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
   B200Q_REQUIRE(seconds > 0 && seconds <= 60, "b200q_set_wait_limit: %g s is outside (0, 60]", seconds);
   ctx->wait_limit_s = seconds;
+  return 0;
+}
+
+int b200q_set_sdpa_variant(b200q_ctx* ctx, int variant) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_REQUIRE(variant == 0 || variant == 1, "b200q_set_sdpa_variant: unknown variant %d", variant);
+  ctx->sdpa_variant = variant;
   return 0;
 }
 
@@ -500,6 +508,22 @@ int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_n
   B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream_d2h));
   B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
   return 0;
+}
+
+int b200q_observer_reset(b200q_ctx* ctx, float* state) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(state != nullptr, "b200q_observer_reset: null pointer");
+  const float init[2] = {std::numeric_limits<float>::infinity(), -std::numeric_limits<float>::infinity()};
+  B200Q_CHECK_CUDA(cudaMemcpyAsync(state, init, sizeof(init), cudaMemcpyHostToDevice, ctx->stream));
+  B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));   // `init` lives on this stack frame
+  return 0;
+}
+
+int b200q_observe_minmax(b200q_ctx* ctx, const float* x, int64_t n, float* state) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(n >= 0, "b200q_observe_minmax: negative length");
+  B200Q_REQUIRE(state != nullptr && (n == 0 || x != nullptr), "b200q_observe_minmax: null pointer");
+  return launch_minmax_observe(ctx, x, n, state);
 }
 
 int b200q_embedding_f32(b200q_ctx* ctx, const float* table, const int32_t* tokens, const float* pos_table, int64_t M, int64_t D,

@@ -71,7 +71,8 @@ struct b200q_ctx {
   int gemm_variant = 0;                  // 0 auto, 1 CUDA-core kernel only, 2 tensor cores with one CTA per tile, 3 with CTA pairs
   int quant_variant = 0;                 // 0 auto (rows staged in shared memory when they fit), 1 register-resident kernel only
   bool quant_staged_ready = false;
-  bool sdpa_ready = false;               // the attention kernel's shared-memory size has been raised
+  bool sdpa_ready = false;               // the attention kernels' shared-memory sizes have been raised
+  int sdpa_variant = 0;                  // 0: CUDA-core binary32 FMA; 1: mma.sync with three-way tf32 products
   uint32_t umma_ready_mask = 0;          // tensor-core kernel variants whose shared-memory attribute is set on this device
   uint64_t launches = 0;                 // kernels launched through this context
   // per-kernel CUDA-event timing (off by default): a ring of event pairs, folded into the sums when it wraps or is read

@@ -213,7 +213,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Waits for the thread's tensor-memory loads.  The loaded registers are in/out operands so that no use of them can
+// be scheduled ahead of the wait (the load itself only starts the transfer).
+__device__ __forceinline__ void tmem_ld_wait16(int (&v)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+                 "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               :
+               : "memory");
+}
 
 // Bulk-tensor store of one staging tile (shared -> global), tracked by the issuing thread's bulk async-group.
 // Rows and columns of the box that lie outside the tensor are not written.
@@ -427,13 +435,18 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const uint32_t taddr = tmem_base + slot * BN + (uint32_t)col0 + ((uint32_t)(quarter * 32) << 16);
       constexpr int NCH = EPI_COLS / EPI_CH;
+      // The accumulator columns of the next chunk travel from tensor memory while the current chunk is computed.
+      int a_next[EPI_CH];
+      if (n0 < p.N) tmem_ld16(taddr, a_next);
 #pragma unroll 1
       for (int c = 0; c < NCH; c++) {
         const int64_t nb = n0 + c * EPI_CH;
         if (nb >= p.N) break;  // uniform across the warp
         int a[EPI_CH];
-        tmem_ld16(taddr + (uint32_t)(c * EPI_CH), a);
-        tmem_ld_wait();
+        tmem_ld_wait16(a_next);
+#pragma unroll
+        for (int j = 0; j < EPI_CH; j++) a[j] = a_next[j];
+        if (c + 1 < NCH && nb + EPI_CH < p.N) tmem_ld16(taddr + (uint32_t)((c + 1) * EPI_CH), a_next);
         // No lane may leave this iteration early: the tensor-memory loads, the votes and the staging protocol below
         // are warp-collective.  Rows past M compute on whatever the accumulator holds and store nothing.
         const bool full = vec_ok && (nb + EPI_CH <= p.N);

@@ -21,6 +21,8 @@ int launch_row_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64
 int launch_quantize_rows_with_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld_in, const float* mn,
                                     const float* mx, int8_t* q, int64_t ld_out, float* scales, int qmin, int qmax);
 int launch_transpose_i8(b200q_ctx* ctx, const int8_t* src_kn, int64_t K, int64_t N, int8_t* dst_nk);
+// Running min / max of a calibration observer: state[0] = min, state[1] = max (device memory, +Inf / -Inf when new).
+int launch_minmax_observe(b200q_ctx* ctx, const float* x, int64_t n, float* state);
 
 int launch_gemm_i8_simt(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,
                         int32_t* C);

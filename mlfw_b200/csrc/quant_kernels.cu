@@ -762,6 +762,52 @@ __global__ void __launch_bounds__(256) quantize_rows_with_range_kernel(const flo
   }
 }
 
+// ---------------------------------------------------------------------------
+// Calibration observer (min/max mode): running minimum and maximum of every value shown to it, NaN ignored,
+// exactly as ValueObserver.update compares (src/compiler/analysis/calibration.ts:24-30).  state[0] = min, state[1] = max.
+// Float atomics through the integer ordering of the bit patterns: non-negative floats order like signed integers,
+// negative ones like unsigned integers in reverse.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void atomic_max_f32(float* addr, float v) {
+  v = __fadd_rn(v, 0.0f);   // -0.0 becomes +0.0: as a bit pattern -0.0 is the smallest integer, not a zero
+  if (v >= 0.0f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+__device__ __forceinline__ void atomic_min_f32(float* addr, float v) {
+  v = __fadd_rn(v, 0.0f);
+  if (v >= 0.0f) atomicMin(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+__global__ void __launch_bounds__(256) minmax_observe_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ state) {
+  __shared__ float s_mn[8], s_mx[8];
+  float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+  const int64_t n4 = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 ? n / 4 : 0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x, first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (int64_t i = first; i < n4; i += stride) {
+    const float4 v = __ldcs(reinterpret_cast<const float4*>(x) + i);
+    mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));   // fminf / fmaxf drop NaN operands
+    mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
+  }
+  for (int64_t i = n4 * 4 + first; i < n; i += stride) {
+    mn = fminf(mn, x[i]);
+    mx = fmaxf(mx, x[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if ((threadIdx.x & 31) == 0) { s_mn[threadIdx.x >> 5] = mn; s_mx[threadIdx.x >> 5] = mx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; w++) { mn = fminf(mn, s_mn[w]); mx = fmaxf(mx, s_mx[w]); }
+    // +Inf / -Inf are the "nothing seen" values: they leave the state alone
+    if (mn != __int_as_float(0x7f800000)) atomic_min_f32(state, mn);
+    if (mx != __int_as_float(0xff800000)) atomic_max_f32(state + 1, mx);
+  }
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -926,6 +972,19 @@ int launch_transpose_i8(b200q_ctx* ctx, const int8_t* src_kn, int64_t K, int64_t
   if (N == 0 || K == 0) return 0;
   dim3 grid((unsigned)((K + 31) / 32), (unsigned)((N + 31) / 32));
   transpose_i8_kernel<<<grid, 256, 0, ctx->stream>>>(src_kn, K, N, dst_nk);
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_minmax_observe(b200q_ctx* ctx, const float* x, int64_t n, float* state) {
+  ProfScope prof(ctx, KK_QUANT_STATIC);
+  if (n == 0) return 0;
+  int64_t blocks = (n / 4 + 255) / 256;
+  const int64_t cap = (int64_t)ctx->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  minmax_observe_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, n, state);
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -253,6 +253,13 @@ class Context:
         check(self.lib.b200q_linear_f32_host(self.handle, _ptr(x_host), _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act], M, N,
                                              K, _ptr(out_host)), "b200q_linear_f32_host")
 
+    # ---- calibration observers
+    def observer_reset(self, state):
+        check(self.lib.b200q_observer_reset(self.handle, _ptr(state)), "b200q_observer_reset")
+
+    def observe_minmax(self, x, n, state):
+        check(self.lib.b200q_observe_minmax(self.handle, _ptr(x), n, _ptr(state)), "b200q_observe_minmax")
+
     # ---- f32 pieces of a transformer block
     def embedding_f32(self, table, tokens, pos_table, M, D, V, S, out):
         check(self.lib.b200q_embedding_f32(self.handle, _ptr(table), _ptr(tokens), _ptr(pos_table), M, D, V, S, _ptr(out)),
@@ -265,6 +272,10 @@ class Context:
         check(self.lib.b200q_layernorm_quantize(self.handle, _ptr(x), _ptr(residual), _ptr(gamma), _ptr(beta), float(eps), M, D,
                                                 _ptr(sum_out), _ptr(y_out), _ptr(q_out), _ptr(scales_out)),
               "b200q_layernorm_quantize")
+
+    def set_sdpa_variant(self, variant: int):
+        """0: CUDA-core binary32 FMA (default); 1: warp-level tensor-core instructions with three-way tf32 products."""
+        check(self.lib.b200q_set_sdpa_variant(self.handle, variant), "b200q_set_sdpa_variant")
 
     def sdpa_f32(self, q, k, v, ld_q, ld_k, ld_v, B, H, S, head_dim, scale, causal, out, ld_out):
         check(self.lib.b200q_sdpa_f32(self.handle, _ptr(q), _ptr(k), _ptr(v), ld_q, ld_k, ld_v, B, H, S, head_dim, float(scale),

@@ -69,6 +69,20 @@ def main():
     acc = orc.qdot_i32(ql, wl)
     outs = {f"out_{a}": orc.epilogue(acc, sl, ws, bias, a) for a in ACTS}
     np.savez(os.path.join(HERE, "linear_tails.npz"), x=xl, w=wl, w_scales=ws, bias=bias, q=ql, a_scales=sl, acc=acc, **outs)
+    # f32 pieces of a transformer block on closed-form inputs: LayerNorm (with a residual) and causal attention,
+    # 2 sequences x 24 positions, 2 heads of 64 -- outputs of the oracle's index-order binary32 restatement
+    Mb, Db = 48, 128
+    xb = np.array([math.sin(0.13 * i) * 2 + math.cos(0.07 * i) for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
+    rb = np.array([math.sin(0.31 * i) for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
+    gamma = np.array([1 + 0.5 * math.sin(d) for d in range(Db)], np.float32)
+    beta = np.array([0.1 * math.cos(d) for d in range(Db)], np.float32)
+    yb, sb = orc.layer_norm(xb, gamma, beta, 1e-5, add=rb, want_sum=True)
+    qb = np.array([math.sin(0.17 * i) * 1.5 for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
+    kb = np.array([math.cos(0.19 * i) * 1.5 for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
+    vb = np.array([math.sin(0.23 * i + 1) for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
+    ab = orc.sdpa(qb, kb, vb, 2, 2, 24, 64, 0.125, True)
+    np.savez(os.path.join(HERE, "block_ops.npz"), x=xb, residual=rb, gamma=gamma, beta=beta, ln_sum=sb, ln_out=yb,
+             q=qb, k=kb, v=vb, attn=ab)
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 

@@ -53,6 +53,14 @@ def test_oracle_reproduces_linear_fixture(orc):
         assert same_bits(orc.epilogue(acc, s, g["w_scales"], g["bias"], a), g[f"out_{a}"])
 
 
+def test_oracle_reproduces_block_fixture(orc):
+    g = load("block_ops.npz")
+    y, s = orc.layer_norm(g["x"], g["gamma"], g["beta"], 1e-5, add=g["residual"], want_sum=True)
+    assert same_bits(y, g["ln_out"]) and same_bits(s, g["ln_sum"])
+    assert same_bits(orc.sdpa(g["q"], g["k"], g["v"], 2, 2, 24, 64, 0.125, True), g["attn"])
+    assert same_bits(g["attn"][0], g["v"][0]) and same_bits(g["attn"][24], g["v"][24])   # a first position attends to itself only
+
+
 # ------------------------------------------------------------------ GPU: the CUDA path against the fixtures
 @pytest.fixture(scope="module")
 def ctx():
@@ -119,3 +127,19 @@ def test_cuda_matches_linear_fixture(ctx, variant):
                 assert same_bits(out, g[f"out_{a}"]), a
     finally:
         ctx.set_gemm_variant(0)
+
+
+@pytest.mark.gpu
+def test_cuda_matches_block_fixture(ctx):
+    """Floating-point reductions: within 1e-5 of the output's largest magnitude; the residual sum bit for bit."""
+    g = load("block_ops.npz")
+    M, D = g["x"].shape
+    dsum, dy = ctx.empty((M, D), np.float32), ctx.empty((M, D), np.float32)
+    ctx.layernorm_quantize(ctx.to_device(g["x"]), ctx.to_device(g["residual"]), ctx.to_device(g["gamma"]), ctx.to_device(g["beta"]),
+                           1e-5, M, D, dsum, dy, None, None)
+    dattn = ctx.empty((M, D), np.float32)
+    ctx.sdpa_f32(ctx.to_device(g["q"]), ctx.to_device(g["k"]), ctx.to_device(g["v"]), D, D, D, 2, 2, 24, 64, 0.125, True, dattn, D)
+    ctx.sync()
+    assert same_bits(dsum.download(), g["ln_sum"])
+    assert np.abs(dy.download() - g["ln_out"]).max() <= 1e-5 * np.abs(g["ln_out"]).max()
+    assert np.abs(dattn.download() - g["attn"]).max() <= 1e-5 * np.abs(g["attn"]).max()

@@ -144,14 +144,36 @@ def run_sdpa(ctx, q, k, v, B, H, S, scale, causal, packed=False):
 
 @pytest.mark.parametrize("B,H,S", [(2, 3, 70), (1, 2, 512), (3, 1, 1), (1, 1, 64), (2, 2, 65), (1, 12, 200)])
 @pytest.mark.parametrize("causal", [True, False])
-def test_sdpa(ctx, orc, B, H, S, causal):
+@pytest.mark.parametrize("variant", [0, 1])   # CUDA-core FMA / mma.sync with three-way tf32 products
+def test_sdpa(ctx, orc, B, H, S, causal, variant):
     rng = np.random.default_rng(B * 100 + H * 10 + S + causal)
     shape = (B * S, H * 64)
     q, k, v = (rng.standard_normal(shape).astype(np.float32) for _ in range(3))
     q *= 2.0   # sharper softmax rows
-    got = run_sdpa(ctx, q, k, v, B, H, S, 0.125, causal)
+    ctx.set_sdpa_variant(variant)
+    try:
+        got = run_sdpa(ctx, q, k, v, B, H, S, 0.125, causal)
+    finally:
+        ctx.set_sdpa_variant(0)
     ref = orc.sdpa(q, k, v, B, H, S, 64, 0.125, causal)
     assert rel_err(got, ref) <= TOL
+
+
+def test_sdpa_large_magnitudes(ctx, orc):
+    """Scores far apart (one key dominates) and values of very different sizes: the split products must not lose them."""
+    rng = np.random.default_rng(77)
+    B, H, S = 1, 2, 192
+    shape = (B * S, H * 64)
+    q = (rng.standard_normal(shape) * 6).astype(np.float32)
+    k = (rng.standard_normal(shape) * 6).astype(np.float32)
+    v = (rng.standard_normal(shape) * np.exp(rng.uniform(-6, 6, size=shape))).astype(np.float32)
+    for variant in (0, 1):
+        ctx.set_sdpa_variant(variant)
+        try:
+            got = run_sdpa(ctx, q, k, v, B, H, S, 0.125, True)
+        finally:
+            ctx.set_sdpa_variant(0)
+        assert rel_err(got, orc.sdpa(q, k, v, B, H, S, 64, 0.125, True)) <= TOL
 
 
 def test_sdpa_reads_packed_projections(ctx, orc):
