@@ -439,9 +439,9 @@ def _run():
         "kernel": "gemm_i8_umma_kernel (tcgen05.mma kind::i8 + fused tail)", "bound": "tensor", "achieved": achieved_tops,
         "peak": int8_peak, "unit": "TOP/s", "frac": (achieved_tops / int8_peak) if achieved_tops else None,
         "peak_note": f"2 x bf16_tflops of {pk['source']} peaks (no int8 figure is measured on this pool); nominal dense int8 is 4500",
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu capture
-        # summarised in profiles/gemm_i8_umma_c3_8192x4096x4096.md (52.0 MB read + 86.0 MB written; the rest of the
-        # 134 MB of output is still in L2 when the kernel ends); algorithmic bytes are 184.6 MB
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from an ncu capture
+        # at full size (52.0 MB read + 86.0 MB written; the rest of the 134 MB of output is still in L2 when the
+        # kernel ends); algorithmic bytes are 184.6 MB
         "traffic": 138.0e6 if (M, K, N) == (8192, 4096, 4096) else None, "avg_launch_ms": gemm_avg_ms, "launches": gemm_n,
         "algorithmic_ops_per_launch": 2.0 * M * N * K,
     }

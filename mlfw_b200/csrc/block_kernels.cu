@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(256) layernorm_quantize_kernel(const float* __
     }
     const float var = warp_sum(sq) * inv_d;
     const float rstd = 1.0f / sqrtf(var + eps);
-    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000), poison = 0.0f;
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
       const int c = lane + 32 * j;
@@ -140,6 +140,8 @@ __global__ void __launch_bounds__(256) layernorm_quantize_kernel(const float* __
         v[j].w = __fadd_rn(__fmul_rn(__fmul_rn(v[j].w, rstd), g.w), b.w);
         mn = fminf(fminf(mn, v[j].x), fminf(fminf(v[j].y, v[j].z), v[j].w));   // NaN operands are dropped, as the reference's
         mx = fmaxf(fmaxf(mx, v[j].x), fmaxf(fmaxf(v[j].y, v[j].z), v[j].w));   // strict comparisons do
+        // ... so a NaN (or infinite) element of this lane has to be noticed separately: 0 * y is NaN exactly then
+        poison = fmaf(v[j].x, 0.0f, fmaf(v[j].y, 0.0f, fmaf(v[j].z, 0.0f, fmaf(v[j].w, 0.0f, poison))));
       }
     }
     if (y_out != nullptr) {
@@ -156,21 +158,32 @@ __global__ void __launch_bounds__(256) layernorm_quantize_kernel(const float* __
       mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     }
-    // Per-token codes of the normalised row: same rule as the standalone quantize kernels.
+    // Per-token codes of the normalised row: same rules as the standalone quantize kernels.  An ordinary row
+    // (finite, not constant) takes the lean packed encode -- its elements are finite and |t| <= 127 (1 + 2^-23), so a
+    // tie is the only thing that can go wrong: a cheap test with the worst-case margin first, the per-element test
+    // only if that trips, the exact binary64 path only if that one does.
     const float absmax = fmaxf(fabsf(mn), fabsf(mx));
     const float inv = __fdiv_rn(127.0f, absmax);
     const float a_inv = fabsf(inv);
     const bool exact_only = !((mn < mx) && absmax <= 3.402823466e38f && a_inv >= 1.17549435e-38f && a_inv <= 3.402823466e38f);
     uint32_t words[VPT];
-    QuantGuard guard;
+    bool exact = exact_only || (poison != poison);   // per lane: the exact path is right for every element
+    if (!exact) {
+      const uint64_t inv2 = f2_pack(inv, inv), magic2 = f2_pack(12582912.0f, 12582912.0f);
+      float far = 0.0f;
 #pragma unroll
-    for (int j = 0; j < VPT; j++) {
-      const int c = lane + 32 * j;
-      const float4 t = (c < D4) ? v[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);   // dead vectors must not trip the guard
-      words[j] = pack_codes(quantize_fast(t.x, inv, guard), quantize_fast(t.y, inv, guard), quantize_fast(t.z, inv, guard),
-                            quantize_fast(t.w, inv, guard));
+      for (int j = 0; j < VPT; j++) words[j] = pack4_fast_lean(v[j], inv2, magic2, far);   // dead vectors are zero: harmless
+      if (far >= 0.49993920f) {                                   // 0.5 - 127.5 * 2^-21
+        int tie = 0;
+#pragma unroll
+        for (int j = 0; j < VPT; j++) {
+          (void)quantize_fast_bounded(v[j].x, inv, tie); (void)quantize_fast_bounded(v[j].y, inv, tie);
+          (void)quantize_fast_bounded(v[j].z, inv, tie); (void)quantize_fast_bounded(v[j].w, inv, tie);
+        }
+        exact = tie >= 0x3f000000;
+      }
     }
-    if (exact_only || guard.unsafe(127.49f)) {   // rare: a tie, a non-finite element, an odd row
+    if (exact) {   // rare: a tie, a non-finite element, an odd row
       const double sd = ln_row_scale(mn, mx);
 #pragma unroll
       for (int j = 0; j < VPT; j++)
@@ -189,10 +202,13 @@ __global__ void __launch_bounds__(256) layernorm_quantize_kernel(const float* __
 
 // ---------------------------------------------------------------------------
 // Scaled-dot-product attention in binary32, head dimension 64, optional causal mask.
-// One block per (batch, head, 64 query rows); key/value tiles of 64 rows pass through shared memory; every thread owns
-// a 4x4 patch of the 64x64 score tile and of the 64x64 output tile; running max / sum per row (the softmax is
-// rescaled tile by tile, so no [S,S] matrix is ever stored).  Rows of q, k, v and out are addressed as
-// base + (b*S + s)*ld + h*64, which reads the projections where the linears wrote them.
+// One block per (batch, head, 64 query rows); key/value tiles of 64 rows pass through shared memory; every thread
+// owns a 4x4 patch of the 64x64 score tile and of the 64x64 output tile;
+// running max / sum per row (the softmax is rescaled tile by tile, so no [S,S] matrix is ever stored).
+// The transposed tiles (Q and K by feature, P by key) are unpadded and XOR-swizzled at float4 granularity -- slot
+// (column / 4) ^ ((row / 4) & 7) -- which keeps both their scalar transposing stores and their float4 reads at the
+// minimum number of shared-memory wavefronts.  Rows of q, k, v and out are addressed as base + (b*S + s)*ld + h*64,
+// which reads the projections where the linears wrote them.
 // ---------------------------------------------------------------------------
 // exp through the hardware base-2 exponential: relative error about 2^-22, far inside the 1e-5 bar of these kernels.
 __device__ __forceinline__ float fast_exp(float x) {
@@ -201,17 +217,22 @@ __device__ __forceinline__ float fast_exp(float x) {
   return r;
 }
 
-constexpr int AT = 64;    // tile edge = head dimension
-constexpr int ALD = 68;   // padded row length of the shared tiles (floats): rows stay 16-byte aligned
+constexpr int AT = 64;     // key tile = head dimension
 
-__global__ void __launch_bounds__(256) sdpa_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
+// element (row, col) of a [rows][LD] tile whose float4 slots are swizzled by the row
+template <int LD>
+__device__ __forceinline__ int swz(int row, int col) {
+  return row * LD + ((((col >> 2) ^ ((row >> 2) & 7)) << 2) | (col & 3));
+}
+
+__global__ void __launch_bounds__(256, 3) sdpa_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
                                                        const float* __restrict__ v, float* __restrict__ out, int64_t ld_q,
                                                        int64_t ld_k, int64_t ld_v, int64_t ld_o, int H, int S, float scale, int causal) {
   extern __shared__ __align__(16) float sm[];
-  float(*Qt)[ALD] = reinterpret_cast<float(*)[ALD]>(sm);                  // [d][query row]
-  float(*Kt)[ALD] = reinterpret_cast<float(*)[ALD]>(sm + AT * ALD);       // [d][key row]
-  float(*Vs)[ALD] = reinterpret_cast<float(*)[ALD]>(sm + 2 * AT * ALD);   // [key row][d]
-  float(*Pt)[ALD] = reinterpret_cast<float(*)[ALD]>(sm + 3 * AT * ALD);   // [key row][query row]
+  float* Qt = sm;                  // [d][query row], swizzled
+  float* Kt = Qt + AT * AT;        // [d][key row], swizzled
+  float* Vs = Kt + AT * AT;        // [key row][d]
+  float* Pt = Vs + AT * AT;        // [key row][query row], swizzled
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
   const int b = blockIdx.y / H, h = blockIdx.y - b * H;
   // Causal work grows with the query tile: the heaviest tiles are scheduled first.
@@ -224,7 +245,7 @@ __global__ void __launch_bounds__(256) sdpa_f32_kernel(const float* __restrict__
     const int r = idx >> 4, d4 = idx & 15;
     float4 val = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (i0 + r < S) val = __ldg(reinterpret_cast<const float4*>(q + (row_base + i0 + r) * ld_q + h * AT) + d4);
-    Qt[d4 * 4 + 0][r] = val.x; Qt[d4 * 4 + 1][r] = val.y; Qt[d4 * 4 + 2][r] = val.z; Qt[d4 * 4 + 3][r] = val.w;
+    Qt[swz<AT>(d4 * 4 + 0, r)] = val.x; Qt[swz<AT>(d4 * 4 + 1, r)] = val.y; Qt[swz<AT>(d4 * 4 + 2, r)] = val.z; Qt[swz<AT>(d4 * 4 + 3, r)] = val.w;
   }
   float o[4][4], m[4], l[4];
 #pragma unroll
@@ -244,8 +265,8 @@ __global__ void __launch_bounds__(256) sdpa_f32_kernel(const float* __restrict__
         kv = __ldg(reinterpret_cast<const float4*>(k + (row_base + j0 + r) * ld_k + h * AT) + d4);
         vv = __ldg(reinterpret_cast<const float4*>(v + (row_base + j0 + r) * ld_v + h * AT) + d4);
       }
-      Kt[d4 * 4 + 0][r] = kv.x; Kt[d4 * 4 + 1][r] = kv.y; Kt[d4 * 4 + 2][r] = kv.z; Kt[d4 * 4 + 3][r] = kv.w;
-      *reinterpret_cast<float4*>(&Vs[r][d4 * 4]) = vv;
+      Kt[swz<AT>(d4 * 4 + 0, r)] = kv.x; Kt[swz<AT>(d4 * 4 + 1, r)] = kv.y; Kt[swz<AT>(d4 * 4 + 2, r)] = kv.z; Kt[swz<AT>(d4 * 4 + 3, r)] = kv.w;
+      *reinterpret_cast<float4*>(&Vs[r * AT + d4 * 4]) = vv;
     }
     __syncthreads();
     float s[4][4];
@@ -255,8 +276,8 @@ __global__ void __launch_bounds__(256) sdpa_f32_kernel(const float* __restrict__
       for (int j = 0; j < 4; j++) s[i][j] = 0.0f;
 #pragma unroll 8
     for (int d = 0; d < AT; d++) {
-      const float4 a = *reinterpret_cast<const float4*>(&Qt[d][ty * 4]);
-      const float4 c = *reinterpret_cast<const float4*>(&Kt[d][tx * 4]);
+      const float4 a = *reinterpret_cast<const float4*>(&Qt[swz<AT>(d, ty * 4)]);
+      const float4 c = *reinterpret_cast<const float4*>(&Kt[swz<AT>(d, tx * 4)]);
       const float av[4] = {a.x, a.y, a.z, a.w}, cv[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
       for (int i = 0; i < 4; i++)
@@ -297,12 +318,12 @@ __global__ void __launch_bounds__(256) sdpa_f32_kernel(const float* __restrict__
     }
 #pragma unroll
     for (int j = 0; j < 4; j++)
-      *reinterpret_cast<float4*>(&Pt[tx * 4 + j][ty * 4]) = make_float4(s[0][j], s[1][j], s[2][j], s[3][j]);
+      *reinterpret_cast<float4*>(&Pt[swz<AT>(tx * 4 + j, ty * 4)]) = make_float4(s[0][j], s[1][j], s[2][j], s[3][j]);
     __syncthreads();
 #pragma unroll 8
     for (int c = 0; c < AT; c++) {
-      const float4 p = *reinterpret_cast<const float4*>(&Pt[c][ty * 4]);
-      const float4 w = *reinterpret_cast<const float4*>(&Vs[c][tx * 4]);
+      const float4 p = *reinterpret_cast<const float4*>(&Pt[swz<AT>(c, ty * 4)]);
+      const float4 w = *reinterpret_cast<const float4*>(&Vs[c * AT + tx * 4]);
       const float pv[4] = {p.x, p.y, p.z, p.w}, wv[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
       for (int i = 0; i < 4; i++)
@@ -550,8 +571,10 @@ int launch_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* resid
   const int vpt = (D4 + 31) / 32;
   const unsigned grid = flat_grid(ctx, M, 8);   // 8 rows (warps) per block
   typedef void (*Kern)(const float*, const float*, const float*, const float*, float, int64_t, int, float*, float*, int8_t*, float*);
-  const Kern kern = vpt <= 2 ? layernorm_quantize_kernel<2> : vpt <= 4 ? layernorm_quantize_kernel<4>
-                    : vpt <= 8 ? layernorm_quantize_kernel<8> : layernorm_quantize_kernel<16>;
+  const Kern kern = vpt <= 1 ? layernorm_quantize_kernel<1> : vpt <= 2 ? layernorm_quantize_kernel<2>
+                    : vpt <= 3 ? layernorm_quantize_kernel<3> : vpt <= 4 ? layernorm_quantize_kernel<4>
+                    : vpt <= 6 ? layernorm_quantize_kernel<6> : vpt <= 8 ? layernorm_quantize_kernel<8>
+                    : vpt <= 12 ? layernorm_quantize_kernel<12> : layernorm_quantize_kernel<16>;
   kern<<<grid, 256, 0, ctx->stream>>>(x, residual, gamma, beta, eps, M, D4, sum_out, y_out, q_out, scales_out);
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
@@ -567,17 +590,19 @@ int launch_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float*
                     ld_o % 4 == 0 && ld_q >= H * Dh && ld_k >= H * Dh && ld_v >= H * Dh && ld_o >= H * Dh,
                 "attention needs 16-byte aligned buffers and row strides that are multiples of 4 and at least H * 64");
   B200Q_REQUIRE(B * H <= 65535 && S < (1 << 24), "attention: batch * heads must not exceed 65535");
-  const size_t smem_fma = (size_t)4 * AT * ALD * sizeof(float), smem_mma = (size_t)4 * AT * TLD * sizeof(float);
+  const size_t smem_fma = (size_t)(4 * AT * AT) * sizeof(float), smem_mma = (size_t)4 * AT * TLD * sizeof(float);
   if (!ctx->sdpa_ready) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(sdpa_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fma));
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(sdpa_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma));
     ctx->sdpa_ready = true;
   }
-  const dim3 grid((unsigned)((S + AT - 1) / AT), (unsigned)(B * H));
-  if (ctx->sdpa_variant == 1)   // mma.sync with three-way tf32 products (measured slower on B200: see the kernel's comment)
+  if (ctx->sdpa_variant == 1) {   // mma.sync with three-way tf32 products (measured slower on B200: see the kernel's comment)
+    const dim3 grid((unsigned)((S + AT - 1) / AT), (unsigned)(B * H));
     sdpa_tf32x3_kernel<<<grid, 128, smem_mma, ctx->stream>>>(q, k, v, out, ld_q, ld_k, ld_v, ld_o, (int)H, (int)S, scale, causal);
-  else
+  } else {
+    const dim3 grid((unsigned)((S + AT - 1) / AT), (unsigned)(B * H));
     sdpa_f32_kernel<<<grid, 256, smem_fma, ctx->stream>>>(q, k, v, out, ld_q, ld_k, ld_v, ld_o, (int)H, (int)S, scale, causal);
+  }
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;

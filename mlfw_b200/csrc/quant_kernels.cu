@@ -217,62 +217,6 @@ __device__ __forceinline__ float fmax3n(float a, float b, float c) {
   return r;
 }
 
-// Packed binary32 arithmetic of sm_100: one instruction works on a pair of floats held in a 64-bit register
-// (round to nearest even per element, no flush to zero: the same values as the scalar instructions).
-__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
-__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ uint64_t f2_sub(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-
-// Leanest form of the fast code, for finite elements of an ordinary per-token row: the four codes, and the running
-// maximum of |t - rint t| (how close any element came to a tie).  t = x * inv, u = t + 1.5*2^23 (the rounding), and
-// the code is the low byte of u's bit pattern (|t| <= 127.00002 here, so no clamp; 0x4B400000 + code keeps the code's
-// two's complement in its low byte).  Packed arithmetic: eight floating-point instructions per four elements.
-// `inv2` and `magic2` hold the reciprocal scale and 1.5*2^23 in both halves.
-__device__ __forceinline__ uint32_t pack4_fast_lean(const float4& v, uint64_t inv2, uint64_t magic2, float& far) {
-  const uint64_t t01 = f2_mul(f2_pack(v.x, v.y), inv2), t23 = f2_mul(f2_pack(v.z, v.w), inv2);
-  const uint64_t u01 = f2_add(t01, magic2), u23 = f2_add(t23, magic2);
-  const uint64_t d01 = f2_sub(t01, f2_sub(u01, magic2)), d23 = f2_sub(t23, f2_sub(u23, magic2));
-  float d0, d1, d2, d3, u0, u1, u2, u3;
-  f2_unpack(d01, d0, d1);
-  f2_unpack(d23, d2, d3);
-  f2_unpack(u01, u0, u1);
-  f2_unpack(u23, u2, u3);
-  far = fmaxf(fmaxf(fmaxf(far, fabsf(d0)), fmaxf(fabsf(d1), fabsf(d2))), fabsf(d3));
-  const uint32_t lo = __byte_perm(__float_as_uint(u0), __float_as_uint(u1), 0x0040);   // bytes: u0.b0, u1.b0
-  const uint32_t hi = __byte_perm(__float_as_uint(u2), __float_as_uint(u3), 0x0040);
-  return __byte_perm(lo, hi, 0x5410);
-}
-
-// tie tracking only: in a per-token row |x * (127/absmax)| <= 127 (1 + 2^-23) by construction, so the magnitude
-// needs no watching; a NaN element still trips the guard through `e`.
-__device__ __forceinline__ int quantize_fast_bounded(float x, float inv, int& tie) {
-  const float t = __fmul_rn(x, inv);
-  const float u = __fadd_rn(t, 12582912.0f);
-  const int c = __float_as_int(u) - 0x4B400000;
-  const float d = __fsub_rn(t, __fsub_rn(u, 12582912.0f));
-  const float e = __fmaf_rn(fabsf(t), 4.76837158203125e-7f, fabsf(d));
-  tie = max(tie, __float_as_int(e));
-  return c;
-}
-
 __global__ void __launch_bounds__(QT_THREADS, 1)
 quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4, int rows_per_chunk, int slots,
                                  int8_t* __restrict__ q, float* __restrict__ scales, float qmin, float qmax, uint32_t* status,

@@ -127,6 +127,22 @@ def test_layernorm_edge_rows(ctx, orc):
     assert (q == rq).all()
 
 
+def test_layernorm_nan_column(ctx, orc):
+    """A NaN in beta poisons one column of every row; the other codes of those rows must not suffer."""
+    rng = np.random.default_rng(12)
+    M, D = 70, 768
+    x = rng.standard_normal((M, D)).astype(np.float32)
+    gamma = np.ones(D, np.float32)
+    beta = np.zeros(D, np.float32)
+    beta[100] = np.nan
+    gamma[5] = np.inf
+    _, y, q, sc = run_layernorm(ctx, x, None, gamma, beta, 1e-5)
+    assert np.isnan(y[:, 100]).all()
+    rq, _, rs = orc.quantize_per_token(y)
+    assert (sc.view(np.uint32) == rs.view(np.uint32)).all()
+    assert (q == rq).all()
+
+
 def run_sdpa(ctx, q, k, v, B, H, S, scale, causal, packed=False):
     D = 64
     ld = H * D
