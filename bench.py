@@ -340,6 +340,8 @@ def _run():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--tail-mode", type=int, default=0, choices=[0, 1],
+                    help="0: exact sigmoid tails (default); 1: hardware exp / reciprocal for f32 outputs (within the 1e-5 bar)")
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [C4_WORKLOAD, C5_WORKLOAD])
     ap.add_argument("--mode", default="mshard", choices=["mshard", "nshard"],
                     help="config 5 only: rows split over the GPUs (no collective) or output channels split (NCCL all-gather)")
@@ -376,6 +378,7 @@ def _run():
         return float(t.item())
 
     ctx = mlfw_b200.Context(local_rank)
+    ctx.set_tail_mode(args.tail_mode)
     if args.roundtrip_only:
         line = {"metric": "quantize_dequantize_GBps", "roundtrip_c2": run_roundtrip(ctx, peaks(), args.steps, args.warmup)}
         ctx.close()

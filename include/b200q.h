@@ -53,6 +53,12 @@ int b200q_set_wait_limit(b200q_ctx* ctx, double seconds);
 /* 0: tensor-core GEMM whenever the shape allows, one CTA or a CTA pair per tile chosen by size (default);
  * 1: CUDA-core kernel only; 2: tensor cores, one CTA per tile; 3: tensor cores, CTA pairs. */
 int b200q_set_gemm_variant(b200q_ctx* ctx, int variant);
+/* Sigmoid-based tails (gelu_sigmoid, silu) of the tensor-core kernel when the output is f32.
+ * 0 (default): every operation rounded as the reference's CPU target rounds it -- bit-identical results, but the exp
+ * runs in binary64 and makes those tails about 1.7x longer than the others;
+ * 1: hardware exponential and reciprocal -- results within about 1e-6 (relative) of mode 0, inside the 1e-5 bar, at the
+ * speed of the other tails.  int8 (requantized) outputs always use the exact form: their codes are integer results. */
+int b200q_set_tail_mode(b200q_ctx* ctx, int mode);
 /* Per-token quantize: 0 = rows staged through shared memory by bulk copies when they fit (default);
  * 1 = register-resident kernel only. */
 int b200q_set_quant_variant(b200q_ctx* ctx, int variant);

@@ -25,6 +25,7 @@ PROTOTYPES = {
     "b200q_clear_status": (c_int, [c_vp]),
     "b200q_set_wait_limit": (c_int, [c_vp, c_dbl]),
     "b200q_set_gemm_variant": (c_int, [c_vp, c_int]),
+    "b200q_set_tail_mode": (c_int, [c_vp, c_int]),
     "b200q_set_quant_variant": (c_int, [c_vp, c_int]),
     "b200q_launch_count": (C.c_uint64, [c_vp]),
     "b200q_sm_count": (c_int, [c_vp]),

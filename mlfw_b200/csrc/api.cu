@@ -173,6 +173,13 @@ int b200q_set_wait_limit(b200q_ctx* ctx, double seconds) {
   return 0;
 }
 
+int b200q_set_tail_mode(b200q_ctx* ctx, int mode) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_REQUIRE(mode == 0 || mode == 1, "b200q_set_tail_mode: unknown mode %d", mode);
+  ctx->tail_mode = mode;
+  return 0;
+}
+
 int b200q_set_sdpa_variant(b200q_ctx* ctx, int variant) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
   B200Q_REQUIRE(variant == 0 || variant == 1, "b200q_set_sdpa_variant: unknown variant %d", variant);

@@ -712,12 +712,20 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
                                           B200Q_ROW(ACT_GELU_TANH), B200Q_ROW(ACT_SILU)};
 #undef B200Q_ROW
   static const KernelFn raw[2] = {gemm_i8_umma_kernel<ACT_NONE, OUT_I32, 1>, gemm_i8_umma_kernel<ACT_NONE, OUT_I32, 2>};
+  // f32 output with the approximate sigmoid tails (b200q_set_tail_mode 1): [gelu_sigmoid, silu][CTAs per tile]
+  static const KernelFn approx[2][2] = {{gemm_i8_umma_kernel<ACT_GELU_SIGMOID_APPROX, OUT_F32, 1>, gemm_i8_umma_kernel<ACT_GELU_SIGMOID_APPROX, OUT_F32, 2>},
+                                        {gemm_i8_umma_kernel<ACT_SILU_APPROX, OUT_F32, 1>, gemm_i8_umma_kernel<ACT_SILU_APPROX, OUT_F32, 2>}};
   B200Q_REQUIRE(act >= 0 && act <= 4, "unknown activation %d", act);
   B200Q_REQUIRE((out_i32 != nullptr) + (out_f32 != nullptr) + (out_q != nullptr) == 1,
                 "tensor-core int8 gemm writes exactly one output");
   KernelFn fn = out_i32 ? raw[ncta - 1] : table[act][out_q ? 1 : 0][ncta - 1];
+  int slot_act = act;
+  if (ctx->tail_mode == 1 && out_f32 != nullptr && (act == ACT_GELU_SIGMOID || act == ACT_SILU)) {
+    fn = approx[act == ACT_SILU ? 1 : 0][ncta - 1];
+    slot_act = act == ACT_SILU ? 6 : 5;
+  }
   const int smem = ncta == 1 ? smem_bytes<1>() : smem_bytes<2>();
-  const int slot_idx = (out_i32 ? 10 : act * 2 + (out_q ? 1 : 0)) * 2 + (ncta - 1);
+  const int slot_idx = (out_i32 ? 14 : slot_act * 2 + (out_q ? 1 : 0)) * 2 + (ncta - 1);   // < 32
   if (!(ctx->umma_ready_mask & (1u << slot_idx))) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     ctx->umma_ready_mask |= 1u << slot_idx;

@@ -15,7 +15,9 @@
 
 namespace b200q {
 
-enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU_SIGMOID = 2, ACT_GELU_TANH = 3, ACT_SILU = 4 };
+enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU_SIGMOID = 2, ACT_GELU_TANH = 3, ACT_SILU = 4,
+                 // internal: the sigmoid forms through the hardware exponential and reciprocal (tolerance only)
+                 ACT_GELU_SIGMOID_APPROX = 5, ACT_SILU_APPROX = 6 };
 
 // ---------------------------------------------------------------------------
 // Rounding a quotient x / s to the nearest integer, ties toward +infinity.
@@ -271,6 +273,15 @@ __device__ __forceinline__ float apply_act_fast(float y, const double* tbl) {
   if (ACT_T == ACT_RELU) return (y > 0.0f) ? y : ((y != y) ? y : 0.0f);
   if (ACT_T == ACT_GELU_SIGMOID) return __fmul_rn(y, sigmoid_fast(mul_1702(y), tbl));
   if (ACT_T == ACT_SILU) return __fmul_rn(y, sigmoid_fast(y, tbl));
+  if (ACT_T == ACT_GELU_SIGMOID_APPROX || ACT_T == ACT_SILU_APPROX) {
+    // x * sigmoid(z) with sigmoid(z) = 1 / (1 + 2^(-z log2 e)): relative error about 2^-21, saturates correctly
+    // (2^+big = Inf -> 1/Inf = 0; 2^-big = 0 -> 1), NaN stays NaN.
+    const float z = (ACT_T == ACT_GELU_SIGMOID_APPROX) ? 1.702f * y : y;
+    float e, sg;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sg) : "f"(1.0f + e));
+    return y * sg;
+  }
   if (ACT_T == ACT_GELU_TANH) {
     // 0.5*(1+tanh(u)) = 1/(1+exp(-2u)), u = sqrt(2/pi)*(y + 0.044715 y^3); binary32, tolerance only
     // (the reference has no tanh form).  Saturates correctly for large |y|.

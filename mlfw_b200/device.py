@@ -149,6 +149,10 @@ class Context:
     def set_gemm_variant(self, variant: int):
         check(self.lib.b200q_set_gemm_variant(self.handle, variant), "b200q_set_gemm_variant")
 
+    def set_tail_mode(self, mode: int):
+        """0: exact sigmoid tails (default); 1: hardware exp / reciprocal for f32 outputs (within the 1e-5 bar, faster)."""
+        check(self.lib.b200q_set_tail_mode(self.handle, mode), "b200q_set_tail_mode")
+
     def set_quant_variant(self, variant: int):
         check(self.lib.b200q_set_quant_variant(self.handle, variant), "b200q_set_quant_variant")
 

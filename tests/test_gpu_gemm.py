@@ -289,3 +289,34 @@ def test_fused_tail_extreme_arguments(ctx, orc, act):
         fin = np.isfinite(ref)
         assert (out[ok & ~fin] == ref[ok & ~fin]).all()
         assert np.abs(out[fin].astype(np.float64) - ref[fin]).max() <= TOL * np.abs(ref[fin]).max()
+
+
+@pytest.mark.parametrize("act", ["gelu_sigmoid", "silu"])
+@pytest.mark.parametrize("M,N,K", [(300, 768, 768), (1100, 512, 256)])
+def test_approximate_tail_mode(ctx, orc, act, M, N, K):
+    """Tail mode 1: hardware exp / reciprocal for f32 outputs -- inside the 1e-5 bar; int8 outputs stay exact."""
+    rng = np.random.default_rng(M + N + K)
+    x, W, ws, bias = linear_case(rng, M, N, K)
+    ws = ws * 40          # pre-activations far into both saturated ends of the sigmoid
+    q, _, s32 = orc.quantize_per_token(x)
+    acc = orc.qdot_i32(q, W)
+    ref = orc.epilogue(acc, s32, ws, bias, act)
+    dq, dW = ctx.to_device(q), ctx.to_device(W)
+    ds, dws, db = ctx.to_device(s32), ctx.to_device(ws), ctx.to_device(bias)
+    dout = Guarded(ctx, (M, N), np.float32)
+    dcodes = Guarded(ctx, (M, N), np.int8)
+    out_scale = float(np.abs(ref).max()) / 127
+    ctx.set_tail_mode(1)
+    try:
+        ctx.int8_linear(dq.ptr, ds.ptr, dW.ptr, dws.ptr, db.ptr, act, M, N, K, dout.ptr)
+        ctx.int8_linear_requant_static(dq.ptr, ds.ptr, dW.ptr, dws.ptr, db.ptr, act, M, N, K, out_scale, dcodes.ptr)
+        ctx.sync()
+    finally:
+        ctx.set_tail_mode(0)
+    got = dout.download()
+    assert rel_err(got, ref) <= TOL
+    assert not (got.view(np.uint32) == ref.view(np.uint32)).all()          # it really is the other code path
+    assert (dcodes.download() == orc.quantize_static(ref, out_scale, 0)).all()
+    ctx.int8_linear(dq.ptr, ds.ptr, dW.ptr, dws.ptr, db.ptr, act, M, N, K, dout.ptr)   # back in mode 0: bit-exact again
+    ctx.sync()
+    assert (dout.download().view(np.uint32) == ref.view(np.uint32)).all()
