@@ -33,6 +33,17 @@ function bind(path: string) {
     linearRequantStatic: f('int b200q_int8_linear_requant_static(void *ctx, const void *A, const void *a_scales, const void *W, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, double out_scale, void *out_q)'),
     linearF32: f('int b200q_linear_f32(void *ctx, const void *x, const void *W, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void *out)'),
     linearF32Host: f('int b200q_linear_f32_host(void *ctx, const void *x_host, const void *W, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void *out_host)'),
+    linearRequantToken: f('int b200q_int8_linear_requant_token(void *ctx, const void *A, const void *a_scales, const void *W, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void *out_q, void *out_scales)'),
+    quantizeWeightsPerChannel: f('int b200q_quantize_weights_per_channel(void *ctx, const void *w, int64_t N, int64_t K, int layout, void *qw, void *scales32, void *scales64)'),
+    setTailMode: f('int b200q_set_tail_mode(void *ctx, int mode)'),
+    // calibration on the device (min/max mode)
+    observerReset: f('int b200q_observer_reset(void *ctx, void *state)'),
+    observeMinmax: f('int b200q_observe_minmax(void *ctx, const void *x, int64_t n, void *state)'),
+    // f32 pieces of a transformer block
+    embeddingF32: f('int b200q_embedding_f32(void *ctx, const void *table, const void *tokens, const void *pos_table, int64_t M, int64_t D, int64_t V, int64_t S, void *out)'),
+    addF32: f('int b200q_add_f32(void *ctx, const void *a, const void *b, int64_t n, void *out)'),
+    layernormQuantize: f('int b200q_layernorm_quantize(void *ctx, const void *x, const void *residual, const void *gamma, const void *beta, float eps, int64_t M, int64_t D, void *sum_out, void *y_out, void *q_out, void *scales_out)'),
+    sdpaF32: f('int b200q_sdpa_f32(void *ctx, const void *q, const void *k, const void *v, int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t B, int64_t H, int64_t S, int64_t head_dim, float scale, int causal, void *out, int64_t ld_out)'),
   };
 }
 
