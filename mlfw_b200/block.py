@@ -45,6 +45,20 @@ class QuantLinear:
         dw.free()
         return QuantLinear(N, K, qw, sc, ctx.to_device(np.ascontiguousarray(bias, np.float32)) if bias is not None else None)
 
+    def state(self):
+        """This linear as it goes into an ``mlfw-ckpt-v1`` checkpoint (:mod:`mlfw_b200.checkpoint`)."""
+        from .checkpoint import quantized_linear_state
+        return quantized_linear_state(self.w.download(), self.scales.download(), self.bias.download() if self.bias is not None else None)
+
+    @staticmethod
+    def from_state(ctx: Context, st) -> "QuantLinear":
+        """Rebuild from :meth:`state` without running the quantization again: the codes and scales are uploaded as they are."""
+        wq = np.ascontiguousarray(st["weight_q"].data, np.int8)
+        N, K = wq.shape
+        bias = st.get("bias")
+        return QuantLinear(N, K, ctx.to_device(wq), ctx.to_device(np.ascontiguousarray(st["weight_scale"].data, np.float32)),
+                           ctx.to_device(np.ascontiguousarray(bias.data, np.float32)) if bias is not None else None)
+
 
 class GPTBlock:
     """One block for activations [B*S, D]; ``forward`` enqueues everything on the context's stream."""

@@ -311,3 +311,22 @@ def test_block_config4_shape(ctx, orc):
     assert (h.view(np.uint32) == table[tokens].view(np.uint32)).all()
     rows = np.unique(np.concatenate([[0, 1, 511, 512, 16383], rng.integers(0, B * S, size=27)]))
     check_block_stages(ctx, orc, blk, params, h, B, S, rows=rows)
+
+
+def test_quantized_linear_survives_a_checkpoint(ctx):
+    """int8 weights + scales + bias through the reference's checkpoint container and back: same device results."""
+    from collections import OrderedDict
+    from mlfw_b200.block import QuantLinear
+    from mlfw_b200.checkpoint import deserialize_checkpoint, serialize_checkpoint
+    rng = np.random.default_rng(21)
+    N, K, M = 256, 512, 300
+    lin = QuantLinear.from_float(ctx, (rng.standard_normal((N, K)) * 0.05).astype(np.float32), rng.standard_normal(N).astype(np.float32))
+    blob = serialize_checkpoint({"epoch": 1, "modelState": OrderedDict([("fc", lin.state())])})
+    lin2 = QuantLinear.from_state(ctx, deserialize_checkpoint(blob)["modelState"]["fc"])
+    x = ctx.to_device(rng.standard_normal((M, K)).astype(np.float32))
+    a, b = ctx.empty((M, N), np.float32), ctx.empty((M, N), np.float32)
+    ctx.linear_f32(x, lin.w, lin.scales, lin.bias, "silu", M, N, K, a)
+    ctx.linear_f32(x, lin2.w, lin2.scales, lin2.bias, "silu", M, N, K, b)
+    ctx.sync()
+    assert (a.download().view(np.uint32) == b.download().view(np.uint32)).all()
+
