@@ -52,8 +52,9 @@ def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -243,8 +244,6 @@ def run_c4(args, ctx, rank, world, barrier, max_over_ranks):
         step(i)
     ctx.sync()
     ctx.check_status()
-    ctx.profile_enable(True)
-    ctx.profile_reset()
     launches0 = ctx.launch_count()
     barrier()
     ctx.sync()
@@ -254,6 +253,17 @@ def run_c4(args, ctx, rank, world, barrier, max_over_ranks):
     ms = ctx.timer_stop()
     ctx.sync()
     barrier()
+    launches = ctx.launch_count() - launches0
+    # the same steps once more with an event pair around every kernel (kept out of the headline: the events sit
+    # between the kernels and switch the dependent launches off)
+    time.sleep(0.5)
+    step(0)
+    ctx.sync()
+    ctx.profile_enable(True)
+    ctx.profile_reset()
+    for i in range(args.steps):
+        step(i)
+    ctx.sync()
     prof = ctx.profile_read()
     ctx.profile_enable(False)
     ctx.check_status()
@@ -275,7 +285,7 @@ def run_c4(args, ctx, rank, world, barrier, max_over_ranks):
                                             "note": "two launches per step: 5 B/element (read x, write codes) and 13 B/element (read x and the residual, write their sum and the codes)"},
             "roofline_sdpa": {"bound": "fp32 CUDA cores", "achieved": attn_flops / (sd_ms * 1e-3) / 1e12 if sd_ms else None, "unit": "TFLOP/s",
                               "note": "binary32 FMA on CUDA cores (the 1e-5 bar rules out tf32 tensor-core products)"},
-            "gpu_launches": ctx.launch_count() - launches0}
+            "gpu_launches": launches}
 
 
 def run_reference_arm(args, rank, world):
@@ -412,8 +422,6 @@ def _run():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ctx.profile_enable(True)
-    ctx.profile_reset()
     launches0 = ctx.launch_count()
     barrier()
     ctx.sync()
@@ -424,6 +432,17 @@ def _run():
     ctx.sync()
     barrier()
     launches = ctx.launch_count() - launches0
+    # The same steps once more with an event pair around every kernel (the per-kernel figures of the roofline); the
+    # events sit between the kernels, so this pass is kept out of the headline.
+    time.sleep(0.5)     # both passes start from the same clocks: a long busy stretch runs into the power cap
+    for i in range(min(args.warmup, 5)):
+        step(i)
+    ctx.sync()
+    ctx.profile_enable(True)
+    ctx.profile_reset()
+    for i in range(args.steps):
+        step(i)
+    ctx.sync()
     prof = ctx.profile_read()
     ctx.profile_enable(False)
     clocks = sampler.stop() if rank == 0 else None
@@ -447,6 +466,10 @@ def _run():
         # kernel ends); algorithmic bytes are 184.6 MB
         "traffic": 138.0e6 if (M, K, N) == (8192, 4096, 4096) else None, "avg_launch_ms": gemm_avg_ms, "launches": gemm_n,
         "algorithmic_ops_per_launch": 2.0 * M * N * K,
+        # a timed region of a tenth of a second or more runs under the power cap: the sustained figure is its yardstick
+        "peak_sustained": 2.0 * pk["bf16_tflops_sustained"],
+        "frac_of_sustained": (achieved_tops / (2.0 * pk["bf16_tflops_sustained"])) if achieved_tops else None,
+        "regime": "sustained (long timed region, power cap)" if ms >= 100.0 else "burst",
     }
     if quant_n:
         q_avg = quant_ms / quant_n

@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(256) layernorm_quantize_kernel(const float* __
   const int lane = threadIdx.x & 31;
   const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const float inv_d = 1.0f / (float)(D4 * 4);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the linear that follows may start its set-up early
   for (int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps) {
     const float4* xr = reinterpret_cast<const float4*>(x) + row * D4;
     float4 v[VPT];

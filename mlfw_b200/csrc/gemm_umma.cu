@@ -304,6 +304,10 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   if (NCTA == 2) cluster_sync_all();  // the partner's barriers are initialised before anything signals them
   tc_fence_after();
+  // Launched as a programmatic dependent of the previous kernel of the stream (which usually produced A and its
+  // scales), everything above overlaps that kernel's tail; nothing below may run before it has finished.
+  // Without that launch attribute this is a no-op.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t tmem_base = misc->tmem_base;
 
   if (warp == 0) {
@@ -673,6 +677,10 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
                         const float* a_scales, const float* w_scales, const float* bias, int act, float* out_f32,
                         int32_t* out_i32, int8_t* out_q, double q_scale) {
   ProfScope prof(ctx, KK_GEMM_UMMA);
+  // The launch may begin while the previous kernel of the stream drains (programmatic dependent launch): the set-up
+  // of this kernel overlaps that tail, and its griddepcontrol.wait holds everything else back until the previous
+  // kernel -- whatever it was -- has completed.  With profiling on an event sits between the two anyway.
+  const bool after_producer = !ctx->profiling;
   B200Q_REQUIRE(gemm_umma_supported(A, W_nk, M, N, K), "tensor-core int8 gemm needs K %% 16 == 0 and 16-byte aligned operands");
   // CTA pairs pay off once there are enough 256-row tiles to go round; small or forced cases use single CTAs.
   const int ncta = ctx->gemm_variant == 2 ? 1 : ctx->gemm_variant == 3 ? 2 : (M >= 1024 ? 2 : 1);
@@ -735,13 +743,18 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = ctx->stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)ncta;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (after_producer) {   // may start while the previous kernel of the stream drains (see griddepcontrol.wait in the kernel)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
   B200Q_CHECK_CUDA(cudaLaunchKernelEx(&cfg, fn, tmA, tmB, tmC, p));
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());

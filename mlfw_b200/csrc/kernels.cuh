@@ -32,6 +32,8 @@ int launch_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, co
 
 bool gemm_umma_supported(const void* A, const void* W, int64_t M, int64_t N, int64_t K);
 // Tensor-core GEMM with the fused tail.  out_i32 != null: raw accumulators (tail arguments ignored).
+// Launched as a programmatic dependent of the previous kernel on the stream: its set-up overlaps that kernel's tail,
+// and it waits for that kernel to complete before it touches anything.
 int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K,
                         const float* a_scales, const float* w_scales, const float* bias, int act, float* out_f32,
                         int32_t* out_i32, int8_t* out_q, double q_scale);

@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(MAXT) quantize_per_token_vec_kernel(const floa
   const int64_t row_stride = (int64_t)gridDim.x * rows_per_block;
   const float limit = guard_limit(qmin, qmax);
 
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the GEMM that follows may start its set-up early
   constexpr bool PREFETCH = MAXT <= 256;
   float4 nxt[PREFETCH ? VPT : 1];
   if (PREFETCH) load_row<VPT>(reinterpret_cast<float4(&)[VPT]>(nxt), x, (int64_t)blockIdx.x * rows_per_block + grp, M, K4, G, t);
@@ -231,6 +232,9 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
   const int64_t row_bytes = (int64_t)K4 * 16;
   const int64_t chunk_bytes = row_bytes * rows_per_chunk;
   const int64_t num_chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
+  // A kernel launched as this one's programmatic dependent (the GEMM of b200q_linear_f32) may take over each SM as
+  // soon as this block leaves it and do its set-up there; it waits for this whole grid before it reads anything.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < slots; s++) {
