@@ -269,6 +269,8 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = NCTA == 2 ? cluster_cta_rank() : 0u;   // 0 = the CTA that issues the MMAs
+  // A programmatic dependent of this launch (the next quantize) may take over SMs as this kernel's CTAs leave them.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + BM * NCTA - 1) / (BM * NCTA);
   const int64_t num_tiles = tiles_m * tiles_n;
   const int64_t tile_first = blockIdx.x / NCTA, tile_step = gridDim.x / NCTA;

@@ -235,6 +235,9 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
   // A kernel launched as this one's programmatic dependent (the GEMM of b200q_linear_f32) may take over each SM as
   // soon as this block leaves it and do its set-up there; it waits for this whole grid before it reads anything.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // ... and this kernel may itself have been launched while its predecessor on the stream (which may have produced x)
+  // was still draining: nothing is read before that kernel has completed.  A no-op for an ordinary launch.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < slots; s++) {
@@ -787,9 +790,19 @@ int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t
     }
     const int64_t num_chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
     const unsigned blocks = (unsigned)(num_chunks < ctx->sm_count ? num_chunks : ctx->sm_count);
-    quantize_per_token_staged_kernel<<<blocks, QT_THREADS, smem, ctx->stream>>>(
-        x, M, K4, rows_per_chunk, slots, q, scales, (float)qmin, (float)qmax, ctx->status_dev,
-        (unsigned long long)(ctx->wait_limit_s * 1e9));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(QT_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->profiling ? 0 : 1;   // with profiling on an event separates the kernels anyway
+    B200Q_CHECK_CUDA(cudaLaunchKernelEx(&cfg, quantize_per_token_staged_kernel, x, M, K4, rows_per_chunk, slots, q, scales,
+                                        (float)qmin, (float)qmax, ctx->status_dev,
+                                        (unsigned long long)(ctx->wait_limit_s * 1e9)));
   } else if (vec) {
     const int K4 = (int)(K / 4);
     int G = 32;
