@@ -299,6 +299,7 @@ def run_reference_arm(args, rank, world):
     M, K, N, act, xs, W, ws, bias = make_case(args.workload, 0)
     rows = min(CPU_SAMPLE_ROWS, M)
     x = xs[0][:rows]
+    oracle.set_num_threads(oracle.usable_cores())   # torchrun exports OMP_NUM_THREADS=1; this arm uses every core it may
     cores = oracle.num_threads()
     for _ in range(max(1, min(args.warmup, 2))):
         oracle.linear(x, W, ws, bias, act)
@@ -524,6 +525,7 @@ def _run():
             import oracle
             oracle.build()
             rows = min(CPU_SAMPLE_ROWS, M)
+            oracle.set_num_threads(oracle.usable_cores())
             cores = oracle.num_threads()
             oracle.linear(xs[0][:rows], W, ws, bias, act)
             t0 = time.perf_counter()

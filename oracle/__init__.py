@@ -283,6 +283,19 @@ def num_threads() -> int:
     return lib().orc_num_threads()
 
 
+def set_num_threads(n: int) -> None:
+    """Threads of the OpenMP loops from now on (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    lib().orc_set_num_threads(C.c_int(int(n)))
+
+
+def usable_cores() -> int:
+    import os
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def linear(x, wq, w_scales, bias=None, act="none", w_layout="NK", threads=0):
     """f32 activations -> per-token quantize -> int32 GEMM -> per-channel tail: the whole hot path."""
     q, _, s32 = quantize_per_token(x)

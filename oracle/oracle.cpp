@@ -539,6 +539,14 @@ void orc_sdpa(const float* q, const float* k, const float* v, int64_t ld_q, int6
 }
 
 double orc_js_round(double x) { return js_round(x); }
+// The benchmark's CPU arm runs under launchers that export OMP_NUM_THREADS=1; it asks for the cores it may use.
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
 int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
