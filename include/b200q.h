@@ -86,7 +86,9 @@ int b200q_timer_stop(b200q_ctx* ctx, float* elapsed_ms);                        
 /* Per-kernel timing: while enabled, every kernel launch is bracketed by CUDA events
  * and its duration added to the sum of its family.  Families (the `kind` argument):
  * 0 quantize_per_token, 1 dequantize_per_token, 2 quantize_static, 3 dequantize_static,
- * 4 weight preparation, 5 tensor-core GEMM (+ fused tail), 6 CUDA-core GEMM, 7 separate tail.
+ * 4 weight preparation, 5 tensor-core GEMM (+ fused tail), 6 CUDA-core GEMM, 7 separate tail, 8 embedding,
+ * 9 LayerNorm + quantize, 10 attention, 11 residual add.  While profiling is on, the events sit between the kernels, so
+ * the dependent launches that let one kernel's set-up overlap the previous kernel's tail are switched off.
  * (No counterpart in the reference, whose runtime only offers measureCudaKernel.) */
 int b200q_profile_enable(b200q_ctx* ctx, int on);
 int b200q_profile_reset(b200q_ctx* ctx);
