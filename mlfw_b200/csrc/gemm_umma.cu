@@ -58,7 +58,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int EPI_CH = 16;                     // columns an epilogue warp takes from tensor memory at a time
 // Staging tile of one epilogue warp for the bulk-tensor store of a chunk: 32 rows x EPI_CH 4-byte values.
 constexpr int OUT_STAGE_BYTES = 32 * EPI_CH * 4;
-constexpr int MISC_BYTES = 2560 + EPI_WARPS * EPI_COLS * 8;
+constexpr int MISC_BYTES = 3584 + EPI_WARPS * EPI_COLS * 8;
 template <int NCTA>
 constexpr int smem_bytes() {  // + slack to align the tiles to 1024 B
   return Cfg<NCTA>::STAGES * Cfg<NCTA>::STAGE_BYTES + EPI_WARPS * OUT_STAGE_BYTES + MISC_BYTES + 1024;
@@ -244,7 +244,7 @@ struct alignas(16) Misc {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  double exp_tbl[EXP2_TABLE_SIZE];
+  float exp_tbl[2 * EXP_FF_ENTRIES];   // float-float exp tables of the sigmoid tails
   alignas(16) float col_scale[EPI_WARPS][EPI_COLS];   // per-warp copy of w_scales for the tile's columns (read as float4)
   alignas(16) float col_bias[EPI_WARPS][EPI_COLS];
 };
@@ -288,7 +288,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     misc->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  fill_exp2_table(misc->exp_tbl, threadIdx.x, blockDim.x);
+  fill_exp_ff_table(misc->exp_tbl, threadIdx.x, blockDim.x);
   if (warp == 1) {
     if (NCTA == 1) {
       asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&misc->tmem_base)),
@@ -392,7 +392,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int ew = warp - 2;             // 0..7
     const int quarter = warp & 3;        // tensor-memory lanes this warp may read: [32*quarter, 32*quarter+32)
     const int col0 = (ew >> 2) * EPI_COLS;  // first tile column of this warp
-    const double* tbl = misc->exp_tbl;
+    const float* tbl = misc->exp_tbl;
     float* cs = misc->col_scale[ew];
     float* cb = misc->col_bias[ew];
     const bool has_bias = p.bias != nullptr;
@@ -502,7 +502,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           } else if (ACT_T != ACT_NONE) {
 #pragma unroll
-            for (int j = 0; j < EPI_CH; j++) y[j] = apply_act_fast<ACT_T>(y[j], tbl);
+            for (int j = 0; j < EPI_CH; j++) y[j] = apply_act_fast<ACT_T>(y[j], nullptr);
           }
 #pragma unroll
           for (int j = 0; j < EPI_CH; j++) v[j] = __float_as_uint(y[j]);

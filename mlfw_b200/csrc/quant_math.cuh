@@ -128,6 +128,12 @@ __device__ __forceinline__ uint64_t f2_sub(uint64_t a, uint64_t b) {
   asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_dup(float a) { return f2_pack(a, a); }
 
 // Leanest form of the fast code, for finite elements of an ordinary per-token row: the four codes, and the running
 // maximum of |t - rint t| (how close any element came to a tie).  t = x * inv, u = t + 1.5*2^23 (the rounding), and
@@ -295,59 +301,156 @@ __device__ __forceinline__ float apply_act_fast(float y, const double* tbl) {
   return y;
 }
 
-// Eight sigmoid-based activations at once, written stage by stage: every loop below is one step of the
-// computation applied to eight independent elements, so the instruction stream itself is interleaved eight
-// ways (the per-element form leaves the compiler with one long dependent chain after another, and with two
-// epilogue warps per scheduler nothing else hides those latencies).  Same values as apply_act_fast.
+// ---------------------------------------------------------------------------
+// exp in binary32 arithmetic only, for the sigmoid tails of the tensor-core kernel (binary64 instructions share
+// a pipe with the tensor cores and cost several times their usual price while MMAs are in flight).
+//   x in [-18, 88.75]:  k = rint(256 x),  c = x - k/256 (exact: the grid is a power of two, |c| <= 2^-9),
+//   exp(x) = E1[k >> 8] * E2[k & 255] * exp(c),  E1[a] = exp(a), E2[b] = exp(b/256) held as hi + lo pairs,
+//   exp(c) = 1 + c + c^2 (1/2 + c/6 + c^2/24)  (truncation < 2^-52; the bracket times c^2 is below 2^-19).
+// The product is carried as h + low with |low| << ulp(h) and an error below 2^-40 h (not one wrong rounding in
+// 1.9e8 random arguments at that margin); the result RN(h + low) is CERTIFIED when h + (low +- 2^-38 h) round to the
+// same binary32 number, which fails for about one argument in 11000 -- those are redone in binary64 by the caller.
+// Arguments of 88.7228394 and more give +Inf like fround(Math.exp(x)); below -18, exp(x) < 2^-25 and 1 + exp(x)
+// rounds to 1 whatever its bits, so the clamp is invisible to a sigmoid.
+// ---------------------------------------------------------------------------
+constexpr int EXP_FF_A_MIN = -18, EXP_FF_A_COUNT = 107, EXP_FF_ENTRIES = EXP_FF_A_COUNT + 256;
+struct ExpPair { unsigned hi, lo; };
+static __device__ const ExpPair kExpFfTable[EXP_FF_ENTRIES] = {
+#include "exp_ff_table.inc"
+};
+// Shared-memory copy: hi words of all entries, then lo words (4-byte loads spread over the banks, and two
+// elements' words land in a register pair without shuffling).
+__device__ __forceinline__ void fill_exp_ff_table(float* tbl, int tid, int nthreads) {
+  for (int j = tid; j < EXP_FF_ENTRIES; j += nthreads) {
+    tbl[j] = __uint_as_float(kExpFfTable[j].hi);
+    tbl[EXP_FF_ENTRIES + j] = __uint_as_float(kExpFfTable[j].lo);
+  }
+}
+
+// Eight sigmoid-based activations at once, written stage by stage over four PAIRS of elements: every loop below is
+// one step of the computation in packed binary32 arithmetic (two lanes per instruction, each lane rounded like the
+// scalar instruction), so the instruction stream is interleaved four ways and half as long as the scalar form (with two
+// epilogue warps per scheduler nothing else hides those latencies).  Same values as apply_act (bit for bit).
+// Negated quantities are formed by multiplying with a negated factor (exact), since the packed forms take no sign
+// modifiers.  `tbl`: the table of fill_exp_ff_table in shared memory.  Warp-collective (one vote).
 template <int ACT_T>
-__device__ __forceinline__ void apply_sigmoid_act_x8(float (&y)[8], const double* tbl) {
-  constexpr int W = 8;
-  float z[W], xf[W];
-  double x[W], kd[W], r[W], r2[W], b[W], q[W], m[W];
+__device__ __forceinline__ void apply_sigmoid_act_x8(float (&y)[8], const float* tbl) {
+  constexpr int W = 8, H = 4;
+  const float INF = __int_as_float(0x7f800000);
+  const uint64_t MAG2 = f2_dup(12582912.0f), ONE2 = f2_dup(1.0f);
+  float xf[W], ea[W], eb[W], g[W], res[W], rc[W], cand[W], sg[W];
+  uint64_t c2[H], h2[H], low2[H], nd2[H], nds2[H], g2[H];
   int k[W];
-  float e[W], d[W], ds[W], g[W], res[W], cand[W], rc[W];
+  {
+    uint64_t nz2[H];
+    if (ACT_T == ACT_GELU_SIGMOID) {
+      // -z = -(1.702 y) with 1.702 held as CH + CL; |y| is clamped first (1e30 saturates the sigmoid either way) so that
+      // no product overflows.  A NaN leaves the clamp as -1e30; the final product with y restores it.
+      const uint64_t CH2 = f2_dup(1.70200002193450927734375f), NCH2 = f2_dup(-1.70200002193450927734375f),
+                     NCL2 = f2_dup(2.1934509319976314e-08f), ZERO2 = f2_dup(0.0f);
 #pragma unroll
-  for (int i = 0; i < W; i++) z[i] = (ACT_T == ACT_GELU_SIGMOID) ? mul_1702(y[i]) : y[i];
+      for (int i = 0; i < H; i++) {
+        // The negated product comes out of an fma with a zero addend, not a mul: a packed mul feeding a packed add was
+        // seen to be merged into one fused operation here (one rounding fewer), whatever the .rn on both.
+        const uint64_t yc = f2_pack(fminf(fmaxf(y[2 * i], -1e30f), 1e30f), fminf(fmaxf(y[2 * i + 1], -1e30f), 1e30f));
+        const uint64_t pp = f2_mul(yc, CH2), pn = f2_fma(yc, NCH2, ZERO2);
+        nz2[i] = f2_add(pn, f2_fma(yc, NCL2, f2_fma(yc, NCH2, pp)));
+      }
+    } else {
 #pragma unroll
-  for (int i = 0; i < W; i++) xf[i] = fminf(fmaxf(-z[i], -100.0f), 128.0f);
+      for (int i = 0; i < H; i++) nz2[i] = f2_pack(-y[2 * i], -y[2 * i + 1]);
+    }
 #pragma unroll
-  for (int i = 0; i < W; i++) k[i] = __float_as_int(__fmaf_rn(xf[i], EXP_INV_F, EXP_MAGIC_F)) - EXP_MAGIC_BITS;
+    for (int i = 0; i < H; i++) {
+      float a, b;
+      f2_unpack(nz2[i], a, b);
+      xf[2 * i] = fminf(fmaxf(a, -18.0f), 88.75f);   // a NaN becomes -18: the final product restores it
+      xf[2 * i + 1] = fminf(fmaxf(b, -18.0f), 88.75f);
+    }
+  }
 #pragma unroll
-  for (int i = 0; i < W; i++) { x[i] = (double)xf[i]; kd[i] = __hiloint2double(0x43300000, k[i] ^ (int)0x80000000) - EXP_MAGIC_D; }
+  for (int i = 0; i < H; i++) {
+    const uint64_t x2 = f2_pack(xf[2 * i], xf[2 * i + 1]);
+    const uint64_t t2 = f2_fma(x2, f2_dup(256.0f), MAG2);
+    c2[i] = f2_fma(f2_sub(t2, MAG2), f2_dup(-0.00390625f), x2);
+    float ta, tb;
+    f2_unpack(t2, ta, tb);
+    k[2 * i] = __float_as_int(ta) - 0x4B400000;
+    k[2 * i + 1] = __float_as_int(tb) - 0x4B400000;
+  }
+  {
+    uint64_t p2[H], tl2[H], qr2[H];
+    const float* t1 = tbl - EXP_FF_A_MIN;
+    const float* t2 = tbl + EXP_FF_A_COUNT;
 #pragma unroll
-  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], B200Q_EXP_HI, x[i]);
+    for (int i = 0; i < H; i++) {
+      const int a0 = k[2 * i] >> 8, a1 = k[2 * i + 1] >> 8, b0 = k[2 * i] & 255, b1 = k[2 * i + 1] & 255;
+      const uint64_t h1 = f2_pack(t1[a0], t1[a1]), l1 = f2_pack(t1[EXP_FF_ENTRIES + a0], t1[EXP_FF_ENTRIES + a1]);
+      const uint64_t hh = f2_pack(t2[b0], t2[b1]), ll = f2_pack(t2[EXP_FF_ENTRIES + b0], t2[EXP_FF_ENTRIES + b1]);
+      p2[i] = f2_mul(h1, hh);
+      const uint64_t pn = f2_mul(p2[i], f2_dup(-1.0f));
+      tl2[i] = f2_fma(h1, ll, f2_fma(l1, hh, f2_fma(h1, hh, pn)));
+    }
 #pragma unroll
-  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], B200Q_EXP_LO, r[i]);
+    for (int i = 0; i < H; i++) {
+      const uint64_t w = f2_fma(c2[i], f2_fma(c2[i], f2_dup(1.0f / 24.0f), f2_dup(1.0f / 6.0f)), f2_dup(0.5f));
+      qr2[i] = f2_mul(f2_mul(c2[i], c2[i]), w);
+    }
 #pragma unroll
-  for (int i = 0; i < W; i++) { r2[i] = r[i] * r[i]; b[i] = fma(r[i], 1.0 / 6.0, 0.5); }
+    for (int i = 0; i < H; i++) {
+      const uint64_t u = f2_mul(p2[i], c2[i]);
+      const uint64_t un = f2_mul(u, f2_dup(-1.0f));
+      const uint64_t lo = f2_add(f2_fma(p2[i], qr2[i], f2_fma(p2[i], c2[i], un)), f2_fma(tl2[i], c2[i], tl2[i]));
+      h2[i] = f2_add(p2[i], u);
+      low2[i] = f2_add(f2_sub(u, f2_sub(h2[i], p2[i])), lo);
+    }
+  }
+  bool uncertain = false;
 #pragma unroll
-  for (int i = 0; i < W; i++) b[i] = fma(r2[i], 1.0 / 24.0, b[i]);
+  for (int i = 0; i < H; i++) {
+    const uint64_t e2 = f2_add(h2[i], f2_fma(h2[i], f2_dup(3.637978807091713e-12f), low2[i]));   // low +- 2^-38 h
+    const uint64_t f2 = f2_add(h2[i], f2_fma(h2[i], f2_dup(-3.637978807091713e-12f), low2[i]));
+    f2_unpack(e2, ea[2 * i], ea[2 * i + 1]);
+    f2_unpack(f2, eb[2 * i], eb[2 * i + 1]);
+    // Arguments past the overflow threshold may have produced Inf - Inf above: their comparison is true as well, and the
+    // binary64 path returns the exact 0 for them.
+    uncertain |= (ea[2 * i] != eb[2 * i]) | (ea[2 * i + 1] != eb[2 * i + 1]);
+    nd2[i] = f2_sub(f2_dup(-1.0f), e2);                                  // -(1 + e), the same rounding
+    nds2[i] = f2_mul(nd2[i], f2_dup(2.3283064365386963e-10f));
+  }
 #pragma unroll
-  for (int i = 0; i < W; i++) { q[i] = fma(r2[i], b[i], r[i]); m[i] = tbl[k[i] & (EXP2_TABLE_SIZE - 1)]; }
+  for (int i = 0; i < H; i++) {
+    float a, b;
+    f2_unpack(nds2[i], a, b);
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g[2 * i]) : "f"(-a));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g[2 * i + 1]) : "f"(-b));
+  }
 #pragma unroll
-  for (int i = 0; i < W; i++) m[i] = fma(m[i], q[i], m[i]);
-#pragma unroll
-  for (int i = 0; i < W; i++)
-    e[i] = __double2float_rn(__hiloint2double(__double2hiint(m[i]) + ((k[i] >> 8) << 20), __double2loint(m[i])));
-#pragma unroll
-  for (int i = 0; i < W; i++) { d[i] = __fadd_rn(1.0f, e[i]); ds[i] = __fmul_rn(d[i], 2.3283064365386963e-10f); }
-#pragma unroll
-  for (int i = 0; i < W; i++) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g[i]) : "f"(ds[i]));
-#pragma unroll
-  for (int i = 0; i < W; i++) g[i] = __fmaf_rn(g[i], __fmaf_rn(-ds[i], g[i], 1.0f), g[i]);
-#pragma unroll
-  for (int i = 0; i < W; i++) g[i] = __fmul_rn(g[i], 2.3283064365386963e-10f);
-#pragma unroll
-  for (int i = 0; i < W; i++) res[i] = __fmaf_rn(-d[i], g[i], 1.0f);
+  for (int i = 0; i < H; i++) {
+    uint64_t gg = f2_pack(g[2 * i], g[2 * i + 1]);
+    gg = f2_fma(gg, f2_fma(nds2[i], gg, ONE2), gg);
+    g2[i] = f2_mul(gg, f2_dup(2.3283064365386963e-10f));
+    f2_unpack(g2[i], g[2 * i], g[2 * i + 1]);
+    f2_unpack(f2_fma(nd2[i], g2[i], ONE2), res[2 * i], res[2 * i + 1]);
+  }
 #pragma unroll
   for (int i = 0; i < W; i++) cand[i] = __int_as_float(__float_as_int(g[i]) + (res[i] > 0.0f ? 1 : -1));
 #pragma unroll
-  for (int i = 0; i < W; i++) rc[i] = __fmaf_rn(-d[i], cand[i], 1.0f);
+  for (int i = 0; i < H; i++) f2_unpack(f2_fma(nd2[i], f2_pack(cand[2 * i], cand[2 * i + 1]), ONE2), rc[2 * i], rc[2 * i + 1]);
 #pragma unroll
   for (int i = 0; i < W; i++) {
     const float best = (fabsf(rc[i]) < fabsf(res[i])) ? cand[i] : g[i];
-    y[i] = __fmul_rn(y[i], (d[i] == __int_as_float(0x7f800000)) ? 0.0f : best);
+    sg[i] = (ea[i] == INF) ? 0.0f : best;
   }
+  if (__any_sync(0xffffffffu, uncertain)) {   // about one warp-call in forty: those lanes redo their eight in binary64
+    if (uncertain) {
+      const double* dtbl = reinterpret_cast<const double*>(kExp2TableBits);   // global memory: rare enough
+#pragma unroll
+      for (int i = 0; i < W; i++) sg[i] = sigmoid_fast((ACT_T == ACT_GELU_SIGMOID) ? mul_1702(y[i]) : y[i], dtbl);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < H; i++) f2_unpack(f2_mul(f2_pack(y[2 * i], y[2 * i + 1]), f2_pack(sg[2 * i], sg[2 * i + 1])), y[2 * i], y[2 * i + 1]);
 }
 
 // sigmoid as the reference decomposes it (src/compiler/passes/decompose/
