@@ -74,7 +74,7 @@ struct b200q_ctx {
   bool sdpa_ready = false;               // the attention kernels' shared-memory sizes have been raised
   int tail_mode = 0;                     // 0: exact sigmoid tails; 1: hardware exp / reciprocal for f32 outputs (tolerance only)
   int sdpa_variant = 0;                  // 0: CUDA-core binary32 FMA; 1: mma.sync with three-way tf32 products
-  uint32_t umma_ready_mask = 0;          // tensor-core kernel variants whose shared-memory attribute is set on this device
+  uint64_t umma_ready_mask = 0;          // tensor-core kernel variants whose shared-memory attribute is set on this device
   uint64_t launches = 0;                 // kernels launched through this context
   // per-kernel CUDA-event timing (off by default): a ring of event pairs, folded into the sums when it wraps or is read
   bool profiling = false;

@@ -244,7 +244,10 @@ struct alignas(16) Misc {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  float exp_tbl[2 * EXP_FF_ENTRIES];   // float-float exp tables of the sigmoid tails
+  union {                                 // one table per kernel variant, by the arithmetic of its sigmoid tail
+    float exp_ff[2 * EXP_FF_ENTRIES];       // binary32 pairs (fill_exp_ff_table)
+    double exp2[EXP2_TABLE_SIZE];           // binary64 (fill_exp2_table)
+  };
   alignas(16) float col_scale[EPI_WARPS][EPI_COLS];   // per-warp copy of w_scales for the tile's columns (read as float4)
   alignas(16) float col_bias[EPI_WARPS][EPI_COLS];
 };
@@ -288,7 +291,8 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     misc->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  fill_exp_ff_table(misc->exp_tbl, threadIdx.x, blockDim.x);
+  if (ACT_T == ACT_GELU_SIGMOID_F32 || ACT_T == ACT_SILU_F32) fill_exp_ff_table(misc->exp_ff, threadIdx.x, blockDim.x);
+  else if (ACT_T == ACT_GELU_SIGMOID || ACT_T == ACT_SILU) fill_exp2_table(misc->exp2, threadIdx.x, blockDim.x);
   if (warp == 1) {
     if (NCTA == 1) {
       asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&misc->tmem_base)),
@@ -392,7 +396,6 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int ew = warp - 2;             // 0..7
     const int quarter = warp & 3;        // tensor-memory lanes this warp may read: [32*quarter, 32*quarter+32)
     const int col0 = (ew >> 2) * EPI_COLS;  // first tile column of this warp
-    const float* tbl = misc->exp_tbl;
     float* cs = misc->col_scale[ew];
     float* cb = misc->col_bias[ew];
     const bool has_bias = p.bias != nullptr;
@@ -490,13 +493,14 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               for (int e = 0; e < 4; e++) y[j4 * 4 + e] = __fadd_rn(scale_acc_wide(a[j4 * 4 + e], __fmul_rn(a_scale, wsv[e])), bv[e]);
             }
           }
-          if (ACT_T == ACT_GELU_SIGMOID || ACT_T == ACT_SILU) {
+          if (ACT_T == ACT_GELU_SIGMOID || ACT_T == ACT_SILU || ACT_T == ACT_GELU_SIGMOID_F32 || ACT_T == ACT_SILU_F32) {
 #pragma unroll
             for (int j0 = 0; j0 < EPI_CH; j0 += 8) {
               float r8[8];
 #pragma unroll
               for (int e = 0; e < 8; e++) r8[e] = y[j0 + e];
-              apply_sigmoid_act_x8<ACT_T>(r8, tbl);
+              if (ACT_T == ACT_GELU_SIGMOID || ACT_T == ACT_SILU) apply_sigmoid_act_x8<ACT_T>(r8, misc->exp2);
+              else apply_sigmoid_act_wide<ACT_T == ACT_SILU_F32 ? ACT_SILU : ACT_GELU_SIGMOID, 8>(r8, misc->exp_ff);
 #pragma unroll
               for (int e = 0; e < 8; e++) y[j0 + e] = r8[e];
             }
@@ -725,20 +729,32 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   // f32 output with the approximate sigmoid tails (b200q_set_tail_mode 1): [gelu_sigmoid, silu][CTAs per tile]
   static const KernelFn approx[2][2] = {{gemm_i8_umma_kernel<ACT_GELU_SIGMOID_APPROX, OUT_F32, 1>, gemm_i8_umma_kernel<ACT_GELU_SIGMOID_APPROX, OUT_F32, 2>},
                                         {gemm_i8_umma_kernel<ACT_SILU_APPROX, OUT_F32, 1>, gemm_i8_umma_kernel<ACT_SILU_APPROX, OUT_F32, 2>}};
+  // The same exact values from binary32 arithmetic alone, for launches whose main loop keeps the tensor pipe busy for
+  // longer than the tail takes: binary64 instructions slow down several times while MMAs are in flight (C3 and
+  // C5 shapes gain 3 to 5 %), but run on an otherwise idle pipe when the tail is the longer part (K 768: 172 us
+  // against 203 us).
+  static const KernelFn tensor_bound[2][2] = {{gemm_i8_umma_kernel<ACT_GELU_SIGMOID_F32, OUT_F32, 1>, gemm_i8_umma_kernel<ACT_GELU_SIGMOID_F32, OUT_F32, 2>},
+                                              {gemm_i8_umma_kernel<ACT_SILU_F32, OUT_F32, 1>, gemm_i8_umma_kernel<ACT_SILU_F32, OUT_F32, 2>}};
+  constexpr int64_t SIGMOID_F32_MIN_K = 4096;
   B200Q_REQUIRE(act >= 0 && act <= 4, "unknown activation %d", act);
   B200Q_REQUIRE((out_i32 != nullptr) + (out_f32 != nullptr) + (out_q != nullptr) == 1,
                 "tensor-core int8 gemm writes exactly one output");
   KernelFn fn = out_i32 ? raw[ncta - 1] : table[act][out_q ? 1 : 0][ncta - 1];
   int slot_act = act;
-  if (ctx->tail_mode == 1 && out_f32 != nullptr && (act == ACT_GELU_SIGMOID || act == ACT_SILU)) {
-    fn = approx[act == ACT_SILU ? 1 : 0][ncta - 1];
-    slot_act = act == ACT_SILU ? 6 : 5;
+  if (out_f32 != nullptr && (act == ACT_GELU_SIGMOID || act == ACT_SILU)) {
+    if (ctx->tail_mode == 1) {
+      fn = approx[act == ACT_SILU ? 1 : 0][ncta - 1];
+      slot_act = act == ACT_SILU ? 6 : 5;
+    } else if (K >= SIGMOID_F32_MIN_K) {
+      fn = tensor_bound[act == ACT_SILU ? 1 : 0][ncta - 1];
+      slot_act = act == ACT_SILU ? 8 : 7;
+    }
   }
   const int smem = ncta == 1 ? smem_bytes<1>() : smem_bytes<2>();
-  const int slot_idx = (out_i32 ? 14 : slot_act * 2 + (out_q ? 1 : 0)) * 2 + (ncta - 1);   // < 32
-  if (!(ctx->umma_ready_mask & (1u << slot_idx))) {
+  const int slot_idx = (out_i32 ? 31 : slot_act * 2 + (out_q ? 1 : 0)) * 2 + (ncta - 1);   // < 64
+  if (!(ctx->umma_ready_mask & (1ull << slot_idx))) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    ctx->umma_ready_mask |= 1u << slot_idx;
+    ctx->umma_ready_mask |= 1ull << slot_idx;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);

@@ -17,7 +17,8 @@ namespace b200q {
 
 enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU_SIGMOID = 2, ACT_GELU_TANH = 3, ACT_SILU = 4,
                  // internal: the sigmoid forms through the hardware exponential and reciprocal (tolerance only)
-                 ACT_GELU_SIGMOID_APPROX = 5, ACT_SILU_APPROX = 6 };
+                 ACT_GELU_SIGMOID_APPROX = 5, ACT_SILU_APPROX = 6,
+                 ACT_GELU_SIGMOID_F32 = 7, ACT_SILU_F32 = 8 };
 
 // ---------------------------------------------------------------------------
 // Rounding a quotient x / s to the nearest integer, ties toward +infinity.
@@ -301,6 +302,61 @@ __device__ __forceinline__ float apply_act_fast(float y, const double* tbl) {
   return y;
 }
 
+// Eight sigmoid-based activations at once, written stage by stage: every loop below is one step of the
+// computation applied to eight independent elements, so the instruction stream itself is interleaved eight
+// ways (the per-element form leaves the compiler with one long dependent chain after another, and with two
+// epilogue warps per scheduler nothing else hides those latencies).  Same values as apply_act_fast.
+template <int ACT_T>
+__device__ __forceinline__ void apply_sigmoid_act_x8(float (&y)[8], const double* tbl) {
+  constexpr int W = 8;
+  float z[W], xf[W];
+  double x[W], kd[W], r[W], r2[W], b[W], q[W], m[W];
+  int k[W];
+  float e[W], d[W], ds[W], g[W], res[W], cand[W], rc[W];
+#pragma unroll
+  for (int i = 0; i < W; i++) z[i] = (ACT_T == ACT_GELU_SIGMOID) ? mul_1702(y[i]) : y[i];
+#pragma unroll
+  for (int i = 0; i < W; i++) xf[i] = fminf(fmaxf(-z[i], -100.0f), 128.0f);
+#pragma unroll
+  for (int i = 0; i < W; i++) k[i] = __float_as_int(__fmaf_rn(xf[i], EXP_INV_F, EXP_MAGIC_F)) - EXP_MAGIC_BITS;
+#pragma unroll
+  for (int i = 0; i < W; i++) { x[i] = (double)xf[i]; kd[i] = __hiloint2double(0x43300000, k[i] ^ (int)0x80000000) - EXP_MAGIC_D; }
+#pragma unroll
+  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], B200Q_EXP_HI, x[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++) r[i] = fma(-kd[i], B200Q_EXP_LO, r[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++) { r2[i] = r[i] * r[i]; b[i] = fma(r[i], 1.0 / 6.0, 0.5); }
+#pragma unroll
+  for (int i = 0; i < W; i++) b[i] = fma(r2[i], 1.0 / 24.0, b[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++) { q[i] = fma(r2[i], b[i], r[i]); m[i] = tbl[k[i] & (EXP2_TABLE_SIZE - 1)]; }
+#pragma unroll
+  for (int i = 0; i < W; i++) m[i] = fma(m[i], q[i], m[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++)
+    e[i] = __double2float_rn(__hiloint2double(__double2hiint(m[i]) + ((k[i] >> 8) << 20), __double2loint(m[i])));
+#pragma unroll
+  for (int i = 0; i < W; i++) { d[i] = __fadd_rn(1.0f, e[i]); ds[i] = __fmul_rn(d[i], 2.3283064365386963e-10f); }
+#pragma unroll
+  for (int i = 0; i < W; i++) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g[i]) : "f"(ds[i]));
+#pragma unroll
+  for (int i = 0; i < W; i++) g[i] = __fmaf_rn(g[i], __fmaf_rn(-ds[i], g[i], 1.0f), g[i]);
+#pragma unroll
+  for (int i = 0; i < W; i++) g[i] = __fmul_rn(g[i], 2.3283064365386963e-10f);
+#pragma unroll
+  for (int i = 0; i < W; i++) res[i] = __fmaf_rn(-d[i], g[i], 1.0f);
+#pragma unroll
+  for (int i = 0; i < W; i++) cand[i] = __int_as_float(__float_as_int(g[i]) + (res[i] > 0.0f ? 1 : -1));
+#pragma unroll
+  for (int i = 0; i < W; i++) rc[i] = __fmaf_rn(-d[i], cand[i], 1.0f);
+#pragma unroll
+  for (int i = 0; i < W; i++) {
+    const float best = (fabsf(rc[i]) < fabsf(res[i])) ? cand[i] : g[i];
+    y[i] = __fmul_rn(y[i], (d[i] == __int_as_float(0x7f800000)) ? 0.0f : best);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // exp in binary32 arithmetic only, for the sigmoid tails of the tensor-core kernel (binary64 instructions share
 // a pipe with the tensor cores and cost several times their usual price while MMAs are in flight).
@@ -313,6 +369,7 @@ __device__ __forceinline__ float apply_act_fast(float y, const double* tbl) {
 // Arguments of 88.7228394 and more give +Inf like fround(Math.exp(x)); below -18, exp(x) < 2^-25 and 1 + exp(x)
 // rounds to 1 whatever its bits, so the clamp is invisible to a sigmoid.
 // ---------------------------------------------------------------------------
+constexpr float EXP_OVERFLOW_F = 88.72283935546875f;   // the smallest binary32 x whose exp rounds to +Inf
 constexpr int EXP_FF_A_MIN = -18, EXP_FF_A_COUNT = 107, EXP_FF_ENTRIES = EXP_FF_A_COUNT + 256;
 struct ExpPair { unsigned hi, lo; };
 static __device__ const ExpPair kExpFfTable[EXP_FF_ENTRIES] = {
@@ -333,10 +390,10 @@ __device__ __forceinline__ void fill_exp_ff_table(float* tbl, int tid, int nthre
 // epilogue warps per scheduler nothing else hides those latencies).  Same values as apply_act (bit for bit).
 // Negated quantities are formed by multiplying with a negated factor (exact), since the packed forms take no sign
 // modifiers.  `tbl`: the table of fill_exp_ff_table in shared memory.  Warp-collective (one vote).
-template <int ACT_T>
-__device__ __forceinline__ void apply_sigmoid_act_x8(float (&y)[8], const float* tbl) {
-  constexpr int W = 8, H = 4;
-  const float INF = __int_as_float(0x7f800000);
+template <int ACT_T, int W>
+__device__ __forceinline__ void apply_sigmoid_act_wide(float (&y)[W], const float* tbl) {
+  static_assert(W % 2 == 0, "elements are processed in pairs");
+  constexpr int H = W / 2;
   const uint64_t MAG2 = f2_dup(12582912.0f), ONE2 = f2_dup(1.0f);
   float xf[W], ea[W], eb[W], g[W], res[W], rc[W], cand[W], sg[W];
   uint64_t c2[H], h2[H], low2[H], nd2[H], nds2[H], g2[H];
@@ -412,9 +469,9 @@ __device__ __forceinline__ void apply_sigmoid_act_x8(float (&y)[8], const float*
     const uint64_t f2 = f2_add(h2[i], f2_fma(h2[i], f2_dup(-3.637978807091713e-12f), low2[i]));
     f2_unpack(e2, ea[2 * i], ea[2 * i + 1]);
     f2_unpack(f2, eb[2 * i], eb[2 * i + 1]);
-    // Arguments past the overflow threshold may have produced Inf - Inf above: their comparison is true as well, and the
-    // binary64 path returns the exact 0 for them.
-    uncertain |= (ea[2 * i] != eb[2 * i]) | (ea[2 * i + 1] != eb[2 * i + 1]);
+    // Arguments from the overflow threshold on (exp rounds to +Inf, the sigmoid is 0) may have produced Inf - Inf above:
+    // they are settled by the comparison with the threshold alone.
+    uncertain |= ((ea[2 * i] != eb[2 * i]) & (xf[2 * i] < EXP_OVERFLOW_F)) | ((ea[2 * i + 1] != eb[2 * i + 1]) & (xf[2 * i + 1] < EXP_OVERFLOW_F));
     nd2[i] = f2_sub(f2_dup(-1.0f), e2);                                  // -(1 + e), the same rounding
     nds2[i] = f2_mul(nd2[i], f2_dup(2.3283064365386963e-10f));
   }
@@ -440,7 +497,7 @@ __device__ __forceinline__ void apply_sigmoid_act_x8(float (&y)[8], const float*
 #pragma unroll
   for (int i = 0; i < W; i++) {
     const float best = (fabsf(rc[i]) < fabsf(res[i])) ? cand[i] : g[i];
-    sg[i] = (ea[i] == INF) ? 0.0f : best;
+    sg[i] = (xf[i] < EXP_OVERFLOW_F) ? best : 0.0f;
   }
   if (__any_sync(0xffffffffu, uncertain)) {   // about one warp-call in forty: those lanes redo their eight in binary64
     if (uncertain) {

@@ -113,7 +113,7 @@ EXACT_ACTS = {"none", "relu", "gelu_sigmoid", "silu"}
 
 @pytest.mark.parametrize("variant", [1, 2, 3])
 @pytest.mark.parametrize("act", ACTS)
-@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (130, 260, 144), (64, 1000, 768), (5, 7, 16)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (130, 260, 144), (64, 1000, 768), (5, 7, 16), (136, 264, 4096)])
 def test_int8_linear_fused_tail(ctx, orc, M, N, K, act, variant):
     rng = np.random.default_rng(M + N + K + len(act))
     x, W, ws, bias = linear_case(rng, M, N, K)
@@ -289,6 +289,49 @@ def test_fused_tail_extreme_arguments(ctx, orc, act):
         fin = np.isfinite(ref)
         assert (out[ok & ~fin] == ref[ok & ~fin]).all()
         assert np.abs(out[fin].astype(np.float64) - ref[fin]).max() <= TOL * np.abs(ref[fin]).max()
+
+
+@pytest.mark.parametrize("K", [64, 4096])
+@pytest.mark.parametrize("act", ["gelu_sigmoid", "silu"])
+def test_sigmoid_tail_argument_sweep(ctx, orc, act, K):
+    """The exact sigmoid tails over their whole argument range: a dense sweep, runs of neighbouring floats around the
+    overflow threshold of exp (88.72...), around the clamp where 1 + exp(x) rounds to 1 (-18) and around zero.  The
+    accumulators are zero, so the pre-activation is the bias itself.  K 64 runs the binary64 form of the tail, K 4096
+    the binary32 form (some of its arguments land on the binary64 redo)."""
+    rng = np.random.default_rng(43)
+    M, N = 128, 8192
+    q = np.zeros((M, K), np.int8)
+    s32 = np.ones(M, np.float32)
+    W = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    ws = np.full(N, 1e-3, np.float32)
+    k = 1.0 if act == "silu" else 1.0 / 1.702
+
+    def run_of_neighbours(center, n):
+        v = np.empty(n, np.float32)
+        v[n // 2] = np.float32(center)
+        for i in range(n // 2 + 1, n):
+            v[i] = np.nextafter(v[i - 1], np.float32(np.inf))
+        for i in range(n // 2 - 1, -1, -1):
+            v[i] = np.nextafter(v[i + 1], np.float32(-np.inf))
+        return v
+
+    biases = [np.linspace(-91.0 * k, 21.0 * k, N).astype(np.float32),
+              (rng.uniform(-90.0, 20.0, N) * k).astype(np.float32),
+              np.concatenate([run_of_neighbours(-88.7228394 * k, 2048), run_of_neighbours(-88.75 * k, 1024),
+                              run_of_neighbours(18.0 * k, 2048), run_of_neighbours(0.0, 1024),
+                              run_of_neighbours(-1.0 / 256 * k, 1024), run_of_neighbours(17.32868 * k, 1024)])]
+    dq, dW, ds, dws = ctx.to_device(q), ctx.to_device(W), ctx.to_device(s32), ctx.to_device(ws)
+    for bias in biases:
+        assert bias.size == N
+        ref = orc.epilogue(np.zeros((M, N), np.int32), s32, ws, bias, act)
+        db = ctx.to_device(bias)
+        dout = Guarded(ctx, (M, N), np.float32)
+        ctx.int8_linear(dq.ptr, ds.ptr, dW.ptr, dws.ptr, db.ptr, act, M, N, K, dout.ptr)
+        ctx.sync()
+        ctx.check_status()
+        out = dout.download()
+        nd = int((out.view(np.uint32) != ref.view(np.uint32)).sum())
+        assert nd == 0, f"{nd} of {out.size} outputs differ from the oracle"
 
 
 @pytest.mark.parametrize("act", ["gelu_sigmoid", "silu"])
