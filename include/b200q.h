@@ -59,8 +59,9 @@ int b200q_set_gemm_variant(b200q_ctx* ctx, int variant);
  * 1: hardware exponential and reciprocal -- results within about 1e-6 (relative) of mode 0, inside the 1e-5 bar, at the
  * speed of the other tails.  int8 (requantized) outputs always use the exact form: their codes are integer results. */
 int b200q_set_tail_mode(b200q_ctx* ctx, int mode);
-/* Per-token quantize: 0 = rows staged through shared memory by bulk copies when they fit (default);
- * 1 = register-resident kernel only. */
+/* Per-token quantize: 0 = rows staged through shared memory by bulk copies when they fit; rows of 8, 12 and 16 KB are
+ * moved on into registers and their slot is handed back before the arithmetic (default);
+ * 1 = unstaged kernel only; 2 = staged, both passes read shared memory whatever the row length. */
 int b200q_set_quant_variant(b200q_ctx* ctx, int variant);
 /* Kernels launched through this context since it was created. */
 uint64_t b200q_launch_count(b200q_ctx* ctx);

@@ -69,8 +69,8 @@ struct b200q_ctx {
   b200q::Workspace ws_stage_in, ws_stage_out;  // device staging of the host-buffer entry points
   double wait_limit_s = 2.0;             // bound of every device-side wait
   int gemm_variant = 0;                  // 0 auto, 1 CUDA-core kernel only, 2 tensor cores with one CTA per tile, 3 with CTA pairs
-  int quant_variant = 0;                 // 0 auto (rows staged in shared memory when they fit), 1 register-resident kernel only
-  bool quant_staged_ready = false;
+  int quant_variant = 0;                 // 0 auto (rows staged in shared memory when they fit), 1 unstaged kernel only, 2 staged with both passes from shared memory
+  uint32_t quant_staged_ready = 0;        // instances of the staged quantize kernel whose shared-memory attribute is set
   bool sdpa_ready = false;               // the attention kernels' shared-memory sizes have been raised
   int tail_mode = 0;                     // 0: exact sigmoid tails; 1: hardware exp / reciprocal for f32 outputs (tolerance only)
   int sdpa_variant = 0;                  // 0: CUDA-core binary32 FMA; 1: mma.sync with three-way tf32 products

@@ -218,7 +218,12 @@ __device__ __forceinline__ float fmax3n(float a, float b, float c) {
   return r;
 }
 
-__global__ void __launch_bounds__(QT_THREADS, 1)
+// NW consumer warps.  VPT == 0: rows of any length, both passes read the slot.  VPT > 0: one row per slot, K4 == 32 * VPT
+// (VPT a multiple of 4): the warp moves its row into registers (VPT float4 per lane), hands the slot back at once and
+// does both passes from registers -- a slot is then busy for the time of the copy instead of the time of the encode,
+// and the ring no longer runs out of free slots while loads are in flight (NW shrinks as VPT grows: register file).
+template <int NW, int VPT>
+__global__ void __launch_bounds__(32 * (NW + 1), 1)
 quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4, int rows_per_chunk, int slots,
                                  int8_t* __restrict__ q, float* __restrict__ scales, float qmin, float qmax, uint32_t* status,
                                  unsigned long long limit_ns) {
@@ -250,7 +255,7 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
   }
   __syncthreads();
 
-  if (warp == QT_CONSUMER_WARPS) {
+  if (warp == NW) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       uint32_t i = 0;
@@ -277,7 +282,7 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
     const float limit = guard_limit(qmin, qmax);
     uint32_t i = 0;
     for (int64_t chunk = blockIdx.x; chunk < num_chunks; chunk += gridDim.x, i++) {
-      if ((int)(i % QT_CONSUMER_WARPS) != warp) continue;   // uniform per warp
+      if ((int)(i % NW) != warp) continue;   // uniform per warp
       const int s = i % slots;
       const int turn = (int)(i / slots);
       const uint32_t ph = (uint32_t)turn & 1u;
@@ -302,6 +307,88 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
       const int64_t row0 = chunk * rows_per_chunk;
       const int rows = (int)((M - row0 < rows_per_chunk) ? (M - row0) : rows_per_chunk);
       const float4* slot = reinterpret_cast<const float4*>(qt_smem + (int64_t)s * chunk_bytes);
+      if (VPT > 0) {
+        constexpr int V = VPT > 0 ? VPT : 4;
+        float4 v[V];
+#pragma unroll
+        for (int j = 0; j < V; j++) v[j] = slot[lane + 32 * j];
+        // the row is in registers: hand the slot back before any arithmetic
+        __syncwarp();
+        if (lane == 0) {
+          turns[s] = turn + 1;
+          __threadfence_block();
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(q_smem_u32(&empty[s])) : "memory");
+        }
+        float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+        float mn2 = mn, mx2 = mx;
+#pragma unroll
+        for (int j = 0; j < V; j += 2) {   // NaN-propagating, two chains per bound (see the two-pass form below)
+          mn = fmin3n(mn, v[j].x, v[j].y); mx = fmax3n(mx, v[j].x, v[j].y);
+          mn2 = fmin3n(mn2, v[j].z, v[j].w); mx2 = fmax3n(mx2, v[j].z, v[j].w);
+          mn = fmin3n(mn, v[j + 1].x, v[j + 1].y); mx = fmax3n(mx, v[j + 1].x, v[j + 1].y);
+          mn2 = fmin3n(mn2, v[j + 1].z, v[j + 1].w); mx2 = fmax3n(mx2, v[j + 1].z, v[j + 1].w);
+        }
+        mn = fmin3n(mn, mn, mn2); mx = fmax3n(mx, mx, mx2);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          mn = fmin3n(mn, mn, __shfl_xor_sync(0xffffffffu, mn, o));
+          mx = fmax3n(mx, mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        const bool nan_row = (mn != mn) || (mx != mx);
+        if (nan_row) {   // the reference's strict comparisons ignore NaN: rescan with the NaN-dropping forms
+          mn = __int_as_float(0x7f800000); mx = __int_as_float(0xff800000);
+#pragma unroll
+          for (int j = 0; j < V; j++) {
+            mn = fminf(fminf(mn, v[j].x), fminf(fminf(v[j].y, v[j].z), v[j].w));
+            mx = fmaxf(fmaxf(mx, v[j].x), fmaxf(fmaxf(v[j].y, v[j].z), v[j].w));
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+          }
+        }
+        const float absmax = fmaxf(fabsf(mn), fabsf(mx));
+        const float inv = __fdiv_rn(127.0f, absmax);
+        const bool exact_only = nan_row || limit < 127.0f || !((mn < mx) && absmax <= 3.402823466e38f && is_normal_f32(inv));
+        uint32_t* qr = reinterpret_cast<uint32_t*>(q) + row0 * K4 + lane;
+        // The unrolled body holds the fast encode only.  Groups that come near a tie are noted and redone afterwards,
+        // and odd rows are encoded entirely, from the row in global memory (just read, so in L2): rare, and it keeps
+        // the register copy of the row statically indexed and the binary64 code out of the unrolled loop.
+        const float4* xg = reinterpret_cast<const float4*>(x) + row0 * K4 + lane;
+        uint32_t redo = 0;
+        if (!exact_only) {
+          const uint64_t inv2 = f2_pack(inv, inv), magic2 = f2_pack(12582912.0f, 12582912.0f);
+#pragma unroll
+          for (int g = 0; g < V; g += 4) {
+            float far = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; j++) __stcs(qr + 32 * (g + j), pack4_fast_lean(v[g + j], inv2, magic2, far));
+            redo |= (far >= 0.49993920f) ? (1u << (g / 4)) : 0u;       // 0.5 - 127.5 * 2^-21
+          }
+        } else {
+          redo = (V / 4 >= 32) ? 0xffffffffu : ((1u << (V / 4)) - 1u);
+        }
+        while (redo) {
+          const int g = (__ffs((int)redo) - 1) * 4;
+          redo &= redo - 1;
+          float4 t[4];
+          int tie = 0;
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            t[j] = xg[32 * (g + j)];
+            (void)quantize_fast_bounded(t[j].x, inv, tie); (void)quantize_fast_bounded(t[j].y, inv, tie);
+            (void)quantize_fast_bounded(t[j].z, inv, tie); (void)quantize_fast_bounded(t[j].w, inv, tie);
+          }
+          if (exact_only || tie >= 0x3f000000) {
+            const double sd = row_scale(mn, mx);
+#pragma unroll
+            for (int j = 0; j < 4; j++) __stcs(qr + 32 * (g + j), pack4_exact_p(t[j], sd, qmin, qmax));
+          }
+        }
+        if (lane == 0) scales[row0] = exact_only ? (float)row_scale(mn, mx) : __fdiv_rn(absmax, 127.0f);
+        continue;
+      }
       for (int r = 0; r < rows; r++) {
         const float4* xr = slot + (int64_t)r * K4;
         // pass 1: range of the row with NaN-PROPAGATING three-input min / max (one instruction per two elements and
@@ -784,15 +871,24 @@ int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t
     int slots = (int)((196 * 1024) / chunk_bytes);
     if (slots > QT_MAX_SLOTS) slots = QT_MAX_SLOTS;
     const size_t smem = (size_t)slots * chunk_bytes;
-    if (!ctx->quant_staged_ready) {
-      B200Q_CHECK_CUDA(cudaFuncSetAttribute(quantize_per_token_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      ctx->quant_staged_ready = true;
+    // Rows of 8, 12 and 16 KB go through the register-resident form (one row per slot there).
+    typedef void (*StagedFn)(const float*, int64_t, int, int, int, int8_t*, float*, float, float, uint32_t*, unsigned long long);
+    StagedFn fn = quantize_per_token_staged_kernel<QT_CONSUMER_WARPS, 0>;
+    int consumer_warps = QT_CONSUMER_WARPS, ready_bit = 0;
+    if (rows_per_chunk == 1 && ctx->quant_variant != 2) {
+      if (K4 == 32 * 32) { fn = quantize_per_token_staged_kernel<11, 32>; consumer_warps = 11; ready_bit = 1; }
+      else if (K4 == 32 * 24) { fn = quantize_per_token_staged_kernel<14, 24>; consumer_warps = 14; ready_bit = 2; }
+      else if (K4 == 32 * 16) { fn = quantize_per_token_staged_kernel<14, 16>; consumer_warps = 14; ready_bit = 3; }
+    }
+    if (!(ctx->quant_staged_ready & (1u << ready_bit))) {
+      B200Q_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      ctx->quant_staged_ready |= 1u << ready_bit;
     }
     const int64_t num_chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
     const unsigned blocks = (unsigned)(num_chunks < ctx->sm_count ? num_chunks : ctx->sm_count);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks);
-    cfg.blockDim = dim3(QT_THREADS);
+    cfg.blockDim = dim3(32 * (consumer_warps + 1));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -800,7 +896,7 @@ int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->profiling ? 0 : 1;   // with profiling on an event separates the kernels anyway
-    B200Q_CHECK_CUDA(cudaLaunchKernelEx(&cfg, quantize_per_token_staged_kernel, x, M, K4, rows_per_chunk, slots, q, scales,
+    B200Q_CHECK_CUDA(cudaLaunchKernelEx(&cfg, fn, x, M, K4, rows_per_chunk, slots, q, scales,
                                         (float)qmin, (float)qmax, ctx->status_dev,
                                         (unsigned long long)(ctx->wait_limit_s * 1e9)));
   } else if (vec) {

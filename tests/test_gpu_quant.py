@@ -35,13 +35,14 @@ def run_quantize_per_token(ctx, x, qmin=-127, qmax=127):
 SHAPES = [(1, 1), (3, 5), (2, 6), (7, 64), (33, 128), (256, 512), (5, 768), (9, 3072), (4, 4096), (17, 4100),
           (3, 8192), (2, 28672), (2, 32772), (1, 40000), (300, 4),
           # 64 rows or more: the shared-memory staged kernel (variant 0) unless a row exceeds 32 KB
-          (100, 768), (65, 3072), (64, 8192), (70, 4096), (333, 512), (64, 4100), (1000, 16), (129, 2052),
+          (100, 768), (65, 3072), (64, 8192), (70, 4096), (333, 512), (64, 4100), (1000, 16), (129, 2052), (200, 2048),
           # many chunks per block: every ring of slots wraps several times
           (6000, 4096), (40000, 512), (20011, 768)]
 
 
-# variant 0: rows staged in shared memory when they fit; 1: register-resident kernel only
-@pytest.mark.parametrize("variant", [0, 1])
+# variant 0: rows staged in shared memory when they fit (rows of 8, 12 and 16 KB are then moved into registers and their
+# slot handed back early); 1: unstaged kernel only; 2: staged, both passes from shared memory for every row length
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("M,K", SHAPES)
 def test_quantize_per_token_bit_exact(ctx, orc, M, K, variant):
     rng = np.random.default_rng(M * 100003 + K)
@@ -97,6 +98,43 @@ def test_quantize_per_token_constructed_ties(ctx, orc):
     rq, _, rs32 = orc.quantize_per_token(x)
     assert (s.view(np.uint32) == rs32.view(np.uint32)).all()
     assert (q == rq).all(), f"{int((q != rq).sum())} tie codes differ"
+
+
+@pytest.mark.parametrize("variant", [0, 2])
+@pytest.mark.parametrize("K", [2048, 3072, 4096])
+def test_quantize_per_token_long_rows_special_and_ties(ctx, orc, K, variant):
+    """Row lengths that take the register-resident form of the staged kernel: odd rows (NaN, infinities, constant,
+    denormal, huge), constructed ties with their neighbours, and ordinary rows in between, many rows per block."""
+    rng = np.random.default_rng(K)
+    rows = []
+    for rep in range(40):
+        rows.append(rng.standard_normal(K).astype(np.float32) * np.float32(10.0 ** rng.integers(-3, 4)))
+        r = rng.standard_normal(K).astype(np.float32); r[rng.integers(0, K, 5)] = np.nan; rows.append(r)
+        r = rng.standard_normal(K).astype(np.float32); r[rng.integers(0, K)] = np.inf; rows.append(r)
+        r = rng.standard_normal(K).astype(np.float32); r[rng.integers(0, K)] = -np.inf; rows.append(r)
+        rows.append(np.full(K, np.float32(rng.standard_normal()), np.float32))
+        rows.append((rng.uniform(-1, 1, K) * 1e-41).astype(np.float32))
+        rows.append((rng.uniform(-1, 1, K) * 3e38).astype(np.float32))
+        absmax = np.float32([1.0, 3.0, 127.0, 6.0, 0.37, 1e-3, 254.0, 5.5, 2.0 / 3.0, 1e20][rep % 10])
+        sc = np.float64(absmax) / 127.0
+        ks = rng.integers(-127, 127, size=(K - 1) // 3).astype(np.float64)
+        base = ((ks + 0.5) * sc).astype(np.float32)
+        row = np.concatenate([[absmax], base, np.nextafter(base, np.float32(np.inf)), np.nextafter(base, np.float32(-np.inf))])
+        row = np.concatenate([row, np.zeros(K - row.size)]).astype(np.float32)
+        rows.append(np.clip(row, -absmax, absmax))
+    rows.append(np.full(K, np.nan, np.float32))
+    rows.append(np.zeros(K, np.float32))
+    x = np.stack(rows)
+    ctx.set_quant_variant(variant)
+    try:
+        for qmin, qmax in [(-127, 127), (-128, 127), (-100, 100)]:
+            q, s = run_quantize_per_token(ctx, x, qmin, qmax)
+            rq, _, rs32 = orc.quantize_per_token(x, qmin, qmax)
+            assert (s.view(np.uint32) == rs32.view(np.uint32)).all()
+            assert (q == rq).all(), f"{int((q != rq).sum())} codes differ"
+    finally:
+        ctx.set_quant_variant(0)
+    ctx.check_status()
 
 
 @pytest.mark.parametrize("M,K", [(1, 1), (3, 5), (33, 128), (5, 768), (4, 4096), (17, 4100), (2, 28672), (300, 4)])
