@@ -143,6 +143,21 @@ def run_roundtrip(ctx, pk, iters, warmup):
         gbs = bytes_each / (t / n * 1e-3) / 1e9
         rt[name] = {"achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
                     "frac_of_nominal_8000": gbs / 8000.0, "avg_launch_ms": t / n}
+    # The same kernels launched back to back (no event between launches: one pair of events around `iters` launches
+    # of one kernel, inputs alternating), which is how they run inside a stream of work; the per-launch figures above
+    # carry the events' own few microseconds per launch.
+    for name, launch in (("quantize_per_token", lambda i: ctx.quantize_per_token(d2[i % 2], M2, K2, q2[i % 2], s2[i % 2])),
+                         ("dequantize_per_token", lambda i: ctx.dequantize_per_token(q2[i % 2], s2[i % 2], M2, K2, y2[i % 2]))):
+        for i in range(3):
+            launch(i)
+        ctx.sync()
+        ctx.timer_start()
+        for i in range(iters):
+            launch(i)
+        ms = ctx.timer_stop() / iters
+        gbs = bytes_each / (ms * 1e-3) / 1e9
+        rt[name]["back_to_back"] = {"achieved": gbs, "frac": gbs / pk["hbm_gbs"], "avg_launch_ms": ms, "launches": iters}
+    ctx.check_status()
     return {"workload": "quantize -> dequantize, f32 [16384,4096], 0.1% outliers", "algorithmic_bytes": bytes_each, **rt}
 
 
