@@ -164,12 +164,19 @@ int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const f
 /* b200q_linear_f32 for callers that must not allocate device memory inside the call (a host whose own pool
  * owns the device, a latency-bound serving loop, a phase in which the CUDA allocation calls are not allowed).
  * This entry point has no counterpart in the reference.  Same arguments and result as b200q_linear_f32; the
- * int8 codes and per-token scales of the activations go to a fixed array inside the library image instead of
- * a workspace, so: M * K <= 4 Mi elements and M <= 16384 rows, and the shape must be one the tensor-core
- * kernel takes (K a multiple of 16, 16-byte aligned weights) - anything else is rejected with an error.
- * The array costs 4 MiB + 64 KiB on every GPU that loads the library, until the process exits.  It is shared by
- * all calls on a GPU: calls that overlap on one GPU (two contexts) race on it.  The first call on each device
- * looks the array's device address up (no allocation); make that call before beginning any stream capture. */
+ * int8 codes and per-token scales of the activations go to a fixed array of static device memory inside the
+ * library instead of a workspace, so: M * K <= 4 Mi elements and M <= 16384 rows, and the shape must be one the
+ * tensor-core kernel takes (K a multiple of 16, 16-byte aligned weights) - anything else is rejected with an error.
+ * The array (4 MiB + 64 KiB) exists on every device on which this process has created a context with
+ * b200q_create - that call loads the array's module on the device and looks its address up, so the memory is
+ * reserved at context creation, not in here - and lives until that device's CUDA context is destroyed (normally
+ * process exit); devices the process never creates a context on hold nothing.  It is shared by all calls on a
+ * device and keeps the last call's contents (nothing in it needs to start at zero).  Calls on one context may be
+ * enqueued back to back; calls that overlap on one device (two contexts, two host threads) race on the array.
+ * The entry point calls no CUDA allocation routine.  The CUDA runtime still loads a kernel's code on its first
+ * launch and this library sets a per-kernel attribute on first use, so a host that must have even that out of the
+ * way (before handing all device memory to its pool, or before a stream capture) makes one warm-up call per
+ * activation and shape class (M below / from 1024 rows; row length 8, 12, 16 KB or other) it is going to use. */
 int b200q_linear_f32_noalloc(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const float* w_scales, const float* bias,
                              int act, int64_t M, int64_t N, int64_t K, float* out);
 /* Same call with HOST activations and HOST result (what RuntimeModule.run hands a

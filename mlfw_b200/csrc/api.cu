@@ -118,6 +118,12 @@ int b200q_create(int device, b200q_ctx** out) {
     b200q_destroy(ctx);
     return 1;
   }
+  // The fixed scratch of b200q_linear_f32_noalloc comes into being here (its module is loaded on this device), not
+  // inside the first call of that entry point.
+  if (int pe = noalloc_prepare(device)) {
+    b200q_destroy(ctx);
+    return pe;
+  }
   *out = ctx;
   return 0;
 }

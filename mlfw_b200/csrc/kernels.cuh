@@ -48,4 +48,8 @@ int launch_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* resid
 int launch_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v,
                     int64_t B, int64_t H, int64_t S, int64_t Dh, float scale, int causal, float* out, int64_t ld_o);
 
+// Looks up (and caches) the device address of the fixed scratch array of b200q_linear_f32_noalloc for `device`, which
+// must be current; called once per context at creation, so the array's module is loaded before any call needs it.
+int noalloc_prepare(int device);
+
 }  // namespace b200q
