@@ -13,11 +13,16 @@ rows against replicated weights (no collective on the data path), so the scaling
 One JSON line is printed by rank 0.  `value` is tokens/s with inputs resident in HBM,
 `e2e` is the same metric through the host-buffer entry point (pinned host memory in, host
 memory out, copies inside the timed region), `roofline` describes the dominant kernel,
-`cpu_baseline` the CPU port timed on this machine.
+`cpu_baseline` the CPU port timed on this machine.  The same line carries, at every N, three
+fixed-size (strong-scaling) records, each checked against the unsharded result on the same
+GPUs: the large GEMM with its 8192 rows split over the ranks (`c3_strong`), and the stack of
+four wide linears split by rows (`c5_mshard`) and by output channels with NCCL collectives
+inside the library (`c5_nshard`).
 """
 from __future__ import annotations
 
 import argparse
+import functools
 import json
 import os
 import statistics
@@ -105,6 +110,62 @@ class ClockSampler:
                 "power_w_max": max(power), "samples": len(sm)}
 
 
+def gpu_numa_info(gpu_index: int) -> dict:
+    """NUMA node of a GPU and the CPUs of that node, from sysfs (read only)."""
+    info = {"gpu": gpu_index, "node": None, "cpus": None}
+    try:
+        bus = subprocess.check_output(["nvidia-smi", f"--id={gpu_index}", "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                                      text=True, stderr=subprocess.DEVNULL).strip().lower()
+        if bus.count(":") == 2 and len(bus.split(":")[0]) == 8:
+            bus = bus[4:]                                    # nvidia-smi prints an 8-digit domain, sysfs a 4-digit one
+        info["pci"] = bus
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read().strip())
+        info["node"] = node
+        if node >= 0:
+            info["cpus"] = open(f"/sys/devices/system/node/node{node}/cpulist").read().strip()
+    except Exception as exc:                                  # no sysfs entry, no nvidia-smi: nothing to bind to
+        info["error"] = f"{type(exc).__name__}: {exc}"
+    return info
+
+
+def _parse_cpulist(text: str):
+    cpus = set()
+    for part in text.split(","):
+        if "-" in part:
+            a, b = part.split("-")
+            cpus.update(range(int(a), int(b) + 1))
+        elif part:
+            cpus.add(int(part))
+    return cpus
+
+
+def bind_to_numa_node(info: dict) -> dict:
+    """Pins this process's threads to the CPUs of the GPU's NUMA node and prefers that node's memory for what it
+    allocates from now on (set_mempolicy MPOL_PREFERRED).  Returns what was done."""
+    out = {"node": info.get("node"), "bound": False}
+    if info.get("node") is None or info["node"] < 0 or not info.get("cpus"):
+        out["why"] = "the platform reports no NUMA node for this GPU" if not info.get("error") else info["error"]
+        return out
+    try:
+        allowed = os.sched_getaffinity(0)
+        want = _parse_cpulist(info["cpus"]) & allowed
+        if want and want != allowed:
+            os.sched_setaffinity(0, want)
+            out["cpus"] = len(want)
+        else:
+            out["cpus"] = len(allowed)
+        import ctypes
+        libc = ctypes.CDLL(None, use_errno=True)
+        mask = ctypes.c_ulong(1 << info["node"])
+        rc = libc.syscall(238, 1, ctypes.byref(mask), ctypes.c_ulong(64))      # set_mempolicy(MPOL_PREFERRED, mask, 64)
+        out["mempolicy"] = "preferred" if rc == 0 else f"set_mempolicy failed (errno {ctypes.get_errno()})"
+        out["bound"] = bool(want and want != allowed) or rc == 0
+        out["same_as_before"] = not (want and want != allowed)
+    except Exception as exc:
+        out["why"] = f"{type(exc).__name__}: {exc}"
+    return out
+
+
 def make_case(workload: str, rank: int):
     from mlfw_b200 import synth
     M, K, N, act = WORKLOADS[workload]
@@ -116,11 +177,18 @@ def make_case(workload: str, rank: int):
     return M, K, N, act, xs, W, ws, bias
 
 
+@functools.lru_cache(maxsize=1)
+def c2_input():
+    from mlfw_b200 import synth
+    M2, K2 = C2_SHAPE
+    return synth.with_outliers(synth.normal(synth.tensor_seed(0, 20), (M2, K2)), synth.tensor_seed(0, 21), synth.tensor_seed(0, 22))
+
+
 def run_roundtrip(ctx, pk, iters, warmup):
     """Standalone quantize -> dequantize of f32 [16384,4096] with 0.1% outliers (HBM bound); per-kernel GB/s."""
     from mlfw_b200 import synth
     M2, K2 = C2_SHAPE
-    x2 = synth.with_outliers(synth.normal(synth.tensor_seed(0, 20), (M2, K2)), synth.tensor_seed(0, 21), synth.tensor_seed(0, 22))
+    x2 = c2_input()
     d2 = [ctx.to_device(x2), ctx.to_device(x2[::-1].copy())]      # two sets alternate: 671 MB per set pair, > L2
     q2 = [ctx.empty((M2, K2), np.int8) for _ in range(2)]
     s2 = [ctx.empty((M2,), np.float32) for _ in range(2)]
@@ -161,85 +229,245 @@ def run_roundtrip(ctx, pk, iters, warmup):
     return {"workload": "quantize -> dequantize, f32 [16384,4096], 0.1% outliers", "algorithmic_bytes": bytes_each, **rt}
 
 
-def run_c5(args, ctx, dist, rank, world, local_rank, barrier, max_over_ranks):
-    """Config 5: four int8 linears 8192 <-> 28672 with SiLU and a per-token requantize between them, M = 4096 rows in
-    total (strong scaling).  mshard: each rank takes M / world rows of every layer, weights replicated, no
-    collective.  nshard: each rank takes N / world output channels of every layer; per layer two [M]-float
-    all-reduces (row ranges) and one int8 all-gather of the column blocks over NVLink."""
-    import torch
-    from mlfw_b200 import sharding, synth
-    M, dims, acts = 4096, [8192, 28672, 8192, 28672, 8192], ["silu", "silu", "silu", "none"]
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    gen = np.random.default_rng(5)                               # same weights on every rank
-    x = synth.normal(synth.tensor_seed(5, 0), (M, dims[0]))
+C5_M, C5_DIMS, C5_ACTS = 4096, [8192, 28672, 8192, 28672, 8192], ["silu", "silu", "silu", "none"]
+
+
+class Comm:
+    """What the benchmark needs from the ranks: a barrier, max / min over ranks of a host number, all ranks' values,
+    and a byte broadcast (torch.distributed when there is more than one rank; identity otherwise)."""
+
+    def __init__(self, dist, local_rank):
+        self.dist, self.local_rank = dist, local_rank
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+
+    def _reduce(self, v, op):
+        if self.dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{self.local_rank}")
+        self.dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    def max(self, v: float) -> float:
+        return self._reduce(v, self.dist.ReduceOp.MAX) if self.dist is not None else v
+
+    def min(self, v: float) -> float:
+        return self._reduce(v, self.dist.ReduceOp.MIN) if self.dist is not None else v
+
+    def all(self, v: float):
+        if self.dist is None:
+            return [v]
+        import torch
+        world = self.dist.get_world_size()
+        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{self.local_rank}")
+        out = torch.empty(world, dtype=torch.float64, device=t.device)
+        self.dist.all_gather_into_tensor(out, t)
+        return [float(x) for x in out.cpu()]
+
+    def broadcast_bytes(self, data: bytes, n: int) -> bytes:
+        if self.dist is None:
+            return data
+        import torch
+        t = torch.zeros(n, dtype=torch.uint8, device=f"cuda:{self.local_rank}")
+        if data is not None:
+            t.copy_(torch.frombuffer(bytearray(data), dtype=torch.uint8))
+        self.dist.broadcast(t, src=0)
+        return bytes(t.cpu().numpy().tobytes())
+
+
+def timed_steps(ctx, comm, step, steps, warmup):
+    """`warmup` untimed steps, then `steps` steps between a barrier + sync on both sides; ms per step, max over ranks."""
+    for i in range(warmup):
+        step(i)
+    ctx.sync()
+    ctx.check_status()
+    comm.barrier()
+    ctx.sync()
+    ctx.timer_start()
+    for i in range(steps):
+        step(i)
+    ms = ctx.timer_stop()
+    ctx.sync()
+    comm.barrier()
+    return comm.max(ms) / steps
+
+
+@functools.lru_cache(maxsize=1)
+def c5_layers():
+    """Weights of the four wide linears, the same on every rank (numpy's PCG64, seed 5; scales ~U(1e-3,1e-2)/sqrt(K)
+    so that activations stay O(1))."""
+    gen = np.random.default_rng(5)
     layers = []
     for i in range(4):
-        K, N = dims[i], dims[i + 1]
+        K, N = C5_DIMS[i], C5_DIMS[i + 1]
         w = gen.integers(-127, 128, size=(N, K), dtype=np.int8)
         ws = (gen.uniform(1e-3, 1e-2, N) / np.sqrt(K)).astype(np.float32)
-        layers.append((w, ws, acts[i]))
+        layers.append((w, ws, C5_ACTS[i]))
+    return layers
+
+
+def run_c5_records(ctx, comm, rank, world, steps, warmup, modes=("mshard", "nshard"), chunk_choices=(1, 2, 4)):
+    """Config 5 at fixed total size (M = 4096 rows): unsharded on this rank's GPU (the yardstick and the expected
+    values), rows split over the ranks (no collective), and output channels split over the ranks (one max-reduction
+    of the row-range keys and one int8 all-gather per layer, NCCL inside the library, b200q_group_linear_nshard).
+    Every sharded result is compared bit for bit with the unsharded one."""
+    import mlfw_b200
+    from mlfw_b200 import sharding, synth
+    M, dims = C5_M, C5_DIMS
+    x = synth.normal(synth.tensor_seed(5, 0), (M, dims[0]))
+    layers = c5_layers()
     ops_total = sum(2.0 * M * dims[i] * dims[i + 1] for i in range(4))
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dx = ctx.to_device(x)
+    dls = [(ctx.to_device(w), ctx.to_device(ws), a) for w, ws, a in layers]
+    q = [ctx.empty((M, d), np.int8) for d in dims[:-1]]
+    sc = [ctx.empty((M,), np.float32) for _ in dims[:-1]]
+    ref_out = ctx.empty((M, dims[-1]), np.float32)
 
-    if args.mode == "mshard":
+    def chain(xbuf, rows, out):
+        ctx.quantize_per_token(xbuf, rows, dims[0], q[0], sc[0])
+        for i, (dw, dws, a) in enumerate(dls):
+            if i < 3:
+                ctx.int8_linear_requant_token(q[i], sc[i], dw, dws, None, a, rows, dims[i + 1], dims[i], q[i + 1], sc[i + 1])
+            else:
+                ctx.int8_linear(q[i], sc[i], dw, dws, None, a, rows, dims[i + 1], dims[i], out)
+
+    l0 = ctx.launch_count()
+    chain(dx, M, ref_out)
+    launches_per_step = ctx.launch_count() - l0
+    ms_unsharded = timed_steps(ctx, comm, lambda i: chain(dx, M, ref_out), steps, warmup)
+    ref_host = ref_out.download()
+    records = {"unsharded_on_each_gpu": {"ms_per_step": ms_unsharded, "tokens_per_s": M / (ms_unsharded * 1e-3),
+                                         "tops": ops_total / (ms_unsharded * 1e-3) / 1e12, "gpu_launches_per_step": launches_per_step}}
+
+    def record(ms, extra):
+        return {"ms_per_step": ms, "tokens_per_s": M / (ms * 1e-3), "tops": ops_total / (ms * 1e-3) / 1e12,
+                "efficiency_vs_n1": ms_unsharded / (world * ms), "n_gpus": world, **extra}
+
+    if "mshard" in modes:
         r0, rows = sharding.row_block(M, world, rank)
-        dx = ctx.to_device(x[r0:r0 + rows])
-        dls = [(ctx.to_device(w), ctx.to_device(ws), a) for w, ws, a in layers]
-        q = [ctx.empty((rows, d), np.int8) for d in dims[:-1]]
-        sc = [ctx.empty((rows,), np.float32) for _ in dims[:-1]]
         out = ctx.empty((rows, dims[-1]), np.float32)
+        xrows = dx.ptr + r0 * dims[0] * 4
+        ms = timed_steps(ctx, comm, lambda i: chain(xrows, rows, out), steps, warmup)
+        same = bool((out.download().view(np.uint32) == ref_host[r0:r0 + rows].view(np.uint32)).all())
+        records["c5_mshard"] = record(ms, {"matches_unsharded": bool(comm.min(1.0 if same else 0.0) == 1.0), "rows_per_gpu": rows,
+                                           "parallelism": f"rows split x{world}, weights replicated, no collective",
+                                           "bound_by": "tensor pipe + the f32 round trip of the per-token requantize; weight reads of 235 MB per layer per GPU stay below it"})
+        out.free()
 
-        def step():
-            ctx.quantize_per_token(dx, rows, dims[0], q[0], sc[0])
-            for i, (dw, dws, a) in enumerate(dls):
-                if i < 3:
-                    ctx.int8_linear_requant_token(q[i], sc[i], dw, dws, None, a, rows, dims[i + 1], dims[i], q[i + 1], sc[i + 1])
-                else:
-                    ctx.int8_linear(q[i], sc[i], dw, dws, None, a, rows, dims[i + 1], dims[i], out)
-            ctx.sync()
-    else:
-        shards = []
-        for i, (w, ws, a) in enumerate(layers):
-            c0, cols = sharding.column_block(dims[i + 1], world, rank)
-            shards.append(sharding.ShardedLayer(dims[i], dims[i + 1], c0, cols, torch.from_numpy(np.ascontiguousarray(w[c0:c0 + cols])).to(dev),
-                                                torch.from_numpy(ws[c0:c0 + cols].copy()).to(dev), None, a))
-        stack = sharding.ColumnShardedStack(sharding.DeviceOps(ctx, torch), dist, rank, world, shards)
-        tx = torch.from_numpy(x).to(dev)
-        tq = torch.empty((M, dims[0]), dtype=torch.int8, device=dev)
-        ts = torch.empty((M,), dtype=torch.float32, device=dev)
+    if "nshard" in modes:
+        uid = mlfw_b200.Group.unique_id() if rank == 0 else None
+        uid = comm.broadcast_bytes(uid, 128)
+        group = mlfw_b200.Group.join(ctx, uid, rank, world)
+        try:
+            cols = [d // world for d in dims[1:]]
+            W = [dls[i][0].ptr + rank * cols[i] * dims[i] for i in range(4)]          # rows [rank*cols, ...) of the K-major weight
+            WS = [dls[i][1].ptr + rank * cols[i] * 4 for i in range(4)]
+            gq = [q[0]] + [ctx.empty((M, d), np.int8) for d in dims[1:-1]]
+            gs = [sc[0]] + [ctx.empty((M,), np.float32) for _ in dims[1:-1]]
+            out = ctx.empty((M, cols[3]), np.float32)
 
-        def step():
-            torch.cuda.current_stream(dev).synchronize()
-            ctx.quantize_per_token(tx.data_ptr(), M, dims[0], tq.data_ptr(), ts.data_ptr())
-            ctx.sync()
-            stack.forward(tq, ts, M, last_f32=True)
-            torch.cuda.current_stream(dev).synchronize()
+            def nstep(i):
+                ctx.quantize_per_token(dx, M, dims[0], gq[0], gs[0])
+                blocks = 1
+                for li in range(4):
+                    act = C5_ACTS[li]
+                    if li < 3:
+                        group.linear_nshard([gq[li]], [gs[li]], blocks, [W[li]], [WS[li]], None, act, M, dims[li + 1], dims[li],
+                                            q_out=[gq[li + 1]], out_scales=[gs[li + 1]])
+                    else:
+                        group.linear_nshard([gq[li]], [gs[li]], blocks, [W[li]], [WS[li]], None, act, M, dims[li + 1], dims[li], out_f32=[out])
+                    blocks = world
 
-    del layers
-    for _ in range(max(args.warmup, 3)):
-        step()
-    ctx.check_status()
-    launches0 = ctx.launch_count()
-    barrier()
-    torch.cuda.synchronize(dev)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize(dev)
-    ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
-    ctx.check_status()
-    return {"metric": "int8_linear_tokens_per_s", "value": M / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "int8 x int8 -> int32, f32 tail", "data": "synthetic (weights from numpy's PCG64, seed 5)",
-            "config": {"workload": C5_WORKLOAD, "M_total": M, "dims": dims, "activation": "silu", "mode": args.mode,
-                       "parallelism": (f"M-sharded x{world}, weights replicated, no collective" if args.mode == "mshard" else
-                                       f"N-sharded x{world}: per layer 2 all-reduces of [M] floats + 1 int8 all-gather (NCCL)")},
-            "tops": ops_total / (ms * 1e-3) / 1e12, "gpu_launches": ctx.launch_count() - launches0}
+            by_chunks = {}
+            all_same = True
+            for ch in chunk_choices:
+                group.set_chunks(ch)
+                ms = timed_steps(ctx, comm, nstep, steps, warmup)
+                group.sync()
+                c0 = rank * cols[3]
+                same = bool((out.download().view(np.uint32) == np.ascontiguousarray(ref_host[:, c0:c0 + cols[3]]).view(np.uint32)).all())
+                same = bool(comm.min(1.0 if same else 0.0) == 1.0)
+                all_same = all_same and same
+                by_chunks[str(ch)] = {"ms_per_step": ms, "matches_unsharded": same}
+            best = min(by_chunks, key=lambda k: by_chunks[k]["ms_per_step"])
+            up_bytes = M * dims[1] * (world - 1) / world
+            records["c5_nshard"] = record(by_chunks[best]["ms_per_step"], {
+                "matches_unsharded": all_same, "row_chunks": int(best), "by_row_chunks": by_chunks, "nccl_version": group.nccl_version(),
+                "parallelism": f"output channels split x{world}; per layer one max-reduction of 2*M range keys and one int8 all-gather (NCCL, inside libb200q.so)",
+                "bytes_received_per_gpu_per_step": (2 * M * dims[1] + M * dims[2]) * (world - 1) / world,
+                "bound_by": ("NVLink: the all-gather of the 28672-wide layers delivers %.0f MB to every GPU, as long as its GEMM share at %d GPUs"
+                             % (up_bytes / 1e6, world)) if world > 1 else "same kernels as unsharded"})
+        finally:
+            group.close()
+    for buf in [dx, ref_out] + q + sc:
+        buf.free()
+    return records
 
 
-def run_c4(args, ctx, rank, world, barrier, max_over_ranks):
+def run_c3_strong(ctx, comm, rank, world, steps, warmup, act="gelu_tanh"):
+    """Config 3 at its fixed size: the 8192 rows split evenly over the ranks, weights replicated, no collective.
+    Each rank cycles through all row blocks of the full input (its own first), so every step reads and writes
+    memory that the previous steps have pushed out of L2 (the full input and output are 134 MB each)."""
+    from mlfw_b200 import sharding, synth
+    M, K, N = 8192, 4096, 4096
+    x = synth.normal(synth.tensor_seed(0, 300), (M, K))
+    W = synth.randint_i8(synth.tensor_seed(0, 1), (N, K))
+    ws = synth.uniform(synth.tensor_seed(0, 2), (N,), 1e-3, 1e-2)
+    bias = synth.normal(synth.tensor_seed(0, 3), (N,), 0.0, 0.01)
+    dx, dW, dws, db = ctx.to_device(x), ctx.to_device(W), ctx.to_device(ws), ctx.to_device(bias)
+    ref, out = ctx.empty((M, N), np.float32), ctx.empty((M, N), np.float32)
+    ms_unsharded = timed_steps(ctx, comm, lambda i: ctx.linear_f32(dx, dW, dws, db, act, M, N, K, ref), steps, warmup)
+    blocks = [sharding.row_block(M, world, r) for r in range(world)]
+
+    def shard_step(i):
+        r0, rows = blocks[(rank + i) % world]
+        ctx.linear_f32(dx.ptr + r0 * K * 4, dW, dws, db, act, rows, N, K, out.ptr + r0 * N * 4)
+
+    ms = timed_steps(ctx, comm, shard_step, steps, warmup)
+    # the same cycle recorded once and replayed: one launch per `world` steps instead of two per step
+    ms_graph, graph_note = None, None
+    try:
+        for i in range(world):
+            shard_step(i)
+        ctx.sync()
+        ctx.graph_begin()
+        try:
+            for i in range(world):
+                shard_step(i)
+        finally:
+            graph = ctx.graph_end()
+        cycles = max(1, steps // world)
+        ms_graph = timed_steps(ctx, comm, lambda i: ctx.graph_launch(graph), cycles, max(1, warmup // world)) / world
+        ctx.graph_destroy(graph)
+    except Exception as exc:                                   # the replayed form is an extra; the plain one stands
+        graph_note = f"{type(exc).__name__}: {exc}"
+    r0, rows = blocks[rank]
+    out.fill_bytes(0)
+    ctx.linear_f32(dx.ptr + r0 * K * 4, dW, dws, db, act, rows, N, K, out.ptr + r0 * N * 4)
+    ctx.sync()
+    got = out.download()[r0:r0 + rows]
+    same = bool((got.view(np.uint32) == ref.download()[r0:r0 + rows].view(np.uint32)).all())
+    same = bool(comm.min(1.0 if same else 0.0) == 1.0)
+    best = min(ms, ms_graph) if ms_graph else ms
+    rec = {"ms_per_step": best, "tokens_per_s": M / (best * 1e-3), "tops": 2.0 * M * N * K / (best * 1e-3) / 1e12,
+           "efficiency_vs_n1": ms_unsharded / (world * best), "matches_unsharded": same, "n_gpus": world, "rows_per_gpu": rows,
+           "ms_per_step_plain_launches": ms, "ms_per_step_replayed": ms_graph, "ms_unsharded_on_each_gpu": ms_unsharded,
+           "parallelism": f"rows split x{world}, weights replicated, no collective; a step is one rank-local quantize + GEMM launch pair",
+           "l2": "each rank cycles through all row blocks of the 134 MB input and output, so no step finds its data in L2",
+           "bound_by": ("one wave of %d tiles of 256x256 on 74 CTA pairs plus launch latency: at %d rows per GPU the GEMM is %d tiles"
+                        % ((rows + 255) // 256 * 16, rows, (rows + 255) // 256 * 16))}
+    if graph_note:
+        rec["replay_unavailable"] = graph_note
+    for b in (dx, dW, dws, db, ref, out):
+        b.free()
+    return rec
+
+
+def run_c4(args, ctx, rank, world, comm):
+    barrier, max_over_ranks = comm.barrier, comm.max
     """Config 4: one pre-norm GPT block (d 768, 12 heads, ff 3072) over 32 x 512 tokens per GPU, from token ids to the
     block's output: embedding, LayerNorm + quantize, four int8 linears, causal attention, residual adds."""
     from mlfw_b200.block import GPTBlock, random_block_params
@@ -301,6 +529,231 @@ def run_c4(args, ctx, rank, world, barrier, max_over_ranks):
             "roofline_sdpa": {"bound": "fp32 CUDA cores", "achieved": attn_flops / (sd_ms * 1e-3) / 1e12 if sd_ms else None, "unit": "TFLOP/s",
                               "note": "binary32 FMA on CUDA cores (the 1e-5 bar rules out tf32 tensor-core products)"},
             "gpu_launches": launches}
+
+
+def run_sustained(ctx, step, M, N, K, ms_burst, gpu_index, seconds=2.5):
+    """The same step back to back for a few seconds, clocks sampled inside: what the part sustains under its power cap.
+    No clock is set or reset; the dependence on the clock shows as throughput x (max MHz / median MHz)."""
+    n = int(max(50, min(60000, seconds * 1e3 / max(ms_burst, 1e-3))))
+    sampler = ClockSampler(gpu_index)
+    ctx.sync()
+    sampler.start()
+    time.sleep(0.1)
+    ctx.timer_start()
+    for i in range(n):
+        step(i)
+    ms = ctx.timer_stop()
+    clocks = sampler.stop()
+    ctx.check_status()
+    per = ms / n
+    tops = 2.0 * M * N * K / (per * 1e-3) / 1e12
+    rec = {"seconds": ms * 1e-3, "steps": n, "ms_per_step": per, "tokens_per_s": M / (per * 1e-3), "tops_step": tops, "clocks": clocks,
+           "note": "tops_step counts the GEMM's 2*M*N*K over the whole step (quantize + GEMM); the GEMM's share of a step is in `roofline`"}
+    if clocks.get("sm_mhz") and clocks.get("sm_max_mhz"):
+        rec["tops_step_scaled_to_max_clock"] = tops * clocks["sm_max_mhz"] / clocks["sm_mhz"]
+    return rec
+
+
+def run_e2e(ctx, comm, rank, world, local_rank, args, M, K, N, act, x_host, dW, dws, db):
+    """The step through the host-buffer entry point (b200q_linear_f32_host): page-locked buffers before and after the
+    process is bound to its GPU's NUMA node, ordinary pageable numpy arrays (what a caller holding typed arrays has),
+    and the bare copy bandwidths of every rank while all ranks copy at once."""
+    out = {}
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def timed(hx, hy):
+        ctx.linear_f32_host(hx, dW, dws, db, act, M, N, K, hy)
+        comm.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            ctx.linear_f32_host(hx, dW, dws, db, act, M, N, K, hy)
+        return comm.max((time.perf_counter() - t0) / e2e_steps)
+
+    hx, hy = ctx.pinned((M, K), np.float32), ctx.pinned((M, N), np.float32)
+    hx.array[...] = x_host
+    dt_before = timed(hx, hy)
+    checksum = float(hy.array[::997, ::97].sum())
+
+    # bare copies, all ranks at once: where the host side saturates
+    dtmp = ctx.empty((M, K), np.float32)
+    reps = 3
+    comm.barrier()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        dtmp.ctx.lib.b200q_upload(ctx.handle, dtmp.ptr, hx.ptr, M * K * 4)
+    h2d = M * K * 4 * reps / (time.perf_counter() - t0) / 1e9
+    comm.barrier()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        dtmp.ctx.lib.b200q_download(ctx.handle, hy.ptr, dtmp.ptr, M * K * 4)
+    d2h = M * K * 4 * reps / (time.perf_counter() - t0) / 1e9
+    dtmp.free()
+    out["copy_bandwidth"] = {"h2d_gbs_per_rank": comm.all(h2d), "d2h_gbs_per_rank": comm.all(d2h),
+                             "note": f"134 MB page-locked copies, one direction at a time, all {world} ranks copying at the same moment"}
+
+    # pageable buffers: the copies stage through the driver and no longer overlap
+    px = np.array(x_host, dtype=np.float32, copy=True)
+    py = np.empty((M, N), np.float32)
+    dt_pageable = timed(px, py)
+    same_pageable = bool(np.array_equal(py[::997, ::97], hy.array[::997, ::97]))
+
+    # bound to the GPU's NUMA node: new page-locked buffers allocated after the binding
+    numa = gpu_numa_info(local_rank)
+    bound = bind_to_numa_node(numa)
+    dt_after = None
+    if bound.get("bound"):
+        hx2, hy2 = ctx.pinned((M, K), np.float32), ctx.pinned((M, N), np.float32)
+        hx2.array[...] = x_host
+        dt_after = timed(hx2, hy2)
+        hx2.free(); hy2.free()
+    any_bound = comm.max(1.0 if dt_after is not None else 0.0) == 1.0
+    if any_bound and dt_after is None:       # every rank takes part in the timed region's barrier
+        dt_after = timed(hx, hy)
+    hx.free(); hy.free()
+    best = min(dt_before, dt_after) if dt_after else dt_before
+    out["e2e"] = {"value": world * M / best, "unit": "tokens/s", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
+                  "ms_per_step": best * 1e3, "steps": e2e_steps, "result_checksum": checksum,
+                  "api": "b200q_linear_f32_host (page-locked host input, host output, synchronous; row blocks pipelined over three streams)",
+                  "ms_per_step_unbound": dt_before * 1e3, "ms_per_step_numa_bound": dt_after * 1e3 if dt_after else None,
+                  "numa": {**{k: v for k, v in numa.items() if k != "gpu"}, **bound}}
+    out["e2e_pageable"] = {"value": world * M / dt_pageable, "unit": "tokens/s", "ms_per_step": dt_pageable * 1e3, "steps": e2e_steps,
+                           "same_result_as_page_locked": same_pageable,
+                           "api": "b200q_linear_f32_host with ordinary (pageable) numpy arrays, as a caller holding typed arrays would pass"}
+    return out
+
+
+def _cpu_time(fn, reps):
+    fn()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        r = fn()
+    return (time.perf_counter() - t0) / reps, r
+
+
+def run_cpu_baselines(ctx, x, W, ws, bias, act, dout, M):
+    """The CPU restatement of the reference timed on this machine's cores for every configuration: configs 1 and 2 in
+    full, the large GEMM and the wide stack on their first 64 rows (rows are independent), the transformer block on
+    one sequence of 512 tokens.  A reported baseline, not a target."""
+    import oracle
+    from mlfw_b200 import synth
+    oracle.build()
+    oracle.set_num_threads(oracle.usable_cores())
+    cores = oracle.num_threads()
+    res = {}
+    rows = min(CPU_SAMPLE_ROWS, M)
+    dt, (ref_out, _, _, _) = _cpu_time(lambda: oracle.linear(x[:rows], W, ws, bias, act), 3)
+    rows1 = min(8, M)      # the reference's own execution model is one thread
+    t0 = time.perf_counter()
+    oracle.linear(x[:rows1], W, ws, bias, act, threads=1)
+    dt1 = time.perf_counter() - t0
+    got = dout.download()[:rows]
+    err = float(np.abs(got.astype(np.float64) - ref_out).max() / np.abs(ref_out).max())
+    c3 = {"value": rows / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+          "sample": f"first {rows} of {M} rows, all of N and K, 3 repetitions; C++ restatement of the reference's CPU path with OpenMP",
+          "gpu_vs_cpu_max_err_over_absmax": err,
+          "single_core": {"value": rows1 / dt1, "unit": "tokens/s", "sample": f"first {rows1} rows, one thread, one repetition"}}
+    res["cpu_baseline"] = c3
+    per = {"c3_gemm_8192x4096x4096": c3}
+
+    # config 1: the two-layer MLP in full
+    x1 = synth.normal(synth.tensor_seed(0, 0), (256, 512))
+    w1 = synth.normal(synth.tensor_seed(0, 1), (1024, 512), 0.0, 0.02)
+    w2 = synth.normal(synth.tensor_seed(0, 3), (256, 1024), 0.0, 0.02)
+    b1 = synth.uniform(synth.tensor_seed(0, 2), (1024,), -0.1, 0.1)
+    b2 = synth.uniform(synth.tensor_seed(0, 4), (256,), -0.1, 0.1)
+    qw = []
+    for w in (w1, w2):
+        sc = oracle.per_channel_scales(w, w.shape, 0)
+        qw.append((oracle.quantize_per_channel(w, w.shape, 0, sc), sc.astype(np.float32)))
+
+    def mlp():
+        h, _, _, _ = oracle.linear(x1, qw[0][0], qw[0][1], b1, "relu")
+        return oracle.linear(h, qw[1][0], qw[1][1], b2, "none")[0]
+
+    dt, _ = _cpu_time(mlp, 5)
+    per["c1_mlp_256x512x1024x256"] = {"value": 256 / dt, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": "in full, 5 repetitions"}
+
+    # config 2: the round trip in full
+    M2, K2 = C2_SHAPE
+    x2 = c2_input()
+
+    def roundtrip():
+        q, _, s32 = oracle.quantize_per_token(x2)
+        return oracle.dequantize_per_token_f32(q, s32)
+
+    dt, _ = _cpu_time(roundtrip, 2)
+    per["c2_roundtrip_16384x4096"] = {"value": 2 * (5.0 * M2 * K2 + 4.0 * M2) / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                                      "sample": "in full (quantize + dequantize of 67.1 M elements), 2 repetitions; algorithmic bytes as for the GPU kernels"}
+
+    # config 4: one sequence of 512 tokens through the whole block
+    from mlfw_b200.block import random_block_params
+    D, H, FF, S = 768, 12, 3072, 512
+    prm = random_block_params(D, FF, seed=4)
+    lin = {}
+    for name, w, b in (("qkv", np.concatenate([prm["wq"], prm["wk"], prm["wv"]]), np.concatenate([prm["bq"], prm["bk"], prm["bv"]])),
+                       ("o", prm["wo"], prm["bo"]), ("f1", prm["w1"], prm["b1"]), ("f2", prm["w2"], prm["b2"])):
+        sc = oracle.per_channel_scales(w, w.shape, 0)
+        lin[name] = (oracle.quantize_per_channel(w, w.shape, 0, sc), sc.astype(np.float32), b)
+    h0 = (np.random.default_rng(40).standard_normal((S, D)) * 0.02).astype(np.float32)
+
+    def block():
+        n1 = oracle.layer_norm(h0, prm["ln1_gamma"], prm["ln1_beta"])
+        qkv = oracle.linear(n1, *lin["qkv"], "none")[0]
+        a = oracle.sdpa(np.ascontiguousarray(qkv[:, :D]), np.ascontiguousarray(qkv[:, D:2 * D]), np.ascontiguousarray(qkv[:, 2 * D:]),
+                        1, H, S, 64, 0.125, True)
+        o = oracle.linear(a, *lin["o"], "none")[0]
+        n2, xsum = oracle.layer_norm(o, prm["ln2_gamma"], prm["ln2_beta"], add=h0, want_sum=True)
+        f1 = oracle.linear(n2, *lin["f1"], "gelu_sigmoid")[0]
+        f2 = oracle.linear(f1, *lin["f2"], "none")[0]
+        return xsum + f2
+
+    dt, _ = _cpu_time(block, 2)
+    per["c4_gpt_block_d768_h12_ff3072"] = {"value": S / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                          "sample": "one sequence of 512 tokens (of 32) through the whole block, 2 repetitions"}
+
+    # config 5: the first 64 rows through the four layers
+    x5 = synth.normal(synth.tensor_seed(5, 0), (C5_M, C5_DIMS[0]))[:CPU_SAMPLE_ROWS]
+    layers = c5_layers()
+
+    def stack():
+        h = x5
+        for w, wsc, a in layers:
+            h = oracle.linear(h, w, wsc, None, a)[0]
+        return h
+
+    dt, _ = _cpu_time(stack, 1)
+    per["c5_stack_4096x8192x28672"] = {"value": CPU_SAMPLE_ROWS / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                      "sample": f"first {CPU_SAMPLE_ROWS} of {C5_M} rows through the four layers, one repetition after one warm-up"}
+    res["cpu_baselines"] = per
+    return res
+
+
+def run_int_mm_peak(gpu_index):
+    """One library int8 GEMM (torch._int_mm, cuBLASLt) at 8192^3 on this GPU, outside the product path: a measured int8
+    tensor-core figure to hold the proxy denominator (2 x the measured bf16 figure) against."""
+    try:
+        import torch
+        dev = torch.device("cuda", gpu_index)
+        n = 8192
+        a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
+        b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev).t()     # column-major second operand
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize(dev)
+        best = None
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        del a, b
+        torch.cuda.empty_cache()
+        return {"tops": 2.0 * n ** 3 / (best * 1e-3) / 1e12, "ms": best, "how": "torch._int_mm 8192^3 (raw int32 result, no tail), best of 10, CUDA events"}
+    except Exception as exc:
+        return {"tops": None, "unavailable": f"{type(exc).__name__}: {exc}"}
 
 
 def run_reference_arm(args, rank, world):
@@ -371,6 +824,10 @@ def _run():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [C4_WORKLOAD, C5_WORKLOAD])
     ap.add_argument("--mode", default="mshard", choices=["mshard", "nshard"],
                     help="config 5 only: rows split over the GPUs (no collective) or output channels split (NCCL all-gather)")
+    ap.add_argument("--chunks", type=int, default=0, help="config 5, nshard: row chunks of the column-sharded call (0: try 1, 2 and 4)")
+    ap.add_argument("--requant-variant", type=int, default=0, choices=[0, 1],
+                    help="per-token requantize after a linear: 0 ranges from the GEMM epilogue + one-pass encode (default); 1 full quantize kernel")
+    ap.add_argument("--no-north-star", action="store_true", help="skip the fixed-size multi-GPU records (c3_strong, c5_mshard, c5_nshard)")
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
     ap.add_argument("--roundtrip-only", action="store_true", help="only the standalone quantize -> dequantize round trip (profiler runs)")
     args = ap.parse_args()
@@ -390,33 +847,33 @@ def _run():
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-
-    def max_over_ranks(v: float) -> float:
-        if dist is None:
-            return v
-        import torch
-        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    comm = Comm(dist, local_rank)
+    barrier, max_over_ranks = comm.barrier, comm.max
 
     ctx = mlfw_b200.Context(local_rank)
     ctx.set_tail_mode(args.tail_mode)
+    ctx.set_requant_variant(args.requant_variant)
     if args.roundtrip_only:
         line = {"metric": "quantize_dequantize_GBps", "roundtrip_c2": run_roundtrip(ctx, peaks(), args.steps, args.warmup)}
         ctx.close()
         return line
     if args.workload == C5_WORKLOAD:
-        line = run_c5(args, ctx, dist, rank, world, local_rank, barrier, max_over_ranks)
+        steps = min(args.steps, 50)
+        recs = run_c5_records(ctx, comm, rank, world, steps, max(args.warmup, 3), modes=(args.mode,),
+                              chunk_choices=(args.chunks,) if args.chunks else (1, 2, 4))
+        rec = recs["c5_" + args.mode]
+        line = {"metric": "int8_linear_tokens_per_s", "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 tail", "data": "synthetic (weights from numpy's PCG64, seed 5)",
+                "config": {"workload": C5_WORKLOAD, "M_total": C5_M, "dims": C5_DIMS, "activation": "silu", "mode": args.mode,
+                           "parallelism": rec["parallelism"]},
+                "tops": rec["tops"], "record": rec, "unsharded_on_each_gpu": recs["unsharded_on_each_gpu"]}
         ctx.close()
         if dist is not None:
             dist.destroy_process_group()
         return line if rank == 0 else None
     if args.workload == C4_WORKLOAD:
-        line = run_c4(args, ctx, rank, world, barrier, max_over_ranks)
+        line = run_c4(args, ctx, rank, world, comm)
         ctx.close()
         if dist is not None:
             dist.destroy_process_group()
@@ -517,49 +974,32 @@ def _run():
         line["step_samples_ms"] = {"n": len(samples), "median": med, "iqr": q3 - q1, "min": float(min(samples)), "max": float(max(samples)),
                                    "note": "CUDA events around single synchronised steps; the headline times all steps back to back"}
 
+        # -------------------------------------------------------- sustained regime (N = 1: a seconds-long stretch under the power cap)
+        if world == 1:
+            line["sustained"] = run_sustained(ctx, step, M, N, K, ms_per_step, local_rank)
+
         # -------------------------------------------------------- end to end (host buffers)
-        hx = ctx.pinned((M, K), np.float32)
-        hy = ctx.pinned((M, N), np.float32)
-        hx.array[...] = xs[0]
-        e2e_steps = max(3, min(args.steps, 10))
-        ctx.linear_f32_host(hx, dW, dws, db, act, M, N, K, hy)
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            ctx.linear_f32_host(hx, dW, dws, db, act, M, N, K, hy)
-        dt = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
-        checksum = float(hy.array[::997, ::97].sum())
-        line["e2e"] = {"value": world * M / dt, "unit": "tokens/s", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
-                       "ms_per_step": dt * 1e3, "steps": e2e_steps, "result_checksum": checksum,
-                       "api": "b200q_linear_f32_host (pinned host input, host output, synchronous)"}
+        line.update(run_e2e(ctx, comm, rank, world, local_rank, args, M, K, N, act, xs[0], dW, dws, db))
+
+        # -------------------------------------------------------- the fixed-size multi-GPU runs (strong scaling, value-checked)
+        if not args.no_north_star:
+            for b in dxs + douts:
+                b.free()
+            ns_steps, ns_warm = min(args.steps, 40), min(max(args.warmup, 3), 5)
+            ns = {"c3_strong": run_c3_strong(ctx, comm, rank, world, ns_steps, ns_warm)}
+            ns.update(run_c5_records(ctx, comm, rank, world, min(ns_steps, 20), 3))
+            line["north_star_runs"] = ns
+            dxs = [ctx.to_device(x) for x in xs]
+            douts = [ctx.empty((M, N), np.float32) for _ in xs]
 
         if rank == 0 and world == 1:
             line["roundtrip_c2"] = run_roundtrip(ctx, pk, iters=20, warmup=4)
-
-            # ---------------------------------------------------- CPU baseline (bounded sample)
-            import oracle
-            oracle.build()
-            rows = min(CPU_SAMPLE_ROWS, M)
-            oracle.set_num_threads(oracle.usable_cores())
-            cores = oracle.num_threads()
-            oracle.linear(xs[0][:rows], W, ws, bias, act)
-            t0 = time.perf_counter()
-            reps = 3
-            for _ in range(reps):
-                ref_out, _, _, _ = oracle.linear(xs[0][:rows], W, ws, bias, act)
-            dt_cpu = (time.perf_counter() - t0) / reps
-            rows1 = min(8, M)      # the reference's own execution model is one thread
-            t0 = time.perf_counter()
-            oracle.linear(xs[0][:rows1], W, ws, bias, act, threads=1)
-            dt_cpu1 = time.perf_counter() - t0
             step(0)
             ctx.sync()
-            got = douts[0].download()[:rows]
-            err = float(np.abs(got.astype(np.float64) - ref_out).max() / np.abs(ref_out).max())
-            line["cpu_baseline"] = {"value": rows / dt_cpu, "unit": "tokens/s", "cores": cores, "kind": "port",
-                                    "sample": f"first {rows} of {M} rows, all of N and K, {reps} repetitions; C++ restatement of the "
-                                              "reference's CPU path with OpenMP", "gpu_vs_cpu_max_err_over_absmax": err,
-                                    "single_core": {"value": rows1 / dt_cpu1, "unit": "tokens/s", "sample": f"first {rows1} rows, one thread, one repetition"}}
+            line.update(run_cpu_baselines(ctx, xs[0], W, ws, bias, act, douts[0], M))
+            line["int8_peak_measured"] = run_int_mm_peak(local_rank)
+            if line["int8_peak_measured"].get("tops") and roofline["achieved"]:
+                roofline["frac_of_int8_peak_measured"] = roofline["achieved"] / line["int8_peak_measured"]["tops"]
 
     ctx.close()
     if dist is not None:

@@ -59,6 +59,10 @@ int b200q_set_gemm_variant(b200q_ctx* ctx, int variant);
  * 1: hardware exponential and reciprocal -- results within about 1e-6 (relative) of mode 0, inside the 1e-5 bar, at the
  * speed of the other tails.  int8 (requantized) outputs always use the exact form: their codes are integer results. */
 int b200q_set_tail_mode(b200q_ctx* ctx, int mode);
+/* b200q_int8_linear_requant_token and the column-sharded group call: 0 (default) = the GEMM's epilogue publishes every
+ * output row's range while the values are in its registers and a one-pass kernel turns the f32 result into codes;
+ * 1 = the f32 result goes through the complete per-token quantize (range pass + encode).  Same codes. */
+int b200q_set_requant_variant(b200q_ctx* ctx, int variant);
 /* Per-token quantize: 0 = rows staged through shared memory by bulk copies when they fit; rows of 8, 12 and 16 KB are
  * moved on into registers and their slot is handed back before the arithmetic (default);
  * 1 = unstaged kernel only; 2 = staged, both passes read shared memory whatever the row length. */
@@ -148,6 +152,12 @@ int b200q_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, con
 /* quantized_dot + tail in one kernel.  A int8 [M,K], W int8 [N,K]. */
 int b200q_int8_linear(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk, const float* w_scales,
                       const float* bias, int act, int64_t M, int64_t N, int64_t K, float* out);
+/* b200q_int8_linear for activations stored as `a_blocks` equal column blocks, block r an int8 row-major
+ * [M, K / a_blocks] matrix at A + r * M * (K / a_blocks): what an all-gather of column-sharded activations leaves
+ * (see b200q_group_linear_nshard; no counterpart in the reference).  The kernel reads the blocks in place through a
+ * three-dimensional tensor map.  K / a_blocks must be a multiple of 128; tensor-core shapes only. */
+int b200q_int8_linear_gathered(b200q_ctx* ctx, const int8_t* A, const float* a_scales, int a_blocks, const int8_t* W_nk,
+                               const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K, float* out);
 /* Same, followed by the next layer's static `quantize` (scale out_scale, zero-point 0, int8) inside the epilogue. */
 int b200q_int8_linear_requant_static(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk,
                                      const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K,
@@ -157,6 +167,10 @@ int b200q_int8_linear_requant_static(b200q_ctx* ctx, const int8_t* A, const floa
 int b200q_int8_linear_requant_token(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk,
                                     const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K,
                                     int8_t* out_q, float* out_scales);
+/* Same, with the f32 result kept as well (out_f32 [M,N], e.g. for a residual branch) instead of a workspace. */
+int b200q_int8_linear_f32_requant_token(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk,
+                                        const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K,
+                                        float* out_f32, int8_t* out_q, float* out_scales);
 /* The whole hot path from f32 activations: per-token quantize (into a context-owned
  * workspace), contraction, tail. */
 int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const float* w_scales, const float* bias, int act,
@@ -223,6 +237,73 @@ int b200q_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* residu
 int b200q_set_sdpa_variant(b200q_ctx* ctx, int variant);
 int b200q_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v,
                    int64_t B, int64_t H, int64_t S, int64_t head_dim, float scale, int causal, float* out, int64_t ld_out);
+
+/* ---- captured steps ----
+ * A sequence of calls on a context recorded once and replayed with one launch (the reference's CUDA runtime replays
+ * captured plans and eager steps the same way: src/runtime/node/cuda/eager_graph.ts:16-41, device_plan.ts:178-219).
+ * Between begin and end every call on the context is recorded instead of executed; calls that synchronise or copy to
+ * or from host memory are not allowed there, and every workspace must already have its size: run the same calls once,
+ * not captured, before capturing them.  The recorded pointers and shapes are fixed; replay as often as wanted. */
+typedef struct b200q_graph b200q_graph;
+int b200q_graph_begin(b200q_ctx* ctx);
+int b200q_graph_end(b200q_ctx* ctx, b200q_graph** out);
+int b200q_graph_launch(b200q_ctx* ctx, b200q_graph* graph);
+int b200q_graph_destroy(b200q_ctx* ctx, b200q_graph* graph);
+
+/* ---- self test of the bounded device-side wait ----
+ * Launches one thread that waits, with the library's own wait routine and the given limit (seconds, at most 1), on a
+ * barrier in its shared memory that nothing ever signals, with no asynchronous work in flight.  The wait must give up:
+ * the kernel then sets bit 6 of the status word and returns.  For tests of the give-up path on a healthy device. */
+int b200q_selftest_bounded_wait(b200q_ctx* ctx, double limit_seconds);
+
+/* ---- several GPUs of one node ----
+ * The reference executes on one device (src/runtime/node/cuda/runtime_api.ts:16-18); nothing below has a counterpart
+ * there.  A group is one NCCL communicator with one rank per GPU.  Either one process drives several of its GPUs
+ * (b200q_group_create: the group creates and owns one context per device, rank i = devices[i]) or every GPU has its
+ * own process (b200q_group_create_rank: the process passes its context; the 128-byte id comes from
+ * b200q_group_unique_id on one rank and reaches the others by the host's own means).  The per-GPU arguments of the
+ * calls below are arrays with one entry per LOCAL rank (b200q_group_local_count: n, or 1), holding device pointers
+ * on that rank's GPU.  NCCL is loaded when the first group function is called (libnccl.so.2). */
+typedef struct b200q_group b200q_group;
+int b200q_group_unique_id(void* id128);                       /* host buffer of 128 bytes */
+int b200q_group_create(const int* devices, int n, b200q_group** out);
+int b200q_group_create_rank(b200q_ctx* ctx, const void* id128, int rank, int world, b200q_group** out);
+int b200q_group_destroy(b200q_group* group);
+int b200q_group_world(b200q_group* group);                    /* ranks of the communicator */
+int b200q_group_local_count(b200q_group* group);              /* ranks this process drives */
+b200q_ctx* b200q_group_ctx(b200q_group* group, int local_index);
+int b200q_group_rank(b200q_group* group, int local_index);
+int b200q_group_nccl_version(b200q_group* group, int* version);
+/* Waits (host) for everything queued on the local ranks' streams. */
+int b200q_group_sync(b200q_group* group);
+/* Rows sharded: local rank i computes b200q_linear_f32 on its own rows[i] rows against its replica of the weights.
+ * No collective: a row depends on nothing but itself. */
+int b200q_group_linear_mshard(b200q_group* group, const float* const* x, const int64_t* rows, const int8_t* const* W_nk,
+                              const float* const* w_scales, const float* const* bias, int act, int64_t N, int64_t K,
+                              float* const* out);
+/* Output channels sharded: every rank holds the int8 activations of all M rows (q_in, in_scales [M]) and the weights,
+ * scales and bias of its own N / world channels (W_shard int8 [N/world, K], rank r owns channels [r*N/world, ...)).
+ * Either out_f32 is given: local rank i receives its channels of the result, f32 [M, N/world] - no collective; or
+ * q_out and out_scales are given: the result is requantized per token exactly as one GPU would (the rows' ranges are
+ * agreed by one max-reduction over the ranks) and the int8 column blocks are all-gathered, so that every rank ends
+ * up with all codes and scales [M].  The gathered codes are left in the layout the all-gather produces - per row
+ * chunk (see b200q_group_set_chunks; one chunk by default), the ranks' blocks one after the other, block r an int8
+ * [rows of the chunk, N/world] matrix; chunk c starts at q_out + N * (first row of the chunk) - and the next call
+ * takes them as they are with in_blocks = world (in_blocks = 1: q_in is an ordinary row-major [M, K] matrix).
+ * N must divide by world, and N/world by 128 for a gathered output.  bias may be null (the array or its entries). */
+int b200q_group_linear_nshard(b200q_group* group, const int8_t* const* q_in, const float* const* in_scales, int in_blocks,
+                              const int8_t* const* W_shard, const float* const* w_scales, const float* const* bias, int act,
+                              int64_t M, int64_t N, int64_t K, int8_t* const* q_out, float* const* out_scales,
+                              float* const* out_f32);
+/* Row chunks of the column-sharded call (default 1).  With more than one, the collectives of a chunk run on a second
+ * stream while the next chunk's GEMM computes, and a following column-sharded call starts on its first chunk while
+ * later chunks are still being gathered; chunks are whole multiples of 256 rows.  After a chunked call the gathered
+ * output is complete on the contexts' streams only once b200q_group_fence (or _sync, or the next column-sharded call,
+ * chunk by chunk) has been issued. */
+int b200q_group_set_chunks(b200q_group* group, int chunks);
+int b200q_group_fence(b200q_group* group);
+/* All-gather of `bytes` bytes per rank on the contexts' streams: recv[i] receives world * bytes, rank after rank. */
+int b200q_group_all_gather(b200q_group* group, const void* const* send, void* const* recv, size_t bytes);
 
 #ifdef __cplusplus
 }

@@ -6,6 +6,6 @@ object layer, and the mirror of the reference's backend interface
 (:mod:`mlfw_b200.backend`).  There is no CPU fallback.
 """
 from ._lib import B200QError, LIB_PATH
-from .device import ACT, Context, DeviceBuffer, PinnedArray, W_KN, W_NK
+from .device import ACT, Context, DeviceBuffer, Group, PinnedArray, W_KN, W_NK
 
-__all__ = ["B200QError", "LIB_PATH", "ACT", "Context", "DeviceBuffer", "PinnedArray", "W_KN", "W_NK"]
+__all__ = ["B200QError", "LIB_PATH", "ACT", "Context", "DeviceBuffer", "Group", "PinnedArray", "W_KN", "W_NK"]

@@ -26,6 +26,7 @@ PROTOTYPES = {
     "b200q_set_wait_limit": (c_int, [c_vp, c_dbl]),
     "b200q_set_gemm_variant": (c_int, [c_vp, c_int]),
     "b200q_set_tail_mode": (c_int, [c_vp, c_int]),
+    "b200q_set_requant_variant": (c_int, [c_vp, c_int]),
     "b200q_set_quant_variant": (c_int, [c_vp, c_int]),
     "b200q_launch_count": (C.c_uint64, [c_vp]),
     "b200q_sm_count": (c_int, [c_vp]),
@@ -52,8 +53,10 @@ PROTOTYPES = {
     "b200q_int8_gemm_i32": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_int, c_vp]),
     "b200q_epilogue": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_int, c_vp]),
     "b200q_int8_linear": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
+    "b200q_int8_linear_gathered": (c_int, [c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_int8_linear_requant_static": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_dbl, c_vp]),
     "b200q_int8_linear_requant_token": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp]),
+    "b200q_int8_linear_f32_requant_token": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "b200q_linear_f32": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_linear_f32_noalloc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_linear_f32_host": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
@@ -65,6 +68,28 @@ PROTOTYPES = {
     "b200q_layernorm_quantize": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, C.c_float, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
     "b200q_set_sdpa_variant": (c_int, [c_vp, c_int]),
     "b200q_sdpa_f32": (c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, C.c_float, c_int, c_vp, c_i64]),
+    "b200q_graph_begin": (c_int, [c_vp]),
+    "b200q_graph_end": (c_int, [c_vp, C.POINTER(c_vp)]),
+    "b200q_graph_launch": (c_int, [c_vp, c_vp]),
+    "b200q_graph_destroy": (c_int, [c_vp, c_vp]),
+    "b200q_selftest_bounded_wait": (c_int, [c_vp, c_dbl]),
+    "b200q_group_unique_id": (c_int, [c_vp]),
+    "b200q_group_create": (c_int, [C.POINTER(c_int), c_int, C.POINTER(c_vp)]),
+    "b200q_group_create_rank": (c_int, [c_vp, c_vp, c_int, c_int, C.POINTER(c_vp)]),
+    "b200q_group_destroy": (c_int, [c_vp]),
+    "b200q_group_world": (c_int, [c_vp]),
+    "b200q_group_local_count": (c_int, [c_vp]),
+    "b200q_group_ctx": (c_vp, [c_vp, c_int]),
+    "b200q_group_rank": (c_int, [c_vp, c_int]),
+    "b200q_group_nccl_version": (c_int, [c_vp, C.POINTER(c_int)]),
+    "b200q_group_sync": (c_int, [c_vp]),
+    "b200q_group_linear_mshard": (c_int, [c_vp, C.POINTER(c_vp), C.POINTER(c_i64), C.POINTER(c_vp), C.POINTER(c_vp), C.POINTER(c_vp),
+                                          c_int, c_i64, c_i64, C.POINTER(c_vp)]),
+    "b200q_group_linear_nshard": (c_int, [c_vp, C.POINTER(c_vp), C.POINTER(c_vp), c_int, C.POINTER(c_vp), C.POINTER(c_vp),
+                                          C.POINTER(c_vp), c_int, c_i64, c_i64, c_i64, C.POINTER(c_vp), C.POINTER(c_vp), C.POINTER(c_vp)]),
+    "b200q_group_set_chunks": (c_int, [c_vp, c_int]),
+    "b200q_group_fence": (c_int, [c_vp]),
+    "b200q_group_all_gather": (c_int, [c_vp, C.POINTER(c_vp), C.POINTER(c_vp), c_sz]),
 }
 
 

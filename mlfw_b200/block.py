@@ -9,7 +9,8 @@ turned the four ``Linear`` modules into quantize -> quantized_dot -> per-channel
     q, k, v = n1 Wq^T + bq, n1 Wk^T + bk, n1 Wv^T + bv   one int8 GEMM over the stacked [3D, D] weight
     a = attention(q, k, v)                               f32, causal, scale 1/sqrt(D/H)
     x = h + (a Wo^T + bo)
-    y = x + (gelu(LayerNorm2(x) W1^T + b1) W2^T + b2)    the residual sum x is formed inside the LayerNorm2 launch
+    y = x + (gelu(LayerNorm2(x) W1^T + b1) W2^T + b2)    the residual sum x is formed inside the LayerNorm2 launch; the
+                                                         requantization of W2's input starts in W1's epilogue
 
 Weights are quantized per output channel on the device when the block is built and stay resident.
 """
@@ -85,7 +86,7 @@ class GPTBlock:
                 "n1_q": c.empty((M, D), np.int8), "n1_s": c.empty((M,), np.float32), "qkv": c.empty((M, 3 * D), np.float32),
                 "attn": c.empty((M, D), np.float32), "o": c.empty((M, D), np.float32), "x": c.empty((M, D), np.float32),
                 "n2_q": c.empty((M, D), np.int8), "n2_s": c.empty((M,), np.float32), "f1": c.empty((M, FF), np.float32),
-                "f2": c.empty((M, D), np.float32),
+                "f1_q": c.empty((M, FF), np.int8), "f1_s": c.empty((M,), np.float32), "f2": c.empty((M, D), np.float32),
             }
             self._M = M
         return self._bufs
@@ -101,8 +102,10 @@ class GPTBlock:
         c.sdpa_f32(base, base + D * 4, base + 2 * D * 4, 3 * D, 3 * D, 3 * D, B, H, S, 64, 1.0 / np.sqrt(64.0), causal, t["attn"], D)
         c.linear_f32(t["attn"], self.wo.w, self.wo.scales, self.wo.bias, "none", M, D, D, t["o"])
         c.layernorm_quantize(t["o"], h, self.g2, self.b2, self.eps, M, D, t["x"], None, t["n2_q"], t["n2_s"])
-        c.int8_linear(t["n2_q"], t["n2_s"], self.fc1.w, self.fc1.scales, self.fc1.bias, self.activation, M, FF, D, t["f1"])
-        c.linear_f32(t["f1"], self.fc2.w, self.fc2.scales, self.fc2.bias, "none", M, D, FF, t["f2"])
+        # FC1 with the requantization of FC2's input behind it: the rows' ranges come out of FC1's epilogue, one pass encodes
+        c.int8_linear_f32_requant_token(t["n2_q"], t["n2_s"], self.fc1.w, self.fc1.scales, self.fc1.bias, self.activation, M, FF, D,
+                                        t["f1"], t["f1_q"], t["f1_s"])
+        c.int8_linear(t["f1_q"], t["f1_s"], self.fc2.w, self.fc2.scales, self.fc2.bias, "none", M, D, FF, t["f2"])
         c.add_f32(t["x"], t["f2"], M * D, out)
         return t
 

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200q.so")
-SOURCES = ["api.cu", "quant_kernels.cu", "gemm_simt.cu", "gemm_umma.cu", "block_kernels.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "quant_kernels.cu", "gemm_simt.cu", "gemm_umma.cu", "block_kernels.cu", "noalloc.cu", "group.cu"]
 HEADERS = ["common.cuh", "kernels.cuh", "quant_math.cuh", "exp2_table.inc", "exp_ff_table.inc", os.path.join("..", "..", "include", "b200q.h")]
 
 
@@ -47,6 +47,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [os.path.join(CSRC, s) for s in SOURCES]
+    cmd += ["-ldl"]   # group.cu looks NCCL up at run time (dlopen), so the library itself does not depend on it
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)

@@ -23,6 +23,7 @@ void set_error(const char* fmt, ...) {
 
 int ws_reserve(b200q_ctx* ctx, Workspace& ws, size_t bytes) {
   if (bytes <= ws.bytes) return 0;
+  B200Q_REQUIRE(!ctx->capturing, "a workspace would have to grow while calls are being recorded: run the same calls once before b200q_graph_begin");
   // Stream-ordered, so a buffer still read by queued kernels is released after them.
   if (ws.ptr) B200Q_CHECK_CUDA(cudaFreeAsync(ws.ptr, ctx->stream));
   ws.ptr = nullptr;
@@ -52,6 +53,10 @@ static int use_device(b200q_ctx* ctx) {
   return 0;
 }
 
+// Entry points that wait on the host or touch host memory cannot be part of a recorded sequence.
+#define B200Q_NOT_CAPTURING(ctx, who) \
+  B200Q_REQUIRE(!(ctx)->capturing, "%s is not allowed between b200q_graph_begin and b200q_graph_end", who)
+
 static bool use_umma(b200q_ctx* ctx, const void* A, const void* W, int64_t M, int64_t N, int64_t K) {
   return ctx->gemm_variant != 1 && gemm_umma_supported(A, W, M, N, K);
 }
@@ -72,6 +77,37 @@ static int linear_core(b200q_ctx* ctx, const int8_t* A, const float* a_scales, c
   int32_t* acc = (int32_t*)ctx->ws_acc.ptr;
   if (int e = launch_gemm_i8_simt(ctx, A, W, M, N, K, 0, 0, acc)) return e;
   return launch_epilogue(ctx, acc, M, N, a_scales, w_scales, bias, act, out_f32, out_q, q_scale);
+}
+
+// Linear followed by the per-token quantization of its result: y f32 [M,N] (scratch or a caller's buffer), codes with
+// row stride ld_q, scales [M].  On the tensor-core path the range pass of that quantization happens in the GEMM's
+// epilogue (every row's minimum and maximum are published as keys while the values are in registers) and a one-pass
+// kernel then turns y into codes; otherwise y goes through the complete per-token quantize.  Same codes either way.
+int linear_requant_token_core(b200q_ctx* ctx, const int8_t* A, const float* a_scales, int a_pieces, const int8_t* W,
+                              const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K, float* y,
+                              int8_t* out_q, int64_t ld_q, float* out_scales) {
+  if (M == 0 || N == 0) return 0;
+  const bool umma = K > 0 && use_umma(ctx, A, W, M, N, K);
+  B200Q_REQUIRE(a_pieces == 1 || umma, "activations stored as column blocks need the tensor-core kernel (K %% 16 == 0, aligned operands)");
+  if (umma && ctx->requant_variant == 0) {
+    if (ws_reserve(ctx, ctx->ws_range, (size_t)2 * M * sizeof(uint32_t))) return 1;
+    uint32_t* keys = (uint32_t*)ctx->ws_range.ptr;
+    B200Q_CHECK_CUDA(cudaMemsetAsync(keys, 0, (size_t)2 * M * sizeof(uint32_t), ctx->stream));
+    if (int e = launch_gemm_i8_umma(ctx, A, W, M, N, K, a_scales, w_scales, bias, act, y, nullptr, nullptr, 1.0, keys, a_pieces)) return e;
+    return launch_quantize_rows_with_keys(ctx, y, M, N, N, keys, out_q, ld_q, out_scales, -127, 127);
+  }
+  if (umma) {
+    if (int e = launch_gemm_i8_umma(ctx, A, W, M, N, K, a_scales, w_scales, bias, act, y, nullptr, nullptr, 1.0, nullptr, a_pieces)) return e;
+  } else if (int e = linear_core(ctx, A, a_scales, W, w_scales, bias, act, M, N, K, y, nullptr, 1.0)) {
+    return e;
+  }
+  if (ld_q == N) return launch_quantize_per_token(ctx, y, M, N, out_q, out_scales, -127, 127);
+  // strided codes: range pass, then the encode that takes row strides
+  if (ws_reserve(ctx, ctx->ws_range, (size_t)4 * M * sizeof(uint32_t))) return 1;
+  float* mn = (float*)ctx->ws_range.ptr + 2 * M;
+  float* mx = mn + M;
+  if (int e = launch_row_range(ctx, y, M, N, N, mn, mx)) return e;
+  return launch_quantize_rows_with_range(ctx, y, M, N, N, mn, mx, out_q, ld_q, out_scales, -127, 127);
 }
 
 }  // namespace b200q
@@ -132,7 +168,7 @@ void b200q_destroy(b200q_ctx* ctx) {
   if (!ctx) return;
   cudaSetDevice(ctx->device);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
-  Workspace* all[] = {&ctx->ws_q, &ctx->ws_scales, &ctx->ws_acc, &ctx->ws_stage_in, &ctx->ws_stage_out};
+  Workspace* all[] = {&ctx->ws_q, &ctx->ws_scales, &ctx->ws_acc, &ctx->ws_stage_in, &ctx->ws_stage_out, &ctx->ws_range};
   for (Workspace* w : all)
     if (w->ptr) cudaFree(w->ptr);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
@@ -154,12 +190,14 @@ void b200q_destroy(b200q_ctx* ctx) {
 
 int b200q_sync(b200q_ctx* ctx) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_sync");
   B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
   return 0;
 }
 
 int b200q_status_word(b200q_ctx* ctx, uint32_t* out) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_status_word");
   B200Q_REQUIRE(out != nullptr, "b200q_status_word: null out pointer");
   B200Q_CHECK_CUDA(cudaMemcpyAsync(out, ctx->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
   B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -200,6 +238,13 @@ int b200q_set_gemm_variant(b200q_ctx* ctx, int variant) {
   return 0;
 }
 
+int b200q_set_requant_variant(b200q_ctx* ctx, int variant) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_REQUIRE(variant == 0 || variant == 1, "b200q_set_requant_variant: unknown variant %d", variant);
+  ctx->requant_variant = variant;
+  return 0;
+}
+
 int b200q_set_quant_variant(b200q_ctx* ctx, int variant) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
   B200Q_REQUIRE(variant >= 0 && variant <= 2, "b200q_set_quant_variant: unknown variant %d", variant);
@@ -209,6 +254,7 @@ int b200q_set_quant_variant(b200q_ctx* ctx, int variant) {
 
 int b200q_profile_enable(b200q_ctx* ctx, int on) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_profile_enable");
   if (on && !ctx->prof_ev[0][0]) {
     for (int i = 0; i < PROFILE_RING; i++)
       for (int j = 0; j < 2; j++) B200Q_CHECK_CUDA(cudaEventCreate(&ctx->prof_ev[i][j]));
@@ -220,6 +266,7 @@ int b200q_profile_enable(b200q_ctx* ctx, int on) {
 
 int b200q_profile_reset(b200q_ctx* ctx) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_profile_reset");
   if (prof_fold(ctx)) return 1;
   for (int k = 0; k < KK_COUNT; k++) { ctx->prof_ms[k] = 0.0; ctx->prof_n[k] = 0; }
   return 0;
@@ -227,6 +274,7 @@ int b200q_profile_reset(b200q_ctx* ctx) {
 
 int b200q_profile_read(b200q_ctx* ctx, int kind, double* total_ms, uint64_t* launches) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_profile_read");
   B200Q_REQUIRE(kind >= 0 && kind < KK_COUNT, "b200q_profile_read: unknown kernel family %d", kind);
   B200Q_REQUIRE(total_ms && launches, "b200q_profile_read: null out pointer");
   if (prof_fold(ctx)) return 1;
@@ -241,6 +289,7 @@ int b200q_sm_count(b200q_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 // ---------------------------------------------------------------- memory
 int b200q_alloc(b200q_ctx* ctx, size_t bytes, void** dev) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_alloc");
   B200Q_REQUIRE(dev != nullptr, "b200q_alloc: null out pointer");
   *dev = nullptr;
   if (bytes == 0) bytes = 16;
@@ -250,6 +299,7 @@ int b200q_alloc(b200q_ctx* ctx, size_t bytes, void** dev) {
 
 int b200q_free(b200q_ctx* ctx, void* dev) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_free");
   if (!dev) return 0;
   B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
   B200Q_CHECK_CUDA(cudaFree(dev));
@@ -265,6 +315,7 @@ int b200q_memset(b200q_ctx* ctx, void* dev, int byte_value, size_t bytes) {
 
 int b200q_upload(b200q_ctx* ctx, void* dev, const void* host, size_t bytes) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_upload");
   B200Q_REQUIRE((dev && host) || bytes == 0, "b200q_upload: null pointer");
   if (bytes) {
     B200Q_CHECK_CUDA(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -275,6 +326,7 @@ int b200q_upload(b200q_ctx* ctx, void* dev, const void* host, size_t bytes) {
 
 int b200q_download(b200q_ctx* ctx, void* host, const void* dev, size_t bytes) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_download");
   B200Q_REQUIRE((dev && host) || bytes == 0, "b200q_download: null pointer");
   if (bytes) {
     B200Q_CHECK_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
@@ -307,6 +359,7 @@ int b200q_timer_start(b200q_ctx* ctx) {
 
 int b200q_timer_stop(b200q_ctx* ctx, float* elapsed_ms) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_timer_stop");
   B200Q_REQUIRE(elapsed_ms != nullptr, "b200q_timer_stop: null out pointer");
   B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_stop, ctx->stream));
   B200Q_CHECK_CUDA(cudaEventSynchronize(ctx->ev_stop));
@@ -430,6 +483,17 @@ int b200q_int8_linear(b200q_ctx* ctx, const int8_t* A, const float* a_scales, co
   return linear_core(ctx, A, a_scales, W_nk, w_scales, bias, act, M, N, K, out, nullptr, 1.0);
 }
 
+int b200q_int8_linear_gathered(b200q_ctx* ctx, const int8_t* A, const float* a_scales, int a_blocks, const int8_t* W_nk,
+                               const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K, float* out) {
+  if (use_device(ctx)) return 1;
+  if (int e = check_linear("b200q_int8_linear_gathered", A, W_nk, w_scales, act, M, N, K, out)) return e;
+  B200Q_REQUIRE(a_blocks >= 1, "b200q_int8_linear_gathered: %d column blocks", a_blocks);
+  if (M == 0 || N == 0) return 0;
+  B200Q_REQUIRE(K > 0 && use_umma(ctx, A, W_nk, M, N, K),
+                "b200q_int8_linear_gathered: needs the tensor-core kernel (K %% 16 == 0, 16-byte aligned operands)");
+  return launch_gemm_i8_umma(ctx, A, W_nk, M, N, K, a_scales, w_scales, bias, act, out, nullptr, nullptr, 1.0, nullptr, a_blocks);
+}
+
 int b200q_int8_linear_requant_static(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk,
                                      const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K,
                                      double out_scale, int8_t* out_q) {
@@ -449,8 +513,17 @@ int b200q_int8_linear_requant_token(b200q_ctx* ctx, const int8_t* A, const float
   // The f32 result lives in its own workspace: ws_acc may be in use by the CUDA-core path.
   if (ws_reserve(ctx, ctx->ws_stage_out, (size_t)M * N * sizeof(float))) return 1;
   float* y = (float*)ctx->ws_stage_out.ptr;
-  if (int e = linear_core(ctx, A, a_scales, W_nk, w_scales, bias, act, M, N, K, y, nullptr, 1.0)) return e;
-  return launch_quantize_per_token(ctx, y, M, N, out_q, out_scales, -127, 127);
+  return linear_requant_token_core(ctx, A, a_scales, 1, W_nk, w_scales, bias, act, M, N, K, y, out_q, N, out_scales);
+}
+
+int b200q_int8_linear_f32_requant_token(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk,
+                                        const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K,
+                                        float* out_f32, int8_t* out_q, float* out_scales) {
+  if (use_device(ctx)) return 1;
+  if (int e = check_linear("b200q_int8_linear_f32_requant_token", A, W_nk, w_scales, act, M, N, K, out_q)) return e;
+  B200Q_REQUIRE(M == 0 || N == 0 || (out_scales && out_f32), "b200q_int8_linear_f32_requant_token: null output");
+  if (M == 0 || N == 0) return 0;
+  return linear_requant_token_core(ctx, A, a_scales, 1, W_nk, w_scales, bias, act, M, N, K, out_f32, out_q, N, out_scales);
 }
 
 int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const float* w_scales, const float* bias, int act,
@@ -485,6 +558,7 @@ static int host_pipeline_ready(b200q_ctx* ctx) {
 int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_nk, const float* w_scales, const float* bias,
                           int act, int64_t M, int64_t N, int64_t K, float* out_host) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_linear_f32_host");
   if (int e = check_linear("b200q_linear_f32_host", x_host, W_nk, w_scales, act, M, N, K, out_host)) return e;
   B200Q_REQUIRE(K > 0 || M == 0, "b200q_linear_f32_host: rows of zero length have no range");
   if (M == 0 || N == 0) return 0;
@@ -523,8 +597,88 @@ int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_n
   return 0;
 }
 
+// ---------------------------------------------------------------- captured steps
+struct b200q_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t kernels = 0;   // kernel launches recorded in it
+};
+
+int b200q_graph_begin(b200q_ctx* ctx) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(!ctx->capturing, "b200q_graph_begin: a recording is already in progress on this context");
+  B200Q_REQUIRE(!ctx->profiling, "b200q_graph_begin: switch per-kernel profiling off first");
+  B200Q_CHECK_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+  ctx->capturing = true;
+  ctx->capture_launches0 = ctx->launches;
+  return 0;
+}
+
+int b200q_graph_end(b200q_ctx* ctx, b200q_graph** out) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(out != nullptr, "b200q_graph_end: null out pointer");
+  *out = nullptr;
+  B200Q_REQUIRE(ctx->capturing, "b200q_graph_end: no recording in progress");
+  ctx->capturing = false;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+  const uint64_t kernels = ctx->launches - ctx->capture_launches0;
+  ctx->launches = ctx->capture_launches0;   // nothing ran: the recorded kernels count when the graph is launched
+  if (e != cudaSuccess || !graph) {
+    set_error("b200q_graph_end: the recording failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return 1;
+  }
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  if (e != cudaSuccess) {
+    set_error("b200q_graph_end: cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    cudaGraphDestroy(graph);
+    return 1;
+  }
+  b200q_graph* g = new (std::nothrow) b200q_graph();
+  if (!g) {
+    cudaGraphExecDestroy(exec);
+    cudaGraphDestroy(graph);
+    set_error("b200q_graph_end: out of host memory");
+    return 2;
+  }
+  g->graph = graph;
+  g->exec = exec;
+  g->kernels = kernels;
+  *out = g;
+  return 0;
+}
+
+int b200q_graph_launch(b200q_ctx* ctx, b200q_graph* graph) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(graph != nullptr && graph->exec != nullptr, "b200q_graph_launch: null graph");
+  B200Q_NOT_CAPTURING(ctx, "b200q_graph_launch");
+  B200Q_CHECK_CUDA(cudaGraphLaunch(graph->exec, ctx->stream));
+  ctx->launches += graph->kernels;
+  return 0;
+}
+
+int b200q_graph_destroy(b200q_ctx* ctx, b200q_graph* graph) {
+  if (use_device(ctx)) return 1;
+  if (!graph) return 0;
+  B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (graph->exec) cudaGraphExecDestroy(graph->exec);
+  if (graph->graph) cudaGraphDestroy(graph->graph);
+  delete graph;
+  return 0;
+}
+
+int b200q_selftest_bounded_wait(b200q_ctx* ctx, double limit_seconds) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(limit_seconds > 0 && limit_seconds <= 1.0, "b200q_selftest_bounded_wait: %g s is outside (0, 1]", limit_seconds);
+  return launch_selftest_bounded_wait(ctx, (unsigned long long)(limit_seconds * 1e9));
+}
+
 int b200q_observer_reset(b200q_ctx* ctx, float* state) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_observer_reset");
   B200Q_REQUIRE(state != nullptr, "b200q_observer_reset: null pointer");
   const float init[2] = {std::numeric_limits<float>::infinity(), -std::numeric_limits<float>::infinity()};
   B200Q_CHECK_CUDA(cudaMemcpyAsync(state, init, sizeof(init), cudaMemcpyHostToDevice, ctx->stream));
@@ -574,6 +728,7 @@ int b200q_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* 
 int b200q_quant_roundtrip_host(b200q_ctx* ctx, const float* x_host, int64_t M, int64_t K, int8_t* q_host, float* scales_host,
                                float* y_host) {
   if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_quant_roundtrip_host");
   B200Q_DIMS_OK(M, 0, K);
   B200Q_REQUIRE(M == 0 || K == 0 || (x_host && y_host), "b200q_quant_roundtrip_host: null pointer");
   if (M == 0 || K == 0) return 0;

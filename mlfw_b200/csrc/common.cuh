@@ -37,6 +37,7 @@ enum StatusBits : uint32_t {
   STATUS_BAD_TMEM_ALLOC = 1u << 3,     // tensor-memory allocation returned an unexpected address
   STATUS_QUANT_WAIT_TIMEOUT = 1u << 4, // the staged quantize kernel gave up waiting for a row chunk or a free slot
   STATUS_BAD_INDEX = 1u << 5,          // an embedding lookup met a token outside its table (the row is zero)
+  STATUS_SELFTEST_WAIT_TIMEOUT = 1u << 6, // b200q_selftest_bounded_wait: the wait on a barrier nothing signals gave up, as it must
 };
 
 // Kernel families timed separately when profiling is on (b200q_profile_*).
@@ -67,6 +68,8 @@ struct b200q_ctx {
   b200q::Workspace ws_scales;            // their per-token scales
   b200q::Workspace ws_acc;               // int32 / f32 intermediates of the unfused paths
   b200q::Workspace ws_stage_in, ws_stage_out;  // device staging of the host-buffer entry points
+  b200q::Workspace ws_range;             // row-range keys of the two-step per-token requantization (2 words per row)
+  int requant_variant = 0;               // 0: ranges published by the GEMM epilogue + one-pass encode; 1: f32 result + full per-token quantize
   double wait_limit_s = 2.0;             // bound of every device-side wait
   int gemm_variant = 0;                  // 0 auto, 1 CUDA-core kernel only, 2 tensor cores with one CTA per tile, 3 with CTA pairs
   int quant_variant = 0;                 // 0 auto (rows staged in shared memory when they fit), 1 unstaged kernel only, 2 staged with both passes from shared memory
@@ -76,6 +79,8 @@ struct b200q_ctx {
   int sdpa_variant = 0;                  // 0: CUDA-core binary32 FMA; 1: mma.sync with three-way tf32 products
   uint64_t umma_ready_mask = 0;          // tensor-core kernel variants whose shared-memory attribute is set on this device
   uint64_t launches = 0;                 // kernels launched through this context
+  bool capturing = false;                // between b200q_graph_begin and _end: calls are recorded, nothing may allocate or synchronise
+  uint64_t capture_launches0 = 0;        // `launches` when the capture began
   // per-kernel CUDA-event timing (off by default): a ring of event pairs, folded into the sums when it wraps or is read
   bool profiling = false;
   cudaEvent_t prof_ev[b200q::PROFILE_RING][2] = {};

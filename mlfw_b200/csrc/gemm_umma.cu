@@ -77,6 +77,14 @@ struct GemmParams {
   float q_inv;
   int q_exact;
   int tma_store;          // results leave through bulk-tensor stores (needs a 16-byte aligned base and row pitch)
+  // f32 output only: when not null, the NaN-ignoring maximum and minimum of every output row are published here as
+  // order-preserving keys (range_key_max / range_key_min in quant_math.cuh), [0, M) maxima and [M, 2M) minima, with
+  // atomicMax -- the range pass of the per-token quantize that follows, done while the values are still in registers.
+  uint32_t* row_range;
+  // A given as `a_pieces` column blocks of a_piece_cols columns each, block r a row-major [M, a_piece_cols] matrix at
+  // A + r * M * a_piece_cols (what an all-gather of column-sharded activations leaves); 1 = plain row-major [M, K].
+  int a_pieces;
+  int a_piece_cols;
   uint32_t* status;
   unsigned long long wait_limit_ns;
 };
@@ -131,6 +139,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Three-dimensional forms (A stored as column blocks: coordinates are column within the block, row, block).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar_cluster, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 
@@ -334,16 +356,22 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           const uint32_t bar = smem_u32(&misc->full[s]);
           uint8_t* st = tiles + s * STAGE_BYTES;
+          // K block kb of A when A is stored as column blocks: block and column inside it (a block boundary never falls
+          // inside a K block: the host requires a_piece_cols to be a multiple of BK)
+          const int a_piece = p.a_pieces > 1 ? (kb * BK) / p.a_piece_cols : 0;
+          const int a_col = p.a_pieces > 1 ? (kb * BK) - a_piece * p.a_piece_cols : 0;
           if (NCTA == 1) {
             mbar_expect_tx(bar, STAGE_BYTES);
-            tma_load_2d(smem_u32(st), &tmA, bar, kb * BK, m0);
+            if (p.a_pieces > 1) tma_load_3d(smem_u32(st), &tmA, bar, a_col, m0, a_piece);
+            else tma_load_2d(smem_u32(st), &tmA, bar, kb * BK, m0);
             tma_load_2d(smem_u32(st + A_BYTES), &tmB, bar, kb * BK, n0);
           } else {
             // Both CTAs' copies complete on the barrier of the MMA-issuing CTA, which expects the bytes of both.
             // (A partner's bytes may land before the expectation is posted; the count is signed.)
             if (cta_rank == 0) mbar_expect_tx(bar, 2 * STAGE_BYTES);
             const uint32_t bar0 = map_to_cta(bar, 0);
-            tma_load_2d_pair(smem_u32(st), &tmA, bar0, kb * BK, m0);
+            if (p.a_pieces > 1) tma_load_3d_pair(smem_u32(st), &tmA, bar0, a_col, m0, a_piece);
+            else tma_load_2d_pair(smem_u32(st), &tmA, bar0, kb * BK, m0);
             tma_load_2d_pair(smem_u32(st + A_BYTES), &tmB, bar0, kb * BK, n0);
           }
         }
@@ -447,6 +475,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // The accumulator columns of the next chunk travel from tensor memory while the current chunk is computed.
       int a_next[EPI_CH];
       if (n0 < p.N) tmem_ld16(taddr, a_next);
+      // running range of this lane's row over the warp's columns of the tile (fminf / fmaxf drop NaN operands)
+      const bool want_range = OUT_T == OUT_F32 && p.row_range != nullptr;
+      float r_mn = __int_as_float(0x7f800000), r_mx = __int_as_float(0xff800000);
 #pragma unroll 1
       for (int c = 0; c < NCH; c++) {
         const int64_t nb = n0 + c * EPI_CH;
@@ -510,6 +541,16 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
 #pragma unroll
           for (int j = 0; j < EPI_CH; j++) v[j] = __float_as_uint(y[j]);
+          if (want_range) {
+            if (nb + EPI_CH <= p.N) {
+#pragma unroll
+              for (int j = 0; j < EPI_CH; j++) { r_mn = fminf(r_mn, y[j]); r_mx = fmaxf(r_mx, y[j]); }
+            } else {
+#pragma unroll
+              for (int j = 0; j < EPI_CH; j++)
+                if (nb + j < p.N) { r_mn = fminf(r_mn, y[j]); r_mx = fmaxf(r_mx, y[j]); }
+            }
+          }
         }
         if (OUT_T != OUT_Q8) {
           if (bulk_store) {
@@ -582,6 +623,10 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
       }
+      if (want_range && row_ok) {   // +Inf / -Inf left in place mean "nothing but NaN seen": nothing to publish
+        if (r_mx != __int_as_float(0xff800000)) atomicMax(p.row_range + m, range_key_max(r_mx));
+        if (r_mn != __int_as_float(0x7f800000)) atomicMax(p.row_range + p.M + m, range_key_min(r_mn));
+      }
       if (OUT_T == OUT_Q8 && q8_pending) {  // N ended inside a group of four chunks: columns past N are clipped
         fence_async_shared();
         __syncwarp();
@@ -620,6 +665,19 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+// The give-up path of mbar_wait on a healthy device: a barrier in shared memory that expects one arrival and never
+// gets it, nothing asynchronous in flight.  The wait must return false after limit_ns.
+__global__ void selftest_bounded_wait_kernel(uint32_t* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  abort_word = 0;
+  mbar_init(smem_u32(&bar), 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  volatile int* abort_flag = &abort_word;
+  if (!mbar_wait(smem_u32(&bar), 0u, abort_flag, limit_ns) && *abort_flag) atomicOr(status, STATUS_SELFTEST_WAIT_TIMEOUT);
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar)) : "memory");
+}
+
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
@@ -655,6 +713,24 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t K, i
   return 0;
 }
 
+// int8 matrix stored as `pieces` column blocks, block r a row-major [rows, piece_cols] matrix at ptr + r * rows * piece_cols:
+// a three-dimensional map (column in block, row, block) with the same box as make_tensor_map, so a K block lands in
+// shared memory exactly as it would from a row-major matrix.
+int make_tensor_map_pieces(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t piece_cols, int pieces, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  B200Q_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[3] = {(cuuint64_t)piece_cols, (cuuint64_t)rows, (cuuint64_t)pieces};
+  cuuint64_t gstride[2] = {(cuuint64_t)piece_cols, (cuuint64_t)piece_cols * (cuuint64_t)rows};
+  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200Q_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (rows=%lld piece_cols=%lld pieces=%d)", (int)r,
+                (long long)rows, (long long)piece_cols, pieces);
+  return 0;
+}
+
 // Row-major output [M, N]; the box is what one epilogue warp stores at a time: 32 rows by 64 bytes (EPI_CH 4-byte
 // values, or 64 int8 codes), 64-byte swizzle.
 int make_output_map(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, CUtensorMapDataType dtype, int elem_bytes) {
@@ -674,6 +750,13 @@ int make_output_map(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, CUtensorMa
 
 }  // namespace
 
+int launch_selftest_bounded_wait(b200q_ctx* ctx, unsigned long long limit_ns) {
+  selftest_bounded_wait_kernel<<<1, 1, 0, ctx->stream>>>(ctx->status_dev, limit_ns);
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 bool gemm_umma_supported(const void* A, const void* W, int64_t M, int64_t N, int64_t K) {
   return M > 0 && N > 0 && K > 0 && (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) &&
          ((reinterpret_cast<uintptr_t>(W) & 15u) == 0) && M < (1ll << 31) - BM && N < (1ll << 31) - BN && K < (1ll << 31) - BK;
@@ -681,8 +764,13 @@ bool gemm_umma_supported(const void* A, const void* W, int64_t M, int64_t N, int
 
 int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K,
                         const float* a_scales, const float* w_scales, const float* bias, int act, float* out_f32,
-                        int32_t* out_i32, int8_t* out_q, double q_scale) {
+                        int32_t* out_i32, int8_t* out_q, double q_scale, uint32_t* row_range, int a_pieces) {
   ProfScope prof(ctx, KK_GEMM_UMMA);
+  B200Q_REQUIRE(a_pieces >= 1, "tensor-core int8 gemm: the activations are stored as at least one column block");
+  B200Q_REQUIRE(a_pieces == 1 || (K % a_pieces == 0 && (K / a_pieces) % BK == 0),
+                "tensor-core int8 gemm: column blocks of the activations must be equal and a multiple of %d columns wide (K=%lld in %d blocks)",
+                BK, (long long)K, a_pieces);
+  B200Q_REQUIRE(row_range == nullptr || out_f32 != nullptr, "tensor-core int8 gemm: row ranges are published with f32 output only");
   // The launch may begin while the previous kernel of the stream drains (programmatic dependent launch): the set-up
   // of this kernel overlaps that tail, and its griddepcontrol.wait holds everything else back until the previous
   // kernel -- whatever it was -- has completed.  With profiling on an event sits between the two anyway.
@@ -691,7 +779,9 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   // CTA pairs pay off once there are enough 256-row tiles to go round; small or forced cases use single CTAs.
   const int ncta = ctx->gemm_variant == 2 ? 1 : ctx->gemm_variant == 3 ? 2 : (M >= 1024 ? 2 : 1);
   CUtensorMap tmA, tmB, tmC;
-  if (int e = make_tensor_map(&tmA, A, M, K, BM)) return e;
+  if (a_pieces > 1) {
+    if (int e = make_tensor_map_pieces(&tmA, A, M, K / a_pieces, a_pieces, BM)) return e;
+  } else if (int e = make_tensor_map(&tmA, A, M, K, BM)) return e;
   if (int e = make_tensor_map(&tmB, W_nk, N, K, BN / ncta)) return e;
   GemmParams p;
   // Bulk-tensor stores need a 16-byte aligned base and row pitch.
@@ -708,6 +798,9 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   p.a_scales = a_scales; p.w_scales = w_scales; p.bias = bias; p.act = act;
   p.out_f32 = out_f32; p.out_i32 = out_i32; p.out_q = out_q;
   p.q_scale = q_scale;
+  p.row_range = row_range;
+  p.a_pieces = a_pieces;
+  p.a_piece_cols = (int)(K / a_pieces);
   p.q_inv = 0.0f; p.q_exact = 0;
   if (out_q) {
     p.q_inv = (float)(1.0 / q_scale);

@@ -20,6 +20,12 @@ int launch_quantize_weights(b200q_ctx* ctx, const float* w, int64_t N, int64_t K
 int launch_row_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld, float* mn, float* mx);
 int launch_quantize_rows_with_range(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld_in, const float* mn,
                                     const float* mx, int8_t* q, int64_t ld_out, float* scales, int qmin, int qmax);
+// The second step of the per-token quantize when the ranges were published as keys by the kernel that produced y
+// (keys: [0, M) maxima, [M, 2M) minima; 0 = nothing seen).  One streaming pass: reads y once, writes the codes.
+int launch_quantize_rows_with_keys(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld_in, const uint32_t* keys,
+                                   int8_t* q, int64_t ld_out, float* scales, int qmin, int qmax);
+// keys[0..2M) from separate min / max arrays (the result of launch_row_range), for the CUDA-core path.
+int launch_range_to_keys(b200q_ctx* ctx, const float* mn, const float* mx, int64_t M, uint32_t* keys);
 int launch_transpose_i8(b200q_ctx* ctx, const int8_t* src_kn, int64_t K, int64_t N, int8_t* dst_nk);
 // Running min / max of a calibration observer: state[0] = min, state[1] = max (device memory, +Inf / -Inf when new).
 int launch_minmax_observe(b200q_ctx* ctx, const float* x, int64_t n, float* state);
@@ -34,9 +40,17 @@ bool gemm_umma_supported(const void* A, const void* W, int64_t M, int64_t N, int
 // Tensor-core GEMM with the fused tail.  out_i32 != null: raw accumulators (tail arguments ignored).
 // Launched as a programmatic dependent of the previous kernel on the stream: its set-up overlaps that kernel's tail,
 // and it waits for that kernel to complete before it touches anything.
+// row_range (f32 output only, may be null): 2*M words, zeroed by the caller, that receive every output row's range as
+// order-preserving keys -- see launch_quantize_rows_with_keys.  a_pieces > 1: A is stored as that many equal column
+// blocks, block r a row-major [M, K / a_pieces] matrix at A + r * M * (K / a_pieces) (the layout an all-gather of
+// column-sharded activations leaves); K / a_pieces must then be a multiple of 128.
 int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K,
                         const float* a_scales, const float* w_scales, const float* bias, int act, float* out_f32,
-                        int32_t* out_i32, int8_t* out_q, double q_scale);
+                        int32_t* out_i32, int8_t* out_q, double q_scale, uint32_t* row_range = nullptr, int a_pieces = 1);
+
+// One thread waits with the tensor-core kernel's bounded wait on a barrier nothing signals (no asynchronous work in
+// flight) and sets STATUS_SELFTEST_WAIT_TIMEOUT when the wait gives up.
+int launch_selftest_bounded_wait(b200q_ctx* ctx, unsigned long long limit_ns);
 
 // f32 pieces of a transformer block (block_kernels.cu).
 int launch_embedding(b200q_ctx* ctx, const float* table, const int32_t* tokens, const float* pos_table, int64_t M, int64_t D,
@@ -47,6 +61,11 @@ int launch_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* resid
                               float eps, int64_t M, int64_t D, float* sum_out, float* y_out, int8_t* q_out, float* scales_out);
 int launch_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v,
                     int64_t B, int64_t H, int64_t S, int64_t Dh, float scale, int causal, float* out, int64_t ld_o);
+
+// api.cu: linear + per-token requantization of its result (see the definition).
+int linear_requant_token_core(b200q_ctx* ctx, const int8_t* A, const float* a_scales, int a_pieces, const int8_t* W,
+                              const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K, float* y,
+                              int8_t* out_q, int64_t ld_q, float* out_scales);
 
 // Looks up (and caches) the device address of the fixed scratch array of b200q_linear_f32_noalloc for `device`, which
 // must be current; called once per context at creation, so the array's module is loaded before any call needs it.

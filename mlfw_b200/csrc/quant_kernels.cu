@@ -800,6 +800,80 @@ __global__ void __launch_bounds__(256) quantize_rows_with_range_kernel(const flo
   }
 }
 
+// The same second step when the ranges arrive as keys (range_key_max / range_key_min): the kernel that produced y
+// published them while the values were in its registers, so this is the only pass over y: 128-bit loads, four codes
+// per 32-bit store, four loads in flight per thread.  Needs N % 4 == 0 and 16-byte aligned rows; the generic form
+// below it takes everything else.
+template <int UNROLL>
+__global__ void __launch_bounds__(256) quantize_rows_with_keys_vec_kernel(const float* __restrict__ y, int64_t M, int N4, int64_t ld_in,
+                                                                          const uint32_t* __restrict__ keys, int8_t* __restrict__ q,
+                                                                          int64_t ld_out, float* __restrict__ scales, float qmin, float qmax) {
+  const float limit = guard_limit(qmin, qmax);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the GEMM that follows may start its set-up early
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float mx = range_max_from_key(__ldg(keys + row)), mn = range_min_from_key(__ldg(keys + M + row));
+    const float absmax = fmaxf(fabsf(mn), fabsf(mx));
+    const float inv = __fdiv_rn(127.0f, absmax);
+    const bool exact_only = !((mn < mx) && absmax <= 3.402823466e38f && is_normal_f32(inv));
+    const double s = row_scale(mn, mx);
+    const float4* yr = reinterpret_cast<const float4*>(y + row * ld_in);
+    uint32_t* qr = reinterpret_cast<uint32_t*>(q + row * ld_out);
+    for (int k0 = threadIdx.x; k0 < N4; k0 += 256 * UNROLL) {
+      float4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; u++) {
+        const int k = k0 + u * 256;
+        if (k < N4) v[u] = ld_stream(yr + k);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; u++) {
+        const int k = k0 + u * 256;
+        if (k < N4) {
+          QuantGuard guard;
+          uint32_t w = pack4_fast(v[u], inv, guard);
+          if (exact_only || guard.unsafe(limit)) w = pack4_exact_p(v[u], s, qmin, qmax);
+          qr[k] = w;
+        }
+      }
+    }
+    if (threadIdx.x == 0 && scales) scales[row] = (float)s;
+  }
+}
+
+__global__ void __launch_bounds__(256) quantize_rows_with_keys_kernel(const float* __restrict__ y, int64_t M, int64_t N, int64_t ld_in,
+                                                                      const uint32_t* __restrict__ keys, int8_t* __restrict__ q,
+                                                                      int64_t ld_out, float* __restrict__ scales, float qmin, float qmax) {
+  const float limit = guard_limit(qmin, qmax);
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float mx = range_max_from_key(keys[row]), mn = range_min_from_key(keys[M + row]);
+    const float absmax = fmaxf(fabsf(mn), fabsf(mx));
+    const float inv = __fdiv_rn(127.0f, absmax);
+    const bool exact_only = !((mn < mx) && absmax <= 3.402823466e38f && is_normal_f32(inv));
+    const double s = row_scale(mn, mx);
+    const float* yr = y + row * ld_in;
+    int8_t* qr = q + row * ld_out;
+    for (int64_t k = threadIdx.x; k < N; k += blockDim.x) {
+      QuantGuard guard;
+      const float xv = yr[k];
+      int c = quantize_fast(xv, inv, guard);
+      if (exact_only || guard.unsafe(limit)) c = quantize_exact_p(xv, s, qmin, qmax);
+      qr[k] = (int8_t)c;
+    }
+    if (threadIdx.x == 0 && scales) scales[row] = (float)s;
+  }
+}
+
+// Ranges as keys from separate minimum / maximum arrays (the row-range pass), so that column-sharded layers can
+// exchange either form with one max-reduction over the GPUs.
+__global__ void __launch_bounds__(256) range_to_keys_kernel(const float* __restrict__ mn, const float* __restrict__ mx, int64_t M,
+                                                            uint32_t* __restrict__ keys) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M) return;
+  const float a = mx[i], b = mn[i];
+  keys[i] = (a != a || a == __int_as_float(0xff800000)) ? 0u : range_key_max(a);
+  keys[M + i] = (b != b || b == __int_as_float(0x7f800000)) ? 0u : range_key_min(b);
+}
+
 // ---------------------------------------------------------------------------
 // Calibration observer (min/max mode): running minimum and maximum of every value shown to it, NaN ignored,
 // exactly as ValueObserver.update compares (src/compiler/analysis/calibration.ts:24-30).  state[0] = min, state[1] = max.
@@ -1019,6 +1093,35 @@ int launch_quantize_rows_with_range(b200q_ctx* ctx, const float* y, int64_t M, i
   if (M == 0 || N == 0) return 0;
   const unsigned blocks = (unsigned)(M < (int64_t)ctx->sm_count * 8 ? M : (int64_t)ctx->sm_count * 8);
   quantize_rows_with_range_kernel<<<blocks, 256, 0, ctx->stream>>>(y, M, N, ld_in, mn, mx, q, ld_out, scales, (float)qmin, (float)qmax);
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_quantize_rows_with_keys(b200q_ctx* ctx, const float* y, int64_t M, int64_t N, int64_t ld_in, const uint32_t* keys,
+                                   int8_t* q, int64_t ld_out, float* scales, int qmin, int qmax) {
+  ProfScope prof(ctx, KK_QUANT_TOKEN);
+  if (M == 0 || N == 0) return 0;
+  const unsigned blocks = (unsigned)(M < (int64_t)ctx->sm_count * 8 ? M : (int64_t)ctx->sm_count * 8);
+  const bool vec = N % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && aligned16(y) && (reinterpret_cast<uintptr_t>(q) & 3u) == 0 &&
+                   N / 4 < (1ll << 31);
+  if (vec) {
+    const int N4 = (int)(N / 4);
+    if (N4 >= 4 * 256)
+      quantize_rows_with_keys_vec_kernel<4><<<blocks, 256, 0, ctx->stream>>>(y, M, N4, ld_in, keys, q, ld_out, scales, (float)qmin, (float)qmax);
+    else
+      quantize_rows_with_keys_vec_kernel<1><<<blocks, 256, 0, ctx->stream>>>(y, M, N4, ld_in, keys, q, ld_out, scales, (float)qmin, (float)qmax);
+  } else {
+    quantize_rows_with_keys_kernel<<<blocks, 256, 0, ctx->stream>>>(y, M, N, ld_in, keys, q, ld_out, scales, (float)qmin, (float)qmax);
+  }
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_range_to_keys(b200q_ctx* ctx, const float* mn, const float* mx, int64_t M, uint32_t* keys) {
+  if (M == 0) return 0;
+  range_to_keys_kernel<<<(unsigned)((M + 255) / 256), 256, 0, ctx->stream>>>(mn, mx, M, keys);
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -50,6 +50,24 @@ __device__ __forceinline__ float js_round_f32(float t) {
   return (__fsub_rn(t, r) >= 0.5f) ? r + 1.0f : r;  // t - floor(t) is exact
 }
 
+// Order-preserving keys of a row's range, for atomicMax on plain 32-bit words that start at zero.
+// range_key_max(v) grows with v, range_key_min(v) grows as v falls; both are at least 1 for every non-NaN v (NaN is
+// never published), so 0 means "nothing seen", which decodes to -Inf (maximum) / +Inf (minimum): the values an
+// empty or all-NaN row has before the scale rule replaces them (quantization_types.ts:308-316).
+__device__ __forceinline__ uint32_t range_key_max(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ uint32_t range_key_min(float v) { return ~range_key_max(v); }
+__device__ __forceinline__ float range_max_from_key(uint32_t k) {
+  if (k == 0u) return __int_as_float(0xff800000);
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ float range_min_from_key(uint32_t k) {
+  if (k == 0u) return __int_as_float(0x7f800000);
+  return range_max_from_key(~k);
+}
+
 struct QuantGuard {
   int tie = 0;  // max of bits(|t - rint(t)| + |t| * 2^-21)
   int mag = 0;  // max of bits(|t|)

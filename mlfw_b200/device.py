@@ -18,7 +18,8 @@ W_NK, W_KN = 0, 1
 KIND = {np.dtype(np.int8): 0, np.dtype(np.uint8): 1, np.dtype(np.int32): 2}
 
 STATUS_BITS = {1: "TMA producer wait ran out", 2: "MMA issuer wait ran out", 4: "epilogue wait ran out",
-               8: "unexpected tensor-memory allocation", 16: "staged quantize wait ran out"}
+               8: "unexpected tensor-memory allocation", 16: "staged quantize wait ran out", 32: "embedding index outside its table",
+               64: "self test: the wait on a barrier nothing signals gave up (as it must)"}
 
 
 class DeviceBuffer:
@@ -97,17 +98,21 @@ def _ptr(b):
 class Context:
     """One GPU.  Raises if no CUDA device (or the library) is available."""
 
-    def __init__(self, device: int = 0):
+    def __init__(self, device: int = 0, _borrowed_handle=None):
         self.lib = _lib.lib()
+        self.device = device
+        self._owned = _borrowed_handle is None
+        if _borrowed_handle is not None:      # a context that belongs to a Group
+            self.handle = _borrowed_handle
+            return
         h = C.c_void_p()
         check(self.lib.b200q_create(device, C.byref(h)), "b200q_create")
         self.handle = h.value
-        self.device = device
 
     def close(self):
-        if self.handle:
+        if self.handle and self._owned:
             self.lib.b200q_destroy(self.handle)
-            self.handle = None
+        self.handle = None
 
     def __enter__(self):
         return self
@@ -152,6 +157,28 @@ class Context:
     def set_tail_mode(self, mode: int):
         """0: exact sigmoid tails (default); 1: hardware exp / reciprocal for f32 outputs (within the 1e-5 bar, faster)."""
         check(self.lib.b200q_set_tail_mode(self.handle, mode), "b200q_set_tail_mode")
+
+    def set_requant_variant(self, variant: int):
+        """0: row ranges out of the GEMM epilogue + one-pass encode (default); 1: full per-token quantize of the f32 result."""
+        check(self.lib.b200q_set_requant_variant(self.handle, variant), "b200q_set_requant_variant")
+
+    def selftest_bounded_wait(self, limit_seconds: float):
+        check(self.lib.b200q_selftest_bounded_wait(self.handle, limit_seconds), "b200q_selftest_bounded_wait")
+
+    # ---- captured steps
+    def graph_begin(self):
+        check(self.lib.b200q_graph_begin(self.handle), "b200q_graph_begin")
+
+    def graph_end(self) -> int:
+        g = C.c_void_p()
+        check(self.lib.b200q_graph_end(self.handle, C.byref(g)), "b200q_graph_end")
+        return g.value
+
+    def graph_launch(self, graph: int):
+        check(self.lib.b200q_graph_launch(self.handle, graph), "b200q_graph_launch")
+
+    def graph_destroy(self, graph: int):
+        check(self.lib.b200q_graph_destroy(self.handle, graph), "b200q_graph_destroy")
 
     def set_quant_variant(self, variant: int):
         check(self.lib.b200q_set_quant_variant(self.handle, variant), "b200q_set_quant_variant")
@@ -232,6 +259,11 @@ class Context:
         check(self.lib.b200q_int8_linear(self.handle, _ptr(A), _ptr(a_scales), _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act],
                                          M, N, K, _ptr(out)), "b200q_int8_linear")
 
+    def int8_linear_gathered(self, A, a_scales, a_blocks, W_nk, w_scales, bias, act, M, N, K, out):
+        """int8_linear with A stored as ``a_blocks`` column blocks (the layout an all-gather of column shards leaves)."""
+        check(self.lib.b200q_int8_linear_gathered(self.handle, _ptr(A), _ptr(a_scales), a_blocks, _ptr(W_nk), _ptr(w_scales),
+                                                  _ptr(bias), ACT[act], M, N, K, _ptr(out)), "b200q_int8_linear_gathered")
+
     def int8_linear_requant_static(self, A, a_scales, W_nk, w_scales, bias, act, M, N, K, out_scale, out_q):
         check(self.lib.b200q_int8_linear_requant_static(self.handle, _ptr(A), _ptr(a_scales), _ptr(W_nk), _ptr(w_scales),
                                                         _ptr(bias), ACT[act], M, N, K, out_scale, _ptr(out_q)),
@@ -241,6 +273,11 @@ class Context:
         check(self.lib.b200q_int8_linear_requant_token(self.handle, _ptr(A), _ptr(a_scales), _ptr(W_nk), _ptr(w_scales),
                                                        _ptr(bias), ACT[act], M, N, K, _ptr(out_q), _ptr(out_scales)),
               "b200q_int8_linear_requant_token")
+
+    def int8_linear_f32_requant_token(self, A, a_scales, W_nk, w_scales, bias, act, M, N, K, out_f32, out_q, out_scales):
+        check(self.lib.b200q_int8_linear_f32_requant_token(self.handle, _ptr(A), _ptr(a_scales), _ptr(W_nk), _ptr(w_scales),
+                                                           _ptr(bias), ACT[act], M, N, K, _ptr(out_f32), _ptr(out_q), _ptr(out_scales)),
+              "b200q_int8_linear_f32_requant_token")
 
     def linear_f32(self, x, W_nk, w_scales, bias, act, M, N, K, out):
         check(self.lib.b200q_linear_f32(self.handle, _ptr(x), _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act], M, N, K,
@@ -288,3 +325,99 @@ class Context:
     def quant_roundtrip_host(self, x_host, M, K, q_host, scales_host, y_host):
         check(self.lib.b200q_quant_roundtrip_host(self.handle, _ptr(x_host), M, K, _ptr(q_host), _ptr(scales_host),
                                                   _ptr(y_host)), "b200q_quant_roundtrip_host")
+
+
+def _ptr_array(items):
+    """ctypes array of device addresses (None entries become null)."""
+    arr = (C.c_void_p * len(items))()
+    for i, b in enumerate(items):
+        arr[i] = _ptr(b)
+    return arr
+
+
+class Group:
+    """Several GPUs of one node behind one NCCL communicator (``b200q_group_*``).
+
+    ``Group(devices=[0, 1])``: this process drives every rank (the group owns one context per device).
+    ``Group.join(ctx, unique_id, rank, world)``: one process per GPU; ``Group.unique_id()`` on one rank makes the id,
+    the host distributes it.  Per-GPU arguments are lists with one entry per local rank."""
+
+    def __init__(self, devices=None, _handle=None, _contexts=None):
+        self.lib = _lib.lib()
+        if _handle is not None:
+            self.handle, self.contexts = _handle, _contexts
+            return
+        devs = (C.c_int * len(devices))(*devices)
+        h = C.c_void_p()
+        check(self.lib.b200q_group_create(devs, len(devices), C.byref(h)), "b200q_group_create")
+        self.handle = h.value
+        self.contexts = [Context(d, _borrowed_handle=self.lib.b200q_group_ctx(self.handle, i)) for i, d in enumerate(devices)]
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        check(_lib.lib().b200q_group_unique_id(buf), "b200q_group_unique_id")
+        return buf.raw
+
+    @classmethod
+    def join(cls, ctx: Context, unique_id: bytes, rank: int, world: int) -> "Group":
+        assert len(unique_id) == 128
+        h = C.c_void_p()
+        buf = C.create_string_buffer(unique_id, 128)
+        check(ctx.lib.b200q_group_create_rank(ctx.handle, buf, rank, world, C.byref(h)), "b200q_group_create_rank")
+        return cls(_handle=h.value, _contexts=[ctx])
+
+    def close(self):
+        if self.handle:
+            for c in self.contexts:
+                if not c._owned:
+                    c.handle = None
+            check(self.lib.b200q_group_destroy(self.handle), "b200q_group_destroy")
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    @property
+    def world(self) -> int:
+        return self.lib.b200q_group_world(self.handle)
+
+    @property
+    def local_count(self) -> int:
+        return self.lib.b200q_group_local_count(self.handle)
+
+    def rank(self, local_index: int = 0) -> int:
+        return self.lib.b200q_group_rank(self.handle, local_index)
+
+    def nccl_version(self) -> int:
+        v = C.c_int()
+        check(self.lib.b200q_group_nccl_version(self.handle, C.byref(v)), "b200q_group_nccl_version")
+        return v.value
+
+    def sync(self):
+        check(self.lib.b200q_group_sync(self.handle), "b200q_group_sync")
+
+    def fence(self):
+        check(self.lib.b200q_group_fence(self.handle), "b200q_group_fence")
+
+    def set_chunks(self, chunks: int):
+        check(self.lib.b200q_group_set_chunks(self.handle, chunks), "b200q_group_set_chunks")
+
+    def linear_mshard(self, x, rows, W_nk, w_scales, bias, act, N, K, out):
+        r = (C.c_int64 * len(rows))(*rows)
+        check(self.lib.b200q_group_linear_mshard(self.handle, _ptr_array(x), r, _ptr_array(W_nk), _ptr_array(w_scales),
+                                                 _ptr_array(bias) if bias is not None else None, ACT[act], N, K, _ptr_array(out)),
+              "b200q_group_linear_mshard")
+
+    def linear_nshard(self, q_in, in_scales, in_blocks, W_shard, w_scales, bias, act, M, N, K, q_out=None, out_scales=None, out_f32=None):
+        check(self.lib.b200q_group_linear_nshard(self.handle, _ptr_array(q_in), _ptr_array(in_scales), in_blocks, _ptr_array(W_shard),
+                                                 _ptr_array(w_scales), _ptr_array(bias) if bias is not None else None, ACT[act], M, N, K,
+                                                 _ptr_array(q_out) if q_out is not None else None,
+                                                 _ptr_array(out_scales) if out_scales is not None else None,
+                                                 _ptr_array(out_f32) if out_f32 is not None else None), "b200q_group_linear_nshard")
+
+    def all_gather(self, send, recv, nbytes: int):
+        check(self.lib.b200q_group_all_gather(self.handle, _ptr_array(send), _ptr_array(recv), nbytes), "b200q_group_all_gather")

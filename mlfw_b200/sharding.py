@@ -1,16 +1,20 @@
-"""Multi-GPU host logic of the quantized linear path (one process per GPU, ``torch.distributed`` for the plumbing).
+"""Planner and host-side mirror of the multi-GPU forms of the quantized linear path.
 
 The reference has no multi-device execution (its ``all_gather`` / ``all_reduce`` graph ops decompose to
-single-device slices, src/compiler/passes/decompose/decomposition_pass.ts:105-143); this is new.
+single-device slices, src/compiler/passes/decompose/decomposition_pass.ts:105-143); this is new.  The execution
+itself lives behind the C ABI (``b200q_group_*`` in ``include/b200q.h``, NCCL inside ``libb200q.so``); this module
+holds what a host needs around it and what can be checked without a GPU:
 
-* **Row (M) sharding** — every output row depends only on its own input row and the replicated weights, so the
+* **Row (M) sharding** - every output row depends only on its own input row and the replicated weights, so the
   ranks take contiguous row blocks and nothing is exchanged on the data path (:func:`row_block`).
-* **Column (N) sharding** — the weights are split by output channel, every rank holds the whole int8 activation.
+* **Column (N) sharding** - the weights are split by output channel, every rank holds the whole int8 activation.
   A layer is then: local GEMM + tail on the rank's columns; per-token requantization of the FULL row, which needs the
-  row's range over all ranks (two tiny all-reduces, min and max) and then gives bit-identical codes on every
-  rank; an all-gather of the int8 column blocks (int8 on the wire, not f32).  :class:`ColumnShardedStack` runs a
-  stack of such layers.  It is written against a small compute interface so that the collective logic runs on CPU
-  ranks (gloo) in the tests with a CPU stand-in, and on GPUs with :class:`DeviceOps`.
+  row's range over all ranks (ONE max-reduction over order-preserving keys of the local minima and maxima,
+  :func:`range_keys`) and then gives bit-identical codes on every rank; an all-gather of the int8 column blocks (int8
+  on the wire, not f32).  :class:`ColumnShardedStack` states that protocol against a small compute interface, so
+  that it runs on CPU ranks (gloo) in the tests with a CPU stand-in for the kernels.
+* The layout ``b200q_group_linear_nshard`` leaves its gathered codes in (:func:`chunk_rows`,
+  :func:`from_gathered_layout`).
 """
 from __future__ import annotations
 
@@ -54,7 +58,7 @@ class ShardedLayer:
 class ColumnShardedStack:
     """Runs consecutive int8 linears with per-token requantization between them, weights split by output channel.
 
-    ``ops`` supplies the computation on one rank (see :class:`DeviceOps`); ``dist`` is ``torch.distributed`` (or
+    ``ops`` supplies the computation on one rank (the tests pass a CPU stand-in); ``dist`` is ``torch.distributed`` (or
     None for a single rank).  Activations travel between layers as int8 codes [M, N] plus f32 scales [M], identical
     on every rank."""
 
@@ -71,9 +75,10 @@ class ColumnShardedStack:
             if final and last_f32:
                 return ops.all_gather_columns(y, M, layer, self.dist, self.world, np.float32), None
             mn, mx = ops.row_range(y, M, layer.cols)
-            if self.dist is not None and self.world > 1:              # the exchange step: row ranges over all ranks
-                ops.all_reduce(mn, "min", self.dist)
-                ops.all_reduce(mx, "max", self.dist)
+            keys = ops.to_keys(mn, mx)                                # [2*M] order-preserving keys, 0 = nothing seen
+            if self.dist is not None and self.world > 1:              # the exchange step: ONE max-reduction over all ranks
+                ops.all_reduce_max(keys, self.dist)
+            mn, mx = ops.from_keys(keys)
             q_local, scales = ops.quantize_with_range(y, M, layer.cols, mn, mx)
             q = ops.all_gather_columns(q_local, M, layer, self.dist, self.world, np.int8)   # int8 on the wire
         return q, scales
@@ -84,54 +89,69 @@ def gather_layout(N: int, world: int, align: int = 256) -> List[Tuple[int, int]]
     return [column_block(N, world, r, align) for r in range(world)]
 
 
-class DeviceOps:
-    """The compute interface of :class:`ColumnShardedStack` on one GPU: torch CUDA tensors hold the buffers (so NCCL can
-    move them), every computation is a call into libb200q.so on the context's stream."""
+def range_keys(mn: np.ndarray, mx: np.ndarray) -> np.ndarray:
+    """Order-preserving uint32 keys of per-row minima and maxima, as the GEMM epilogue publishes them: ``[0, M)`` the
+    maxima (a key grows with the value), ``[M, 2M)`` the minima (a key grows as the value falls), 0 where nothing was
+    seen (``mx = -inf`` / ``mn = +inf``, or NaN).  The maximum of two ranks' keys is the key of their joint range."""
+    def key_max(v):
+        u = np.ascontiguousarray(v, np.float32).view(np.uint32)
+        k = np.where(u & np.uint32(0x80000000), ~u, u | np.uint32(0x80000000)).astype(np.uint32)
+        return k
+    mn, mx = np.asarray(mn, np.float32), np.asarray(mx, np.float32)
+    kmax = np.where(np.isnan(mx) | (mx == -np.inf), np.uint32(0), key_max(mx))
+    kmin = np.where(np.isnan(mn) | (mn == np.inf), np.uint32(0), ~key_max(mn))
+    return np.concatenate([kmax, kmin]).astype(np.uint32)
 
-    def __init__(self, ctx, torch):
-        self.ctx, self.torch = ctx, torch
-        self.dev = torch.device("cuda", ctx.device)
 
-    def _sync_in(self):                 # torch work (collectives, copies) before library kernels
-        self.torch.cuda.current_stream(self.dev).synchronize()
+def range_from_keys(keys: np.ndarray):
+    """(minima, maxima) f32 from :func:`range_keys` output; 0 decodes to +inf / -inf."""
+    keys = np.asarray(keys, np.uint32)
+    M = keys.size // 2
 
-    def _sync_out(self):                # library kernels before torch work
-        self.ctx.sync()
+    def val_max(k):
+        u = np.where(k & np.uint32(0x80000000), k & np.uint32(0x7FFFFFFF), ~k).astype(np.uint32)
+        return u.view(np.float32)
+    kmax, kmin = keys[:M], keys[M:]
+    mx = np.where(kmax == 0, np.float32(-np.inf), val_max(kmax)).astype(np.float32)
+    mn = np.where(kmin == 0, np.float32(np.inf), val_max(~kmin)).astype(np.float32)
+    return mn, mx
 
-    def linear(self, q, scales, layer: ShardedLayer, M: int):
-        t = self.torch
-        y = t.empty((M, layer.cols), dtype=t.float32, device=self.dev)
-        self._sync_in()
-        self.ctx.int8_linear(q.data_ptr(), scales.data_ptr(), layer.w.data_ptr(), layer.w_scales.data_ptr(),
-                             layer.bias.data_ptr() if layer.bias is not None else None, layer.act, M, layer.cols, layer.K, y.data_ptr())
-        self._sync_out()
-        return y
 
-    def row_range(self, y, M: int, cols: int):
-        t = self.torch
-        mn = t.empty((M,), dtype=t.float32, device=self.dev)
-        mx = t.empty((M,), dtype=t.float32, device=self.dev)
-        self._sync_in()
-        self.ctx.row_range(y.data_ptr(), M, cols, cols, mn.data_ptr(), mx.data_ptr())
-        self._sync_out()
-        return mn, mx
+def chunk_rows(M: int, chunks: int, c: int) -> Tuple[int, int]:
+    """(first row, rows) of row chunk ``c`` of the column-sharded call: whole 256-row tiles, the last takes the rest."""
+    per = ((M + chunks - 1) // chunks + 255) // 256 * 256
+    a, b = min(per * c, M), min(per * (c + 1), M)
+    return a, b - a
 
-    def all_reduce(self, v, op: str, dist):
-        dist.all_reduce(v, op=dist.ReduceOp.MIN if op == "min" else dist.ReduceOp.MAX)
 
-    def quantize_with_range(self, y, M: int, cols: int, mn, mx):
-        t = self.torch
-        q = t.empty((M, cols), dtype=t.int8, device=self.dev)
-        s = t.empty((M,), dtype=t.float32, device=self.dev)
-        self._sync_in()
-        self.ctx.quantize_rows_with_range(y.data_ptr(), M, cols, cols, mn.data_ptr(), mx.data_ptr(), q.data_ptr(), cols, s.data_ptr())
-        self._sync_out()
-        return q, s
+def from_gathered_layout(buf: np.ndarray, M: int, N: int, world: int, chunks: int = 1) -> np.ndarray:
+    """Row-major ``[M, N]`` from the layout ``b200q_group_linear_nshard`` leaves its gathered codes in: per row chunk
+    (starting at element ``N * first_row``) the ranks' column blocks one after the other, block ``r`` a row-major
+    ``[rows of the chunk, N / world]`` matrix."""
+    cols = N // world
+    flat = np.asarray(buf).reshape(-1)
+    out = np.empty((M, N), flat.dtype)
+    for c in range(chunks):
+        r0, rows = chunk_rows(M, chunks, c)
+        if rows == 0:
+            continue
+        blk = flat[r0 * N:(r0 + rows) * N].reshape(world, rows, cols)
+        for r in range(world):
+            out[r0:r0 + rows, r * cols:(r + 1) * cols] = blk[r]
+    return out
 
-    def all_gather_columns(self, local, M: int, layer: ShardedLayer, dist, world: int, dtype):
-        if dist is None or world == 1:
-            return local
-        return gather_columns(self.torch, dist, local, M, layer.N, world)
+
+def to_gathered_layout(a: np.ndarray, world: int, chunks: int = 1) -> np.ndarray:
+    """Inverse of :func:`from_gathered_layout` (flat array of ``M * N`` elements)."""
+    M, N = a.shape
+    cols = N // world
+    out = np.empty(M * N, a.dtype)
+    for c in range(chunks):
+        r0, rows = chunk_rows(M, chunks, c)
+        if rows == 0:
+            continue
+        out[r0 * N:(r0 + rows) * N] = np.stack([a[r0:r0 + rows, r * cols:(r + 1) * cols] for r in range(world)]).reshape(-1)
+    return out
 
 
 def gather_columns(torch, dist, local, M: int, N: int, world: int):

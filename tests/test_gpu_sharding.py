@@ -1,5 +1,5 @@
 """Device side of the column-sharded path on one GPU: the two-step per-token quantize (local row range, then codes from
-an agreed range) reproduces the one-step kernel, and a single-rank ColumnShardedStack over DeviceOps matches the oracle."""
+an agreed range) reproduces the one-step kernel.  The sharded layers themselves are in test_gpu_group.py."""
 import numpy as np
 import pytest
 
@@ -40,27 +40,3 @@ def test_two_step_quantize_over_column_blocks(ctx, orc):
         ctx.quantize_rows_with_range(dy.ptr + 4 * c0, M, cols, N, dmn, dmx, dq.ptr + c0, N, ds.ptr)
     ctx.sync()
     assert (dq.download() == rq).all() and (ds.download().view(np.uint32) == rs.view(np.uint32)).all()
-
-
-def test_single_rank_stack_on_device(ctx, orc):
-    import torch
-    from mlfw_b200 import sharding
-    rng = np.random.default_rng(4)
-    M, dims = 130, [256, 768, 512]
-    dev = torch.device("cuda", 0)
-    x = rng.standard_normal((M, dims[0])).astype(np.float32)
-    layers, ref_layers = [], []
-    for i in range(2):
-        K, N = dims[i], dims[i + 1]
-        w = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
-        ws = (rng.uniform(1e-3, 1e-2, N) / np.sqrt(K) * 8).astype(np.float32)
-        act = "silu" if i == 0 else "none"
-        ref_layers.append((w, ws, act))
-        layers.append(sharding.ShardedLayer(K, N, 0, N, torch.from_numpy(w).to(dev), torch.from_numpy(ws).to(dev), None, act))
-    q, _, s = orc.quantize_per_token(x)
-    stack = sharding.ColumnShardedStack(sharding.DeviceOps(ctx, torch), None, 0, 1, layers)
-    y, _ = stack.forward(torch.from_numpy(q).to(dev), torch.from_numpy(s).to(dev), M, last_f32=True)
-    h = orc.epilogue(orc.qdot_i32(q, ref_layers[0][0]), s, ref_layers[0][1], None, "silu")
-    hq, _, hs = orc.quantize_per_token(h)
-    ref = orc.epilogue(orc.qdot_i32(hq, ref_layers[1][0]), hs, ref_layers[1][1], None, "none")
-    assert (y.cpu().numpy().view(np.uint32) == ref.view(np.uint32)).all()

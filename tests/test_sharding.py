@@ -6,7 +6,8 @@ import socket
 import numpy as np
 import pytest
 
-from mlfw_b200.sharding import ColumnShardedStack, ShardedLayer, column_block, gather_columns, gather_layout, row_block
+from mlfw_b200.sharding import (ColumnShardedStack, ShardedLayer, chunk_rows, column_block, from_gathered_layout, gather_columns,
+                                gather_layout, range_from_keys, range_keys, row_block, to_gathered_layout)
 
 
 def test_row_blocks_partition_the_rows():
@@ -32,8 +33,41 @@ def test_column_blocks_are_tile_aligned_and_cover_n():
     assert gather_layout(8192, 8) == [(i * 1024, 1024) for i in range(8)]
 
 
+def test_range_keys_order_like_the_values_and_round_trip():
+    vals = np.array([-np.inf, -3e38, -1.5, -1e-45, -0.0, 0.0, 1e-45, 2.5, 3e38, np.inf], np.float32)
+    keys = range_keys(vals, vals)
+    kmax, kmin = keys[:vals.size].astype(np.int64), keys[vals.size:].astype(np.int64)
+    assert kmax[0] == 0 and (np.diff(kmax[1:]) > 0).all() and (kmax[1:] > 0).all()       # -inf as a maximum = nothing seen
+    assert kmin[-1] == 0 and (np.diff(kmin[:-1]) < 0).all() and (kmin[:-1] > 0).all()    # +inf as a minimum = nothing seen
+    mn, mx = range_from_keys(keys)
+    assert (mx[1:].view(np.uint32) == vals[1:].view(np.uint32)).all() and mx[0] == -np.inf
+    assert (mn[:-1].view(np.uint32) == vals[:-1].view(np.uint32)).all() and mn[-1] == np.inf
+    nan = np.array([np.nan], np.float32)
+    assert (range_keys(nan, nan) == 0).all()
+    # the maximum of two ranks' keys is the key of the joint range
+    rng = np.random.default_rng(0)
+    a, b = rng.standard_normal((2, 100)).astype(np.float32) * 50, rng.standard_normal((2, 100)).astype(np.float32) * 50
+    lo1, hi1, lo2, hi2 = np.minimum(a[0], a[1]), np.maximum(a[0], a[1]), np.minimum(b[0], b[1]), np.maximum(b[0], b[1])
+    mn, mx = range_from_keys(np.maximum(range_keys(lo1, hi1), range_keys(lo2, hi2)))
+    assert (mn == np.minimum(lo1, lo2)).all() and (mx == np.maximum(hi1, hi2)).all()
+
+
+def test_gathered_layout_round_trip_and_chunks():
+    assert [chunk_rows(4096, 4, c) for c in range(4)] == [(0, 1024), (1024, 1024), (2048, 1024), (3072, 1024)]
+    assert [chunk_rows(600, 2, c) for c in range(2)] == [(0, 512), (512, 88)]
+    assert [chunk_rows(100, 3, c) for c in range(3)] == [(0, 100), (100, 0), (100, 0)]
+    rng = np.random.default_rng(1)
+    for M, N, world, chunks in [(600, 512, 4, 2), (700, 1024, 8, 3), (64, 256, 2, 1), (300, 384, 1, 2)]:
+        a = rng.integers(-127, 128, size=(M, N)).astype(np.int8)
+        g = to_gathered_layout(a, world, chunks)
+        assert (from_gathered_layout(g, M, N, world, chunks) == a).all()
+        if chunks == 1:      # one chunk: exactly what an all-gather of the ranks' [M, N/world] blocks produces
+            cols = N // world
+            assert (g.reshape(world, M, cols)[world - 1] == a[:, (world - 1) * cols:]).all()
+
+
 class OracleOps:
-    """CPU stand-in for DeviceOps (test infrastructure): numpy + the oracle, torch CPU tensors for the collectives."""
+    """CPU stand-in for the device computation (test infrastructure): numpy + the oracle, torch CPU tensors for the collectives."""
 
     def __init__(self, orc, torch):
         self.orc, self.torch = orc, torch
@@ -46,8 +80,15 @@ class OracleOps:
         a = y.numpy()
         return self.torch.from_numpy(np.fmin.reduce(a, axis=1).astype(np.float32)), self.torch.from_numpy(np.fmax.reduce(a, axis=1).astype(np.float32))
 
-    def all_reduce(self, v, op, dist):
-        dist.all_reduce(v, op=dist.ReduceOp.MIN if op == "min" else dist.ReduceOp.MAX)
+    def to_keys(self, mn, mx):
+        return self.torch.from_numpy(range_keys(mn.numpy(), mx.numpy()).astype(np.int64))     # gloo reduces int64
+
+    def all_reduce_max(self, keys, dist):
+        dist.all_reduce(keys, op=dist.ReduceOp.MAX)
+
+    def from_keys(self, keys):
+        mn, mx = range_from_keys(keys.numpy().astype(np.uint32))
+        return self.torch.from_numpy(mn), self.torch.from_numpy(mx)
 
     def quantize_with_range(self, y, M, cols, mn, mx):
         # codes of each local element given the row's agreed range: append the two range ends to the row, quantize, drop them
