@@ -263,7 +263,9 @@ int b200q_selftest_bounded_wait(b200q_ctx* ctx, double limit_seconds);
  * own process (b200q_group_create_rank: the process passes its context; the 128-byte id comes from
  * b200q_group_unique_id on one rank and reaches the others by the host's own means).  The per-GPU arguments of the
  * calls below are arrays with one entry per LOCAL rank (b200q_group_local_count: n, or 1), holding device pointers
- * on that rank's GPU.  NCCL is loaded when the first group function is called (libnccl.so.2). */
+ * on that rank's GPU.  NCCL is loaded when the first group function is called: the libnccl.so.2 the process already
+ * holds if there is one, else the file named by the environment variable B200Q_NCCL_LIBRARY, else the system's.  Two
+ * different NCCL builds do not mix in one process, so a host that brings its own loads it first. */
 typedef struct b200q_group b200q_group;
 int b200q_group_unique_id(void* id128);                       /* host buffer of 128 bytes */
 int b200q_group_create(const int* devices, int n, b200q_group** out);

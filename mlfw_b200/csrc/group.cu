@@ -24,6 +24,7 @@
 // host except create, destroy and sync.
 #include <dlfcn.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -60,8 +61,17 @@ NcclApi g_nccl;
 
 int nccl_api(NcclApi** out) {
   if (!g_nccl.handle) {
-    // A copy that the process already holds (for instance the one a Python host's torch brought) comes first.
+    // A copy that the process already holds comes first (two different NCCL builds in one process do not mix: a
+    // host that will load its own later, as a Python process importing torch does, loads it before the first group
+    // call or names it in B200Q_NCCL_LIBRARY); then the named one; then the system's.
     void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    if (!h) {
+      const char* named = getenv("B200Q_NCCL_LIBRARY");
+      if (named && *named) {
+        h = dlopen(named, RTLD_NOW | RTLD_GLOBAL);
+        B200Q_REQUIRE(h != nullptr, "multi-GPU groups: B200Q_NCCL_LIBRARY=%s could not be loaded (%s)", named, dlerror());
+      }
+    }
     if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
     if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_LOCAL);
     B200Q_REQUIRE(h != nullptr, "multi-GPU groups need NCCL: libnccl.so.2 could not be loaded (%s)", dlerror());
@@ -104,7 +114,13 @@ struct Member {
   int rank = 0;
   NcclComm comm = nullptr;
   cudaStream_t comm_stream = nullptr;         // collectives of a chunked call; the context's stream otherwise
-  Workspace y, keys, q_local;                 // f32 result of the local channels, range keys, local codes
+  Workspace y, keys;                          // f32 result of the local channels, range keys
+  // Local codes, two buffers used in turn by successive calls: chunk c of one call sits at a different offset than
+  // chunk c of the next (the channel counts differ), so a call must not write where the previous call's later
+  // all-gathers may still be reading.  By the end of a call the context's stream has waited for every all-gather of
+  // the call before it, which makes the buffer of two calls ago free again.
+  Workspace q_local[2];
+  int q_flip = 0;
   cudaEvent_t ev_gemm[MAX_CHUNKS] = {}, ev_reduced[MAX_CHUNKS] = {}, ev_coded[MAX_CHUNKS] = {}, ev_gathered[MAX_CHUNKS] = {};
   int gathers_pending = 0;                    // chunks of the previous channel-sharded call whose all-gather the context's stream has not waited for
 };
@@ -242,7 +258,7 @@ int b200q_group_destroy(b200q_group* g) {
   for (Member& m : g->members) {
     if (!m.ctx) continue;
     cudaSetDevice(m.ctx->device);
-    Workspace* all[] = {&m.y, &m.keys, &m.q_local};
+    Workspace* all[] = {&m.y, &m.keys, &m.q_local[0], &m.q_local[1]};
     for (Workspace* w : all)
       if (w->ptr) cudaFree(w->ptr);
     for (int c = 0; c < MAX_CHUNKS; c++) {
@@ -361,13 +377,14 @@ int b200q_group_linear_nshard(b200q_group* g, const int8_t* const* q_in, const f
       // A workspace that has to grow is freed in the order of the context's stream, which knows nothing of the
       // collectives still running on the second stream: wait for those first (sizes settle after the first pass).
       const bool grows = (size_t)M * cols * sizeof(float) > m.y.bytes || (size_t)2 * M * sizeof(uint32_t) > m.keys.bytes ||
-                         (W > 1 && (size_t)M * cols > m.q_local.bytes);
+                         (W > 1 && ((size_t)M * cols > m.q_local[0].bytes || (size_t)M * cols > m.q_local[1].bytes));
       if (grows) {
         if (int e = fence_member(m)) return e;
       }
       if (member_reserve(m, m.y, (size_t)M * cols * sizeof(float))) return 1;
       if (member_reserve(m, m.keys, (size_t)2 * M * sizeof(uint32_t))) return 1;
-      if (W > 1 && member_reserve(m, m.q_local, (size_t)M * cols)) return 1;
+      if (W > 1 && (member_reserve(m, m.q_local[0], (size_t)M * cols) || member_reserve(m, m.q_local[1], (size_t)M * cols))) return 1;
+      m.q_flip ^= 1;
       B200Q_CHECK_CUDA(cudaMemsetAsync(m.keys.ptr, 0, (size_t)2 * M * sizeof(uint32_t), m.ctx->stream));
     }
   }
@@ -429,7 +446,7 @@ int b200q_group_linear_nshard(b200q_group* g, const int8_t* const* q_in, const f
       if (side) B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, m.ev_reduced[c], 0));
       const float* y = (const float*)m.y.ptr + r0 * cols;
       const uint32_t* keys = (const uint32_t*)m.keys.ptr + 2 * r0;
-      int8_t* dst = W > 1 ? (int8_t*)m.q_local.ptr + r0 * cols : q_out[i] + r0 * N;
+      int8_t* dst = W > 1 ? (int8_t*)m.q_local[m.q_flip].ptr + r0 * cols : q_out[i] + r0 * N;
       if (int e = launch_quantize_rows_with_keys(ctx, y, rc, cols, cols, keys, dst, cols, out_scales[i] + r0, -127, 127)) return e;
       if (side) B200Q_CHECK_CUDA(cudaEventRecord(m.ev_coded[c], ctx->stream));
     }
@@ -441,7 +458,7 @@ int b200q_group_linear_nshard(b200q_group* g, const int8_t* const* q_in, const f
         B200Q_CHECK_CUDA(cudaSetDevice(m.ctx->device));
         cudaStream_t cs = side ? m.comm_stream : m.ctx->stream;
         if (side) B200Q_CHECK_CUDA(cudaStreamWaitEvent(cs, m.ev_coded[c], 0));
-        const int8_t* src = (const int8_t*)m.q_local.ptr + r0 * cols;
+        const int8_t* src = (const int8_t*)m.q_local[m.q_flip].ptr + r0 * cols;
         B200Q_CHECK_NCCL(api, api->AllGather(src, q_out[i] + r0 * N, (size_t)rc * cols, NCCL_INT8, m.comm, cs));
         if (side) B200Q_CHECK_CUDA(cudaEventRecord(m.ev_gathered[c], cs));
       }

@@ -327,6 +327,24 @@ class Context:
                                                   _ptr(y_host)), "b200q_quant_roundtrip_host")
 
 
+def _preload_nccl():
+    """The library takes the NCCL that is already in the process.  In a Python process that is, sooner or later, the
+    one torch is built against (``nvidia.nccl`` in site-packages), and a second, different build next to it breaks
+    torch's import: so that one is loaded first when it exists.  Without it the library finds the system's."""
+    import importlib.util
+    import os
+    try:
+        spec = importlib.util.find_spec("nvidia.nccl")
+    except (ImportError, ValueError):
+        spec = None
+    for base in (spec.submodule_search_locations if spec is not None and spec.submodule_search_locations else []):
+        path = os.path.join(base, "lib", "libnccl.so.2")
+        if os.path.exists(path):
+            C.CDLL(path, mode=C.RTLD_GLOBAL)
+            return path
+    return None
+
+
 def _ptr_array(items):
     """ctypes array of device addresses (None entries become null)."""
     arr = (C.c_void_p * len(items))()
@@ -344,6 +362,7 @@ class Group:
 
     def __init__(self, devices=None, _handle=None, _contexts=None):
         self.lib = _lib.lib()
+        _preload_nccl()
         if _handle is not None:
             self.handle, self.contexts = _handle, _contexts
             return
@@ -355,6 +374,7 @@ class Group:
 
     @staticmethod
     def unique_id() -> bytes:
+        _preload_nccl()
         buf = C.create_string_buffer(128)
         check(_lib.lib().b200q_group_unique_id(buf), "b200q_group_unique_id")
         return buf.raw
@@ -362,6 +382,7 @@ class Group:
     @classmethod
     def join(cls, ctx: Context, unique_id: bytes, rank: int, world: int) -> "Group":
         assert len(unique_id) == 128
+        _preload_nccl()
         h = C.c_void_p()
         buf = C.create_string_buffer(unique_id, 128)
         check(ctx.lib.b200q_group_create_rank(ctx.handle, buf, rank, world, C.byref(h)), "b200q_group_create_rank")

@@ -2,10 +2,11 @@
 
 Inputs are the closed-form ones the reference's own tests use (the reference stores no arrays for this path;
 tests/compiler/passes/quantization/pass.test.js:461-549, tests/e2e/cuda/training-quant.cuda.test.js:70-125,
-tests/compiler/passes/quantization/params.test.js:148-184 inside the reference project).  Outputs are what the CPU
-oracle computes for them; the oracle itself is pinned to the formulas and thresholds those tests assert
-(tests/test_oracle_reference_vectors.py).  The fixtures freeze that state: a later change of the oracle or of the
-CUDA kernels that alters a single bit shows up against them.
+tests/compiler/passes/quantization/params.test.js:148-184 inside the reference project).  Outputs are computed by
+``oracle/jsport.py`` - the pure-Python, line-by-line restatement of the reference's TypeScript - and by nothing else:
+the C++ oracle is not imported here.  ``tests/test_golden.py`` then holds the C++ oracle (CPU) and the CUDA path (GPU)
+to these values bit for bit, so the fixtures are a check of both against an independent restatement, not a snapshot of
+either.  numpy only packs the results.
 """
 import math
 import os
@@ -15,28 +16,37 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
-import oracle as orc  # noqa: E402
+from oracle import jsport as js  # noqa: E402   (the Python port only; importing the package builds nothing)
 
 ACTS = ["none", "relu", "gelu_sigmoid", "silu", "gelu_tanh"]
 
 
+def f32(v):
+    return js.fround(v)
+
+
 def int8_matmul_case(M, K, N, a_step, w_fn, a_scale, per_channel):
-    A = np.array([math.sin(i * a_step) for i in range(M * K)], np.float32).reshape(M, K)
-    W = np.array([w_fn(k, n) for k in range(K) for n in range(N)], np.float32).reshape(K, N)
+    A = [[f32(math.sin((m * K + k) * a_step)) for k in range(K)] for m in range(M)]
+    W = [[f32(w_fn(k, n)) for n in range(N)] for k in range(K)]                     # [K, N], as the reference's tests build it
     if a_scale is None:
-        a_scale = float(np.abs(A).max()) / 127 or 1e-10
+        a_scale = js.js_or(max(abs(v) for r in A for v in r) / 127, 1e-10)
+    flat_w = [v for r in W for v in r]
     if per_channel:
-        wsc = orc.per_channel_scales(W.astype(np.float64), (K, N), 1)
-        wq = orc.quantize_per_channel(W.astype(np.float64), (K, N), 1, wsc)
-        sv = np.array([a_scale * s for s in wsc])
+        wp = js.QuantizationParams.from_constant_array_per_channel(flat_w, [K, N], 1)
+        codes = wp.quantize_array_per_channel(flat_w, [K, N])
+        wq = [[js.to_int8(codes[k * N + n]) for n in range(N)] for k in range(K)]
+        sv = [a_scale * s for s in wp.scale]                                          # binary64 products, stored as f32 below
     else:
-        ws, _ = orc.from_constant_array(W.astype(np.float64).reshape(-1))
-        wq = np.array([orc.qp_quantize(float(v), ws, 0, -127, 127) for v in W.reshape(-1)], np.int8).reshape(K, N)
-        sv = np.full(N, a_scale * ws)
-    aq = orc.quantize_static(A, a_scale, 0)
-    acc = orc.qdot_i32(aq, wq, "KN")
-    out = orc.epilogue_sv(acc, sv.astype(np.float32))
-    return dict(A=A, W=W, a_scale=np.float64(a_scale), wq=wq, sv=sv.astype(np.float32), aq=aq, acc=acc, out=out)
+        wp = js.QuantizationParams.from_constant_array(flat_w, js.PER_TENSOR_SYMMETRIC)
+        wq = [[js.to_int8(wp.quantize(W[k][n])) for n in range(N)] for k in range(K)]
+        sv = [a_scale * wp.scale] * N
+    aq = [[js.compiled_quantize(v, a_scale, 0) for v in r] for r in A]
+    w_nk = [[wq[k][n] for k in range(K)] for n in range(N)]
+    acc = js.quantized_dot(aq, w_nk)
+    sv32 = [f32(v) for v in sv]
+    out = js.tail_sv(acc, sv32, None, "none")
+    return dict(A=np.array(A, np.float32), W=np.array(W, np.float32), a_scale=np.float64(a_scale), wq=np.array(wq, np.int8),
+                sv=np.array(sv32, np.float32), aq=np.array(aq, np.int8), acc=np.array(acc, np.int32), out=np.array(out, np.float32))
 
 
 def main():
@@ -47,42 +57,47 @@ def main():
     np.savez(os.path.join(HERE, "matmul_m64k128n32.npz"),
              **int8_matmul_case(64, 128, 32, 0.3, lambda k, n: math.sin((k * 32 + n) * 1.1) * 3, 0.02, False))
     # pass.test.js:461-491 + training-quant fake-quant n=16: static quantize / dequantize at scale 6/127
-    s, _ = orc.from_range(-6, 6)
-    x = np.array([3.5, -2.1, 5.9, 1.234, -5.9, 0.001] + [math.sin(i) * 3 for i in range(16)] +
-                 [(k + 0.5) * s for k in range(-6, 6)] + [float("nan"), float("inf"), float("-inf"), 0.0, -0.0, 1e30], np.float32)
-    q = orc.quantize_static(x, s, 0)
-    np.savez(os.path.join(HERE, "static_quant.npz"), x=x, scale=np.float64(s), q=q, y=orc.dequantize_static(q, s, 0))
+    s = js.QuantizationParams.from_range(-6, 6, js.PER_TENSOR_SYMMETRIC).scale
+    x = [f32(v) for v in [3.5, -2.1, 5.9, 1.234, -5.9, 0.001] + [math.sin(i) * 3 for i in range(16)] +
+         [(k + 0.5) * s for k in range(-6, 6)] + [float("nan"), float("inf"), float("-inf"), 0.0, -0.0, 1e30]]
+    q = [js.compiled_quantize(v, s, 0) for v in x]
+    np.savez(os.path.join(HERE, "static_quant.npz"), x=np.array(x, np.float32), scale=np.float64(s), q=np.array(q, np.int8),
+             y=np.array([js.compiled_dequantize(c, s, 0) for c in q], np.float32))
     # per-token quantize of a [12, 40] tensor of sines with one constant row, one zero row and one row with a NaN
-    xt = np.array([math.sin(0.37 * i) * (1 + (i % 7)) for i in range(12 * 40)], np.float32).reshape(12, 40)
-    xt[3] = 2.5
-    xt[5] = 0.0
-    xt[7, 11] = np.nan
-    qt, s64, s32 = orc.quantize_per_token(xt)
-    np.savez(os.path.join(HERE, "per_token.npz"), x=xt, q=qt, scales64=s64, scales32=s32, y=orc.dequantize_per_token_f32(qt, s32))
+    xt = [[f32(math.sin(0.37 * (m * 40 + k)) * (1 + ((m * 40 + k) % 7))) for k in range(40)] for m in range(12)]
+    xt[3] = [2.5] * 40
+    xt[5] = [0.0] * 40
+    xt[7][11] = float("nan")
+    qt, s64, s32 = js.quantize_per_token(xt)
+    np.savez(os.path.join(HERE, "per_token.npz"), x=np.array(xt, np.float32), q=np.array(qt, np.int8), scales64=np.array(s64, np.float64),
+             scales32=np.array(s32, np.float32), y=np.array(js.dequantize_per_token_f32(qt, s32), np.float32))
     # one small linear with every tail (K multiple of 16 so that the tensor-core kernel takes it)
     M, K, N = 8, 64, 16
-    xl = np.array([math.sin(0.11 * i) * 2 for i in range(M * K)], np.float32).reshape(M, K)
-    wl = np.array([round(math.sin(0.23 * i) * 127) for i in range(N * K)], np.int8).reshape(N, K)
-    ws = np.array([1e-3 * (1 + n) for n in range(N)], np.float32)
-    bias = np.array([math.cos(n) * 0.1 for n in range(N)], np.float32)
-    ql, _, sl = orc.quantize_per_token(xl)
-    acc = orc.qdot_i32(ql, wl)
-    outs = {f"out_{a}": orc.epilogue(acc, sl, ws, bias, a) for a in ACTS}
-    np.savez(os.path.join(HERE, "linear_tails.npz"), x=xl, w=wl, w_scales=ws, bias=bias, q=ql, a_scales=sl, acc=acc, **outs)
+    xl = [[f32(math.sin(0.11 * (m * K + k)) * 2) for k in range(K)] for m in range(M)]
+    wl = [[js.to_int8(float(round(math.sin(0.23 * (n * K + k)) * 127))) for k in range(K)] for n in range(N)]
+    ws = [f32(1e-3 * (1 + n)) for n in range(N)]
+    bias = [f32(math.cos(n) * 0.1) for n in range(N)]
+    ql, _, sl = js.quantize_per_token(xl)
+    acc = js.quantized_dot(ql, wl)
+    outs = {f"out_{a}": np.array(js.tail(acc, sl, ws, bias, a), np.float32) for a in ACTS}
+    np.savez(os.path.join(HERE, "linear_tails.npz"), x=np.array(xl, np.float32), w=np.array(wl, np.int8), w_scales=np.array(ws, np.float32),
+             bias=np.array(bias, np.float32), q=np.array(ql, np.int8), a_scales=np.array(sl, np.float32), acc=np.array(acc, np.int32), **outs)
     # f32 pieces of a transformer block on closed-form inputs: LayerNorm (with a residual) and causal attention,
-    # 2 sequences x 24 positions, 2 heads of 64 -- outputs of the oracle's index-order binary32 restatement
+    # 2 sequences x 24 positions, 2 heads of 64 -- index-order binary32 arithmetic
     Mb, Db = 48, 128
-    xb = np.array([math.sin(0.13 * i) * 2 + math.cos(0.07 * i) for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
-    rb = np.array([math.sin(0.31 * i) for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
-    gamma = np.array([1 + 0.5 * math.sin(d) for d in range(Db)], np.float32)
-    beta = np.array([0.1 * math.cos(d) for d in range(Db)], np.float32)
-    yb, sb = orc.layer_norm(xb, gamma, beta, 1e-5, add=rb, want_sum=True)
-    qb = np.array([math.sin(0.17 * i) * 1.5 for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
-    kb = np.array([math.cos(0.19 * i) * 1.5 for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
-    vb = np.array([math.sin(0.23 * i + 1) for i in range(Mb * Db)], np.float32).reshape(Mb, Db)
-    ab = orc.sdpa(qb, kb, vb, 2, 2, 24, 64, 0.125, True)
-    np.savez(os.path.join(HERE, "block_ops.npz"), x=xb, residual=rb, gamma=gamma, beta=beta, ln_sum=sb, ln_out=yb,
-             q=qb, k=kb, v=vb, attn=ab)
+    grid = lambda fn: [[f32(fn(m * Db + d)) for d in range(Db)] for m in range(Mb)]
+    xb = grid(lambda i: math.sin(0.13 * i) * 2 + math.cos(0.07 * i))
+    rb = grid(lambda i: math.sin(0.31 * i))
+    gamma = [f32(1 + 0.5 * math.sin(d)) for d in range(Db)]
+    beta = [f32(0.1 * math.cos(d)) for d in range(Db)]
+    yb, sb = js.layer_norm(xb, gamma, beta, 1e-5, add=rb)
+    qb = grid(lambda i: math.sin(0.17 * i) * 1.5)
+    kb = grid(lambda i: math.cos(0.19 * i) * 1.5)
+    vb = grid(lambda i: math.sin(0.23 * i + 1))
+    ab = js.sdpa(qb, kb, vb, 2, 2, 24, 64, 0.125, True)
+    a32 = lambda v: np.array(v, np.float32)
+    np.savez(os.path.join(HERE, "block_ops.npz"), x=a32(xb), residual=a32(rb), gamma=a32(gamma), beta=a32(beta), ln_sum=a32(sb), ln_out=a32(yb),
+             q=a32(qb), k=a32(kb), v=a32(vb), attn=a32(ab))
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 

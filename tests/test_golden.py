@@ -1,5 +1,6 @@
 """Committed golden fixtures (tests/golden/*.npz, made by tests/golden/make_golden.py from the reference tests'
-closed-form inputs): the oracle must still reproduce them bit for bit (CPU), and so must the CUDA path (GPU)."""
+closed-form inputs with the pure-Python restatement oracle/jsport.py): the C++ oracle must reproduce them bit for bit
+(CPU) - two independent restatements agreeing - and so must the CUDA path (GPU)."""
 import os
 
 import numpy as np
@@ -16,6 +17,12 @@ def load(name):
 def same_bits(a, b):
     a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
     return a.shape == b.shape and a.dtype == b.dtype and (a.view(np.uint8) == b.view(np.uint8)).all()
+
+
+def test_fixture_generator_uses_the_python_port_only():
+    src = open(os.path.join(GOLD, "make_golden.py")).read()
+    assert "from oracle import jsport" in src
+    assert "import oracle as" not in src and "orc." not in src and "liboracle" not in src
 
 
 # ------------------------------------------------------------------ CPU: the oracle against the fixtures
