@@ -318,11 +318,88 @@ def plan_function(func: GraphFunction, dynamic: bool) -> List[Step]:
     return _Planner(func, dynamic).plan()
 
 
+# ----------------------------------------------------------------------------- native programs
+# A planned function as data: what RuntimeModule.serialize() of the reference keeps per kernel is
+# {name, source, target, metadata} (src/runtime/runtime.ts:399-414); for this backend `source` is the JSON text below
+# and metadata.kind is 'b200', so a quantized model reloads through RuntimeModule.deserialize() and the 'b200' runtime
+# backend without running the quantization pass or the matcher again.  Values are numbered in order of appearance;
+# weights, scale vectors and biases travel as base64 of their little-endian bytes.
+PROGRAM_VERSION = 1
+_ARRAY_PARAMS = {"w": np.int8, "w_scales": np.float32, "bias": np.float32}
+
+
+def program_of(args: Sequence[Value], returns: Sequence[Value], steps: Sequence[Step]) -> dict:
+    import base64
+    ids: Dict[int, int] = {}
+
+    def vid(v: Value) -> int:
+        if id(v) not in ids:
+            ids[id(v)] = len(ids)
+        return ids[id(v)]
+
+    out_args = [{"id": vid(v), "shape": list(v.shape), "dtype": v.dtype} for v in args]
+    out_steps = []
+    for st in steps:
+        params = {}
+        for k, val in st.params.items():
+            if k in ("dW", "dws", "db"):          # device buffers of a live plan are not part of the program
+                continue
+            if k in _ARRAY_PARAMS:
+                params[k] = None if val is None else {"shape": list(np.shape(val)),
+                                                      "b64": base64.b64encode(np.ascontiguousarray(val, _ARRAY_PARAMS[k]).tobytes()).decode("ascii")}
+            else:
+                params[k] = val
+        out_steps.append({"kind": st.kind, "ins": [vid(v) for v in st.ins],
+                          "out": {"id": vid(st.out), "shape": list(st.out.shape), "dtype": st.out.dtype}, "params": params})
+    return {"version": PROGRAM_VERSION, "args": out_args, "steps": out_steps, "returns": [vid(v) for v in returns]}
+
+
+def steps_from_program(program: dict):
+    """(args, returns, steps) rebuilt from :func:`program_of` output (after a trip through JSON)."""
+    import base64
+    if program.get("version") != PROGRAM_VERSION:
+        raise B200CompileError(f"native program version {program.get('version')} is not understood (this build reads {PROGRAM_VERSION})")
+    vals: Dict[int, Value] = {}
+    args = []
+    for a in program["args"]:
+        vals[a["id"]] = Value(tuple(a["shape"]), a["dtype"], None, f"arg{len(args)}")
+        args.append(vals[a["id"]])
+    steps = []
+    for st in program["steps"]:
+        if st["kind"] not in ("quantize_static", "quantize_token", "dequantize_static", "linear"):
+            raise B200CompileError(f"native program: unknown step '{st['kind']}'")
+        o = st["out"]
+        vals[o["id"]] = Value(tuple(o["shape"]), o["dtype"])
+        params = {}
+        for k, val in st["params"].items():
+            if k in _ARRAY_PARAMS and val is not None:
+                params[k] = np.frombuffer(base64.b64decode(val["b64"]), _ARRAY_PARAMS[k]).reshape(val["shape"]).copy()
+            else:
+                params[k] = val
+        try:
+            ins = [vals[i] for i in st["ins"]]
+        except KeyError as exc:
+            raise B200CompileError(f"native program: step reads value {exc} before it is produced") from None
+        steps.append(Step(st["kind"], ins, vals[o["id"]], params))
+    try:
+        returns = [vals[i] for i in program["returns"]]
+    except KeyError as exc:
+        raise B200CompileError(f"native program: returned value {exc} is never produced") from None
+    return args, returns, steps
+
+
 # ----------------------------------------------------------------------------- execution
+class _Signature:
+    """What a plan needs of a function once it is planned: its arguments and returned values."""
+
+    def __init__(self, args, returns):
+        self.args, self.returns = list(args), list(returns)
+
+
 class _FunctionPlan:
-    def __init__(self, ctx: Context, func: GraphFunction, dynamic: bool):
+    def __init__(self, ctx: Context, func, dynamic: bool = False, steps: Optional[List[Step]] = None):
         self.func = func
-        self.steps = plan_function(func, dynamic)
+        self.steps = plan_function(func, dynamic) if steps is None else steps
         self.inputs = len(func.args)
         self.outputs = len(func.returns)
         self.ctx = ctx
@@ -351,6 +428,14 @@ class _FunctionPlan:
         missing = [r for r in func.returns if id(r) not in self.buf]
         if missing:
             raise B200CompileError("a returned value is not produced by any native step")
+
+    @classmethod
+    def from_program(cls, ctx: Context, program: dict) -> "_FunctionPlan":
+        args, returns, steps = steps_from_program(program)
+        return cls(ctx, _Signature(args, returns), steps=steps)
+
+    def program(self) -> dict:
+        return program_of(self.func.args, self.func.returns, self.steps)
 
     def _alloc(self, v: Value):
         if id(v) not in self.buf:
@@ -405,11 +490,36 @@ def _as_array(arg) -> np.ndarray:
 class B200RuntimeModule:
     """RuntimeModuleLike over libb200q.so: one native plan per function of the module."""
 
-    def __init__(self, module: Dict[str, GraphFunction], options: Optional[dict] = None):
+    def __init__(self, module: Dict[str, GraphFunction], options: Optional[dict] = None, _programs: Optional[dict] = None):
         options = options or {}
+        self.name = options.get("name", "module")
         self.ctx = Context(int(options.get("device", 0) or 0))      # raises without a GPU: no fallback
+        if _programs is not None:
+            self.plans = {name: _FunctionPlan.from_program(self.ctx, prog) for name, prog in _programs.items()}
+            return
         dynamic = options.get("activationQuant", "static") == "per_token_dynamic"
         self.plans = {name: _FunctionPlan(self.ctx, f, dynamic) for name, f in module.items()}
+
+    def serialize(self) -> dict:
+        """``SerializedRuntimeModule`` of the reference (src/runtime/runtime.ts:399-406): one entry per function whose
+        ``source`` is the native program as JSON text."""
+        import json
+        return {"name": self.name, "kernels": [
+            {"name": name, "source": json.dumps(p.program()), "target": "b200_int8",
+             "metadata": {"kind": "b200", "inputs": p.inputs, "outputs": p.outputs, "steps": len(p.steps)}}
+            for name, p in self.plans.items()]}
+
+    @classmethod
+    def deserialize(cls, data: dict, options: Optional[dict] = None) -> "B200RuntimeModule":
+        """The counterpart of ``RuntimeModule.deserialize`` (runtime.ts:408-414): rebuilds the plans from the stored
+        programs - weights and scales are uploaded as they are, nothing is quantized or matched again."""
+        import json
+        programs = {}
+        for k in data["kernels"]:
+            if k.get("metadata", {}).get("kind") != "b200":
+                raise B200CompileError(f"kernel '{k.get('name')}' is of kind {k.get('metadata', {}).get('kind')!r}, not 'b200'")
+            programs[k["name"]] = json.loads(k["source"])
+        return cls({}, {**(options or {}), "name": data.get("name", "module")}, _programs=programs)
 
     def run(self, funcName: str, *args):
         plan = self.plans.get(funcName)

@@ -174,8 +174,8 @@ export function planGraph(module: GraphModule, options: B200Options, b: B200QBin
           if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, numel(shapeOf(st.in)), st.scale, st.zeroPoint, st.dst, y), 'b200q_quantize_static');
           else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, st.M, st.K, y, tokScales.get(st.out), -127, 127), 'b200q_quantize_per_token');
           else if (st.kind === 'dequantize_static') check(bind, bind.dequantizeStatic(c, x, st.src, numel(shapeOf(st.in)), st.scale, st.zeroPoint, y), 'b200q_dequantize_static');
-          else if (st.requantScale !== null) check(bind, bind.linearRequantStatic(c, x, null, st.dW, st.dWs, st.dBias, ACT[st.act], st.M, st.N, st.K, st.requantScale, y), 'b200q_int8_linear_requant_static');
-          else check(bind, bind.linear(c, x, st.dynamic ? tokScales.get(st.in) : null, st.dW, st.dWs, st.dBias, ACT[st.act], st.M, st.N, st.K, y), 'b200q_int8_linear');
+          else if (st.requantScale !== null) check(bind, bind.int8LinearRequantStatic(c, x, null, st.dW, st.dWs, st.dBias, ACT[st.act], st.M, st.N, st.K, st.requantScale, y), 'b200q_int8_linear_requant_static');
+          else check(bind, bind.int8Linear(c, x, st.dynamic ? tokScales.get(st.in) : null, st.dW, st.dWs, st.dBias, ACT[st.act], st.M, st.N, st.K, y), 'b200q_int8_linear');
         }
         check(bind, bind.sync(c), 'b200q_sync');
         rets.forEach((v, i) => { const a = args[f.args.length + i]; check(bind, bind.download(c, a, buf.get(v), a.byteLength), 'b200q_download'); });
@@ -183,4 +183,78 @@ export function planGraph(module: GraphModule, options: B200Options, b: B200QBin
     });
   }
   return plans;
+}
+
+// ---------------------------------------------------------------------------------------------- native programs
+// A planned function as data: what RuntimeModule.serialize() keeps per kernel is {name, source, target, metadata}
+// (src/runtime/runtime.ts:399-414); for this backend `source` is JSON.stringify(programOf(...)) and metadata.kind is
+// 'b200', so a quantized model reloads through RuntimeModule.deserialize() and the 'b200' runtime backend
+// (register.ts) without running the quantization pass or the matcher again.  Same format as program_of /
+// steps_from_program in mlfw_b200/backend.py: values numbered in order of appearance, arrays as base64.
+export const PROGRAM_VERSION = 1;
+type ValueRec = { id: number; shape: number[]; dtype: string };
+export type NativeProgram = { version: number; args: ValueRec[]; returns: number[];
+                              steps: { kind: Step['kind']; ins: number[]; out: ValueRec; params: Record<string, unknown> }[] };
+
+const b64 = (a: ArrayBufferView) => ({ shape: [a.byteLength / (a as unknown as { BYTES_PER_ELEMENT: number }).BYTES_PER_ELEMENT],
+                                       b64: Buffer.from(a.buffer, a.byteOffset, a.byteLength).toString('base64') });
+const unb64 = <T>(rec: { b64: string } | null, make: (b: ArrayBuffer) => T): T | null => {
+  if (!rec) return null;
+  const buf = Buffer.from(rec.b64, 'base64');
+  return make(buf.buffer.slice(buf.byteOffset, buf.byteOffset + buf.byteLength));
+};
+
+export function programOf(f: GraphFunction, steps: Step[]): NativeProgram {
+  const ids = new Map<Value, number>();
+  const vid = (v: Value) => { if (!ids.has(v)) ids.set(v, ids.size); return ids.get(v)!; };
+  const rec = (v: Value): ValueRec => ({ id: vid(v), shape: shapeOf(v), dtype: dtypeOf(v) });
+  const args = f.args.map(rec);
+  const out = steps.map((st) => {
+    const params: Record<string, unknown> = {};
+    if (st.kind === 'linear') Object.assign(params, { M: st.M, N: st.N, K: st.K, act: st.act, a_dynamic: st.dynamic, requant_scale: st.requantScale,
+      w_layout: st.wIsKN ? 1 : 0, w: { ...b64(st.w), shape: st.wIsKN ? [st.K, st.N] : [st.N, st.K] }, w_scales: b64(st.wScales), bias: st.bias ? b64(st.bias) : null });
+    else if (st.kind === 'quantize_token') Object.assign(params, { M: st.M, K: st.K });
+    else if (st.kind === 'quantize_static') Object.assign(params, { scale: st.scale, zero_point: st.zeroPoint, kind: st.dst });
+    else Object.assign(params, { scale: st.scale, zero_point: st.zeroPoint, kind: st.src });
+    return { kind: st.kind, ins: [vid(st.in)], out: rec(st.out), params };
+  });
+  return { version: PROGRAM_VERSION, args, steps: out, returns: f.returnValues().map(vid) };
+}
+
+/** A FunctionPlan straight from a stored program: weights, scale vectors and biases are uploaded as they are. */
+export function planFromProgram(p: NativeProgram, b: B200QBinding, ctx: unknown): FunctionPlan {
+  if (p.version !== PROGRAM_VERSION) throw new Error(`b200: native program version ${p.version} is not understood`);
+  const alloc = (bytes: number): unknown => { const out: [unknown] = [null]; check(b, b.alloc(ctx, bytes, out), 'b200q_alloc'); return out[0]; };
+  const upload = (a: ArrayBufferView): unknown => { const d = alloc(a.byteLength); check(b, b.upload(ctx, d, a, a.byteLength), 'b200q_upload'); return d; };
+  const size = (v: ValueRec) => numel(v.shape) * ({ f32: 4, i32: 4, i8: 1, ui8: 1 } as Record<string, number>)[v.dtype];
+  const buf = new Map<number, unknown>(), scales = new Map<number, unknown>(), elems = new Map<number, number>();
+  for (const a of p.args) { buf.set(a.id, alloc(size(a))); elems.set(a.id, numel(a.shape)); }
+  const dev = p.steps.map((st) => {
+    buf.set(st.out.id, alloc(size(st.out))); elems.set(st.out.id, numel(st.out.shape));
+    const q = st.params as Record<string, any>;
+    if (st.kind === 'quantize_token') scales.set(st.out.id, alloc(q.M * 4));
+    if (st.kind !== 'linear') return null;
+    const w = unb64(q.w, (x) => new Int8Array(x))!;
+    let dW = upload(w);
+    if (q.w_layout === 1) { const t = alloc(w.byteLength); check(b, b.transposeI8(ctx, dW, q.K, q.N, t), 'b200q_transpose_i8'); check(b, b.sync(ctx), 'b200q_sync'); check(b, b.free(ctx, dW), 'b200q_free'); dW = t; }
+    const bias = unb64(q.bias, (x) => new Float32Array(x));
+    return { dW, dWs: upload(unb64(q.w_scales, (x) => new Float32Array(x))!), dBias: bias ? upload(bias) : null };
+  });
+  return {
+    inputs: p.args.length, outputs: p.returns.length, steps: [],
+    describe: () => p.steps.map((s) => s.kind).join('\n'),
+    execute(bind, c, args) {
+      p.args.forEach((a, i) => check(bind, bind.upload(c, buf.get(a.id), args[i], args[i].byteLength), 'b200q_upload'));
+      p.steps.forEach((st, i) => {
+        const q = st.params as Record<string, any>, x = buf.get(st.ins[0]), y = buf.get(st.out.id), d = dev[i];
+        if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, elems.get(st.ins[0])!, q.scale, q.zero_point, q.kind, y), 'b200q_quantize_static');
+        else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, q.M, q.K, y, scales.get(st.out.id), -127, 127), 'b200q_quantize_per_token');
+        else if (st.kind === 'dequantize_static') check(bind, bind.dequantizeStatic(c, x, q.kind, elems.get(st.ins[0])!, q.scale, q.zero_point, y), 'b200q_dequantize_static');
+        else if (q.requant_scale !== null) check(bind, bind.int8LinearRequantStatic(c, x, null, d!.dW, d!.dWs, d!.dBias, ACT[q.act as Act], q.M, q.N, q.K, q.requant_scale, y), 'b200q_int8_linear_requant_static');
+        else check(bind, bind.int8Linear(c, x, q.a_dynamic ? scales.get(st.ins[0]) : null, d!.dW, d!.dWs, d!.dBias, ACT[q.act as Act], q.M, q.N, q.K, y), 'b200q_int8_linear');
+      });
+      check(bind, bind.sync(c), 'b200q_sync');
+      p.returns.forEach((id, i) => { const a = args[p.args.length + i]; check(bind, bind.download(c, a, buf.get(id), a.byteLength), 'b200q_download'); });
+    },
+  };
 }

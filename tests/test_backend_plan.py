@@ -4,7 +4,7 @@ import pytest
 
 from graph_util import activation, quantized_linear
 from mlfw_b200.backend import (B200CompileError, B200Target, GraphBuilder, TARGET_ATTR_EXTERNAL_COMPILER,
-                               TARGET_ATTR_FUSION, compile_with_b200, plan_function)
+                               TARGET_ATTR_FUSION, compile_with_b200, plan_function, program_of, steps_from_program)
 
 
 def mlp_graph(orc, act="relu", w_is_kn=True, M=8, K=32, H=64, N=16):
@@ -105,3 +105,41 @@ def test_rank3_lhs_flattens_to_rows(orc):
     y, _ = quantized_linear(b, orc, x, rng.standard_normal((24, 16)).astype(np.float32), None, 0.03, "none", w_is_kn=False)
     steps = plan_function(b.ret(y), dynamic=True)
     assert steps[0].params["M"] == 10 and steps[1].params["M"] == 10 and steps[1].params["N"] == 24
+
+
+@pytest.mark.parametrize("dynamic", [False, True])
+def test_native_program_round_trips_through_json(orc, dynamic):
+    """The planned function as data (the `source` of a serialized kernel): through JSON and back it yields the same
+    steps, shapes, parameters and constant arrays, wired to the same values."""
+    import json
+    func, _ = mlp_graph(orc, "gelu_sigmoid", w_is_kn=False)
+    steps = plan_function(func, dynamic=dynamic)
+    text = json.dumps(program_of(func.args, func.returns, steps))
+    args, returns, again = steps_from_program(json.loads(text))
+    assert [(a.shape, a.dtype) for a in args] == [(a.shape, a.dtype) for a in func.args]
+    assert len(again) == len(steps) and len(returns) == 1 and returns[0] is again[-1].out
+    for a, b in zip(steps, again):
+        assert a.kind == b.kind and a.out.shape == b.out.shape and a.out.dtype == b.out.dtype
+        assert set(a.params) == set(b.params)
+        for k, v in a.params.items():
+            if isinstance(v, np.ndarray):
+                assert b.params[k].dtype == v.dtype and b.params[k].shape == v.shape and (b.params[k] == v).all()
+            else:
+                assert b.params[k] == v
+    # the data flow survives: every step after the first reads what an earlier step (or an argument) produced
+    produced = {id(v) for v in args}
+    for st in again:
+        assert all(id(v) in produced for v in st.ins)
+        produced.add(id(st.out))
+
+
+def test_native_program_rejects_what_it_does_not_understand(orc):
+    func, _ = mlp_graph(orc)
+    prog = program_of(func.args, func.returns, plan_function(func, dynamic=False))
+    with pytest.raises(B200CompileError, match="version"):
+        steps_from_program({**prog, "version": 99})
+    bad = {**prog, "steps": [{**prog["steps"][0], "kind": "conv"}] + prog["steps"][1:]}
+    with pytest.raises(B200CompileError, match="unknown step"):
+        steps_from_program(bad)
+    with pytest.raises(B200CompileError, match="never produced"):
+        steps_from_program({**prog, "returns": [12345]})

@@ -57,7 +57,17 @@ def test_c1_mlp_static_scales_match_the_reference_chain(orc):
     assert (out2 == out).all()
     with pytest.raises(ValueError, match="takes 1 tensors"):
         mod.run("mlp", x)
+    # the serialized module (RuntimeModule.serialize()'s shape, native program as `source`) reloads without the graph
+    import json
+    from mlfw_b200.backend import B200RuntimeModule
+    data = json.loads(json.dumps(mod.serialize()))
+    assert data["kernels"][0]["metadata"]["kind"] == "b200" and data["kernels"][0]["target"] == "b200_int8"
     mod.release()
+    again = B200RuntimeModule.deserialize(data)
+    out3 = np.zeros((256, 256), np.float32)
+    again.run("mlp", x, out3)
+    assert (out3.view(np.uint32) == ref.view(np.uint32)).all()
+    again.release()
 
 
 def test_c1_mlp_per_token_dynamic(orc):
