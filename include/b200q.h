@@ -210,6 +210,22 @@ int b200q_quant_roundtrip_host(b200q_ctx* ctx, const float* x_host, int64_t M, i
 int b200q_observer_reset(b200q_ctx* ctx, float* state);
 int b200q_observe_minmax(b200q_ctx* ctx, const float* x, int64_t n, float* state);
 
+/* Histogram modes of the calibration observer (percentile 0.999 and entropy; HistogramCollector,
+ * src/compiler/analysis/calibration.ts:41-186).  b200q_histogram_f32 adds the n values of x to `bins` (num_bins 64-bit
+ * counters in device memory, at most 4096) exactly as HistogramCollector.update bins them: index
+ * min(num_bins - 1, floor((v - range_min) * (num_bins / (range_max - range_min)))) in binary64; NaN lands in no bin;
+ * nothing is counted when the range is empty.  The caller keeps the range covering the data (the reference widens it
+ * and re-buckets on the host when a batch falls outside: mlfw_b200/calibration.py does the same with 2048 numbers).
+ * The two threshold functions are HOST arithmetic on the downloaded counts (bins as binary64, like the reference's
+ * Float64Array) and need no device: computePercentileThreshold (:130-141) and computeEntropyThreshold (:143-186),
+ * the sums taken in the reference's order. */
+int b200q_histogram_f32(b200q_ctx* ctx, const float* x, int64_t n, double range_min, double range_max, int num_bins,
+                        uint64_t* bins);
+int b200q_histogram_percentile_threshold(const double* bins, int num_bins, double total_count, double range_min, double range_max,
+                                         double percentile, double* threshold);
+int b200q_histogram_entropy_threshold(const double* bins, int num_bins, double total_count, double range_min, double range_max,
+                                      int num_quant_bins, double* threshold);
+
 /* ---- f32 pieces of a transformer block around the int8 linears ("next" components of the hot path) ----
  * Floating-point kernels: results agree with the reference's CPU target to 1e-5 of the output's largest magnitude
  * (its own summation order depends on which lowering runs); the int8 codes b200q_layernorm_quantize emits are the exact

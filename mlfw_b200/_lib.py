@@ -63,6 +63,9 @@ PROTOTYPES = {
     "b200q_quant_roundtrip_host": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "b200q_observer_reset": (c_int, [c_vp, c_vp]),
     "b200q_observe_minmax": (c_int, [c_vp, c_vp, c_i64, c_vp]),
+    "b200q_histogram_f32": (c_int, [c_vp, c_vp, c_i64, c_dbl, c_dbl, c_int, c_vp]),
+    "b200q_histogram_percentile_threshold": (c_int, [c_vp, c_int, c_dbl, c_dbl, c_dbl, c_dbl, C.POINTER(c_dbl)]),
+    "b200q_histogram_entropy_threshold": (c_int, [c_vp, c_int, c_dbl, c_dbl, c_dbl, c_int, C.POINTER(c_dbl)]),
     "b200q_embedding_f32": (c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp]),
     "b200q_add_f32": (c_int, [c_vp, c_vp, c_vp, c_i64, c_vp]),
     "b200q_layernorm_quantize": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, C.c_float, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),

@@ -65,7 +65,9 @@ def _encode(value: Any, buffers: List[Tuple[dict, bytes]]) -> Any:
     if isinstance(value, dict):
         return {str(k): _encode(v, buffers) for k, v in value.items()}
     if isinstance(value, (np.integer, np.floating, np.bool_)):
-        return value.item()
+        value = value.item()
+    if isinstance(value, float) and (value != value or value in (float("inf"), float("-inf"))):
+        return None    # JSON.stringify writes null for NaN and the infinities; a bare NaN token would not parse there
     return value   # None, str, int, float, bool
 
 
@@ -79,7 +81,7 @@ def serialize_checkpoint(checkpoint: Any) -> bytes:
         offset += len(raw)
     # JSON.stringify writes no whitespace and keeps insertion order
     header = json.dumps({"format": MAGIC, "tree": tree, "buffers": [m for m, _ in buffers]}, separators=(",", ":"),
-                        ensure_ascii=False).encode("utf-8")
+                        ensure_ascii=False, allow_nan=False).encode("utf-8")
     return struct.pack("<Q", len(header)) + header + b"".join(raw for _, raw in buffers)
 
 

@@ -1,6 +1,7 @@
 // The C ABI of libb200q.so (declared in include/b200q.h): argument checks on the
 // host before any launch, CUDA errors turned into return codes and a
 // thread-local message, no exceptions or aborts across the boundary.
+#include <cmath>
 #include <cstdarg>
 #include <cstring>
 #include <new>
@@ -691,6 +692,77 @@ int b200q_observe_minmax(b200q_ctx* ctx, const float* x, int64_t n, float* state
   B200Q_REQUIRE(n >= 0, "b200q_observe_minmax: negative length");
   B200Q_REQUIRE(state != nullptr && (n == 0 || x != nullptr), "b200q_observe_minmax: null pointer");
   return launch_minmax_observe(ctx, x, n, state);
+}
+
+int b200q_histogram_f32(b200q_ctx* ctx, const float* x, int64_t n, double range_min, double range_max, int num_bins,
+                        uint64_t* bins) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(n >= 0, "b200q_histogram_f32: negative length");
+  B200Q_REQUIRE(bins != nullptr && (n == 0 || x != nullptr), "b200q_histogram_f32: null pointer");
+  return launch_histogram_f32(ctx, x, n, range_min, range_max, num_bins, reinterpret_cast<unsigned long long*>(bins));
+}
+
+// HistogramCollector.computePercentileThreshold (src/compiler/analysis/calibration.ts:130-141).
+int b200q_histogram_percentile_threshold(const double* bins, int num_bins, double total_count, double range_min, double range_max,
+                                         double percentile, double* threshold) {
+  B200Q_REQUIRE(bins != nullptr && threshold != nullptr && num_bins >= 1, "b200q_histogram_percentile_threshold: bad argument");
+  const double target = total_count * percentile;
+  double cumulative = 0.0;
+  const double bin_width = (range_max - range_min) / num_bins;
+  for (int i = 0; i < num_bins; i++) {
+    cumulative += bins[i];
+    if (cumulative >= target) {
+      *threshold = range_min + (i + 1) * bin_width;
+      return 0;
+    }
+  }
+  *threshold = range_max;
+  return 0;
+}
+
+// HistogramCollector.computeEntropyThreshold (calibration.ts:143-186): the clipping point whose quantized
+// distribution has the smallest KL divergence from the observed one; every sum in the reference's order.
+int b200q_histogram_entropy_threshold(const double* bins, int num_bins, double total_count, double range_min, double range_max,
+                                      int num_quant_bins, double* threshold) {
+  B200Q_REQUIRE(bins != nullptr && threshold != nullptr && num_bins >= 1 && num_quant_bins >= 1,
+                "b200q_histogram_entropy_threshold: bad argument");
+  if (total_count == 0.0) {
+    *threshold = range_max;
+    return 0;
+  }
+  double* ref = new (std::nothrow) double[2 * (size_t)num_bins];
+  B200Q_REQUIRE(ref != nullptr, "b200q_histogram_entropy_threshold: out of host memory");
+  double* q = ref + num_bins;
+  for (int i = 0; i < num_bins; i++) ref[i] = bins[i] / total_count;
+  int best_idx = num_bins;
+  double best_kl = std::numeric_limits<double>::infinity();
+  for (int t = num_quant_bins; t <= num_bins; t++) {
+    const double quant_bin_width = (double)t / (double)num_quant_bins;
+    for (int i = 0; i < t; i++) q[i] = 0.0;
+    for (int i = 0; i < num_quant_bins; i++) {
+      const int start = (int)std::floor(i * quant_bin_width);
+      int end = (int)std::floor((i + 1) * quant_bin_width);
+      if (end > t) end = t;
+      double sum = 0.0;
+      for (int j = start; j < end; j++) sum += ref[j];
+      const int bin_count = end - start;
+      if (bin_count > 0) {
+        const double avg = sum / bin_count;
+        for (int j = start; j < end; j++) q[j] = avg;
+      }
+    }
+    double kl = 0.0;
+    for (int i = 0; i < t; i++)
+      if (ref[i] > 0.0 && q[i] > 0.0) kl += ref[i] * std::log(ref[i] / q[i]);
+    if (kl < best_kl) {
+      best_kl = kl;
+      best_idx = t;
+    }
+  }
+  delete[] ref;
+  const double bin_width = (range_max - range_min) / num_bins;
+  *threshold = range_min + best_idx * bin_width;
+  return 0;
 }
 
 int b200q_embedding_f32(b200q_ctx* ctx, const float* table, const int32_t* tokens, const float* pos_table, int64_t M, int64_t D,

@@ -27,6 +27,9 @@ int launch_quantize_rows_with_keys(b200q_ctx* ctx, const float* y, int64_t M, in
 // keys[0..2M) from separate min / max arrays (the result of launch_row_range), for the CUDA-core path.
 int launch_range_to_keys(b200q_ctx* ctx, const float* mn, const float* mx, int64_t M, uint32_t* keys);
 int launch_transpose_i8(b200q_ctx* ctx, const int8_t* src_kn, int64_t K, int64_t N, int8_t* dst_nk);
+// Adds the values of x to a histogram of num_bins (<= 4096) equal bins over [range_min, range_max] (64-bit counters in device memory).
+int launch_histogram_f32(b200q_ctx* ctx, const float* x, int64_t n, double range_min, double range_max, int num_bins,
+                         unsigned long long* bins);
 // Running min / max of a calibration observer: state[0] = min, state[1] = max (device memory, +Inf / -Inf when new).
 int launch_minmax_observe(b200q_ctx* ctx, const float* x, int64_t n, float* state);
 

@@ -920,6 +920,29 @@ __global__ void __launch_bounds__(256) minmax_observe_kernel(const float* __rest
   }
 }
 
+// Histogram observer (percentile / entropy calibration): HistogramCollector.update's binning
+// (src/compiler/analysis/calibration.ts:64-79), idx = min(numBins - 1, floor((v - rangeMin) * (numBins / range))) in
+// binary64 as the reference evaluates it; a value whose index is not a number (NaN input, or an infinite range) lands
+// in no bin there (a typed-array store at index NaN does nothing), so it is skipped here.  Counts per block in shared
+// memory, then added to 64-bit global counters.
+constexpr int HIST_MAX_BINS = 4096;
+__global__ void __launch_bounds__(256) histogram_f32_kernel(const float* __restrict__ x, int64_t n, double range_min, double scale,
+                                                            int num_bins, unsigned long long* __restrict__ bins) {
+  __shared__ unsigned int local[HIST_MAX_BINS];
+  for (int i = threadIdx.x; i < num_bins; i += blockDim.x) local[i] = 0u;
+  __syncthreads();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const double top = (double)(num_bins - 1);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const double raw = ((double)__ldcs(x + i) - range_min) * scale;
+    const double f = floor(raw);
+    if (raw == raw && f >= 0.0) atomicAdd(&local[f > top ? num_bins - 1 : (int)f], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < num_bins; i += blockDim.x)
+    if (local[i]) atomicAdd(bins + i, (unsigned long long)local[i]);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -1122,6 +1145,20 @@ int launch_quantize_rows_with_keys(b200q_ctx* ctx, const float* y, int64_t M, in
 int launch_range_to_keys(b200q_ctx* ctx, const float* mn, const float* mx, int64_t M, uint32_t* keys) {
   if (M == 0) return 0;
   range_to_keys_kernel<<<(unsigned)((M + 255) / 256), 256, 0, ctx->stream>>>(mn, mx, M, keys);
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_histogram_f32(b200q_ctx* ctx, const float* x, int64_t n, double range_min, double range_max, int num_bins,
+                         unsigned long long* bins) {
+  ProfScope prof(ctx, KK_WEIGHTS);
+  B200Q_REQUIRE(num_bins >= 1 && num_bins <= HIST_MAX_BINS, "histogram: %d bins is outside [1, %d]", num_bins, HIST_MAX_BINS);
+  if (n == 0) return 0;
+  const double range = range_max - range_min;
+  if (!(range > 0.0)) return 0;                       // HistogramCollector.update returns before binning (calibration.ts:62-63)
+  const double scale = (double)num_bins / range;
+  histogram_f32_kernel<<<flat_blocks(ctx, n / 8 + 1), 256, 0, ctx->stream>>>(x, n, range_min, scale, num_bins, bins);
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -301,6 +301,10 @@ class Context:
     def observe_minmax(self, x, n, state):
         check(self.lib.b200q_observe_minmax(self.handle, _ptr(x), n, _ptr(state)), "b200q_observe_minmax")
 
+    def histogram_f32(self, x, n, range_min, range_max, num_bins, bins):
+        check(self.lib.b200q_histogram_f32(self.handle, _ptr(x), n, float(range_min), float(range_max), num_bins, _ptr(bins)),
+              "b200q_histogram_f32")
+
     # ---- f32 pieces of a transformer block
     def embedding_f32(self, table, tokens, pos_table, M, D, V, S, out):
         check(self.lib.b200q_embedding_f32(self.handle, _ptr(table), _ptr(tokens), _ptr(pos_table), M, D, V, S, _ptr(out)),

@@ -64,6 +64,9 @@ function bind(path: string) {
     quantRoundtripHost: f('int b200q_quant_roundtrip_host(void *ctx, const void *x_host, int64_t M, int64_t K, void *q_host, void *scales_host, void *y_host)'),
     observerReset: f('int b200q_observer_reset(void *ctx, void *state)'),
     observeMinmax: f('int b200q_observe_minmax(void *ctx, const void *x, int64_t n, void *state)'),
+    histogramF32: f('int b200q_histogram_f32(void *ctx, const void *x, int64_t n, double range_min, double range_max, int num_bins, void *bins)'),
+    histogramPercentileThreshold: f('int b200q_histogram_percentile_threshold(const void *bins, int num_bins, double total_count, double range_min, double range_max, double percentile, _Out_ double *threshold)'),
+    histogramEntropyThreshold: f('int b200q_histogram_entropy_threshold(const void *bins, int num_bins, double total_count, double range_min, double range_max, int num_quant_bins, _Out_ double *threshold)'),
     embeddingF32: f('int b200q_embedding_f32(void *ctx, const void *table, const void *tokens, const void *pos_table, int64_t M, int64_t D, int64_t V, int64_t S, void *out)'),
     addF32: f('int b200q_add_f32(void *ctx, const void *a, const void *b, int64_t n, void *out)'),
     layernormQuantize: f('int b200q_layernorm_quantize(void *ctx, const void *x, const void *residual, const void *gamma, const void *beta, float eps, int64_t M, int64_t D, void *sum_out, void *y_out, void *q_out, void *scales_out)'),

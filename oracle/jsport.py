@@ -391,6 +391,108 @@ def sdpa(q, k, v, B, H, S, Dh, scale, causal=True):
     return out
 
 
+# ------------------------------------------------- calibration observers (src/compiler/analysis/calibration.ts:11-186)
+class HistogramCollector:
+    def __init__(self, num_bins=2048):
+        self.num_bins, self.bins = num_bins, [0.0] * num_bins
+        self.range_min = self.range_max = 0.0
+        self.initialized, self.total_count = False, 0
+
+    def update(self, data):                                   # :57-79
+        if not self.initialized:
+            self._init_range(data)
+        rng = self.range_max - self.range_min
+        if not rng > 0:
+            return
+        for v in data:
+            if v < self.range_min or v > self.range_max:
+                self._expand_and_rebucket(data)
+                return
+        scale = _div(self.num_bins, rng)
+        for v in data:
+            self._bump((v - self.range_min) * scale)
+        self.total_count += len(data)
+
+    def _bump(self, raw, by=1.0):
+        """bins[Math.min(numBins - 1, Math.floor(raw))] += by; an index that is not a number stores nowhere."""
+        if raw != raw:
+            return
+        f = raw if raw in (INF, -INF) else float(math.floor(raw))
+        idx = math_min(self.num_bins - 1, f)
+        if idx == idx and idx >= 0:
+            self.bins[int(idx)] += by
+
+    def _init_range(self, data):                              # :81-90
+        mn, mx = INF, -INF
+        for v in data:
+            if v < mn:
+                mn = v
+            if v > mx:
+                mx = v
+        if mn == mx:
+            mx = mn + 1
+        self.range_min, self.range_max, self.initialized = mn, mx, True
+
+    def _expand_and_rebucket(self, new_data):                 # :92-120
+        new_min, new_max = self.range_min, self.range_max
+        for v in new_data:
+            if v < new_min:
+                new_min = v
+            if v > new_max:
+                new_max = v
+        old_bins, old_min, old_range = list(self.bins), self.range_min, self.range_max - self.range_min
+        self.range_min, self.range_max = new_min, new_max
+        new_scale = _div(self.num_bins, new_max - new_min)
+        self.bins = [0.0] * self.num_bins
+        if old_range > 0:
+            width = old_range / self.num_bins
+            for i in range(self.num_bins):
+                if old_bins[i] == 0:
+                    continue
+                center = old_min + (i + 0.5) * width
+                self._bump((center - new_min) * new_scale, old_bins[i])
+        for v in new_data:
+            self._bump((v - new_min) * new_scale)
+        self.total_count += len(new_data)
+
+    def compute_percentile_threshold(self, percentile):       # :130-141
+        target = self.total_count * percentile
+        cumulative = 0.0
+        width = (self.range_max - self.range_min) / self.num_bins
+        for i in range(self.num_bins):
+            cumulative += self.bins[i]
+            if cumulative >= target:
+                return self.range_min + (i + 1) * width
+        return self.range_max
+
+    def compute_entropy_threshold(self, num_quant_bins):      # :143-186
+        if self.total_count == 0:
+            return self.range_max
+        ref = [b / self.total_count for b in self.bins]
+        best_idx, best_kl = self.num_bins, INF
+        for t in range(num_quant_bins, self.num_bins + 1):
+            qw = t / num_quant_bins
+            q = [0.0] * t
+            for i in range(num_quant_bins):
+                start = math.floor(i * qw)
+                end = min(t, math.floor((i + 1) * qw))
+                total = 0.0
+                for j in range(start, end):
+                    total += ref[j]
+                if end - start > 0:
+                    avg = total / (end - start)
+                    for j in range(start, end):
+                        q[j] = avg
+            kl = 0.0
+            for i in range(t):
+                if ref[i] > 0 and q[i] > 0:
+                    kl += ref[i] * math.log(ref[i] / q[i])
+            if kl < best_kl:
+                best_kl, best_idx = kl, t
+        width = (self.range_max - self.range_min) / self.num_bins
+        return self.range_min + best_idx * width
+
+
 # ----------------------------------------------------------------------------------------------------- seeded data
 def make_rng(seed: int):
     """mulberry32, src/util/random.ts:5-14."""
