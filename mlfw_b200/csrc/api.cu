@@ -248,7 +248,7 @@ int b200q_set_requant_variant(b200q_ctx* ctx, int variant) {
 
 int b200q_set_quant_variant(b200q_ctx* ctx, int variant) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
-  B200Q_REQUIRE(variant >= 0 && variant <= 2, "b200q_set_quant_variant: unknown variant %d", variant);
+  B200Q_REQUIRE(variant >= 0 && variant <= 4, "b200q_set_quant_variant: unknown variant %d", variant);
   ctx->quant_variant = variant;
   return 0;
 }

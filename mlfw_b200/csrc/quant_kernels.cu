@@ -517,6 +517,130 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
   __syncthreads();
 }
 
+// ---------------------------------------------------------------------------
+// Per-token quantize, a team of TEAM warps per row, the row in registers straight from global memory.
+// Warp p of a team holds vectors [p * 32 * VPT, (p + 1) * 32 * VPT) of the row; lane l loads float4 number
+// l + 32 j of that part (j < VPT): every load instruction of a warp covers 512 contiguous bytes, all VPT of them are
+// issued before the first use.  TEAM == 1: nothing but the warp itself is involved afterwards (shuffle reductions, no
+// shared memory, no barrier, no producer).  TEAM > 1: the warps of a team exchange their partial range through
+// shared memory and a named barrier of their own, once per row.  Parts shorter than 32 * VPT vectors repeat the
+// row's first vectors in the unused registers (harmless to the range, never stored).  Short rows leave room for many
+// warps per SM, whose loads overlap each other's arithmetic; long rows are split so that a warp keeps few enough
+// registers for that to stay true.
+// ---------------------------------------------------------------------------
+template <int TEAM>
+__device__ __forceinline__ void team_exchange(float& mn, float& mx, float2* slots, int team, int part, int lane, bool nan_dropping) {
+  if (TEAM == 1) return;
+  if (lane == 0) slots[team * TEAM + part] = make_float2(mn, mx);
+  asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(32 * TEAM) : "memory");
+#pragma unroll
+  for (int p = 0; p < TEAM; p++) {
+    const float2 o = slots[team * TEAM + p];
+    if (nan_dropping) { mn = fminf(mn, o.x); mx = fmaxf(mx, o.y); }
+    else { mn = fmin3n(mn, mn, o.x); mx = fmax3n(mx, mx, o.y); }
+  }
+  asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(32 * TEAM) : "memory");   // the slots may be written again
+}
+
+// KEYS: the rows' ranges are given (order-preserving keys published by the kernel that produced x, [0, M) maxima and
+// [M, 2M) minima), so the range pass and the exchange fall away and the kernel is one streaming pass; rows may then
+// hold NaN or infinite elements the kernel has not looked for, which the encode notices by itself.  ld_in4 / ld_out4:
+// row strides of x and q in units of four elements.
+template <int VPT, int TEAM, int WARPS, bool KEYS>
+__global__ void __launch_bounds__(32 * WARPS) quantize_per_token_warp_kernel(const float* __restrict__ x, int64_t M, int K4,
+                                                                             int64_t ld_in4, int64_t ld_out4,
+                                                                             const uint32_t* __restrict__ keys,
+                                                                             int8_t* __restrict__ q, float* __restrict__ scales,
+                                                                             float qmin, float qmax) {
+  static_assert(VPT % 4 == 0 && WARPS % TEAM == 0, "the encode works on groups of four vectors; whole teams per block");
+  __shared__ float2 slots[(TEAM > 1 && !KEYS) ? WARPS : 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int team = warp / TEAM, part = warp - team * TEAM;
+  const int64_t row = (int64_t)blockIdx.x * (WARPS / TEAM) + team;
+  const float limit = guard_limit(qmin, qmax);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the GEMM that follows may start its set-up early
+  asm volatile("griddepcontrol.wait;" ::: "memory");                // ... and x may come from the kernel before this one
+  if (row >= M) return;                                             // whole teams leave together
+  const int c0 = part * 32 * VPT + lane;                            // this lane's first vector of the row
+  const float4* xrow = reinterpret_cast<const float4*>(x) + row * ld_in4;
+  float4 v[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; j++) v[j] = ld_stream(xrow + ((c0 + 32 * j < K4) ? c0 + 32 * j : lane));
+  float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+  bool nan_row = false;
+  if (KEYS) {
+    mx = range_max_from_key(__ldg(keys + row));
+    mn = range_min_from_key(__ldg(keys + M + row));
+  } else {
+    float mn2 = mn, mx2 = mx;
+#pragma unroll
+    for (int j = 0; j < VPT; j += 2) {   // NaN-propagating three-input forms, two chains per bound
+      mn = fmin3n(mn, v[j].x, v[j].y); mx = fmax3n(mx, v[j].x, v[j].y);
+      mn2 = fmin3n(mn2, v[j].z, v[j].w); mx2 = fmax3n(mx2, v[j].z, v[j].w);
+      mn = fmin3n(mn, v[j + 1].x, v[j + 1].y); mx = fmax3n(mx, v[j + 1].x, v[j + 1].y);
+      mn2 = fmin3n(mn2, v[j + 1].z, v[j + 1].w); mx2 = fmax3n(mx2, v[j + 1].z, v[j + 1].w);
+    }
+    mn = fmin3n(mn, mn, mn2); mx = fmax3n(mx, mx, mx2);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mn = fmin3n(mn, mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmax3n(mx, mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    team_exchange<TEAM>(mn, mx, slots, team, part, lane, false);
+    nan_row = (mn != mn) || (mx != mx);                               // the same in every warp of the team
+    if (nan_row) {   // the reference's strict comparisons ignore NaN: rescan with the NaN-dropping forms
+      mn = __int_as_float(0x7f800000); mx = __int_as_float(0xff800000);
+#pragma unroll
+      for (int j = 0; j < VPT; j++) {
+        mn = fminf(fminf(mn, v[j].x), fminf(fminf(v[j].y, v[j].z), v[j].w));
+        mx = fmaxf(fmaxf(mx, v[j].x), fmaxf(fmaxf(v[j].y, v[j].z), v[j].w));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      }
+      team_exchange<TEAM>(mn, mx, slots, team, part, lane, true);
+    }
+  }
+  const float absmax = fmaxf(fabsf(mn), fabsf(mx));
+  const float inv = __fdiv_rn(127.0f, absmax);
+  const bool exact_only = nan_row || limit < 127.0f || !((mn < mx) && absmax <= 3.402823466e38f && is_normal_f32(inv));
+  uint32_t* qr = reinterpret_cast<uint32_t*>(q) + row * ld_out4 + c0;
+  uint32_t redo = 0;
+  if (!exact_only) {
+    const uint64_t inv2 = f2_pack(inv, inv), magic2 = f2_pack(12582912.0f, 12582912.0f);
+#pragma unroll
+    for (int g = 0; g < VPT; g += 4) {
+      float far = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const uint32_t w = KEYS ? pack4_fast_lean_nan(v[g + j], inv2, magic2, far) : pack4_fast_lean(v[g + j], inv2, magic2, far);
+        if (c0 + 32 * (g + j) < K4) __stcs(qr + 32 * (g + j), w);
+      }
+      redo |= !(far < 0.49993920f) ? (1u << (g / 4)) : 0u;       // 0.5 - 127.5 * 2^-21; a NaN counts as near
+    }
+  } else {
+    redo = (1u << (VPT / 4)) - 1u;
+  }
+  // Groups that came near a tie, and odd rows entirely, are redone from global memory (just read, so from L2) with
+  // the exact routine: rare, and it keeps the register copy statically indexed and binary64 out of the unrolled body.
+  while (redo) {
+    const int g = (__ffs((int)redo) - 1) * 4;
+    redo &= redo - 1;
+    const double sd = row_scale(mn, mx);
+    for (int j = 0; j < 4; j++) {
+      if (c0 + 32 * (g + j) >= K4) continue;
+      const float4 t = xrow[c0 + 32 * (g + j)];
+      int tie = 0;
+      (void)quantize_fast_bounded(t.x, inv, tie); (void)quantize_fast_bounded(t.y, inv, tie);
+      (void)quantize_fast_bounded(t.z, inv, tie); (void)quantize_fast_bounded(t.w, inv, tie);
+      if (exact_only || tie >= 0x3f000000) __stcs(qr + 32 * (g + j), pack4_exact_p(t, sd, qmin, qmax));
+    }
+  }
+  if (lane == 0 && part == 0 && scales) scales[row] = exact_only ? (float)row_scale(mn, mx) : __fdiv_rn(absmax, 127.0f);
+}
+
 // Any K, any alignment: one block per row, the row is read twice (the second
 // read is served by L2 for rows up to tens of megabytes).
 __global__ void __launch_bounds__(256) quantize_per_token_generic_kernel(const float* __restrict__ x, int64_t M, int64_t K,
@@ -943,6 +1067,41 @@ __global__ void __launch_bounds__(256) histogram_f32_kernel(const float* __restr
     if (local[i]) atomicAdd(bins + i, (unsigned long long)local[i]);
 }
 
+// Picks the instance of quantize_per_token_warp_kernel for a row length: vectors per lane and warps per row chosen so
+// that a lane holds at most 24 vectors (128 registers or fewer) and short rows leave room for many warps per SM.
+template <bool KEYS>
+int launch_warp_rows(b200q_ctx* ctx, const float* x, int64_t M, int64_t K, int64_t ld_in4, int64_t ld_out4, const uint32_t* keys,
+                     int8_t* q, float* scales, int qmin, int qmax) {
+  const int K4 = (int)(K / 4);
+  typedef void (*WarpFn)(const float*, int64_t, int, int64_t, int64_t, const uint32_t*, int8_t*, float*, float, float);
+  WarpFn fn;
+  int rows_per_block, threads;
+  if (K4 <= 128)       { fn = quantize_per_token_warp_kernel<4, 1, 8, KEYS>;  rows_per_block = 8; threads = 256; }
+  else if (K4 <= 256)  { fn = quantize_per_token_warp_kernel<8, 1, 8, KEYS>;  rows_per_block = 8; threads = 256; }
+  else if (K4 <= 384)  { fn = quantize_per_token_warp_kernel<12, 1, 4, KEYS>; rows_per_block = 4; threads = 128; }
+  else if (K4 <= 512)  { fn = quantize_per_token_warp_kernel<16, 1, 4, KEYS>; rows_per_block = 4; threads = 128; }
+  else if (K4 <= 768)  { fn = quantize_per_token_warp_kernel<24, 1, 4, KEYS>; rows_per_block = 4; threads = 128; }
+  else if (K4 <= 1024) { fn = quantize_per_token_warp_kernel<16, 2, 4, KEYS>; rows_per_block = 2; threads = 128; }
+  else if (K4 <= 1536) { fn = quantize_per_token_warp_kernel<24, 2, 4, KEYS>; rows_per_block = 2; threads = 128; }
+  else if (K4 <= 2048) { fn = quantize_per_token_warp_kernel<16, 4, 4, KEYS>; rows_per_block = 1; threads = 128; }
+  else if (K4 <= 3072) { fn = quantize_per_token_warp_kernel<24, 4, 4, KEYS>; rows_per_block = 1; threads = 128; }
+  else if (K4 <= 4096) { fn = quantize_per_token_warp_kernel<16, 8, 8, KEYS>; rows_per_block = 1; threads = 256; }
+  else if (K4 <= 6144) { fn = quantize_per_token_warp_kernel<24, 8, 8, KEYS>; rows_per_block = 1; threads = 256; }
+  else                 { fn = quantize_per_token_warp_kernel<16, 16, 16, KEYS>; rows_per_block = 1; threads = 512; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((M + rows_per_block - 1) / rows_per_block));
+  cfg.blockDim = dim3(threads);
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->profiling ? 0 : 1;
+  B200Q_CHECK_CUDA(cudaLaunchKernelEx(&cfg, fn, x, M, K4, ld_in4, ld_out4, keys, q, scales, (float)qmin, (float)qmax));
+  return 0;
+}
+constexpr int64_t WARP_ROWS_MAX_K = 32768;   // 16 warps of 16 vectors
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -957,9 +1116,13 @@ int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t
     return 0;
   }
   const bool vec = (K % 4 == 0) && aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 3u) == 0) && (K / 4 <= 8 * 1024);
-  // Rows of up to 16 KB are staged through shared memory by bulk copies; longer rows stay in registers.
-  const bool staged = vec && ctx->quant_variant != 1 && K * 4 <= 16384 && M >= 64;
-  if (staged) {
+  // Teams of warps per row, the row in registers straight from global memory: rows of 128 to 16384 elements.
+  const bool warp_rows = vec && K >= 128 && K <= WARP_ROWS_MAX_K && (ctx->quant_variant == 3 || ctx->quant_variant == 0);
+  // Otherwise rows of up to 16 KB are staged through shared memory by bulk copies; longer rows stay in registers.
+  const bool staged = vec && !warp_rows && ctx->quant_variant != 1 && ctx->quant_variant != 3 && K * 4 <= 16384 && M >= 64;
+  if (warp_rows) {
+    if (int e = launch_warp_rows<false>(ctx, x, M, K, K / 4, K / 4, nullptr, q, scales, qmin, qmax)) return e;
+  } else if (staged) {
     const int K4 = (int)(K / 4);
     const int64_t row_bytes = K * 4;
     int rows_per_chunk = (int)(8192 / row_bytes);
@@ -972,7 +1135,7 @@ int launch_quantize_per_token(b200q_ctx* ctx, const float* x, int64_t M, int64_t
     typedef void (*StagedFn)(const float*, int64_t, int, int, int, int8_t*, float*, float, float, uint32_t*, unsigned long long);
     StagedFn fn = quantize_per_token_staged_kernel<QT_CONSUMER_WARPS, 0>;
     int consumer_warps = QT_CONSUMER_WARPS, ready_bit = 0;
-    if (rows_per_chunk == 1 && ctx->quant_variant != 2) {
+    if (rows_per_chunk == 1 && ctx->quant_variant != 2) {   // variants 0 and 4
       if (K4 == 32 * 32) { fn = quantize_per_token_staged_kernel<11, 32>; consumer_warps = 11; ready_bit = 1; }
       else if (K4 == 32 * 24) { fn = quantize_per_token_staged_kernel<14, 24>; consumer_warps = 14; ready_bit = 2; }
       else if (K4 == 32 * 16) { fn = quantize_per_token_staged_kernel<14, 16>; consumer_warps = 14; ready_bit = 3; }
@@ -1128,7 +1291,9 @@ int launch_quantize_rows_with_keys(b200q_ctx* ctx, const float* y, int64_t M, in
   const unsigned blocks = (unsigned)(M < (int64_t)ctx->sm_count * 8 ? M : (int64_t)ctx->sm_count * 8);
   const bool vec = N % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && aligned16(y) && (reinterpret_cast<uintptr_t>(q) & 3u) == 0 &&
                    N / 4 < (1ll << 31);
-  if (vec) {
+  if (vec && N >= 128 && N <= WARP_ROWS_MAX_K && ctx->quant_variant != 1) {
+    if (int e = launch_warp_rows<true>(ctx, y, M, N, ld_in / 4, ld_out / 4, keys, q, scales, qmin, qmax)) return e;
+  } else if (vec) {
     const int N4 = (int)(N / 4);
     if (N4 >= 4 * 256)
       quantize_rows_with_keys_vec_kernel<4><<<blocks, 256, 0, ctx->stream>>>(y, M, N4, ld_in, keys, q, ld_out, scales, (float)qmin, (float)qmax);

@@ -174,6 +174,25 @@ __device__ __forceinline__ uint32_t pack4_fast_lean(const float4& v, uint64_t in
   return __byte_perm(lo, hi, 0x5410);
 }
 
+// The same four codes when the row may hold values the range pass has not seen as such (NaN, +-Inf: the range came
+// from elsewhere): `far` is kept with NaN-PROPAGATING three-input maxima (d is NaN for a NaN or infinite element), so
+// the caller's test must be !(far < threshold).
+__device__ __forceinline__ uint32_t pack4_fast_lean_nan(const float4& v, uint64_t inv2, uint64_t magic2, float& far) {
+  const uint64_t t01 = f2_mul(f2_pack(v.x, v.y), inv2), t23 = f2_mul(f2_pack(v.z, v.w), inv2);
+  const uint64_t u01 = f2_add(t01, magic2), u23 = f2_add(t23, magic2);
+  const uint64_t d01 = f2_sub(t01, f2_sub(u01, magic2)), d23 = f2_sub(t23, f2_sub(u23, magic2));
+  float d0, d1, d2, d3, u0, u1, u2, u3;
+  f2_unpack(d01, d0, d1);
+  f2_unpack(d23, d2, d3);
+  f2_unpack(u01, u0, u1);
+  f2_unpack(u23, u2, u3);
+  asm("max.NaN.f32 %0, %0, %1, %2;" : "+f"(far) : "f"(fabsf(d0)), "f"(fabsf(d1)));
+  asm("max.NaN.f32 %0, %0, %1, %2;" : "+f"(far) : "f"(fabsf(d2)), "f"(fabsf(d3)));
+  const uint32_t lo = __byte_perm(__float_as_uint(u0), __float_as_uint(u1), 0x0040);
+  const uint32_t hi = __byte_perm(__float_as_uint(u2), __float_as_uint(u3), 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
+}
+
 // tie tracking only: in a per-token row |x * (127/absmax)| <= 127 (1 + 2^-23) by construction, so the magnitude
 // needs no watching; a NaN element still trips the guard through `e`.
 __device__ __forceinline__ int quantize_fast_bounded(float x, float inv, int& tie) {
