@@ -526,8 +526,9 @@ def run_c4(args, ctx, rank, world, comm):
             "roofline_layernorm_quantize": {"bound": "hbm", "achieved": (2 * 5.0 + 8.0) * M * D / (ln_ms * 1e-3) / 1e9 if ln_ms else None,
                                             "peak": pk["hbm_gbs"], "unit": "GB/s",
                                             "note": "two launches per step: 5 B/element (read x, write codes) and 13 B/element (read x and the residual, write their sum and the codes)"},
-            "roofline_sdpa": {"bound": "fp32 CUDA cores", "achieved": attn_flops / (sd_ms * 1e-3) / 1e12 if sd_ms else None, "unit": "TFLOP/s",
-                              "note": "binary32 FMA on CUDA cores (the 1e-5 bar rules out tf32 tensor-core products)"},
+            "roofline_sdpa": {"bound": "tensor (tcgen05.mma kind::tf32, every product three ways)", "achieved": attn_flops / (sd_ms * 1e-3) / 1e12 if sd_ms else None,
+                              "unit": "TFLOP/s of binary32-equivalent work", "tf32_tflops_issued": 3 * attn_flops / (sd_ms * 1e-3) / 1e12 if sd_ms else None,
+                              "note": "the 1e-5 bar rules out single tf32 products: hi*hi + hi*lo + lo*hi per term, scores and P in tensor memory, two CTAs per SM"},
             "gpu_launches": launches}
 
 
@@ -952,7 +953,7 @@ def _run():
     }
     if quant_n:
         q_avg = quant_ms / quant_n
-        roofline_quant = {"kernel": "quantize_per_token_staged_kernel", "bound": "hbm", "achieved": 5.0 * M * K / (q_avg * 1e-3) / 1e9,
+        roofline_quant = {"kernel": "quantize_per_token_warp_kernel (teams of warps, the row in registers)", "bound": "hbm", "achieved": 5.0 * M * K / (q_avg * 1e-3) / 1e9,
                           "peak": pk["hbm_gbs"], "unit": "GB/s", "avg_launch_ms": q_avg, "launches": quant_n}
         roofline_quant["frac"] = roofline_quant["achieved"] / pk["hbm_gbs"]
     else:

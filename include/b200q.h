@@ -248,8 +248,10 @@ int b200q_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* residu
 /* softmax(q k^T * scale + mask) v per (batch, head) in binary32; head dimension 64.  Row (b, s) of head h starts at
  * base + (b*S + s)*ld + h*64 for q, k, v and out (so the projections are read where the linears wrote them);
  * causal != 0 masks keys j > i.  src/nn/functional/attention.ts:42-74. */
-/* 0 (default): b200q_sdpa_f32 runs on the CUDA cores with binary32 FMAs; 1: warp-level tensor-core instructions with
- * three-way tf32 products (binary32 accuracy to ~2^-22; measured slightly slower on B200).  Both meet the 1e-5 bar. */
+/* Which kernel b200q_sdpa_f32 runs.  0 (default): the tensor-core kernel (tcgen05.mma.kind::tf32 with every product
+ * taken three ways - hi*hi + hi*lo + lo*hi - so the result keeps binary32 accuracy, scores and P in tensor memory)
+ * whenever the buffers are 16-byte aligned; otherwise the CUDA-core kernel.  1: warp-level mma.sync with the same
+ * three-way products.  2: the tensor-core kernel or an error.  3: CUDA cores, binary32 FMA.  All meet the 1e-5 bar. */
 int b200q_set_sdpa_variant(b200q_ctx* ctx, int variant);
 int b200q_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v,
                    int64_t B, int64_t H, int64_t S, int64_t head_dim, float scale, int causal, float* out, int64_t ld_out);

@@ -227,7 +227,7 @@ int b200q_set_tail_mode(b200q_ctx* ctx, int mode) {
 
 int b200q_set_sdpa_variant(b200q_ctx* ctx, int variant) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
-  B200Q_REQUIRE(variant == 0 || variant == 1, "b200q_set_sdpa_variant: unknown variant %d", variant);
+  B200Q_REQUIRE(variant >= 0 && variant <= 3, "b200q_set_sdpa_variant: unknown variant %d", variant);
   ctx->sdpa_variant = variant;
   return 0;
 }

@@ -592,6 +592,14 @@ int launch_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float*
                     ld_o % 4 == 0 && ld_q >= H * Dh && ld_k >= H * Dh && ld_v >= H * Dh && ld_o >= H * Dh,
                 "attention needs 16-byte aligned buffers and row strides that are multiples of 4 and at least H * 64");
   B200Q_REQUIRE(B * H <= 65535 && S < (1 << 24), "attention: batch * heads must not exceed 65535");
+  const bool umma_ok = sdpa_umma_supported(q, k, v, out, ld_q, ld_k, ld_v, ld_o, B, H, S, Dh);
+  B200Q_REQUIRE(ctx->sdpa_variant != 2 || umma_ok, "attention: the tensor-core kernel does not take this shape or alignment");
+  if ((ctx->sdpa_variant == 0 || ctx->sdpa_variant == 2) && umma_ok) {
+    if (int e = launch_sdpa_umma(ctx, q, k, v, ld_q, ld_k, ld_v, B, H, S, scale, causal, out, ld_o)) return e;
+    ctx->launches++;
+    B200Q_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
   const size_t smem_fma = (size_t)(4 * AT * AT) * sizeof(float), smem_mma = (size_t)4 * AT * TLD * sizeof(float);
   if (!ctx->sdpa_ready) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(sdpa_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fma));

@@ -37,6 +37,7 @@ enum StatusBits : uint32_t {
   STATUS_BAD_TMEM_ALLOC = 1u << 3,     // tensor-memory allocation returned an unexpected address
   STATUS_QUANT_WAIT_TIMEOUT = 1u << 4, // the staged quantize kernel gave up waiting for a row chunk or a free slot
   STATUS_BAD_INDEX = 1u << 5,          // an embedding lookup met a token outside its table (the row is zero)
+  STATUS_SDPA_WAIT_TIMEOUT = 1u << 7,  // the tensor-core attention kernel gave up waiting for its MMAs
   STATUS_SELFTEST_WAIT_TIMEOUT = 1u << 6, // b200q_selftest_bounded_wait: the wait on a barrier nothing signals gave up, as it must
 };
 
@@ -75,8 +76,9 @@ struct b200q_ctx {
   int quant_variant = 0;                 // 0 auto (rows staged in shared memory when they fit), 1 unstaged kernel only, 2 staged with both passes from shared memory
   uint32_t quant_staged_ready = 0;        // instances of the staged quantize kernel whose shared-memory attribute is set
   bool sdpa_ready = false;               // the attention kernels' shared-memory sizes have been raised
+  bool sdpa_umma_ready = false;          // ... and that of the tensor-core attention kernel
   int tail_mode = 0;                     // 0: exact sigmoid tails; 1: hardware exp / reciprocal for f32 outputs (tolerance only)
-  int sdpa_variant = 0;                  // 0: CUDA-core binary32 FMA; 1: mma.sync with three-way tf32 products
+  int sdpa_variant = 0;                  // 0: tcgen05 with three-way tf32 products when the shape allows; 1: mma.sync, three-way tf32; 2: tcgen05 or fail; 3: CUDA-core binary32 FMA
   uint64_t umma_ready_mask = 0;          // tensor-core kernel variants whose shared-memory attribute is set on this device
   uint64_t launches = 0;                 // kernels launched through this context
   bool capturing = false;                // between b200q_graph_begin and _end: calls are recorded, nothing may allocate or synchronise

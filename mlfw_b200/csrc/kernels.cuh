@@ -74,4 +74,10 @@ int linear_requant_token_core(b200q_ctx* ctx, const int8_t* A, const float* a_sc
 // must be current; called once per context at creation, so the array's module is loaded before any call needs it.
 int noalloc_prepare(int device);
 
+// attention_umma.cu: the same attention on the tensor cores (tcgen05.mma.kind::tf32, every product three ways).
+bool sdpa_umma_supported(const float* q, const float* k, const float* v, const float* out, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                         int64_t ld_o, int64_t B, int64_t H, int64_t S, int64_t Dh);
+int launch_sdpa_umma(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t B,
+                     int64_t H, int64_t S, float scale, int causal, float* out, int64_t ld_o);
+
 }  // namespace b200q

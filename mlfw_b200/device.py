@@ -19,7 +19,7 @@ KIND = {np.dtype(np.int8): 0, np.dtype(np.uint8): 1, np.dtype(np.int32): 2}
 
 STATUS_BITS = {1: "TMA producer wait ran out", 2: "MMA issuer wait ran out", 4: "epilogue wait ran out",
                8: "unexpected tensor-memory allocation", 16: "staged quantize wait ran out", 32: "embedding index outside its table",
-               64: "self test: the wait on a barrier nothing signals gave up (as it must)"}
+               64: "self test: the wait on a barrier nothing signals gave up (as it must)", 128: "attention kernel's wait for its MMAs ran out"}
 
 
 class DeviceBuffer:
@@ -319,7 +319,8 @@ class Context:
               "b200q_layernorm_quantize")
 
     def set_sdpa_variant(self, variant: int):
-        """0: CUDA-core binary32 FMA (default); 1: warp-level tensor-core instructions with three-way tf32 products."""
+        """0: tcgen05 kernel with three-way tf32 products when the alignment allows (default); 1: warp-level mma.sync, three-way
+        tf32; 2: tcgen05 or an error; 3: CUDA-core binary32 FMA."""
         check(self.lib.b200q_set_sdpa_variant(self.handle, variant), "b200q_set_sdpa_variant")
 
     def sdpa_f32(self, q, k, v, ld_q, ld_k, ld_v, B, H, S, head_dim, scale, causal, out, ld_out):

@@ -160,7 +160,7 @@ def run_sdpa(ctx, q, k, v, B, H, S, scale, causal, packed=False):
 
 @pytest.mark.parametrize("B,H,S", [(2, 3, 70), (1, 2, 512), (3, 1, 1), (1, 1, 64), (2, 2, 65), (1, 12, 200)])
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("variant", [0, 1])   # CUDA-core FMA / mma.sync with three-way tf32 products
+@pytest.mark.parametrize("variant", [0, 1, 3])   # tcgen05 / mma.sync (both with three-way tf32 products) / CUDA-core FMA
 def test_sdpa(ctx, orc, B, H, S, causal, variant):
     rng = np.random.default_rng(B * 100 + H * 10 + S + causal)
     shape = (B * S, H * 64)
@@ -183,7 +183,7 @@ def test_sdpa_large_magnitudes(ctx, orc):
     q = (rng.standard_normal(shape) * 6).astype(np.float32)
     k = (rng.standard_normal(shape) * 6).astype(np.float32)
     v = (rng.standard_normal(shape) * np.exp(rng.uniform(-6, 6, size=shape))).astype(np.float32)
-    for variant in (0, 1):
+    for variant in (0, 1, 3):
         ctx.set_sdpa_variant(variant)
         try:
             got = run_sdpa(ctx, q, k, v, B, H, S, 0.125, True)
