@@ -45,6 +45,10 @@ WORKLOADS = {
     "small_2048x4096x4096_gelu_tanh": (2048, 4096, 4096, "gelu_tanh"),       # profiler-sized case
     "small_2048x4096x4096_gelu_sigmoid": (2048, 4096, 4096, "gelu_sigmoid"),
     "small_2048x4096x4096_none": (2048, 4096, 4096, "none"),
+    # the short-K linears of the transformer block (config 4), as single-linear steps
+    "c4_qkv_16384x768x2304_none": (16384, 768, 2304, "none"),
+    "c4_fc1_16384x768x3072_gelu_sigmoid": (16384, 768, 3072, "gelu_sigmoid"),
+    "c4_fc2_16384x3072x768_none": (16384, 3072, 768, "none"),
 }
 DEFAULT_WORKLOAD = "c3_gemm_8192x4096x4096_gelu_tanh"
 C4_WORKLOAD = "c4_gpt_block_d768_h12_ff3072_32x512"
