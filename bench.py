@@ -838,6 +838,8 @@ def _run():
     ap.add_argument("--chunks", type=int, default=0, help="config 5, nshard: row chunks of the column-sharded call (0: try 1, 2 and 4)")
     ap.add_argument("--requant-variant", type=int, default=0, choices=[0, 1],
                     help="per-token requantize after a linear: 0 ranges from the GEMM epilogue + one-pass encode (default); 1 full quantize kernel")
+    ap.add_argument("--epilogue-warps", type=int, default=0, choices=[0, 8, 16],
+                    help="epilogue warps of the tensor-core GEMM for f32 output (0: sixteen for K <= 1024, eight otherwise)")
     ap.add_argument("--no-north-star", action="store_true", help="skip the fixed-size multi-GPU records (c3_strong, c5_mshard, c5_nshard)")
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
     ap.add_argument("--roundtrip-only", action="store_true", help="only the standalone quantize -> dequantize round trip (profiler runs)")
@@ -864,6 +866,7 @@ def _run():
     ctx = mlfw_b200.Context(local_rank)
     ctx.set_tail_mode(args.tail_mode)
     ctx.set_requant_variant(args.requant_variant)
+    ctx.set_epilogue_warps(args.epilogue_warps)
     if args.roundtrip_only:
         line = {"metric": "quantize_dequantize_GBps", "roundtrip_c2": run_roundtrip(ctx, peaks(), args.steps, args.warmup)}
         ctx.close()

@@ -59,6 +59,10 @@ int b200q_set_gemm_variant(b200q_ctx* ctx, int variant);
  * 1: hardware exponential and reciprocal -- results within about 1e-6 (relative) of mode 0, inside the 1e-5 bar, at the
  * speed of the other tails.  int8 (requantized) outputs always use the exact form: their codes are integer results. */
 int b200q_set_tail_mode(b200q_ctx* ctx, int mode);
+/* Epilogue warps of the tensor-core GEMM when the output is f32: 0 (default) = sixteen for the exact sigmoid tails
+ * (gelu_sigmoid, silu) when the contraction is short (K <= 1024: the tail, not the tensor pipe, sets the pace there),
+ * eight otherwise; 8 or 16 = always that many.  Same results either way. */
+int b200q_set_epilogue_warps(b200q_ctx* ctx, int warps);
 /* b200q_int8_linear_requant_token and the column-sharded group call: 0 (default) = the GEMM's epilogue publishes every
  * output row's range while the values are in its registers and a one-pass kernel turns the f32 result into codes;
  * 1 = the f32 result goes through the complete per-token quantize (range pass + encode).  Same codes. */

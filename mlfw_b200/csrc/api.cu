@@ -239,6 +239,13 @@ int b200q_set_gemm_variant(b200q_ctx* ctx, int variant) {
   return 0;
 }
 
+int b200q_set_epilogue_warps(b200q_ctx* ctx, int warps) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_REQUIRE(warps == 0 || warps == 8 || warps == 16, "b200q_set_epilogue_warps: %d is not 0, 8 or 16", warps);
+  ctx->epilogue_warps = warps;
+  return 0;
+}
+
 int b200q_set_requant_variant(b200q_ctx* ctx, int variant) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
   B200Q_REQUIRE(variant == 0 || variant == 1, "b200q_set_requant_variant: unknown variant %d", variant);

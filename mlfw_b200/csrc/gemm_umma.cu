@@ -45,23 +45,27 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 128;  // per-CTA tile; int8: bytes == elements
 constexpr int UMMA_K = 32;
 constexpr int MAX_STAGES = 6;
-template <int NCTA>
+// EW epilogue warps: 8 (two per tensor-memory lane quarter, 128 columns of a tile each) or 16 (four per quarter, 64
+// columns each).  Sixteen hide the latencies of the epilogue's chain (tensor-memory load, staging, proxy fence, bulk
+// store) twice as well and are used where the epilogue, not the tensor pipe, sets the pace: short K.  They cost one
+// operand stage (their staging tiles) and leave 113 registers per thread.
+template <int NCTA, int EW = 8>
 struct Cfg {
   static constexpr int B_ROWS = BN / NCTA;  // rows of the W tile one CTA stages
   static constexpr int A_BYTES = BM * BK, B_BYTES = B_ROWS * BK, STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = NCTA == 1 ? 4 : 6;
+  static constexpr int STAGES = (NCTA == 1 ? 4 : 6) - (EW == 16 ? 1 : 0);
+  static constexpr int EPI_COLS = BN / (EW / 4);   // columns of a tile one epilogue warp handles
+  static constexpr int THREADS = 64 + 32 * EW;
 };
-constexpr int EPI_WARPS = 8;                   // two warps per tensor-memory lane quarter, 128 columns each
-constexpr int EPI_COLS = BN / (EPI_WARPS / 4); // columns of a tile one epilogue warp handles
-constexpr int THREADS = 64 + 32 * EPI_WARPS;
+constexpr int MAX_EPI_WARPS = 16;
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_CH = 16;                     // columns an epilogue warp takes from tensor memory at a time
 // Staging tile of one epilogue warp for the bulk-tensor store of a chunk: 32 rows x EPI_CH 4-byte values.
 constexpr int OUT_STAGE_BYTES = 32 * EPI_CH * 4;
-constexpr int MISC_BYTES = 3584 + EPI_WARPS * EPI_COLS * 8;
-template <int NCTA>
+constexpr int MISC_BYTES = 3584 + 4 * BN * 8;     // per-warp column scales and biases: EW * EPI_COLS = 4 * BN floats each
+template <int NCTA, int EW = 8>
 constexpr int smem_bytes() {  // + slack to align the tiles to 1024 B
-  return Cfg<NCTA>::STAGES * Cfg<NCTA>::STAGE_BYTES + EPI_WARPS * OUT_STAGE_BYTES + MISC_BYTES + 1024;
+  return Cfg<NCTA, EW>::STAGES * Cfg<NCTA, EW>::STAGE_BYTES + EW * OUT_STAGE_BYTES + MISC_BYTES + 1024;
 }
 
 struct GemmParams {
@@ -76,6 +80,10 @@ struct GemmParams {
   double q_scale;
   float q_inv;
   int q_exact;
+  // What the contraction length guarantees about the accumulators (|a|, |w| <= 128): 0: below 2^22 (K <= 255), the
+  // conversion without a conversion instruction is exact; 1: at most 2^24 (K <= 1024), the conversion instruction is
+  // exact; 2: nothing, every chunk tests its accumulators and goes through binary64 when one reaches 2^22.
+  int acc_class;
   int tma_store;          // results leave through bulk-tensor stores (needs a 16-byte aligned base and row pitch)
   // f32 output only: when not null, the NaN-ignoring maximum and minimum of every output row are published here as
   // order-preserving keys (range_key_max / range_key_min in quant_math.cuh), [0, M) maxima and [M, 2M) minima, with
@@ -270,20 +278,21 @@ struct alignas(16) Misc {
     float exp_ff[2 * EXP_FF_ENTRIES];       // binary32 pairs (fill_exp_ff_table)
     double exp2[EXP2_TABLE_SIZE];           // binary64 (fill_exp2_table)
   };
-  alignas(16) float col_scale[EPI_WARPS][EPI_COLS];   // per-warp copy of w_scales for the tile's columns (read as float4)
-  alignas(16) float col_bias[EPI_WARPS][EPI_COLS];
+  alignas(16) float col_scale[4 * BN];   // per-warp copy of w_scales for the warp's columns of the tile (read as float4)
+  alignas(16) float col_bias[4 * BN];
 };
 static_assert(sizeof(Misc) <= MISC_BYTES, "misc region too small");
 static_assert(offsetof(Misc, col_scale) % 16 == 0 && offsetof(Misc, col_bias) % 16 == 0, "float4 reads need 16-byte alignment");
 
 enum OutMode : int { OUT_F32 = 0, OUT_I32 = 1, OUT_Q8 = 2 };
 
-template <int ACT_T, int OUT_T, int NCTA>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int ACT_T, int OUT_T, int NCTA, int EW = 8>
+__global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-  using C = Cfg<NCTA>;
+  using C = Cfg<NCTA, EW>;
   constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, A_BYTES = C::A_BYTES;
+  constexpr int EPI_WARPS = EW, EPI_COLS = C::EPI_COLS;
   extern __shared__ uint8_t smem_raw[];
   // The pair variant needs the same shared-memory offsets in both CTAs: the dynamic region starts at the
   // same window offset in every CTA of a kernel, so rounding it up to 1024 B gives the same result in both.
@@ -421,11 +430,11 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int ew = warp - 2;             // 0..7
+    const int ew = warp - 2;             // 0 .. EW-1
     const int quarter = warp & 3;        // tensor-memory lanes this warp may read: [32*quarter, 32*quarter+32)
     const int col0 = (ew >> 2) * EPI_COLS;  // first tile column of this warp
-    float* cs = misc->col_scale[ew];
-    float* cb = misc->col_bias[ew];
+    float* cs = misc->col_scale + ew * EPI_COLS;
+    float* cb = misc->col_bias + ew * EPI_COLS;
     const bool has_bias = p.bias != nullptr;
     // 16-byte stores need every row segment 16-byte aligned: N a multiple of 4 elements (f32, i32) or of 16 (int8).
     const bool vec_ok = OUT_T == OUT_Q8 ? ((p.N % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out_q) & 15u) == 0))
@@ -498,16 +507,28 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         } else {
           // An accumulator of 2^22 or more anywhere in the warp's chunk sends the whole chunk through the binary64
           // product (the cheap int -> float conversion and the binary32 product are only exact below that).
-          int big = 0;
+          bool wide = false;
+          if (p.acc_class == 2) {
+            int big = 0;
 #pragma unroll
-          for (int j = 0; j < EPI_CH; j++) big |= (abs(a[j]) >> 22);
-          const bool wide = __any_sync(0xffffffffu, big != 0);
+            for (int j = 0; j < EPI_CH; j++) big |= (abs(a[j]) >> 22);
+            wide = __any_sync(0xffffffffu, big != 0);
+          }
           const float4* cs4 = reinterpret_cast<const float4*>(cs + c * EPI_CH);
           const float4* cb4 = reinterpret_cast<const float4*>(cb + c * EPI_CH);
           // The loops below contain no branch at all (the choice between the two conversions is made once per
           // chunk, a missing bias was staged as -0.0, which is the identity of the rounded addition), so the
           // independent element chains of a thread can be interleaved freely.
-          if (!wide) {
+          if (p.acc_class == 1) {
+#pragma unroll
+            for (int j4 = 0; j4 < EPI_CH / 4; j4++) {
+              const float4 w4 = cs4[j4], b4 = cb4[j4];
+              const float wsv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+              for (int e = 0; e < 4; e++)
+                y[j4 * 4 + e] = __fadd_rn(__fmul_rn(__int2float_rn(a[j4 * 4 + e]), __fmul_rn(a_scale, wsv[e])), bv[e]);
+            }
+          } else if (!wide) {
 #pragma unroll
             for (int j4 = 0; j4 < EPI_CH / 4; j4++) {
               const float4 w4 = cs4[j4], b4 = cb4[j4];
@@ -799,6 +820,7 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   p.out_f32 = out_f32; p.out_i32 = out_i32; p.out_q = out_q;
   p.q_scale = q_scale;
   p.row_range = row_range;
+  p.acc_class = K <= 255 ? 0 : K <= 1024 ? 1 : 2;
   p.a_pieces = a_pieces;
   p.a_piece_cols = (int)(K / a_pieces);
   p.q_inv = 0.0f; p.q_exact = 0;
@@ -828,6 +850,12 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   // against 203 us).
   static const KernelFn tensor_bound[2][2] = {{gemm_i8_umma_kernel<ACT_GELU_SIGMOID_F32, OUT_F32, 1>, gemm_i8_umma_kernel<ACT_GELU_SIGMOID_F32, OUT_F32, 2>},
                                               {gemm_i8_umma_kernel<ACT_SILU_F32, OUT_F32, 1>, gemm_i8_umma_kernel<ACT_SILU_F32, OUT_F32, 2>}};
+  // Sixteen epilogue warps for f32 output when the main loop of a tile is short (K up to 1024): [activation][CTAs per tile]
+#define B200Q_WIDE(A) {gemm_i8_umma_kernel<A, OUT_F32, 1, 16>, gemm_i8_umma_kernel<A, OUT_F32, 2, 16>}
+  static const KernelFn wide[5][2] = {B200Q_WIDE(ACT_NONE), B200Q_WIDE(ACT_RELU), B200Q_WIDE(ACT_GELU_SIGMOID), B200Q_WIDE(ACT_GELU_TANH),
+                                      B200Q_WIDE(ACT_SILU)};
+#undef B200Q_WIDE
+  constexpr int64_t WIDE_EPILOGUE_MAX_K = 1024;
   constexpr int64_t SIGMOID_F32_MIN_K = 4096;
   B200Q_REQUIRE(act >= 0 && act <= 4, "unknown activation %d", act);
   B200Q_REQUIRE((out_i32 != nullptr) + (out_f32 != nullptr) + (out_q != nullptr) == 1,
@@ -843,7 +871,17 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
       slot_act = act == ACT_SILU ? 8 : 7;
     }
   }
-  const int smem = ncta == 1 ? smem_bytes<1>() : smem_bytes<2>();
+  int epi_warps = 8;
+  // Measured at M 16384, K 768: the exact sigmoid tails gain 9 % from sixteen warps (168 -> 153 us at N 3072), the
+  // short tails gain nothing (52 us either way at N 2304: their pace is set by the stores), so only the former switch.
+  const bool long_tail = act == ACT_GELU_SIGMOID || act == ACT_SILU;
+  if (out_f32 != nullptr && fn == table[act][0][ncta - 1] && ctx->epilogue_warps != 8 &&
+      (ctx->epilogue_warps == 16 || (K <= WIDE_EPILOGUE_MAX_K && long_tail))) {
+    fn = wide[act][ncta - 1];
+    slot_act = 9 + act;
+    epi_warps = 16;
+  }
+  const int smem = epi_warps == 16 ? (ncta == 1 ? smem_bytes<1, 16>() : smem_bytes<2, 16>()) : (ncta == 1 ? smem_bytes<1>() : smem_bytes<2>());
   const int slot_idx = (out_i32 ? 31 : slot_act * 2 + (out_q ? 1 : 0)) * 2 + (ncta - 1);   // < 64
   if (!(ctx->umma_ready_mask & (1ull << slot_idx))) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -851,7 +889,7 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(THREADS);
+  cfg.blockDim = dim3(64 + 32 * epi_warps);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[2];

@@ -528,18 +528,27 @@ quantize_per_token_staged_kernel(const float* __restrict__ x, int64_t M, int K4,
 // warps per SM, whose loads overlap each other's arithmetic; long rows are split so that a warp keeps few enough
 // registers for that to stay true.
 // ---------------------------------------------------------------------------
+// Named barrier of one team (a block holds at most two teams of more than one warp).  The barrier number is an
+// immediate, so that the kernel reserves the barriers it uses and no more (a register operand reserves all sixteen,
+// which limits the blocks per SM).
+template <int TEAM>
+__device__ __forceinline__ void team_barrier(int team) {
+  if (team == 0) asm volatile("bar.sync 1, %0;" ::"n"(32 * TEAM) : "memory");
+  else asm volatile("bar.sync 2, %0;" ::"n"(32 * TEAM) : "memory");
+}
+
 template <int TEAM>
 __device__ __forceinline__ void team_exchange(float& mn, float& mx, float2* slots, int team, int part, int lane, bool nan_dropping) {
   if (TEAM == 1) return;
   if (lane == 0) slots[team * TEAM + part] = make_float2(mn, mx);
-  asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(32 * TEAM) : "memory");
+  team_barrier<TEAM>(team);
 #pragma unroll
   for (int p = 0; p < TEAM; p++) {
     const float2 o = slots[team * TEAM + p];
     if (nan_dropping) { mn = fminf(mn, o.x); mx = fmaxf(mx, o.y); }
     else { mn = fmin3n(mn, mn, o.x); mx = fmax3n(mx, mx, o.y); }
   }
-  asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(32 * TEAM) : "memory");   // the slots may be written again
+  team_barrier<TEAM>(team);   // the slots may be written again
 }
 
 // KEYS: the rows' ranges are given (order-preserving keys published by the kernel that produced x, [0, M) maxima and
@@ -553,6 +562,7 @@ __global__ void __launch_bounds__(32 * WARPS) quantize_per_token_warp_kernel(con
                                                                              int8_t* __restrict__ q, float* __restrict__ scales,
                                                                              float qmin, float qmax) {
   static_assert(VPT % 4 == 0 && WARPS % TEAM == 0, "the encode works on groups of four vectors; whole teams per block");
+  static_assert(TEAM == 1 || WARPS / TEAM <= 2, "team_barrier knows two barriers");
   __shared__ float2 slots[(TEAM > 1 && !KEYS) ? WARPS : 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int team = warp / TEAM, part = warp - team * TEAM;

@@ -158,6 +158,10 @@ class Context:
         """0: exact sigmoid tails (default); 1: hardware exp / reciprocal for f32 outputs (within the 1e-5 bar, faster)."""
         check(self.lib.b200q_set_tail_mode(self.handle, mode), "b200q_set_tail_mode")
 
+    def set_epilogue_warps(self, warps: int):
+        """Epilogue warps of the tensor-core GEMM for f32 output: 0 = sixteen for K <= 1024, eight otherwise (default); 8; 16."""
+        check(self.lib.b200q_set_epilogue_warps(self.handle, warps), "b200q_set_epilogue_warps")
+
     def set_requant_variant(self, variant: int):
         """0: row ranges out of the GEMM epilogue + one-pass encode (default); 1: full per-token quantize of the f32 result."""
         check(self.lib.b200q_set_requant_variant(self.handle, variant), "b200q_set_requant_variant")

@@ -27,6 +27,7 @@ function bind(path: string) {
     setWaitLimit: f('int b200q_set_wait_limit(void *ctx, double seconds)'),
     setGemmVariant: f('int b200q_set_gemm_variant(void *ctx, int variant)'),
     setTailMode: f('int b200q_set_tail_mode(void *ctx, int mode)'),
+    setEpilogueWarps: f('int b200q_set_epilogue_warps(void *ctx, int warps)'),
     setRequantVariant: f('int b200q_set_requant_variant(void *ctx, int variant)'),
     setQuantVariant: f('int b200q_set_quant_variant(void *ctx, int variant)'),
     launchCount: f('uint64_t b200q_launch_count(void *ctx)'),
