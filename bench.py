@@ -188,6 +188,36 @@ def c2_input():
     return synth.with_outliers(synth.normal(synth.tensor_seed(0, 20), (M2, K2)), synth.tensor_seed(0, 21), synth.tensor_seed(0, 22))
 
 
+def run_quant_sweep(ctx, pk, iters=40):
+    """Per-token quantize over row lengths and row counts, launched back to back (one event pair around `iters` launches,
+    inputs rotating through more than L2's worth of buffers): the default kernel choice against the earlier
+    shared-memory-staged kernel (b200q_set_quant_variant 4)."""
+    rng = np.random.default_rng(0)
+    out = {}
+    for M in (8192, 16384):
+        for K in (768, 1024, 2048, 3072, 4096, 8192):
+            xs = [ctx.to_device(rng.standard_normal((M, K)).astype(np.float32)) for _ in range(max(2, int(300e6 / (M * K * 4)) + 1))]
+            q, s = ctx.empty((M, K), np.int8), ctx.empty((M,), np.float32)
+            rec = {}
+            for variant, name in ((4, "staged"), (0, "default")):
+                ctx.set_quant_variant(variant)
+                for i in range(5):
+                    ctx.quantize_per_token(xs[i % len(xs)], M, K, q, s)
+                ctx.sync()
+                ctx.timer_start()
+                for i in range(iters):
+                    ctx.quantize_per_token(xs[i % len(xs)], M, K, q, s)
+                ms = ctx.timer_stop() / iters
+                gbs = (5.0 * M * K + 4.0 * M) / (ms * 1e-3) / 1e9
+                rec[name] = {"us": ms * 1e3, "GBps": gbs, "frac": gbs / pk["hbm_gbs"]}
+            ctx.set_quant_variant(0)
+            out[f"{M}x{K}"] = rec
+            for b in xs + [q, s]:
+                b.free()
+    ctx.check_status()
+    return out
+
+
 def run_roundtrip(ctx, pk, iters, warmup):
     """Standalone quantize -> dequantize of f32 [16384,4096] with 0.1% outliers (HBM bound); per-kernel GB/s."""
     from mlfw_b200 import synth
@@ -842,6 +872,7 @@ def _run():
                     help="epilogue warps of the tensor-core GEMM for f32 output (0: sixteen for K <= 1024, eight otherwise)")
     ap.add_argument("--no-north-star", action="store_true", help="skip the fixed-size multi-GPU records (c3_strong, c5_mshard, c5_nshard)")
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
+    ap.add_argument("--quant-sweep", action="store_true", help="only the per-token quantize over row lengths 768..8192 and 8192 / 16384 rows")
     ap.add_argument("--roundtrip-only", action="store_true", help="only the standalone quantize -> dequantize round trip (profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" and not args.no_extras else args.warmup
@@ -869,6 +900,11 @@ def _run():
     ctx.set_epilogue_warps(args.epilogue_warps)
     if args.roundtrip_only:
         line = {"metric": "quantize_dequantize_GBps", "roundtrip_c2": run_roundtrip(ctx, peaks(), args.steps, args.warmup)}
+        ctx.close()
+        return line
+    if args.quant_sweep:
+        line = {"metric": "quantize_per_token_GBps", "unit": "GB/s", "timing": "back to back, 40 launches per point",
+                "quant_sweep": run_quant_sweep(ctx, peaks())}
         ctx.close()
         return line
     if args.workload == C5_WORKLOAD:

@@ -434,9 +434,17 @@ int b200q_group_linear_nshard(b200q_group* g, const int8_t* const* q_in, const f
         if (side) B200Q_CHECK_CUDA(cudaStreamWaitEvent(cs, m.ev_gemm[c], 0));
         uint32_t* keys = (uint32_t*)m.keys.ptr + 2 * r0;
         B200Q_CHECK_NCCL(api, api->AllReduce(keys, keys, (size_t)2 * rc, NCCL_UINT32, NCCL_MAX, m.comm, cs));
-        if (side) B200Q_CHECK_CUDA(cudaEventRecord(m.ev_reduced[c], cs));
       }
       if (many) B200Q_CHECK_NCCL(api, api->GroupEnd());
+      // Inside a group the collectives reach their streams only at ncclGroupEnd: an event recorded before that would
+      // not cover them.
+      if (side) {
+        for (size_t i = 0; i < nm; i++) {
+          Member& m = g->members[i];
+          B200Q_CHECK_CUDA(cudaSetDevice(m.ctx->device));
+          B200Q_CHECK_CUDA(cudaEventRecord(m.ev_reduced[c], m.comm_stream));
+        }
+      }
     }
     // codes of the local channels from the agreed range
     for (size_t i = 0; i < nm; i++) {
@@ -460,9 +468,15 @@ int b200q_group_linear_nshard(b200q_group* g, const int8_t* const* q_in, const f
         if (side) B200Q_CHECK_CUDA(cudaStreamWaitEvent(cs, m.ev_coded[c], 0));
         const int8_t* src = (const int8_t*)m.q_local[m.q_flip].ptr + r0 * cols;
         B200Q_CHECK_NCCL(api, api->AllGather(src, q_out[i] + r0 * N, (size_t)rc * cols, NCCL_INT8, m.comm, cs));
-        if (side) B200Q_CHECK_CUDA(cudaEventRecord(m.ev_gathered[c], cs));
       }
       if (many) B200Q_CHECK_NCCL(api, api->GroupEnd());
+      if (side) {
+        for (size_t i = 0; i < nm; i++) {
+          Member& m = g->members[i];
+          B200Q_CHECK_CUDA(cudaSetDevice(m.ctx->device));
+          B200Q_CHECK_CUDA(cudaEventRecord(m.ev_gathered[c], m.comm_stream));
+        }
+      }
     }
   }
   for (size_t i = 0; i < nm; i++) {
