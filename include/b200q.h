@@ -140,6 +140,17 @@ int b200q_dequantize_static(b200q_ctx* ctx, const void* q, int src_kind, int64_t
  * w_scales64 (binary64, as the pass keeps them) may be null. */
 int b200q_quantize_weights_per_channel(b200q_ctx* ctx, const float* w, int64_t N, int64_t K, int layout, int8_t* qw,
                                        float* w_scales32, double* w_scales64);
+/* Per-group symmetric quantization of a constant (GPTQ / AWQ-style INT4): QuantizationParams.fromConstantArrayPerGroup
+ * and quantizeArrayPerGroup (src/compiler/ir/graph/quantization_types.ts:319-340, 143-153).  Groups are runs of
+ * group_size consecutive elements of the flat array x[n] (the last may be shorter); scale = absMax / (2^(bits-1) - 1),
+ * or 1e-10 when that is 0, in binary64; codes = clamp(Math.round(x / scale)) to [-2^(bits-1), 2^(bits-1) - 1], one per
+ * int8 as the reference keeps them (not packed).  num_bits 2..8.  q, scales64, scales32 may each be null. */
+int b200q_quantize_per_group(b200q_ctx* ctx, const float* x, int64_t n, int64_t group_size, int num_bits, int8_t* q,
+                             double* scales64, float* scales32);
+/* dequantizeArrayPerGroup (quantization_types.ts:155-162): (q - 0) * scale[group] in binary64; y32 is that number
+ * stored to a Float32Array.  Either output may be null. */
+int b200q_dequantize_per_group(b200q_ctx* ctx, const int8_t* q, int64_t n, int64_t group_size, const double* scales64,
+                               double* y64, float* y32);
 /* Re-lay int8 weights [K,N] as [N,K] (the layout the tensor-core kernel reads). */
 int b200q_transpose_i8(b200q_ctx* ctx, const int8_t* w_kn, int64_t K, int64_t N, int8_t* w_nk);
 
@@ -148,6 +159,20 @@ int b200q_transpose_i8(b200q_ctx* ctx, const int8_t* w_kn, int64_t K, int64_t N,
  * C[m,n] = sum_k (A[m,k]-zpA) * (W[n,k]-zpW), int32.  W is [N,K]. */
 int b200q_int8_gemm_i32(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA,
                         int zpW, int32_t* C);
+/* quantized_conv with two spatial dimensions (ops/quantization.ts:156-190; lowering rules/quantization.ts:44-62 over
+ * the loop nest of src/compiler/passes/lowering/lowering_registry.ts:335-449; extents ops/linalg.ts:236-246):
+ *   out[n,oc,oh,ow] = sum_{ic,kh,kw} (in[n, g*C/groups + ic, oh*sh + kh*dh - pad_top, ow*sw + kw*dw - pad_left] - zp_in)
+ *                                    * (ker[oc,ic,kh,kw] - zp_ker),   g = oc / (O / groups),
+ * a tap outside the input adds 0; int32.  layout B200Q_CONV_NCHW: input [N,C,H,W], kernel [O,C/groups,KH,KW], output
+ * [N,O,OH,OW] (the reference's); B200Q_CONV_NHWC: input [N,H,W,C], kernel [O,KH,KW,C/groups], output [N,OH,OW,O].
+ * Runs as gather + contraction (tensor cores when both zero-points are 0) through context-owned workspaces of
+ * N*OH*OW*ceil16(C/groups*KH*KW) bytes and, unless the output is channel-last with one group, 4*N*OH*OW*O/groups. */
+#define B200Q_CONV_NCHW 0
+#define B200Q_CONV_NHWC 1
+int b200q_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker, int64_t N, int64_t C, int64_t H, int64_t W,
+                           int64_t O, int64_t KH, int64_t KW, int stride_h, int stride_w, int pad_top, int pad_bottom,
+                           int pad_left, int pad_right, int dil_h, int dil_w, int groups, int zp_in, int zp_ker, int layout,
+                           int32_t* out);
 /* The per-channel tail as separate ops (quantization_pass.ts:427-456, nn/functional/linear.ts:13-15):
  * out = act(fround(fround(acc * sv) + bias[n])) with sv = fround(a_scales[m] * w_scales[n]),
  * or sv = w_scales[n] when a_scales is null (static activation scale folded by the host). */

@@ -466,6 +466,50 @@ int b200q_int8_gemm_i32(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   return launch_gemm_i8_simt(ctx, A, W_nk, M, N, K, zpA, zpW, C);
 }
 
+int b200q_quantize_per_group(b200q_ctx* ctx, const float* x, int64_t n, int64_t group_size, int num_bits, int8_t* q,
+                             double* scales64, float* scales32) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(n >= 0 && group_size >= 1, "b200q_quantize_per_group: bad size (n=%lld group_size=%lld)", (long long)n,
+                (long long)group_size);
+  B200Q_REQUIRE(num_bits >= 2 && num_bits <= 8, "b200q_quantize_per_group: %d bits do not fit an int8 code", num_bits);
+  B200Q_REQUIRE(n == 0 || x, "b200q_quantize_per_group: null input");
+  return launch_quantize_per_group(ctx, x, n, group_size, num_bits, q, scales64, scales32);
+}
+
+int b200q_dequantize_per_group(b200q_ctx* ctx, const int8_t* q, int64_t n, int64_t group_size, const double* scales64,
+                               double* y64, float* y32) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(n >= 0 && group_size >= 1, "b200q_dequantize_per_group: bad size (n=%lld group_size=%lld)", (long long)n,
+                (long long)group_size);
+  B200Q_REQUIRE(n == 0 || (q && scales64), "b200q_dequantize_per_group: null codes or scales");
+  return launch_dequantize_per_group(ctx, q, n, group_size, scales64, y64, y32);
+}
+
+int b200q_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker, int64_t N, int64_t C, int64_t H, int64_t W,
+                           int64_t O, int64_t KH, int64_t KW, int stride_h, int stride_w, int pad_top, int pad_bottom,
+                           int pad_left, int pad_right, int dil_h, int dil_w, int groups, int zp_in, int zp_ker, int layout,
+                           int32_t* out) {
+  if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_quantized_conv2d");
+  B200Q_REQUIRE(N >= 0 && C >= 1 && H >= 1 && W >= 1 && O >= 0 && KH >= 1 && KW >= 1,
+                "b200q_quantized_conv2d: bad extent (N=%lld C=%lld H=%lld W=%lld O=%lld KH=%lld KW=%lld)", (long long)N, (long long)C,
+                (long long)H, (long long)W, (long long)O, (long long)KH, (long long)KW);
+  B200Q_REQUIRE(stride_h >= 1 && stride_w >= 1 && dil_h >= 1 && dil_w >= 1, "b200q_quantized_conv2d: strides and dilations start at 1");
+  B200Q_REQUIRE(pad_top >= 0 && pad_bottom >= 0 && pad_left >= 0 && pad_right >= 0, "b200q_quantized_conv2d: negative padding");
+  B200Q_REQUIRE(groups >= 1 && C % groups == 0 && O % groups == 0,
+                "b200q_quantized_conv2d: %d groups do not divide C=%lld and O=%lld", groups, (long long)C, (long long)O);
+  B200Q_REQUIRE(zp_in >= -128 && zp_in <= 127 && zp_ker >= -128 && zp_ker <= 127, "b200q_quantized_conv2d: zero point outside int8");
+  B200Q_REQUIRE(layout == B200Q_CONV_NCHW || layout == B200Q_CONV_NHWC, "b200q_quantized_conv2d: unknown layout %d", layout);
+  B200Q_REQUIRE(H + pad_top + pad_bottom >= (KH - 1) * dil_h + 1 && W + pad_left + pad_right >= (KW - 1) * dil_w + 1,
+                "b200q_quantized_conv2d: the dilated kernel is larger than the padded input");
+  B200Q_REQUIRE(N <= 65535, "b200q_quantized_conv2d: at most 65535 images per call");
+  B200Q_REQUIRE((C / groups) * KH * KW <= 131072, "b200q_quantized_conv2d: more than 131072 taps per output could overflow the int32 sum");
+  if (N == 0 || O == 0) return 0;
+  B200Q_REQUIRE(in && ker && out, "b200q_quantized_conv2d: null pointer");
+  return launch_quantized_conv2d(ctx, in, ker, N, C, H, W, O, KH, KW, stride_h, stride_w, pad_top, pad_bottom, pad_left, pad_right,
+                                 dil_h, dil_w, groups, zp_in, zp_ker, layout, out);
+}
+
 int b200q_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
                    const float* bias, int act, float* out) {
   if (use_device(ctx)) return 1;

@@ -65,6 +65,16 @@ int launch_layernorm_quantize(b200q_ctx* ctx, const float* x, const float* resid
 int launch_sdpa_f32(b200q_ctx* ctx, const float* q, const float* k, const float* v, int64_t ld_q, int64_t ld_k, int64_t ld_v,
                     int64_t B, int64_t H, int64_t S, int64_t Dh, float scale, int causal, float* out, int64_t ld_o);
 
+// conv_group.cu: per-group (INT4-style) codes of a constant and the int8 convolution.
+int launch_quantize_per_group(b200q_ctx* ctx, const float* x, int64_t n, int64_t group_size, int num_bits, int8_t* q,
+                              double* scales64, float* scales32);
+int launch_dequantize_per_group(b200q_ctx* ctx, const int8_t* q, int64_t n, int64_t group_size, const double* scales64, double* y64,
+                                float* y32);
+// layout 0: input / output NCHW, kernel OIHW; 1: input / output NHWC, kernel OHWI.  Uses the context's workspaces.
+int launch_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker, int64_t N, int64_t C, int64_t H, int64_t W, int64_t O,
+                            int64_t KH, int64_t KW, int sh, int sw, int pt, int pb, int pl, int pr, int dh, int dw, int groups,
+                            int zp_in, int zp_ker, int layout, int32_t* out);
+
 // api.cu: linear + per-token requantization of its result (see the definition).
 int linear_requant_token_core(b200q_ctx* ctx, const int8_t* A, const float* a_scales, int a_pieces, const int8_t* W,
                               const float* w_scales, const float* bias, int act, int64_t M, int64_t N, int64_t K, float* y,

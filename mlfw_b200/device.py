@@ -248,6 +248,26 @@ class Context:
         check(self.lib.b200q_quantize_weights_per_channel(self.handle, _ptr(w), N, K, layout, _ptr(qw), _ptr(scales32),
                                                           _ptr(scales64)), "b200q_quantize_weights_per_channel")
 
+    def quantize_per_group(self, x, n, group_size, num_bits, q, scales64=None, scales32=None):
+        """Per-group (INT4-style) scales and codes of the flat f32 array x[n]; one code per int8."""
+        check(self.lib.b200q_quantize_per_group(self.handle, _ptr(x), n, group_size, num_bits, _ptr(q), _ptr(scales64),
+                                                _ptr(scales32)), "b200q_quantize_per_group")
+
+    def dequantize_per_group(self, q, n, group_size, scales64, y64=None, y32=None):
+        check(self.lib.b200q_dequantize_per_group(self.handle, _ptr(q), n, group_size, _ptr(scales64), _ptr(y64), _ptr(y32)),
+              "b200q_dequantize_per_group")
+
+    def quantized_conv2d(self, x, ker, shape, kernel_shape, out, strides=(1, 1), padding=((0, 0), (0, 0)), dilation=(1, 1),
+                         groups=1, zp_in=0, zp_ker=0, layout="NCHW"):
+        """quantized_conv: ``shape`` = (N, C, H, W) and ``kernel_shape`` = (O, KH, KW) whatever the layout
+        ("NCHW" with an OIHW kernel, or "NHWC" with an OHWI kernel); int32 output in the input's layout."""
+        N, Cc, H, W = shape
+        O, KH, KW = kernel_shape
+        check(self.lib.b200q_quantized_conv2d(self.handle, _ptr(x), _ptr(ker), N, Cc, H, W, O, KH, KW, strides[0], strides[1],
+                                              padding[0][0], padding[0][1], padding[1][0], padding[1][1], dilation[0], dilation[1],
+                                              groups, zp_in, zp_ker, {"NCHW": 0, "NHWC": 1}[layout], _ptr(out)),
+              "b200q_quantized_conv2d")
+
     def transpose_i8(self, w_kn, K, N, w_nk):
         check(self.lib.b200q_transpose_i8(self.handle, _ptr(w_kn), K, N, _ptr(w_nk)), "b200q_transpose_i8")
 

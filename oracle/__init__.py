@@ -162,6 +162,74 @@ def dequantize_per_channel(q, shape, axis, scales) -> np.ndarray:
     return out.reshape(shape)
 
 
+def per_group_scales(data, group_size, num_bits=4) -> np.ndarray:
+    """QuantizationParams.fromConstantArrayPerGroup (quantization_types.ts:319-340): one binary64 scale per run of
+    ``group_size`` consecutive elements of the flat array."""
+    flat = np.asarray(data).reshape(-1)
+    n = flat.size
+    scales = np.empty((n + group_size - 1) // group_size, np.float64)
+    if flat.dtype == np.float32:
+        d = _f32(flat)
+        lib().orc_per_group_scales_f32(_p(d), C.c_int64(n), C.c_int64(group_size), C.c_int(num_bits), _p(scales))
+    else:
+        d = np.ascontiguousarray(flat, np.float64)
+        lib().orc_per_group_scales_f64(_p(d), C.c_int64(n), C.c_int64(group_size), C.c_int(num_bits), _p(scales))
+    return scales
+
+
+def quantize_per_group(data, group_size, scales, num_bits=4, want_double=False):
+    """quantizeArrayPerGroup (quantization_types.ts:143-153): codes as stored to an Int8Array, optionally the raw doubles."""
+    flat = np.asarray(data).reshape(-1)
+    n = flat.size
+    scales = np.ascontiguousarray(scales, np.float64)
+    q8 = np.empty(n, np.int8)
+    qd = np.empty(n, np.float64) if want_double else None
+    if flat.dtype == np.float32:
+        d, fn = _f32(flat), lib().orc_quantize_per_group_f32
+    else:
+        d, fn = np.ascontiguousarray(flat, np.float64), lib().orc_quantize_per_group_f64
+    fn(_p(d), C.c_int64(n), C.c_int64(group_size), C.c_int(num_bits), _p(scales), _p(q8), _p(qd))
+    return (q8, qd) if want_double else q8
+
+
+def dequantize_per_group(q, group_size, scales) -> np.ndarray:
+    """dequantizeArrayPerGroup (quantization_types.ts:155-162), binary64 result."""
+    q = np.ascontiguousarray(np.asarray(q).reshape(-1), np.int8)
+    scales = np.ascontiguousarray(scales, np.float64)
+    out = np.empty(q.size, np.float64)
+    lib().orc_dequantize_per_group(_p(q), C.c_int64(q.size), C.c_int64(group_size), _p(scales), _p(out))
+    return out
+
+
+def conv_out_extent(size, pad_lo, pad_hi, k, stride, dilation) -> int:
+    """ops/linalg.ts:236-246."""
+    return (size + pad_lo + pad_hi - ((k - 1) * dilation + 1)) // stride + 1
+
+
+def quantized_conv2d(x, ker, strides=(1, 1), padding=((0, 0), (0, 0)), dilation=(1, 1), groups=1, zp_in=0, zp_ker=0,
+                     layout="NCHW") -> np.ndarray:
+    """quantized_conv (lowering rules/quantization.ts:44-62): int8 input [N,C,H,W] x int8 kernel [O,C/groups,KH,KW]
+    -> int32 [N,O,OH,OW]; with layout "NHWC": [N,H,W,C] x [O,KH,KW,C/groups] -> [N,OH,OW,O]."""
+    x = np.ascontiguousarray(x, np.int8)
+    ker = np.ascontiguousarray(ker, np.int8)
+    lay = {"NCHW": 0, "NHWC": 1}[layout]
+    if lay == 0:
+        N, Cc, H, W = x.shape
+        O, _, KH, KW = ker.shape
+    else:
+        N, H, W, Cc = x.shape
+        O, KH, KW, _ = ker.shape
+    OH = conv_out_extent(H, padding[0][0], padding[0][1], KH, strides[0], dilation[0])
+    OW = conv_out_extent(W, padding[1][0], padding[1][1], KW, strides[1], dilation[1])
+    out = np.empty((N, O, OH, OW) if lay == 0 else (N, OH, OW, O), np.int32)
+    lib().orc_quantized_conv2d(_p(x), _p(ker), C.c_int64(N), C.c_int64(Cc), C.c_int64(H), C.c_int64(W), C.c_int64(O),
+                               C.c_int64(KH), C.c_int64(KW), C.c_int(strides[0]), C.c_int(strides[1]),
+                               C.c_int(padding[0][0]), C.c_int(padding[0][1]), C.c_int(padding[1][0]), C.c_int(padding[1][1]),
+                               C.c_int(dilation[0]), C.c_int(dilation[1]), C.c_int(groups), C.c_int(zp_in), C.c_int(zp_ker),
+                               C.c_int(lay), _p(out))
+    return out
+
+
 def quantize_per_token(x, cmin=-127.0, cmax=127.0):
     """Per-token (row) symmetric int8: returns (codes int8 [M,K], scales f64 [M], scales f32 [M])."""
     x = _f32(x)

@@ -82,13 +82,15 @@ def js_or(x: float, fallback: float) -> float:
 
 # ------------------------------------------------------------- QuantizationParams (src/compiler/ir/graph/quantization_types.ts)
 PER_TENSOR_SYMMETRIC, PER_TENSOR_ASYMMETRIC, PER_CHANNEL = "per_tensor_symmetric", "per_tensor_asymmetric", "per_channel"
+PER_GROUP = "per_group"
 
 
 class QuantizationParams:
     """quantization_types.ts:41-141.  `scale` / `zero_point` are numbers, or lists for the per-channel scheme."""
 
-    def __init__(self, scheme, scale, zero_point, axis=None, dtype="i8", num_bits=8):
+    def __init__(self, scheme, scale, zero_point, axis=None, dtype="i8", num_bits=8, group_size=None):
         self.scheme, self.scale, self.zero_point, self.axis, self.dtype, self.num_bits = scheme, scale, zero_point, axis, dtype, num_bits
+        self.group_size = group_size
 
     def is_symmetric(self):
         return self.scheme == PER_TENSOR_SYMMETRIC
@@ -139,6 +141,18 @@ class QuantizationParams:
         stride = self._channel_stride(shape)
         num_ch = shape[self.axis]
         return [(arr[i] - self.zero_point[(i // stride) % num_ch]) * self.scale[(i // stride) % num_ch] for i in range(len(arr))]
+
+    def quantize_array_per_group(self, arr):                 # :143-153
+        c_min, c_max = self.clamp_range()
+        out = [0.0] * len(arr)
+        for i in range(len(arr)):
+            g = i // self.group_size
+            s, zp = self.scale[g], self.zero_point[g]
+            out[i] = math_max(c_min, math_min(c_max, math_round(_div(arr[i], s) + zp)))
+        return out
+
+    def dequantize_array_per_group(self, arr):               # :155-162
+        return [(arr[i] - self.zero_point[i // self.group_size]) * self.scale[i // self.group_size] for i in range(len(arr))]
 
     # ---- factories
     @staticmethod
@@ -209,6 +223,22 @@ class QuantizationParams:
                 maxs[c] += 0.5
         return QuantizationParams.from_range_per_channel(mins, maxs, axis, dtype, num_bits)
 
+    @staticmethod
+    def from_constant_array_per_group(data, group_size, dtype="i8", num_bits=4):      # :319-340
+        num_groups = -(-len(data) // group_size)
+        scales, zero_points = [0.0] * num_groups, [0] * num_groups
+        bound = 2 ** (num_bits - 1) - 1
+        for g in range(num_groups):
+            start = g * group_size
+            end = min(start + group_size, len(data))
+            abs_max = 0.0
+            for i in range(start, end):
+                a = abs(data[i])
+                if a > abs_max:
+                    abs_max = a
+            scales[g] = js_or(abs_max / bound, 1e-10)
+        return QuantizationParams(PER_GROUP, scales, zero_points, None, dtype, num_bits, group_size)
+
 
 def _div(a: float, b: float) -> float:
     """JavaScript division: a zero divisor gives an infinity or NaN instead of raising."""
@@ -274,6 +304,39 @@ def quantized_dot(A, W_nk, zp_a=0, zp_b=0):
                 acc = acc + (x - zp_a) * (y - zp_b)
             row.append(to_int32(float(acc)))
         out.append(row)
+    return out
+
+
+# ------------------------------------------------------ quantized_conv (src/compiler/passes/lowering/rules/quantization.ts:44-62
+# over the loop nest of lowering_registry.ts:335-449; output extents ops/linalg.ts:236-246)
+def quantized_conv2d(x, ker, strides=(1, 1), padding=((0, 0), (0, 0)), dilation=(1, 1), groups=1, zp_in=0, zp_ker=0):
+    """x: nested lists [N][C][H][W] of int8 codes, ker: [O][C/groups][KH][KW]; returns [N][O][OH][OW] as stored to an
+    Int32Array.  The loops run in the nest's order (n, oc, oh, ow, ic, kh, kw); a tap outside the input adds the guard's 0."""
+    N, C, H, W = len(x), len(x[0]), len(x[0][0]), len(x[0][0][0])
+    O, Cg, KH, KW = len(ker), len(ker[0]), len(ker[0][0]), len(ker[0][0][0])
+    OH = math.floor((H + padding[0][0] + padding[0][1] - ((KH - 1) * dilation[0] + 1)) / strides[0]) + 1
+    OW = math.floor((W + padding[1][0] + padding[1][1] - ((KW - 1) * dilation[1] + 1)) / strides[1]) + 1
+    group_size = O // groups
+    out = [[[[0] * OW for _ in range(OH)] for _ in range(O)] for _ in range(N)]
+    for n in range(N):
+        for oc in range(O):
+            for oh in range(OH):
+                for ow in range(OW):
+                    acc = 0
+                    for ic in range(Cg):
+                        c = (oc // group_size) * Cg + ic if groups > 1 else ic
+                        for kh in range(KH):
+                            for kw in range(KW):
+                                ih = oh * strides[0] + (kh * dilation[0] + -padding[0][0])
+                                iw = ow * strides[1] + (kw * dilation[1] + -padding[1][0])
+                                inside = 1
+                                if padding[0][0] != 0 or padding[0][1] != 0:
+                                    inside *= (1 if ih >= 0 else 0) * (1 if ih < H else 0)
+                                if padding[1][0] != 0 or padding[1][1] != 0:
+                                    inside *= (1 if iw >= 0 else 0) * (1 if iw < W else 0)
+                                prod = (x[n][c][ih][iw] - zp_in) * (ker[oc][ic][kh][kw] - zp_ker) if inside else 0
+                                acc = to_int32(float(acc + prod))
+                    out[n][oc][oh][ow] = acc
     return out
 
 

@@ -25,6 +25,7 @@
 //   src/compiler/passes/decompose/decomposition_pass.ts:156-174, 232-260 and src/nn/functional/attention.ts:42-74
 //                                                   softmax, layer_norm, attention (tolerance only)
 //   src/util/random.ts, src/tensor/factory/creation_ops.ts, src/nn/init.ts  seeded data
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -536,6 +537,89 @@ void orc_sdpa(const float* q, const float* k, const float* v, int64_t ld_q, int6
       o[d] = acc;
     }
   }
+}
+
+// ---------------------------------------------------------------------------
+// Per-group quantization (GPTQ / AWQ-style INT4): quantization_types.ts:319-340
+// (fromConstantArrayPerGroup), :143-153 (quantizeArrayPerGroup), :155-162
+// (dequantizeArrayPerGroup).  Groups are runs of groupSize consecutive elements of
+// the flat array (the last one may be shorter); zero-points are 0; the scheme is
+// not the symmetric one, so the clamp is [-2^(b-1), 2^(b-1)-1] (:62-73).
+// ---------------------------------------------------------------------------
+#define ORC_PER_GROUP_SCALES(NAME, T)                                                            \
+  void NAME(const T* data, int64_t n, int64_t groupSize, int numBits, double* scales) {          \
+    const int64_t groups = (n + groupSize - 1) / groupSize;                                      \
+    const double bound = std::ldexp(1.0, numBits - 1) - 1.0;                                     \
+    _Pragma("omp parallel for schedule(static)")                                                 \
+    for (int64_t g = 0; g < groups; g++) {                                                       \
+      const int64_t start = g * groupSize, end = std::min(start + groupSize, n);                 \
+      double absMax = 0;                                                                         \
+      for (int64_t i = start; i < end; i++) {                                                    \
+        double a = std::fabs((double)data[i]);                                                   \
+        if (a > absMax) absMax = a;                                                              \
+      }                                                                                          \
+      scales[g] = js_or(absMax / bound, 1e-10);                                                  \
+    }                                                                                            \
+  }
+ORC_PER_GROUP_SCALES(orc_per_group_scales_f32, float)
+ORC_PER_GROUP_SCALES(orc_per_group_scales_f64, double)
+
+#define ORC_QUANT_PER_GROUP(NAME, T)                                                             \
+  void NAME(const T* data, int64_t n, int64_t groupSize, int numBits, const double* scales,      \
+            int8_t* q8, double* qd) {                                                            \
+    const double cMin = -std::ldexp(1.0, numBits - 1), cMax = std::ldexp(1.0, numBits - 1) - 1.0; \
+    _Pragma("omp parallel for schedule(static)")                                                 \
+    for (int64_t i = 0; i < n; i++) {                                                            \
+      double q = qp_quantize((double)data[i], scales[i / groupSize], 0.0, cMin, cMax);           \
+      if (q8) q8[i] = js_to_int8(q);                                                             \
+      if (qd) qd[i] = q;                                                                         \
+    }                                                                                            \
+  }
+ORC_QUANT_PER_GROUP(orc_quantize_per_group_f32, float)
+ORC_QUANT_PER_GROUP(orc_quantize_per_group_f64, double)
+
+void orc_dequantize_per_group(const int8_t* q, int64_t n, int64_t groupSize, const double* scales, double* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) out[i] = ((double)q[i] - 0.0) * scales[i / groupSize];
+}
+
+// ---------------------------------------------------------------------------
+// quantized_conv, two spatial dimensions: ops/quantization.ts:156-190, lowering
+// rules/quantization.ts:44-62 over the loop nest of lowering_registry.ts:335-449.
+//   out[n,oc,oh,ow] = sum_{ic,kh,kw} inside ? (in[n, g*Cg+ic, ih, iw] - zpIn) * (ker[oc,ic,kh,kw] - zpKer) : 0
+//   ih = oh*sh + kh*dh - padTop, iw = ow*sw + kw*dw - padLeft, g = oc / (O / groups)
+// A tap outside the input adds 0 (the guard's fill), not (0 - zpIn) * (...).  The accumulator is an Int32Array
+// element: every addition is stored back with ToInt32.  Output extents follow ops/linalg.ts:236-246.
+// layout 0: input / output NCHW, kernel OIHW;  1: input / output NHWC, kernel OHWI.
+// ---------------------------------------------------------------------------
+void orc_quantized_conv2d(const int8_t* in, const int8_t* ker, int64_t N, int64_t C, int64_t H, int64_t W, int64_t O,
+                          int64_t KH, int64_t KW, int sh, int sw, int padTop, int padBottom, int padLeft, int padRight,
+                          int dh, int dw, int groups, int zpIn, int zpKer, int layout, int32_t* out) {
+  const int64_t OH = (H + padTop + padBottom - ((KH - 1) * dh + 1)) / sh + 1;
+  const int64_t OW = (W + padLeft + padRight - ((KW - 1) * dw + 1)) / sw + 1;
+  const int64_t Cg = C / groups, Og = O / groups;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t n = 0; n < N; n++)
+    for (int64_t oc = 0; oc < O; oc++) {
+      const int64_t g = oc / Og;
+      for (int64_t oh = 0; oh < OH; oh++)
+        for (int64_t ow = 0; ow < OW; ow++) {
+          int32_t acc = 0;
+          for (int64_t ic = 0; ic < Cg; ic++)
+            for (int64_t kh = 0; kh < KH; kh++)
+              for (int64_t kw = 0; kw < KW; kw++) {
+                const int64_t ih = oh * sh + kh * dh - padTop, iw = ow * sw + kw * dw - padLeft;
+                if (ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
+                const int64_t c = g * Cg + ic;
+                const int64_t ii = layout == 0 ? ((n * C + c) * H + ih) * W + iw : ((n * H + ih) * W + iw) * C + c;
+                const int64_t ki = layout == 0 ? ((oc * Cg + ic) * KH + kh) * KW + kw : ((oc * KH + kh) * KW + kw) * Cg + ic;
+                const double prod = (double)((int)in[ii] - zpIn) * (double)((int)ker[ki] - zpKer);
+                acc = js_to_int32((double)acc + prod);
+              }
+          const int64_t oi = layout == 0 ? ((n * O + oc) * OH + oh) * OW + ow : ((n * OH + oh) * OW + ow) * O + oc;
+          out[oi] = acc;
+        }
+    }
 }
 
 double orc_js_round(double x) { return js_round(x); }

@@ -249,3 +249,47 @@ def test_layer_norm_and_attention_agree(orc):
 def test_mulberry32_agrees(orc):
     nxt = js.make_rng(12345)
     assert [nxt() for _ in range(100)] == list(orc.rng_uniform(12345, 100))
+
+
+# ------------------------------------------------------------------ per-group codes and the int8 convolution
+@pytest.mark.parametrize("n,G,bits", [(4096, 32, 4), (1000, 128, 4), (777, 16, 3), (513, 64, 8), (64, 7, 2)])
+def test_per_group_matches(orc, n, G, bits):
+    rng = np.random.default_rng(n + G)
+    x = (rng.standard_normal(n) * np.exp(rng.uniform(-3, 3, n))).astype(np.float32)
+    x[3] = np.nan; x[G:2 * G] = 0.0; x[2 * G + 1] = np.inf; x[5 * G:6 * G] = -2.5      # NaN, an all-zero group, an infinite scale, a constant group
+    x[7 * G % n] = np.float32(1e-42)
+    qp = js.QuantizationParams.from_constant_array_per_group(f32_list(x), G, "i8", bits)
+    s = orc.per_group_scales(x, G, bits)
+    assert list(s) == qp.scale
+    q8, qd = orc.quantize_per_group(x, G, s, bits, want_double=True)
+    q_js = qp.quantize_array_per_group(f32_list(x))
+    assert all((a == b) or (a != a and b != b) for a, b in zip(qd, q_js))
+    assert list(q8) == [js.to_int8(v) for v in q_js]
+    d = orc.dequantize_per_group(q8, G, s)
+    d_js = qp.dequantize_array_per_group([int(v) for v in q8])
+    assert all((a == b) or (a != a and b != b) for a, b in zip(d, d_js))
+
+
+CONV_CASES = [
+    # N, C, H, W, O, KH, KW, strides, padding, dilation, groups, zp_in, zp_ker
+    (2, 4, 7, 6, 6, 3, 3, (2, 1), ((1, 0), (2, 1)), (1, 2), 2, 3, -2),
+    (1, 3, 8, 8, 5, 3, 3, (1, 1), ((1, 1), (1, 1)), (1, 1), 1, 0, 0),
+    (2, 16, 5, 5, 8, 1, 1, (1, 1), ((0, 0), (0, 0)), (1, 1), 1, 0, 0),
+    (1, 6, 9, 7, 6, 2, 3, (2, 2), ((0, 1), (1, 0)), (2, 1), 6, -5, 7),
+    (1, 2, 4, 4, 2, 4, 4, (1, 1), ((3, 3), (3, 3)), (1, 1), 1, 127, -128),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_quantized_conv_matches(orc, case):
+    N, C, H, W, O, KH, KW, st, pad, dil, groups, zi, zk = case
+    rng = np.random.default_rng(N * 100 + C)
+    x = rng.integers(-128, 128, (N, C, H, W), dtype=np.int8)
+    k = rng.integers(-128, 128, (O, C // groups, KH, KW), dtype=np.int8)
+    ref = js.quantized_conv2d(x.tolist(), k.tolist(), st, pad, dil, groups, zi, zk)
+    got = orc.quantized_conv2d(x, k, st, pad, dil, groups, zi, zk, "NCHW")
+    assert np.array_equal(got, np.array(ref, np.int32))
+    # the channel-last form is the same numbers re-laid
+    got_l = orc.quantized_conv2d(np.ascontiguousarray(x.transpose(0, 2, 3, 1)), np.ascontiguousarray(k.transpose(0, 2, 3, 1)),
+                                 st, pad, dil, groups, zi, zk, "NHWC")
+    assert np.array_equal(got_l.transpose(0, 3, 1, 2), got)

@@ -214,3 +214,24 @@ def test_minmax_calibration(orc):
     mn, mx = orc.minmax_observe([b1, b2])
     assert (mn, mx) == (-2.0, 3.0)
     assert orc.from_range(mn, mx, SYM)[0] == 3.0 / 127
+
+
+# params.test.js:204-234 -- INT4 group-wise quantization (both restatements)
+def test_per_group_int4_known_answers(orc):
+    from oracle import jsport as js
+    N, G = 64, 16
+    data = [math.sin(i * 0.9) * (1 + (i % G) * 0.1) for i in range(N)]
+    qp = js.QuantizationParams.from_constant_array_per_group(data, G, "i8", 4)
+    scales = orc.per_group_scales(np.array(data), G, 4)
+    assert qp.scheme == js.PER_GROUP and qp.num_bits == 4 and len(qp.scale) == math.ceil(N / G) == len(scales)
+    assert list(scales) == qp.scale
+    q_js = qp.quantize_array_per_group(data)
+    q = orc.quantize_per_group(np.array(data), G, scales, 4)
+    assert list(q) == q_js and all(float(v).is_integer() and -7 <= v <= 7 for v in q_js)
+    deq = orc.dequantize_per_group(q, G, scales)
+    assert list(deq) == qp.dequantize_array_per_group(q_js)
+    assert max(abs(d - x) for d, x in zip(deq, data)) <= max(scales) / 2 + 1e-9
+    # beats per-tensor INT4 (params.test.js:225-233)
+    pt = js.QuantizationParams.from_constant_array(data, js.PER_TENSOR_SYMMETRIC, "i8", 4)
+    pt_err = max(abs(d - x) for d, x in zip(pt.dequantize_array(pt.quantize_array(data)), data))
+    assert max(abs(d - x) for d, x in zip(deq, data)) < pt_err
