@@ -115,7 +115,7 @@ def compile_with_b200(module: Dict[str, GraphFunction], config: dict) -> "B200Ru
 # ----------------------------------------------------------------------------- planning
 @dataclass
 class Step:
-    kind: str                       # 'quantize_static' | 'quantize_token' | 'dequantize_static' | 'linear'
+    kind: str                       # 'quantize_static' | 'quantize_token' | 'dequantize_static' | 'linear' | 'conv' | 'const'
     ins: List[Value]
     out: Value
     params: Dict[str, Any]
@@ -154,6 +154,7 @@ class _Planner:
         self.f = func
         self.dynamic = dynamic
         self.steps: List[Step] = []
+        self.consts: set = set()    # ids of constant values already turned into 'const' steps
         self.done: set = set()      # ids of ops absorbed into a step
 
     def other(self, op: Op, v: Value) -> Value:
@@ -282,6 +283,37 @@ class _Planner:
             y = nq.result
         self.steps.append(Step("linear", [lhs], y, params))
 
+    def materialize(self, v: Value):
+        """A constant that a native step reads as a buffer (the kernel of a convolution, the f32 source of its
+        `quantize`) becomes a 'const' step: uploaded once when the plan is built."""
+        if v.producer is not None and v.producer.name == "constant" and id(v) not in self.consts:
+            self.consts.add(id(v))
+            self.steps.append(Step("const", [], v, {"data": np.ascontiguousarray(_const_array(v), NP_DTYPE[v.dtype])}))
+
+    def plan_conv(self, op: Op):
+        """quantized_conv (ops/quantization.ts:156-190): both operands are device buffers (the pass quantizes input
+        and kernel with `quantize` ops, tests/compiler/passes/quantization/pass.test.js:428-440); the int32 result is
+        read by the `dequantize` that follows as a step of its own."""
+        x, k = op.operands
+        if x.dtype != "i8" or k.dtype != "i8":
+            raise B200CompileError("quantized_conv takes int8 operands (ui8 is not supported by the convolution kernels)")
+        layouts = (op.attrs.get("input_layout", "NCHW"), op.attrs.get("kernel_layout", "OIHW"))
+        if layouts not in (("NCHW", "OIHW"), ("NHWC", "OHWI")) or len(x.shape) != 4 or len(k.shape) != 4:
+            raise B200CompileError("quantized_conv: two spatial dimensions, layouts NCHW / OIHW or NHWC / OHWI")
+        strides = [int(v) for v in op.attrs["strides"]]
+        padding = [[int(a), int(b)] for a, b in op.attrs["padding"]]
+        dilation = [int(v) for v in (op.attrs.get("dilation") or [1] * len(strides))]
+        if layouts[0] == "NCHW":
+            (N, C, H, W), (O, _, KH, KW) = x.shape, k.shape
+        else:
+            (N, H, W, C), (O, KH, KW, _) = x.shape, k.shape
+        self.materialize(x)
+        self.materialize(k)
+        self.steps.append(Step("conv", [x, k], op.result, {
+            "shape": [N, C, H, W], "kernel_shape": [O, KH, KW], "strides": strides, "padding": padding, "dilation": dilation,
+            "groups": int(op.attrs.get("groups") or 1), "zp_in": int(op.attrs.get("input_zero_point", 0) or 0),
+            "zp_ker": int(op.attrs.get("kernel_zero_point", 0) or 0), "layout": layouts[0]}))
+
     def plan(self) -> List[Step]:
         for op in self.f.ops:
             if id(op) in self.done:
@@ -291,6 +323,7 @@ class _Planner:
                 continue                       # consumed through their users
             if n == "quantize":
                 x = op.operands[0]
+                self.materialize(x)
                 users = self.f.users(op.result)
                 feeds_dot = bool(users) and all(u.name == "quantized_dot" and u.operands[0] is op.result for u in users)
                 if self.dynamic and feeds_dot and len(x.shape) >= 2:
@@ -305,11 +338,13 @@ class _Planner:
                     "kind": {"i8": 0, "ui8": 1, "i32": 2}[op.operands[0].dtype]}))
             elif n == "quantized_dot":
                 self.plan_dot(op)
+            elif n == "quantized_conv":
+                self.plan_conv(op)
             elif n == "return":
                 continue
             else:
                 raise B200CompileError(f"op '{n}' is outside the graph contract of the B200 backend "
-                                       "(quantize, dequantize, quantized_dot and its per-channel tail); "
+                                       "(quantize, dequantize, quantized_dot and its per-channel tail, quantized_conv); "
                                        "compile with quantizableOps = {'dot'} and keep other ops on another target")
         return self.steps
 
@@ -344,9 +379,10 @@ def program_of(args: Sequence[Value], returns: Sequence[Value], steps: Sequence[
         for k, val in st.params.items():
             if k in ("dW", "dws", "db"):          # device buffers of a live plan are not part of the program
                 continue
-            if k in _ARRAY_PARAMS:
+            if k in _ARRAY_PARAMS or k == "data":
+                dt = NP_DTYPE[st.out.dtype] if k == "data" else _ARRAY_PARAMS[k]   # a constant travels in its own dtype
                 params[k] = None if val is None else {"shape": list(np.shape(val)),
-                                                      "b64": base64.b64encode(np.ascontiguousarray(val, _ARRAY_PARAMS[k]).tobytes()).decode("ascii")}
+                                                      "b64": base64.b64encode(np.ascontiguousarray(val, dt).tobytes()).decode("ascii")}
             else:
                 params[k] = val
         out_steps.append({"kind": st.kind, "ins": [vid(v) for v in st.ins],
@@ -366,14 +402,15 @@ def steps_from_program(program: dict):
         args.append(vals[a["id"]])
     steps = []
     for st in program["steps"]:
-        if st["kind"] not in ("quantize_static", "quantize_token", "dequantize_static", "linear"):
+        if st["kind"] not in ("quantize_static", "quantize_token", "dequantize_static", "linear", "conv", "const"):
             raise B200CompileError(f"native program: unknown step '{st['kind']}'")
         o = st["out"]
         vals[o["id"]] = Value(tuple(o["shape"]), o["dtype"])
         params = {}
         for k, val in st["params"].items():
-            if k in _ARRAY_PARAMS and val is not None:
-                params[k] = np.frombuffer(base64.b64decode(val["b64"]), _ARRAY_PARAMS[k]).reshape(val["shape"]).copy()
+            if (k in _ARRAY_PARAMS or k == "data") and val is not None:
+                dt = NP_DTYPE[o["dtype"]] if k == "data" else _ARRAY_PARAMS[k]
+                params[k] = np.frombuffer(base64.b64decode(val["b64"]), dt).reshape(val["shape"]).copy()
             else:
                 params[k] = val
         try:
@@ -411,6 +448,8 @@ class _FunctionPlan:
             self._alloc(st.out)
             if st.kind == "quantize_token":
                 self.scales[id(st.out)] = ctx.empty((st.params["M"],), np.float32)
+            if st.kind == "const":
+                self.buf[id(st.out)].upload(np.ascontiguousarray(st.params["data"], NP_DTYPE[st.out.dtype]).reshape(st.out.shape if st.out.shape else (1,)))
             if st.kind == "linear":
                 p = st.params
                 w = p["w"]
@@ -453,10 +492,15 @@ class _FunctionPlan:
         for v, a in zip(self.func.args, arrays[: self.inputs]):
             self.buf[id(v)].upload(np.ascontiguousarray(a, NP_DTYPE[v.dtype]).reshape(v.shape))
         for st in self.steps:
+            if st.kind == "const":              # uploaded when the plan was built
+                continue
             x = self.buf[id(st.ins[0])]
             out = self.buf[id(st.out)]
             p = st.params
-            if st.kind == "quantize_static":
+            if st.kind == "conv":
+                ctx.quantized_conv2d(x, self.buf[id(st.ins[1])], p["shape"], p["kernel_shape"], out, p["strides"], p["padding"],
+                                     p["dilation"], p["groups"], p["zp_in"], p["zp_ker"], p["layout"])
+            elif st.kind == "quantize_static":
                 ctx.quantize_static(x, int(np.prod(st.ins[0].shape)), p["scale"], p["zero_point"], p["kind"], out)
             elif st.kind == "quantize_token":
                 ctx.quantize_per_token(x, p["M"], p["K"], out, self.scales[id(st.out)])

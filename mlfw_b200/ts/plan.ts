@@ -6,6 +6,7 @@
 // src/compiler/passes/quantization/quantization_pass.ts:286-459):
 //   quantize · quantized_dot(constant i8 rhs) · convert · mul(broadcast_in_dim(constant f32[N]))
 //   [· add(broadcast(bias))] [· maximum(·,0) | x·sigmoid(1.702x) | x·sigmoid(x)] [· quantize]   -> one 'linear' step
+//   quantize(x) · quantize(kernel) · quantized_conv  -> 'conv' (int32; the `dequantize` after it is a step of its own)
 //   quantized_dot · dequantize{scale}                                                               -> 'linear' with a constant scale vector
 //   standalone quantize / dequantize                                                                 -> static steps
 // Anything else throws: the backend has no fallback.
@@ -26,7 +27,13 @@ type Step =
   | { kind: 'dequantize_static'; in: Value; out: Value; scale: number; zeroPoint: number; src: number }
   | { kind: 'linear'; in: Value; out: Value; M: number; N: number; K: number; act: Act; dynamic: boolean;
       w: Int8Array; wIsKN: boolean; wScales: Float32Array; bias: Float32Array | null; requantScale: number | null;
-      dW?: unknown; dWs?: unknown; dBias?: unknown };
+      dW?: unknown; dWs?: unknown; dBias?: unknown }
+  // a constant that a native step reads as a buffer (a convolution's kernel, the f32 source of its `quantize`): uploaded once
+  | { kind: 'const'; out: Value; data: ArrayBufferView }
+  // quantized_conv (ops/quantization.ts:156-190): both operands are device buffers, the int32 result feeds a `dequantize`
+  | { kind: 'conv'; in: Value; ker: Value; out: Value; shape: number[]; kernelShape: number[]; strides: number[]; padding: number[][];
+      dilation: number[]; groups: number; zpIn: number; zpKer: number; layout: 'NCHW' | 'NHWC' };
+const TYPED = { f32: Float32Array, i32: Int32Array, i8: Int8Array, ui8: Uint8Array } as const;
 
 const shapeOf = (v: Value): number[] => (v.type as { shape: number[] }).shape;
 const dtypeOf = (v: Value): string => (v.type as { dtype: string }).dtype;
@@ -84,6 +91,13 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
   const steps: Step[] = [];
   const done = new Set<Operation>();
   const returns = new Set<Value>(f.returnValues());
+  const consts = new Set<Value>();
+  const materialize = (v: Value) => {
+    const a = constArray(v);
+    if (!a || consts.has(v)) return;
+    consts.add(v);
+    steps.push({ kind: 'const', out: v, data: TYPED[dtypeOf(v) as keyof typeof TYPED].from(a) });
+  };
   for (const op of f.ops()) {
     if (done.has(op)) continue;
     const n = op.opName;
@@ -92,6 +106,7 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
       const x = op.getOperand(0), us = users(f, op.getResult(0), done);
       const feedsDot = us.length > 0 && us.every((u) => u.opName === 'quantized_dot' && u.getOperand(0) === op.getResult(0));
       const s = shapeOf(x);
+      materialize(x);
       if (dynamic && feedsDot && s.length >= 2) steps.push({ kind: 'quantize_token', in: x, out: op.getResult(0), M: numel(s.slice(0, -1)), K: s[s.length - 1] });
       else steps.push({ kind: 'quantize_static', in: x, out: op.getResult(0), scale: op.getAttr<number>('scale')!, zeroPoint: op.getAttr<number>('zero_point') || 0,
                         dst: op.getAttr<string>('target_dtype') === 'ui8' ? 1 : 0 });
@@ -133,11 +148,32 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
         requantScale = nq[0].getAttr<number>('scale')!; done.add(nq[0]); y = nq[0].getResult(0);
       }
       steps.push({ kind: 'linear', in: lhs, out: y, M, N, K, act: a.act, dynamic, w: Int8Array.from(w), wIsKN: rc[0] === 0, wScales, bias, requantScale });
+    } else if (n === 'quantized_conv') {
+      const x = op.getOperand(0), k = op.getOperand(1), xs = shapeOf(x), ks = shapeOf(k);
+      if (dtypeOf(x) !== 'i8' || dtypeOf(k) !== 'i8') throw new Error('b200: quantized_conv takes int8 operands');
+      const il = op.getAttr<string>('input_layout') || 'NCHW', kl = op.getAttr<string>('kernel_layout') || 'OIHW';
+      if (!((il === 'NCHW' && kl === 'OIHW') || (il === 'NHWC' && kl === 'OHWI')) || xs.length !== 4 || ks.length !== 4)
+        throw new Error('b200: quantized_conv: two spatial dimensions, layouts NCHW / OIHW or NHWC / OHWI');
+      const strides = op.getAttr<number[]>('strides')!, padding = op.getAttr<number[][]>('padding')!;
+      const first = il === 'NCHW';
+      materialize(x); materialize(k);
+      steps.push({ kind: 'conv', in: x, ker: k, out: op.getResult(0),
+                   shape: first ? xs : [xs[0], xs[3], xs[1], xs[2]], kernelShape: first ? [ks[0], ks[2], ks[3]] : [ks[0], ks[1], ks[2]],
+                   strides, padding, dilation: op.getAttr<number[]>('dilation') || strides.map(() => 1), groups: op.getAttr<number>('groups') || 1,
+                   zpIn: op.getAttr<number>('input_zero_point') || 0, zpKer: op.getAttr<number>('kernel_zero_point') || 0, layout: il as 'NCHW' | 'NHWC' });
     } else {
-      throw new Error(`b200: op '${n}' is outside the graph contract (quantize, dequantize, quantized_dot and its tail)`);
+      throw new Error(`b200: op '${n}' is outside the graph contract (quantize, dequantize, quantized_dot and its tail, quantized_conv)`);
     }
   }
   return steps;
+}
+
+type ConvParams = { shape: number[]; kernelShape: number[]; strides: number[]; padding: number[][]; dilation: number[]; groups: number;
+                    zpIn: number; zpKer: number; layout: string };
+function runConv(b: B200QBinding, c: unknown, x: unknown, k: unknown, y: unknown, q: ConvParams): void {
+  const [N, C, H, W] = q.shape, [O, KH, KW] = q.kernelShape;
+  check(b, b.quantizedConv2d(c, x, k, N, C, H, W, O, KH, KW, q.strides[0], q.strides[1], q.padding[0][0], q.padding[0][1], q.padding[1][0],
+                             q.padding[1][1], q.dilation[0], q.dilation[1], q.groups, q.zpIn, q.zpKer, q.layout === 'NHWC' ? 1 : 0, y), 'b200q_quantized_conv2d');
 }
 
 export type FunctionPlan = { inputs: number; outputs: number; steps: Step[]; describe(): string; execute(b: B200QBinding, ctx: unknown, args: ArrayBufferView[]): void };
@@ -153,6 +189,7 @@ export function planGraph(module: GraphModule, options: B200Options, b: B200QBin
     const buf = new Map<Value, unknown>(), tokScales = new Map<Value, unknown>();
     for (const v of f.args) buf.set(v, alloc(bytesOf(v)));
     for (const st of steps) {
+      if (st.kind === 'const') { buf.set(st.out, upload(st.data)); continue; }
       buf.set(st.out, alloc(bytesOf(st.out)));
       if (st.kind === 'quantize_token') tokScales.set(st.out, alloc(st.M * 4));
       if (st.kind === 'linear') {                     // weights cross the boundary once, as buffers
@@ -170,8 +207,10 @@ export function planGraph(module: GraphModule, options: B200Options, b: B200QBin
       execute(bind, c, args) {
         f.args.forEach((v, i) => check(bind, bind.upload(c, buf.get(v), args[i], args[i].byteLength), 'b200q_upload'));
         for (const st of steps) {
+          if (st.kind === 'const') continue;              // uploaded when the plan was built
           const x = buf.get(st.in), y = buf.get(st.out);
-          if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, numel(shapeOf(st.in)), st.scale, st.zeroPoint, st.dst, y), 'b200q_quantize_static');
+          if (st.kind === 'conv') runConv(bind, c, x, buf.get(st.ker), y, st);
+          else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, numel(shapeOf(st.in)), st.scale, st.zeroPoint, st.dst, y), 'b200q_quantize_static');
           else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, st.M, st.K, y, tokScales.get(st.out), -127, 127), 'b200q_quantize_per_token');
           else if (st.kind === 'dequantize_static') check(bind, bind.dequantizeStatic(c, x, st.src, numel(shapeOf(st.in)), st.scale, st.zeroPoint, y), 'b200q_dequantize_static');
           else if (st.requantScale !== null) check(bind, bind.int8LinearRequantStatic(c, x, null, st.dW, st.dWs, st.dBias, ACT[st.act], st.M, st.N, st.K, st.requantScale, y), 'b200q_int8_linear_requant_static');
@@ -215,7 +254,12 @@ export function programOf(f: GraphFunction, steps: Step[]): NativeProgram {
       w_layout: st.wIsKN ? 1 : 0, w: { ...b64(st.w), shape: st.wIsKN ? [st.K, st.N] : [st.N, st.K] }, w_scales: b64(st.wScales), bias: st.bias ? b64(st.bias) : null });
     else if (st.kind === 'quantize_token') Object.assign(params, { M: st.M, K: st.K });
     else if (st.kind === 'quantize_static') Object.assign(params, { scale: st.scale, zero_point: st.zeroPoint, kind: st.dst });
-    else Object.assign(params, { scale: st.scale, zero_point: st.zeroPoint, kind: st.src });
+    else if (st.kind === 'const') return { kind: st.kind, ins: [], out: rec(st.out), params: { data: { ...b64(st.data), shape: shapeOf(st.out) } } };
+    else if (st.kind === 'conv') {
+      Object.assign(params, { shape: st.shape, kernel_shape: st.kernelShape, strides: st.strides, padding: st.padding, dilation: st.dilation,
+                              groups: st.groups, zp_in: st.zpIn, zp_ker: st.zpKer, layout: st.layout });
+      return { kind: st.kind, ins: [vid(st.in), vid(st.ker)], out: rec(st.out), params };
+    } else Object.assign(params, { scale: st.scale, zero_point: st.zeroPoint, kind: st.src });
     return { kind: st.kind, ins: [vid(st.in)], out: rec(st.out), params };
   });
   return { version: PROGRAM_VERSION, args, steps: out, returns: f.returnValues().map(vid) };
@@ -230,8 +274,10 @@ export function planFromProgram(p: NativeProgram, b: B200QBinding, ctx: unknown)
   const buf = new Map<number, unknown>(), scales = new Map<number, unknown>(), elems = new Map<number, number>();
   for (const a of p.args) { buf.set(a.id, alloc(size(a))); elems.set(a.id, numel(a.shape)); }
   const dev = p.steps.map((st) => {
-    buf.set(st.out.id, alloc(size(st.out))); elems.set(st.out.id, numel(st.out.shape));
     const q = st.params as Record<string, any>;
+    elems.set(st.out.id, numel(st.out.shape));
+    if (st.kind === 'const') { buf.set(st.out.id, upload(unb64(q.data, (x) => new Uint8Array(x))!)); return null; }
+    buf.set(st.out.id, alloc(size(st.out)));
     if (st.kind === 'quantize_token') scales.set(st.out.id, alloc(q.M * 4));
     if (st.kind !== 'linear') return null;
     const w = unb64(q.w, (x) => new Int8Array(x))!;
@@ -246,8 +292,10 @@ export function planFromProgram(p: NativeProgram, b: B200QBinding, ctx: unknown)
     execute(bind, c, args) {
       p.args.forEach((a, i) => check(bind, bind.upload(c, buf.get(a.id), args[i], args[i].byteLength), 'b200q_upload'));
       p.steps.forEach((st, i) => {
+        if (st.kind === 'const') return;
         const q = st.params as Record<string, any>, x = buf.get(st.ins[0]), y = buf.get(st.out.id), d = dev[i];
-        if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, elems.get(st.ins[0])!, q.scale, q.zero_point, q.kind, y), 'b200q_quantize_static');
+        if (st.kind === 'conv') runConv(bind, c, x, buf.get(st.ins[1]), y, { ...(q as ConvParams), kernelShape: q.kernel_shape, zpIn: q.zp_in, zpKer: q.zp_ker });
+        else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, elems.get(st.ins[0])!, q.scale, q.zero_point, q.kind, y), 'b200q_quantize_static');
         else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, q.M, q.K, y, scales.get(st.out.id), -127, 127), 'b200q_quantize_per_token');
         else if (st.kind === 'dequantize_static') check(bind, bind.dequantizeStatic(c, x, q.kind, elems.get(st.ins[0])!, q.scale, q.zero_point, y), 'b200q_dequantize_static');
         else if (q.requant_scale !== null) check(bind, bind.int8LinearRequantStatic(c, x, null, d!.dW, d!.dWs, d!.dBias, ACT[q.act as Act], q.M, q.N, q.K, q.requant_scale, y), 'b200q_int8_linear_requant_static');

@@ -98,6 +98,33 @@ def main():
     a32 = lambda v: np.array(v, np.float32)
     np.savez(os.path.join(HERE, "block_ops.npz"), x=a32(xb), residual=a32(rb), gamma=a32(gamma), beta=a32(beta), ln_sum=a32(sb), ln_out=a32(yb),
              q=a32(qb), k=a32(kb), v=a32(vb), attn=a32(ab))
+    # per-group INT4 on the reference test's own data (tests/compiler/passes/quantization/params.test.js:204-207) and on a
+    # longer closed-form array with a ragged last group, a zero group and 3-bit codes
+    pg = {}
+    for tag, n, G, bits in (("a", 64, 16, 4), ("b", 203, 32, 4), ("c", 96, 8, 3)):
+        data = [f32(math.sin(i * 0.9) * (1 + (i % G) * 0.1)) for i in range(n)]
+        if tag == "b":
+            data[64:96] = [0.0] * 32
+        qp = js.QuantizationParams.from_constant_array_per_group(data, G, "i8", bits)
+        q = qp.quantize_array_per_group(data)
+        pg.update({f"x_{tag}": np.array(data, np.float32), f"meta_{tag}": np.array([G, bits], np.int64),
+                   f"scales_{tag}": np.array(qp.scale, np.float64), f"q_{tag}": np.array([js.to_int8(v) for v in q], np.int8),
+                   f"deq_{tag}": np.array(qp.dequantize_array_per_group(q), np.float64)})
+    np.savez(os.path.join(HERE, "per_group.npz"), **pg)
+    # quantized_conv on closed-form int8 codes: strides, uneven padding, dilation, two groups, both zero-points; and a
+    # plain 3x3 / padding 1 layer with 16 taps per group so that the tensor-core contraction is the one checked
+    cv = {}
+    for tag, (N, C, H, W, O, KH, KW, st, pad, dil, groups, zi, zk) in (
+            ("a", (2, 4, 7, 6, 6, 3, 3, (2, 1), ((1, 0), (2, 1)), (1, 2), 2, 3, -2)),
+            ("b", (1, 16, 6, 6, 8, 3, 3, (1, 1), ((1, 1), (1, 1)), (1, 1), 1, 0, 0))):
+        code = lambda i, f: int(js.math_round(127 * math.sin(f * i + 0.5)))
+        x = [[[[code(((n * C + c) * H + h) * W + w, 0.37) for w in range(W)] for h in range(H)] for c in range(C)] for n in range(N)]
+        k = [[[[code(((o * (C // groups) + c) * KH + a) * KW + b, 0.11) for b in range(KW)] for a in range(KH)] for c in range(C // groups)]
+             for o in range(O)]
+        out = js.quantized_conv2d(x, k, st, pad, dil, groups, zi, zk)
+        cv.update({f"x_{tag}": np.array(x, np.int8), f"k_{tag}": np.array(k, np.int8), f"out_{tag}": np.array(out, np.int32),
+                   f"geom_{tag}": np.array([st[0], st[1], pad[0][0], pad[0][1], pad[1][0], pad[1][1], dil[0], dil[1], groups, zi, zk], np.int64)})
+    np.savez(os.path.join(HERE, "quantized_conv.npz"), **cv)
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 

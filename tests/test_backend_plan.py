@@ -138,8 +138,64 @@ def test_native_program_rejects_what_it_does_not_understand(orc):
     prog = program_of(func.args, func.returns, plan_function(func, dynamic=False))
     with pytest.raises(B200CompileError, match="version"):
         steps_from_program({**prog, "version": 99})
-    bad = {**prog, "steps": [{**prog["steps"][0], "kind": "conv"}] + prog["steps"][1:]}
+    bad = {**prog, "steps": [{**prog["steps"][0], "kind": "pooling"}] + prog["steps"][1:]}
     with pytest.raises(B200CompileError, match="unknown step"):
         steps_from_program(bad)
     with pytest.raises(B200CompileError, match="never produced"):
         steps_from_program({**prog, "returns": [12345]})
+
+
+def conv_graph(orc, layout="NCHW"):
+    """The reference pass's conv pipeline (tests/compiler/passes/quantization/pass.test.js:428-440):
+    quantize(input), quantize(kernel), quantized_conv, dequantize."""
+    rng = np.random.default_rng(3)
+    N, C, H, W, O, KH, KW = 2, 4, 9, 8, 6, 3, 3
+    k = (rng.standard_normal((O, C // 2, KH, KW)) * 0.2).astype(np.float32)
+    x_shape = (N, C, H, W)
+    if layout == "NHWC":
+        k = np.ascontiguousarray(k.transpose(0, 2, 3, 1))
+        x_shape = (N, H, W, C)
+    in_scale, _ = orc.from_range(-6, 6)
+    k_scale, _ = orc.from_constant_array(k.astype(np.float64).reshape(-1))
+    b = GraphBuilder("conv")
+    x = b.arg(x_shape)
+    xq = b.op("quantize", [x], x_shape, "i8", scale=in_scale, zero_point=0, target_dtype="i8")
+    kc = b.constant(k.tolist(), k.shape, "f32")
+    kq = b.op("quantize", [kc], k.shape, "i8", scale=k_scale, zero_point=0, target_dtype="i8")
+    OH, OW = orc.conv_out_extent(H, 1, 1, KH, 2, 1), orc.conv_out_extent(W, 0, 2, KW, 1, 1)
+    out_shape = (N, O, OH, OW) if layout == "NCHW" else (N, OH, OW, O)
+    acc = b.op("quantized_conv", [xq, kq], out_shape, "i32", strides=[2, 1], padding=[[1, 1], [0, 2]], dilation=[1, 1], groups=2,
+               input_layout=layout, kernel_layout="OIHW" if layout == "NCHW" else "OHWI", input_scale=in_scale, input_zero_point=0,
+               kernel_scale=k_scale, kernel_zero_point=0, output_scale=in_scale * k_scale, output_zero_point=0)
+    y = b.op("dequantize", [acc], out_shape, "f32", scale=in_scale * k_scale, zero_point=0)
+    return b.ret(y), {"k": k, "in_scale": in_scale, "k_scale": k_scale, "x_shape": x_shape, "out_shape": out_shape}
+
+
+@pytest.mark.parametrize("layout", ["NCHW", "NHWC"])
+def test_conv_pipeline_plans_and_round_trips(orc, layout):
+    import json
+    func, info = conv_graph(orc, layout)
+    steps = plan_function(func, dynamic=False)
+    assert [s.kind for s in steps] == ["quantize_static", "const", "quantize_static", "conv", "dequantize_static"]
+    assert steps[1].params["data"].dtype == np.float32 and (steps[1].params["data"] == info["k"]).all()
+    conv = steps[3]
+    assert conv.params["shape"] == [2, 4, 9, 8] and conv.params["kernel_shape"] == [6, 3, 3] and conv.params["groups"] == 2
+    assert conv.params["layout"] == layout and conv.out.dtype == "i32" and conv.out.shape == info["out_shape"]
+    args, returns, again = steps_from_program(json.loads(json.dumps(program_of(func.args, func.returns, steps))))
+    assert [s.kind for s in again] == [s.kind for s in steps]
+    assert again[1].params["data"].dtype == np.float32 and (again[1].params["data"] == info["k"]).all()
+    assert again[3].params == conv.params and again[3].ins[1] is again[2].out and returns[0] is again[4].out
+
+
+def test_conv_outside_the_contract_is_refused(orc):
+    b = GraphBuilder("c")
+    x = b.arg((1, 2, 4, 4), "ui8")
+    k = b.arg((2, 2, 1, 1), "i8")
+    y = b.op("quantized_conv", [x, k], (1, 2, 4, 4), "i32", strides=[1, 1], padding=[[0, 0], [0, 0]], input_layout="NCHW", kernel_layout="OIHW")
+    with pytest.raises(B200CompileError, match="int8 operands"):
+        plan_function(b.ret(y), dynamic=False)
+    b = GraphBuilder("c")
+    x, k = b.arg((1, 2, 4, 4), "i8"), b.arg((2, 2, 1, 1), "i8")
+    y = b.op("quantized_conv", [x, k], (1, 2, 4, 4), "i32", strides=[1, 1], padding=[[0, 0], [0, 0]], input_layout="NCHW", kernel_layout="HWIO")
+    with pytest.raises(B200CompileError, match="layouts"):
+        plan_function(b.ret(y), dynamic=False)

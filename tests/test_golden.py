@@ -26,6 +26,22 @@ def test_fixture_generator_uses_the_python_port_only():
 
 
 # ------------------------------------------------------------------ CPU: the oracle against the fixtures
+def test_oracle_reproduces_per_group_and_conv_fixtures(orc):
+    g = load("per_group.npz")
+    for tag in "abc":
+        G, bits = (int(v) for v in g[f"meta_{tag}"])
+        s = orc.per_group_scales(g[f"x_{tag}"], G, bits)
+        assert same_bits(s, g[f"scales_{tag}"])
+        q = orc.quantize_per_group(g[f"x_{tag}"], G, s, bits)
+        assert same_bits(q, g[f"q_{tag}"])
+        assert same_bits(orc.dequantize_per_group(q, G, s), g[f"deq_{tag}"])
+    g = load("quantized_conv.npz")
+    for tag in "ab":
+        sh, sw, pt, pb, pl, pr, dh, dw, groups, zi, zk = (int(v) for v in g[f"geom_{tag}"])
+        out = orc.quantized_conv2d(g[f"x_{tag}"], g[f"k_{tag}"], (sh, sw), ((pt, pb), (pl, pr)), (dh, dw), groups, zi, zk, "NCHW")
+        assert same_bits(out, g[f"out_{tag}"])
+
+
 def test_oracle_reproduces_matmul_fixtures(orc):
     for name in ("matmul_m4k8n6.npz", "matmul_m64k128n32.npz"):
         g = load(name)
@@ -150,3 +166,27 @@ def test_cuda_matches_block_fixture(ctx):
     assert same_bits(dsum.download(), g["ln_sum"])
     assert np.abs(dy.download() - g["ln_out"]).max() <= 1e-5 * np.abs(g["ln_out"]).max()
     assert np.abs(dattn.download() - g["attn"]).max() <= 1e-5 * np.abs(g["attn"]).max()
+
+
+@pytest.mark.gpu
+def test_cuda_matches_per_group_and_conv_fixtures(ctx):
+    g = load("per_group.npz")
+    for tag in "abc":
+        G, bits = (int(v) for v in g[f"meta_{tag}"])
+        x = g[f"x_{tag}"]
+        n, groups = x.size, (x.size + G - 1) // G
+        dq, ds = ctx.empty((n,), np.int8), ctx.empty((groups,), np.float64)
+        ctx.quantize_per_group(ctx.to_device(x), n, G, bits, dq, ds, None)
+        dy = ctx.empty((n,), np.float64)
+        ctx.dequantize_per_group(dq, n, G, ds, dy, None)
+        ctx.sync()
+        assert same_bits(ds.download(), g[f"scales_{tag}"]) and same_bits(dq.download(), g[f"q_{tag}"]) and same_bits(dy.download(), g[f"deq_{tag}"])
+    g = load("quantized_conv.npz")
+    for tag in "ab":
+        sh, sw, pt, pb, pl, pr, dh, dw, groups, zi, zk = (int(v) for v in g[f"geom_{tag}"])
+        x, k, ref = g[f"x_{tag}"], g[f"k_{tag}"], g[f"out_{tag}"]
+        do = ctx.empty(ref.shape, np.int32)
+        ctx.quantized_conv2d(ctx.to_device(x), ctx.to_device(k), x.shape, (k.shape[0], k.shape[2], k.shape[3]), do, (sh, sw), ((pt, pb), (pl, pr)),
+                             (dh, dw), groups, zi, zk, "NCHW")
+        ctx.sync()
+        assert same_bits(do.download(), ref)

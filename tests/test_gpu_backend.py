@@ -123,3 +123,27 @@ def test_fake_quant_roundtrip_is_lossy(orc):
         applied |= abs(out[i] - v) > 1e-6
     assert applied
     mod.release()
+
+
+@pytest.mark.parametrize("layout", ["NCHW", "NHWC"])
+def test_conv_pipeline_matches_the_reference_chain(orc, layout):
+    """quantize(input), quantize(kernel), quantized_conv, dequantize through the target object, and once more from the
+    serialized native program; every stage is the CPU oracle's, bit for bit."""
+    from test_backend_plan import conv_graph
+    from mlfw_b200.backend import B200RuntimeModule
+    func, info = conv_graph(orc, layout)
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal(info["x_shape"]) * 2.5).astype(np.float32)
+    mod = compile_with_b200({"conv": func}, {"target": B200Target()})
+    out = np.zeros(info["out_shape"], np.float32)
+    mod.run("conv", x, out)
+    xq = orc.quantize_static(x.reshape(-1), info["in_scale"]).reshape(x.shape)
+    kq = orc.quantize_static(info["k"].reshape(-1), info["k_scale"]).reshape(info["k"].shape)
+    acc = orc.quantized_conv2d(xq, kq, (2, 1), ((1, 1), (0, 2)), (1, 1), 2, 0, 0, layout)
+    ref = orc.dequantize_static(acc.reshape(-1), info["in_scale"] * info["k_scale"]).reshape(info["out_shape"])
+    assert (out.view(np.uint32) == ref.view(np.uint32)).all()
+    again = B200RuntimeModule.deserialize(mod.serialize())
+    out2 = np.zeros(info["out_shape"], np.float32)
+    again.run("conv", x, out2)
+    assert (out2.view(np.uint32) == ref.view(np.uint32)).all()
+    mod.release(); again.release()
