@@ -218,6 +218,44 @@ def run_quant_sweep(ctx, pk, iters=40):
     return out
 
 
+def run_conv_bench(ctx, pk, iters=20):
+    """quantized_conv2d (gather + tensor-core contraction) on ResNet-sized 3x3 and 1x1 layers, channel-last and
+    channel-first, 32 images: time per call back to back, TOP/s over 2 * outputs * taps, and the split between the
+    gather / re-lay kernels and the contraction from the per-family event timing of a second pass."""
+    rng = np.random.default_rng(0)
+    out = {}
+    for (C, HW, O, KK, pad) in ((64, 56, 64, 3, 1), (128, 28, 128, 3, 1), (256, 14, 256, 3, 1), (256, 56, 64, 1, 0)):
+        N = 32
+        for layout in ("NHWC", "NCHW"):
+            xs = (N, HW, HW, C) if layout == "NHWC" else (N, C, HW, HW)
+            ks = (O, KK, KK, C) if layout == "NHWC" else (O, C, KK, KK)
+            dx = ctx.to_device(rng.integers(-127, 128, xs, dtype=np.int8))
+            dk = ctx.to_device(rng.integers(-127, 128, ks, dtype=np.int8))
+            do = ctx.empty((N * HW * HW * O,), np.int32)
+            call = lambda: ctx.quantized_conv2d(dx, dk, (N, C, HW, HW), (O, KK, KK), do, (1, 1), ((pad, pad), (pad, pad)), (1, 1), 1, 0, 0, layout)
+            for _ in range(3):
+                call()
+            ctx.sync()
+            ctx.timer_start()
+            for _ in range(iters):
+                call()
+            ms = ctx.timer_stop() / iters
+            ctx.profile_enable(True); ctx.profile_reset()
+            for _ in range(iters):
+                call()
+            fam = ctx.profile_read()
+            ctx.profile_enable(False)
+            ops = 2.0 * N * HW * HW * O * C * KK * KK
+            out[f"c{C}_{HW}x{HW}_o{O}_k{KK}_{layout}"] = {
+                "us": ms * 1e3, "TOPs": ops / (ms * 1e-3) / 1e12, "frac_of_int8_proxy": ops / (ms * 1e-3) / 1e12 / (2 * pk["bf16_tflops"]),
+                "gather_and_relay_us": fam.get("weights", (0.0, 1))[0] / iters * 1e3, "contraction_us": fam.get("gemm_tensor_core", (0.0, 1))[0] / iters * 1e3,
+                "gathered_bytes": N * HW * HW * ((C * KK * KK + 15) // 16 * 16)}
+            for b in (dx, dk, do):
+                b.free()
+    ctx.check_status()
+    return out
+
+
 def run_roundtrip(ctx, pk, iters, warmup):
     """Standalone quantize -> dequantize of f32 [16384,4096] with 0.1% outliers (HBM bound); per-kernel GB/s."""
     from mlfw_b200 import synth
@@ -873,6 +911,7 @@ def _run():
     ap.add_argument("--no-north-star", action="store_true", help="skip the fixed-size multi-GPU records (c3_strong, c5_mshard, c5_nshard)")
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
     ap.add_argument("--quant-sweep", action="store_true", help="only the per-token quantize over row lengths 768..8192 and 8192 / 16384 rows")
+    ap.add_argument("--conv-bench", action="store_true", help="only quantized_conv2d on ResNet-sized layers (gather + contraction), both layouts")
     ap.add_argument("--roundtrip-only", action="store_true", help="only the standalone quantize -> dequantize round trip (profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" and not args.no_extras else args.warmup
@@ -905,6 +944,10 @@ def _run():
     if args.quant_sweep:
         line = {"metric": "quantize_per_token_GBps", "unit": "GB/s", "timing": "back to back, 40 launches per point",
                 "quant_sweep": run_quant_sweep(ctx, peaks())}
+        ctx.close()
+        return line
+    if args.conv_bench:
+        line = {"metric": "quantized_conv2d_TOPs", "unit": "TOP/s", "timing": "back to back, 20 calls per point", "conv_bench": run_conv_bench(ctx, peaks())}
         ctx.close()
         return line
     if args.workload == C5_WORKLOAD:

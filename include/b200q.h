@@ -166,7 +166,9 @@ int b200q_int8_gemm_i32(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
  * a tap outside the input adds 0; int32.  layout B200Q_CONV_NCHW: input [N,C,H,W], kernel [O,C/groups,KH,KW], output
  * [N,O,OH,OW] (the reference's); B200Q_CONV_NHWC: input [N,H,W,C], kernel [O,KH,KW,C/groups], output [N,OH,OW,O].
  * Runs as gather + contraction (tensor cores when both zero-points are 0) through context-owned workspaces of
- * N*OH*OW*ceil16(C/groups*KH*KW) bytes and, unless the output is channel-last with one group, 4*N*OH*OW*O/groups. */
+ * N*OH*OW*ceil16(C/groups*KH*KW) bytes and, unless the output is channel-last with one group, 4*N*OH*OW*O/groups;
+ * a channel-first call with a multiple of 16 channels per group also re-lays input and kernel channel-last
+ * (N*C*H*W + O*C/groups*KH*KW bytes more).  Channel-last with C/groups a multiple of 16 is the fast form. */
 #define B200Q_CONV_NCHW 0
 #define B200Q_CONV_NHWC 1
 int b200q_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker, int64_t N, int64_t C, int64_t H, int64_t W,

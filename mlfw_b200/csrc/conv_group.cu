@@ -10,7 +10,9 @@
 // ([N*OH*OW, C/groups*KH*KW], padded to a multiple of 16 columns, padding taps holding the input zero-point so that
 // their term vanishes), the tensor-core GEMM (or the CUDA-core one when a zero-point is not 0) multiplies it with the
 // kernel tensor read in place as [O, C/groups*KH*KW], and channel-first output is transposed out of the GEMM's
-// channel-last result.  Groups are handled one contraction per group.
+// channel-last result.  Groups are handled one contraction per group.  With a multiple of 16 channels per group the
+// gather moves 16 bytes at a time from a channel-last input; a channel-first input and its kernel tensor are re-laid
+// channel-last first.
 #include <cstdint>
 
 #include "common.cuh"
@@ -112,6 +114,45 @@ __global__ void __launch_bounds__(256) conv_gather_kernel(const int8_t* __restri
   }
 }
 
+// The same rows when the input is channel-last and a group has a multiple of 16 channels: a 16-byte piece of a row is
+// 16 consecutive channels of one tap, i.e. one aligned 16-byte load (or the zero-point, outside the input).
+__global__ void __launch_bounds__(256) conv_gather_nhwc16_kernel(const int8_t* __restrict__ in, ConvGeom p, int g, int8_t* __restrict__ a) {
+  const uint32_t ppt = (uint32_t)(p.Cg / 16), pieces = (uint32_t)(p.Kp / 16);
+  const int64_t M = p.N * p.OH * p.OW, total = M * pieces, stride = (int64_t)gridDim.x * blockDim.x;
+  const uint32_t fill = 0x01010101u * (uint32_t)(uint8_t)p.zp_in;
+  const uint32_t OW = (uint32_t)p.OW, OH = (uint32_t)p.OH, KW = (uint32_t)p.KW;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const uint32_t m = (uint32_t)(t / pieces), r = (uint32_t)(t - (int64_t)m * pieces);
+    const uint32_t tap = r / ppt, c16 = r - tap * ppt, kh = tap / KW, kw = tap - kh * KW;
+    const uint32_t ow = m % OW, mo = m / OW, oh = mo % OH, n = mo / OH;
+    const int64_t ih = (int64_t)oh * p.sh + (int64_t)kh * p.dh - p.pt, iw = (int64_t)ow * p.sw + (int64_t)kw * p.dw - p.pl;
+    uint4 v = make_uint4(fill, fill, fill, fill);
+    if (ih >= 0 && ih < p.H && iw >= 0 && iw < p.W)
+      v = __ldg(reinterpret_cast<const uint4*>(in + ((n * p.H + ih) * p.W + iw) * p.C + (int64_t)g * p.Cg + (int64_t)c16 * 16));
+    *reinterpret_cast<uint4*>(a + (int64_t)m * p.Kp + (int64_t)r * 16) = v;
+  }
+}
+
+// Batched int8 transpose: `batch` matrices [rows, cols] -> [cols, rows] (an image from channel-first to channel-last,
+// an output channel's taps from (ic, kh, kw) to (kh, kw, ic) order).
+__global__ void __launch_bounds__(256) conv_relay_i8_kernel(const int8_t* __restrict__ src, int64_t rows, int64_t cols,
+                                                            int8_t* __restrict__ dst) {
+  __shared__ int8_t tile[32][33];
+  const int64_t b = blockIdx.z, r0 = (int64_t)blockIdx.y * 32, c0 = (int64_t)blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  src += b * rows * cols;
+  dst += b * rows * cols;
+  for (int j = ty; j < 32; j += 8) {
+    const int64_t r = r0 + j, c = c0 + tx;
+    tile[j][tx] = (r < rows && c < cols) ? src[r * cols + c] : (int8_t)0;
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int64_t c = c0 + j, r = r0 + tx;
+    if (c < cols && r < rows) dst[c * rows + r] = tile[tx][j];
+  }
+}
+
 // Kernel rows of group g padded from Kg to Kp columns; the padding holds the kernel zero-point (its term vanishes).
 __global__ void __launch_bounds__(256) conv_pad_kernel_rows(const int8_t* __restrict__ ker, int64_t rows, int64_t Kg, int64_t Kp,
                                                             int zp_ker, int8_t* __restrict__ w) {
@@ -201,18 +242,43 @@ int launch_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker,
     B200Q_CHECK_CUDA(cudaMemsetAsync(out, 0, (size_t)M * O * sizeof(int32_t), ctx->stream));
     return 0;
   }
-  // gathered rows (int8), padded kernel rows (int8) when the tap count is not a multiple of 16, and the GEMM's result
-  // when it has to be re-laid (channel-first output, or groups)
-  const bool pad_w = p.Kp != p.Kg;
-  const bool direct_out = layout == 1 && groups == 1;
-  if (ws_reserve(ctx, ctx->ws_q, (size_t)M * p.Kp)) return 1;
-  if (pad_w && ws_reserve(ctx, ctx->ws_stage_in, (size_t)p.Og * p.Kp)) return 1;
+  // With a multiple of 16 channels per group the rows are gathered 16 bytes at a time from a channel-last input; a
+  // channel-first input (and its kernel tensor) is re-laid channel-last first, which costs one pass over each.
+  const bool out_nchw = layout == 0;
+  const bool fast = p.Cg % 16 == 0 && N <= 65535 && O <= 65535;
+  const bool relay = fast && layout == 0;
+  const bool pad_w = p.Kp != p.Kg;                 // never with `fast`
+  const bool direct_out = !out_nchw && groups == 1;
+  // workspaces: gathered rows (int8); the re-laid input and kernel, or the padded kernel rows of a group (int8);
+  // the GEMM's result when it has to be re-laid (channel-first output, or groups)
+  const bool aligned = relay || (reinterpret_cast<uintptr_t>(in) & 15u) == 0;   // 16-byte loads of the fast gather
+  // A pointwise layer over a channel-last input with one group IS the row matrix: nothing to gather.
+  const bool pointwise = fast && aligned && groups == 1 && KH == 1 && KW == 1 && sh == 1 && sw == 1 && pt == 0 && pb == 0 && pl == 0 && pr == 0;
+  if (!pointwise && ws_reserve(ctx, ctx->ws_q, (size_t)M * p.Kp)) return 1;
+  if (relay && ws_reserve(ctx, ctx->ws_stage_out, (size_t)N * C * H * W)) return 1;
+  if ((relay || pad_w) && ws_reserve(ctx, ctx->ws_stage_in, relay ? (size_t)O * p.Kg : (size_t)p.Og * p.Kp)) return 1;
   if (!direct_out && ws_reserve(ctx, ctx->ws_acc, (size_t)M * p.Og * sizeof(int32_t))) return 1;
   int8_t* a = (int8_t*)ctx->ws_q.ptr;
+  if (relay) {
+    ProfScope prof(ctx, KK_WEIGHTS);
+    const int64_t HW = H * W, taps = KH * KW;
+    dim3 gi((unsigned)((HW + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)N);
+    conv_relay_i8_kernel<<<gi, 256, 0, ctx->stream>>>(in, C, HW, (int8_t*)ctx->ws_stage_out.ptr);
+    dim3 gk((unsigned)((taps + 31) / 32), (unsigned)((p.Cg + 31) / 32), (unsigned)O);
+    conv_relay_i8_kernel<<<gk, 256, 0, ctx->stream>>>(ker, p.Cg, taps, (int8_t*)ctx->ws_stage_in.ptr);
+    ctx->launches += 2;
+    B200Q_CHECK_CUDA(cudaGetLastError());
+    in = (const int8_t*)ctx->ws_stage_out.ptr;
+    ker = (const int8_t*)ctx->ws_stage_in.ptr;
+    p.layout = 1;
+  }
   for (int g = 0; g < groups; g++) {
-    {
+    if (pointwise) {
+      a = const_cast<int8_t*>(in);
+    } else {
       ProfScope prof(ctx, KK_WEIGHTS);
-      conv_gather_kernel<<<flat_grid(ctx, M * (p.Kp / 16)), 256, 0, ctx->stream>>>(in, p, g, a);
+      if (fast && aligned) conv_gather_nhwc16_kernel<<<flat_grid(ctx, M * (p.Kp / 16)), 256, 0, ctx->stream>>>(in, p, g, a);
+      else conv_gather_kernel<<<flat_grid(ctx, M * (p.Kp / 16)), 256, 0, ctx->stream>>>(in, p, g, a);
       ctx->launches++;
     }
     const int8_t* w = ker + (int64_t)g * p.Og * p.Kg;
@@ -231,7 +297,7 @@ int launch_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker,
     }
     if (!direct_out) {
       ProfScope prof(ctx, KK_WEIGHTS);
-      if (layout == 0) {
+      if (out_nchw) {
         dim3 grid((unsigned)((P + 31) / 32), (unsigned)((p.Og + 31) / 32), (unsigned)N);
         conv_scatter_nchw_kernel<<<grid, 256, 0, ctx->stream>>>(c, P, p.Og, O, g, out);
       } else {

@@ -83,6 +83,9 @@ CONV_CASES = [
     (2, 32, 15, 13, 64, 3, 3, (2, 2), ((1, 1), (1, 1)), (1, 1), 4, 0, 0),        # groups on the tensor cores
     (1, 8, 6, 6, 4, 3, 3, (1, 1), ((0, 0), (0, 0)), (1, 1), 1, 0, 9),            # one zero-point: CUDA-core contraction
     (2, 64, 9, 9, 130, 5, 5, (1, 1), ((2, 2), (2, 2)), (1, 1), 1, 0, 0),         # 1600 taps, ragged channel count
+    (3, 48, 11, 7, 40, 1, 1, (1, 1), ((0, 0), (0, 0)), (1, 1), 1, 0, 0),         # pointwise: channel-last input is the row matrix itself
+    (2, 32, 8, 8, 16, 1, 1, (2, 2), ((0, 0), (0, 0)), (1, 1), 1, 0, 0),          # pointwise with a stride: gathered
+    (2, 32, 10, 9, 24, 3, 2, (1, 2), ((1, 2), (0, 1)), (2, 1), 2, 0, 0),         # 16 channels per group: the 16-byte gather with groups
 ]
 
 
