@@ -145,3 +145,15 @@ def test_c5_wide_projection_pair(ctx, orc):
     assert (dh.download()[rows] == hq_ref).all() and (dhs.download()[rows] == hs_ref).all()     # int8 codes through the chain
     y_ref = orc.epilogue(orc.qdot_i32(hq_ref, W2), hs_ref, ws2, None, "none")
     assert (dy.download()[rows].view(np.uint32) == y_ref.view(np.uint32)).all()
+    # every accumulator of both layers: the tensor-core kernel against the CUDA-core (dp4a) kernel on the same codes
+    for (a, w, n_out, k_in) in ((dq, dW1, N, K), (dh, dW2, K, N)):
+        acc_t, acc_s = ctx.empty((M, n_out), np.int32), ctx.empty((M, n_out), np.int32)
+        ctx.set_gemm_variant(0)
+        ctx.int8_gemm_i32(a, w, M, n_out, k_in, acc_t)
+        ctx.set_gemm_variant(1)
+        ctx.int8_gemm_i32(a, w, M, n_out, k_in, acc_s)
+        ctx.set_gemm_variant(0)
+        ctx.sync()
+        assert (acc_t.download() == acc_s.download()).all()
+        acc_t.free(); acc_s.free()
+    ctx.check_status()
