@@ -669,7 +669,9 @@ def run_e2e(ctx, comm, rank, world, local_rank, args, M, K, N, act, x_host, dW, 
     out["copy_bandwidth"] = {"h2d_gbs_per_rank": comm.all(h2d), "d2h_gbs_per_rank": comm.all(d2h),
                              "note": f"134 MB page-locked copies, one direction at a time, all {world} ranks copying at the same moment"}
 
-    # pageable buffers: the copies stage through the driver and no longer overlap
+    # pageable buffers: staged through the context's page-locked ring by its copy threads, in step with the transfers
+    host_threads = max(1, min(8, (os.cpu_count() or 2) // (2 * world)))
+    ctx.set_host_threads(host_threads)
     px = np.array(x_host, dtype=np.float32, copy=True)
     py = np.empty((M, N), np.float32)
     dt_pageable = timed(px, py)
@@ -697,7 +699,9 @@ def run_e2e(ctx, comm, rank, world, local_rank, args, M, K, N, act, x_host, dW, 
                   "numa": {**{k: v for k, v in numa.items() if k != "gpu"}, **bound}}
     out["e2e_pageable"] = {"value": world * M / dt_pageable, "unit": "tokens/s", "ms_per_step": dt_pageable * 1e3, "steps": e2e_steps,
                            "same_result_as_page_locked": same_pageable,
-                           "api": "b200q_linear_f32_host with ordinary (pageable) numpy arrays, as a caller holding typed arrays would pass"}
+                           "host_threads": host_threads,
+                           "api": "b200q_linear_f32_host with ordinary (pageable) numpy arrays, as a caller holding typed arrays would pass: "
+                                  "row blocks staged through a page-locked ring by the context's copy threads"}
     return out
 
 

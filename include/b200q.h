@@ -63,6 +63,9 @@ int b200q_set_tail_mode(b200q_ctx* ctx, int mode);
  * (gelu_sigmoid, silu) when the contraction is short (K <= 1024: the tail, not the tensor pipe, sets the pace there),
  * eight otherwise; 8 or 16 = always that many.  Same results either way. */
 int b200q_set_epilogue_warps(b200q_ctx* ctx, int warps);
+/* Host threads (the caller's included) that stage pageable arrays of the host-buffer entry points through page-locked
+ * memory: 0 (default) = half the host's cores, at most 8; takes effect before the first such call of the context. */
+int b200q_set_host_threads(b200q_ctx* ctx, int threads);
 /* b200q_int8_linear_requant_token and the column-sharded group call: 0 (default) = the GEMM's epilogue publishes every
  * output row's range while the values are in its registers and a one-pass kernel turns the f32 result into codes;
  * 1 = the f32 result goes through the complete per-token quantize (range pass + encode).  Same codes. */
@@ -226,7 +229,10 @@ int b200q_linear_f32_noalloc(b200q_ctx* ctx, const float* x, const int8_t* W_nk,
                              int act, int64_t M, int64_t N, int64_t K, float* out);
 /* Same call with HOST activations and HOST result (what RuntimeModule.run hands a
  * backend: typed arrays, src/runtime/runtime.ts:239-268); weights stay on the device.
- * Copies both ways and synchronises. */
+ * Copies both ways and synchronises.  Row blocks are pipelined: one on its way in, one computing, one on its way out.
+ * Page-locked (cudaHostAlloc / cudaHostRegister) arrays go to the copy engines as they are; ordinary (pageable) arrays
+ * -- what a caller holding typed arrays has -- are staged block by block through a page-locked ring of the context
+ * (3 blocks per direction, allocated at the first such call) by a few host threads of the context. */
 int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_nk, const float* w_scales, const float* bias,
                           int act, int64_t M, int64_t N, int64_t K, float* out_host);
 /* Host-buffer round trip of the standalone ops: quantize_per_token then dequantize_per_token. */

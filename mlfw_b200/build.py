@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200q.so")
-SOURCES = ["api.cu", "quant_kernels.cu", "gemm_simt.cu", "gemm_umma.cu", "block_kernels.cu", "attention_umma.cu", "noalloc.cu", "group.cu", "conv_group.cu"]
+SOURCES = ["api.cu", "quant_kernels.cu", "gemm_simt.cu", "gemm_umma.cu", "block_kernels.cu", "attention_umma.cu", "noalloc.cu", "group.cu", "conv_group.cu", "host_stage.cu"]
 HEADERS = ["common.cuh", "kernels.cuh", "quant_math.cuh", "exp2_table.inc", "exp_ff_table.inc", os.path.join("..", "..", "include", "b200q.h")]
 
 

@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstring>
 #include <new>
+#include <thread>
 
 #include "../../include/b200q.h"
 #include <limits>
@@ -179,7 +180,11 @@ void b200q_destroy(b200q_ctx* ctx) {
   for (int i = 0; i < HOST_CHUNKS; i++) {
     if (ctx->ev_in[i]) cudaEventDestroy(ctx->ev_in[i]);
     if (ctx->ev_done[i]) cudaEventDestroy(ctx->ev_done[i]);
+    if (ctx->ev_out[i]) cudaEventDestroy(ctx->ev_out[i]);
   }
+  host_stager_destroy(ctx->stager);
+  if (ctx->pin_in) cudaFreeHost(ctx->pin_in);
+  if (ctx->pin_out) cudaFreeHost(ctx->pin_out);
   if (ctx->ev_free) cudaEventDestroy(ctx->ev_free);
   if (ctx->stream_h2d) cudaStreamDestroy(ctx->stream_h2d);
   if (ctx->stream_d2h) cudaStreamDestroy(ctx->stream_d2h);
@@ -236,6 +241,14 @@ int b200q_set_gemm_variant(b200q_ctx* ctx, int variant) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
   B200Q_REQUIRE(variant >= 0 && variant <= 3, "b200q_set_gemm_variant: unknown variant %d", variant);
   ctx->gemm_variant = variant;
+  return 0;
+}
+
+int b200q_set_host_threads(b200q_ctx* ctx, int threads) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_REQUIRE(threads >= 0 && threads <= 64, "b200q_set_host_threads: %d is not between 0 and 64", threads);
+  B200Q_REQUIRE(ctx->stager == nullptr, "b200q_set_host_threads: the staging threads of this context already run");
+  ctx->host_threads = threads;
   return 0;
 }
 
@@ -592,6 +605,47 @@ int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const f
   return linear_core(ctx, q, s, W_nk, w_scales, bias, act, M, N, K, out, nullptr, 1.0);
 }
 
+// True when the copy engines can stream from / to the pointer directly: page-locked by cudaHostAlloc /
+// cudaHostRegister, or managed.  Ordinary malloc'ed memory reports cudaMemoryTypeUnregistered.
+static bool host_pointer_is_page_locked(const void* p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeHost || attr.type == cudaMemoryTypeManaged;
+}
+
+// The page-locked ring (HOST_SLOTS row blocks per direction that is staged) and the copy threads.
+static int host_staging_ready(b200q_ctx* ctx, size_t in_block, size_t out_block) {
+  if (!ctx->stager) {
+    int n = ctx->host_threads;
+    if (n <= 0) {
+      const unsigned hw = std::thread::hardware_concurrency();
+      n = hw >= 16 ? 8 : (hw >= 4 ? (int)hw / 2 : 1);
+    }
+    ctx->stager = host_stager_create(n);
+    B200Q_REQUIRE(ctx->stager != nullptr, "out of host memory for the staging threads");
+  }
+  if (in_block * HOST_SLOTS > ctx->pin_in_bytes) {
+    B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream_h2d));
+    if (ctx->pin_in) B200Q_CHECK_CUDA(cudaFreeHost(ctx->pin_in));
+    ctx->pin_in = nullptr;
+    ctx->pin_in_bytes = 0;
+    B200Q_CHECK_CUDA(cudaHostAlloc(&ctx->pin_in, in_block * HOST_SLOTS, cudaHostAllocDefault));
+    ctx->pin_in_bytes = in_block * HOST_SLOTS;
+  }
+  if (out_block * HOST_SLOTS > ctx->pin_out_bytes) {
+    B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream_d2h));
+    if (ctx->pin_out) B200Q_CHECK_CUDA(cudaFreeHost(ctx->pin_out));
+    ctx->pin_out = nullptr;
+    ctx->pin_out_bytes = 0;
+    B200Q_CHECK_CUDA(cudaHostAlloc(&ctx->pin_out, out_block * HOST_SLOTS, cudaHostAllocDefault));
+    ctx->pin_out_bytes = out_block * HOST_SLOTS;
+  }
+  return 0;
+}
+
 static int host_pipeline_ready(b200q_ctx* ctx) {
   if (ctx->stream_h2d) return 0;
   B200Q_CHECK_CUDA(cudaStreamCreateWithFlags(&ctx->stream_h2d, cudaStreamNonBlocking));
@@ -599,6 +653,7 @@ static int host_pipeline_ready(b200q_ctx* ctx) {
   for (int i = 0; i < HOST_CHUNKS; i++) {
     B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming));
     B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_done[i], cudaEventDisableTiming));
+    B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_out[i], cudaEventDisableTiming));
   }
   B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_free, cudaEventDisableTiming));
   return 0;
@@ -630,19 +685,53 @@ int b200q_linear_f32_host(b200q_ctx* ctx, const float* x_host, const int8_t* W_n
   B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_free, ctx->stream));
   B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream_h2d, ctx->ev_free, 0));
   B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream_d2h, ctx->ev_free, 0));
-  int c = 0;
-  for (int64_t m0 = 0; m0 < M; m0 += rows, c++) {
-    const int64_t mc = (M - m0 < rows) ? (M - m0) : rows;
-    B200Q_CHECK_CUDA(cudaMemcpyAsync(x + m0 * K, x_host + m0 * K, (size_t)mc * K * sizeof(float), cudaMemcpyHostToDevice,
-                                     ctx->stream_h2d));
+  // Ordinary (pageable) host arrays are staged through page-locked memory by the context's copy threads, row block by
+  // row block and in step with the transfers; page-locked (or registered) arrays are handed to the copy engines as
+  // they are.
+  const bool stage_in = !host_pointer_is_page_locked(x_host), stage_out = !host_pointer_is_page_locked(out_host);
+  const size_t in_block = (size_t)rows * K * sizeof(float), out_block = (size_t)rows * N * sizeof(float);
+  if (stage_in || stage_out) {
+    if (int e = host_staging_ready(ctx, stage_in ? in_block : 0, stage_out ? out_block : 0)) return e;
+  }
+  const int chunks = (int)((M + rows - 1) / rows);
+  constexpr int LAG = HOST_SLOTS - 1;     // a block's result is copied out this many blocks after the block went in
+  for (int c = 0; c < chunks + (stage_out ? LAG : 0); c++) {
+    const int64_t m0 = (int64_t)c * rows;
+    const int64_t mc = c < chunks ? ((M - m0 < rows) ? (M - m0) : rows) : 0;
+    const int slot = c % HOST_SLOTS;
+    // host copies of this turn: block c into the ring, block c - LAG out of it
+    void* in_dst = nullptr;
+    size_t in_n = 0;
+    if (stage_in && c < chunks) {
+      if (c >= HOST_SLOTS) B200Q_CHECK_CUDA(cudaEventSynchronize(ctx->ev_in[c - HOST_SLOTS]));   // the slot's last transfer has read it
+      in_dst = (char*)ctx->pin_in + (size_t)slot * in_block;
+      in_n = (size_t)mc * K * sizeof(float);
+    }
+    void* out_dst = nullptr;
+    const void* out_src = nullptr;
+    size_t out_n = 0;
+    if (stage_out && c >= LAG) {
+      const int d = c - LAG;
+      const int64_t d0 = (int64_t)d * rows, dc = (M - d0 < rows) ? (M - d0) : rows;
+      B200Q_CHECK_CUDA(cudaEventSynchronize(ctx->ev_out[d]));
+      out_dst = out_host + d0 * N;
+      out_src = (char*)ctx->pin_out + (size_t)(d % HOST_SLOTS) * out_block;
+      out_n = (size_t)dc * N * sizeof(float);
+    }
+    if (in_n || out_n) host_stager_copy2(ctx->stager, in_dst, x_host + m0 * K, in_n, out_dst, out_src, out_n);
+    if (c >= chunks) continue;
+    const void* h2d_src = stage_in ? in_dst : (const void*)(x_host + m0 * K);
+    B200Q_CHECK_CUDA(cudaMemcpyAsync(x + m0 * K, h2d_src, (size_t)mc * K * sizeof(float), cudaMemcpyHostToDevice, ctx->stream_h2d));
     B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_in[c], ctx->stream_h2d));
     B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_in[c], 0));
     if (int e = launch_quantize_per_token(ctx, x + m0 * K, mc, K, q + m0 * K, sc + m0, -127, 127)) return e;
     if (int e = linear_core(ctx, q + m0 * K, sc + m0, W_nk, w_scales, bias, act, mc, N, K, y + m0 * N, nullptr, 1.0)) return e;
     B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_done[c], ctx->stream));
     B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream_d2h, ctx->ev_done[c], 0));
-    B200Q_CHECK_CUDA(cudaMemcpyAsync(out_host + m0 * N, y + m0 * N, (size_t)mc * N * sizeof(float), cudaMemcpyDeviceToHost,
-                                     ctx->stream_d2h));
+    // (the slot of the ring this block's result lands in was copied out LAG blocks ago, before this point)
+    void* d2h_dst = stage_out ? (void*)((char*)ctx->pin_out + (size_t)slot * out_block) : (void*)(out_host + m0 * N);
+    B200Q_CHECK_CUDA(cudaMemcpyAsync(d2h_dst, y + m0 * N, (size_t)mc * N * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream_d2h));
+    B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_out[c], ctx->stream_d2h));
   }
   B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream_d2h));
   B200Q_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));

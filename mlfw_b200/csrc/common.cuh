@@ -47,6 +47,9 @@ enum KernelKind : int { KK_QUANT_TOKEN = 0, KK_DEQUANT_TOKEN, KK_QUANT_STATIC, K
 constexpr int PROFILE_RING = 256;
 constexpr int HOST_CHUNKS = 16;   // most pieces a host-buffer call is split into
 
+struct HostStager;
+constexpr int HOST_SLOTS = 3;   // row blocks of the page-locked staging ring per direction
+
 struct Workspace {
   void* ptr = nullptr;
   size_t bytes = 0;
@@ -63,6 +66,13 @@ struct b200q_ctx {
   // copy streams and events of the pipelined host-buffer entry points (created on first use)
   cudaStream_t stream_h2d = nullptr, stream_d2h = nullptr;
   cudaEvent_t ev_in[b200q::HOST_CHUNKS] = {}, ev_done[b200q::HOST_CHUNKS] = {}, ev_free = nullptr;
+  // pageable host buffers: a page-locked ring of HOST_SLOTS row blocks per direction and the threads that fill / drain it
+  cudaEvent_t ev_out[b200q::HOST_CHUNKS] = {};
+  void* pin_in = nullptr;
+  void* pin_out = nullptr;
+  size_t pin_in_bytes = 0, pin_out_bytes = 0;
+  b200q::HostStager* stager = nullptr;
+  int host_threads = 0;                  // threads of the stager (0: chosen at first use)
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
   uint32_t* status_dev = nullptr;        // device status word
   b200q::Workspace ws_q;                 // int8 activations of the fused linear

@@ -1,6 +1,7 @@
 // Launchers implemented by the kernel translation units; called by the C ABI (api.cu).
 // All of them enqueue on ctx->stream and return 0 or a non-zero code after set_error().
 #pragma once
+#include <cstddef>
 #include <cstdint>
 
 struct b200q_ctx;
@@ -74,6 +75,12 @@ int launch_dequantize_per_group(b200q_ctx* ctx, const int8_t* q, int64_t n, int6
 int launch_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker, int64_t N, int64_t C, int64_t H, int64_t W, int64_t O,
                             int64_t KH, int64_t KW, int sh, int sw, int pt, int pb, int pl, int pr, int dh, int dw, int groups,
                             int zp_in, int zp_ker, int layout, int32_t* out);
+
+// host_stage.cu: threads that copy between pageable host arrays and the page-locked staging ring.
+struct HostStager;
+HostStager* host_stager_create(int threads);
+void host_stager_destroy(HostStager* s);
+void host_stager_copy2(HostStager* s, void* d0, const void* s0, size_t n0, void* d1, const void* s1, size_t n1);
 
 // api.cu: linear + per-token requantization of its result (see the definition).
 int linear_requant_token_core(b200q_ctx* ctx, const int8_t* A, const float* a_scales, int a_pieces, const int8_t* W,

@@ -158,6 +158,10 @@ class Context:
         """0: exact sigmoid tails (default); 1: hardware exp / reciprocal for f32 outputs (within the 1e-5 bar, faster)."""
         check(self.lib.b200q_set_tail_mode(self.handle, mode), "b200q_set_tail_mode")
 
+    def set_host_threads(self, threads: int):
+        """Host threads that stage pageable arrays of the host-buffer entry points (0: half the cores, at most 8)."""
+        check(self.lib.b200q_set_host_threads(self.handle, threads), "b200q_set_host_threads")
+
     def set_epilogue_warps(self, warps: int):
         """Epilogue warps of the tensor-core GEMM for f32 output: 0 = sixteen for K <= 1024, eight otherwise (default); 8; 16."""
         check(self.lib.b200q_set_epilogue_warps(self.handle, warps), "b200q_set_epilogue_warps")

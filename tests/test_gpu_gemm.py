@@ -232,6 +232,35 @@ def test_linear_f32_whole_path(ctx, orc, M, N, K):
     assert (out_host.view(np.uint32) == ref.view(np.uint32)).all()
 
 
+@pytest.mark.parametrize("in_locked,out_locked", [(False, False), (True, False), (False, True), (True, True)])
+def test_linear_f32_host_pipelines_row_blocks(ctx, in_locked, out_locked, M=5000, N=384, K=256):
+    """Five row blocks through the host-buffer entry point: ordinary (pageable) arrays are staged through the context's
+    page-locked ring by its copy threads, page-locked arrays go to the copy engines directly; every combination gives
+    the device path's bits, twice in a row (the ring and its events are reused)."""
+    rng = np.random.default_rng(77)
+    x, W, ws, bias = linear_case(rng, M, N, K)
+    dx, dW, dws, db = ctx.to_device(x), ctx.to_device(W), ctx.to_device(ws), ctx.to_device(bias)
+    dout = ctx.empty((M, N), np.float32)
+    ctx.linear_f32(dx, dW, dws, db, "gelu_sigmoid", M, N, K, dout)
+    ctx.sync()
+    ref = dout.download()
+    hx = ctx.pinned((M, K), np.float32) if in_locked else None
+    hy = ctx.pinned((M, N), np.float32) if out_locked else None
+    xin = hx if in_locked else x.copy()
+    if in_locked:
+        hx.array[...] = x
+    for _ in range(2):
+        out = hy if out_locked else np.full((M, N), np.nan, np.float32)
+        if out_locked:
+            hy.array[...] = np.nan
+        ctx.linear_f32_host(xin, dW.ptr, dws.ptr, db.ptr, "gelu_sigmoid", M, N, K, out)
+        got = hy.array if out_locked else out
+        assert (got.view(np.uint32) == ref.view(np.uint32)).all()
+    for h in (hx, hy):
+        if h is not None:
+            h.free()
+
+
 def test_epilogue_separate_op(ctx, orc):
     """convert -> mul(scale vector) -> add(bias) -> activation as its own kernel (the reference's unfused chain)."""
     rng = np.random.default_rng(23)
