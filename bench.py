@@ -252,6 +252,20 @@ def run_conv_bench(ctx, pk, iters=20):
                 "gathered_bytes": N * HW * HW * ((C * KK * KK + 15) // 16 * 16)}
             for b in (dx, dk, do):
                 b.free()
+    # per-group INT4 codes of a weight the size of config 5's (8192 x 28672 f32 = 940 MB read, 235 MB of codes written)
+    n, G = 8192 * 28672, 128
+    dw = ctx.to_device(rng.standard_normal(n).astype(np.float32))
+    dq, ds = ctx.empty((n,), np.int8), ctx.empty((n // G,), np.float64)
+    ctx.quantize_per_group(dw, n, G, 4, dq, ds, None)
+    ctx.sync()
+    ctx.timer_start()
+    for _ in range(3):
+        ctx.quantize_per_group(dw, n, G, 4, dq, ds, None)
+    ms = ctx.timer_stop() / 3
+    out["per_group_int4_8192x28672_g128"] = {"ms": ms, "GBps": (5.0 * n + 8.0 * n / G) / (ms * 1e-3) / 1e9,
+                                             "frac": (5.0 * n + 8.0 * n / G) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+    for b in (dw, dq, ds):
+        b.free()
     ctx.check_status()
     return out
 

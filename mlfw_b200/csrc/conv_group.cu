@@ -34,19 +34,34 @@ __device__ __forceinline__ int quantize_exact_g(float x, double s, float qmin, f
 }
 
 // One warp per group at a time: |x| maximum with the reference's comparison (a > absMax: NaN never wins), the scale in
-// binary64 (absMax / bound, or 1e-10 when that is 0), then the codes.
+// binary64 (absMax / bound, or 1e-10 when that is 0), then the codes: x * fl32(1 / scale) rounded by the streaming
+// kernels' fast rule, and the exact binary64 division for every element the guard does not clear (near a tie, NaN,
+// infinite, a scale whose reciprocal is not a normal binary32 number).  VEC: the group size is a multiple of 4 and the
+// arrays are 16-byte aligned, so a lane moves four elements at a time.
+template <bool VEC>
 __global__ void __launch_bounds__(256) group_quantize_kernel(const float* __restrict__ x, int64_t n, int64_t group_size,
                                                              int64_t groups, double bound, float qmin, float qmax,
                                                              int8_t* __restrict__ q, double* __restrict__ scales64,
                                                              float* __restrict__ scales32) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const float limit = fminf(-qmin, qmax) + 0.49f;
   for (int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); g < groups; g += warps) {
     const int64_t start = g * group_size, end = (start + group_size < n) ? start + group_size : n;
     float am = 0.0f;
-    for (int64_t i = start + lane; i < end; i += 32) {
-      const float a = fabsf(x[i]);
-      if (a > am) am = a;
+    if (VEC) {
+      for (int64_t i = start + 4 * lane; i < end; i += 128) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(x + i));
+        const float a[4] = {fabsf(v.x), fabsf(v.y), fabsf(v.z), fabsf(v.w)};
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+          if (a[e] > am) am = a[e];
+      }
+    } else {
+      for (int64_t i = start + lane; i < end; i += 32) {
+        const float a = fabsf(x[i]);
+        if (a > am) am = a;
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -59,8 +74,28 @@ __global__ void __launch_bounds__(256) group_quantize_kernel(const float* __rest
       if (scales64) scales64[g] = s;
       if (scales32) scales32[g] = (float)s;
     }
-    if (q) {
-      for (int64_t i = start + lane; i < end; i += 32) q[i] = (int8_t)quantize_exact_g(x[i], s, qmin, qmax);
+    if (!q) continue;
+    const float inv = (float)(1.0 / s);
+    if (VEC) {
+      for (int64_t i = start + 4 * lane; i < end; i += 128) {       // the group was just read: these loads hit the cache
+        const float4 v = __ldg(reinterpret_cast<const float4*>(x + i));
+        const float xv[4] = {v.x, v.y, v.z, v.w};
+        int c[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          QuantGuard guard;
+          c[e] = quantize_fast(xv[e], inv, guard);
+          if (guard.unsafe(limit)) c[e] = quantize_exact_g(xv[e], s, qmin, qmax);
+        }
+        *reinterpret_cast<uint32_t*>(q + i) = pack_codes(c[0], c[1], c[2], c[3]);
+      }
+    } else {
+      for (int64_t i = start + lane; i < end; i += 32) {
+        QuantGuard guard;
+        int c = quantize_fast(x[i], inv, guard);
+        if (guard.unsafe(limit)) c = quantize_exact_g(x[i], s, qmin, qmax);
+        q[i] = (int8_t)c;
+      }
     }
   }
 }
@@ -117,19 +152,28 @@ __global__ void __launch_bounds__(256) conv_gather_kernel(const int8_t* __restri
 // The same rows when the input is channel-last and a group has a multiple of 16 channels: a 16-byte piece of a row is
 // 16 consecutive channels of one tap, i.e. one aligned 16-byte load (or the zero-point, outside the input).
 __global__ void __launch_bounds__(256) conv_gather_nhwc16_kernel(const int8_t* __restrict__ in, ConvGeom p, int g, int8_t* __restrict__ a) {
-  const uint32_t ppt = (uint32_t)(p.Cg / 16), pieces = (uint32_t)(p.Kp / 16);
-  const int64_t M = p.N * p.OH * p.OW, total = M * pieces, stride = (int64_t)gridDim.x * blockDim.x;
+  // One thread per (output position, 16-channel piece): the position is decoded once, the taps are a plain double loop.
+  const uint32_t ppt = (uint32_t)(p.Cg / 16);
+  const int64_t M = p.N * p.OH * p.OW, total = M * ppt, stride = (int64_t)gridDim.x * blockDim.x;
   const uint32_t fill = 0x01010101u * (uint32_t)(uint8_t)p.zp_in;
-  const uint32_t OW = (uint32_t)p.OW, OH = (uint32_t)p.OH, KW = (uint32_t)p.KW;
+  const uint32_t OW = (uint32_t)p.OW, OH = (uint32_t)p.OH;
+  const int KH = (int)p.KH, KW = (int)p.KW, H = (int)p.H, W = (int)p.W;
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
-    const uint32_t m = (uint32_t)(t / pieces), r = (uint32_t)(t - (int64_t)m * pieces);
-    const uint32_t tap = r / ppt, c16 = r - tap * ppt, kh = tap / KW, kw = tap - kh * KW;
+    const uint32_t m = (uint32_t)(t / ppt), c16 = (uint32_t)(t - (int64_t)m * ppt);
     const uint32_t ow = m % OW, mo = m / OW, oh = mo % OH, n = mo / OH;
-    const int64_t ih = (int64_t)oh * p.sh + (int64_t)kh * p.dh - p.pt, iw = (int64_t)ow * p.sw + (int64_t)kw * p.dw - p.pl;
-    uint4 v = make_uint4(fill, fill, fill, fill);
-    if (ih >= 0 && ih < p.H && iw >= 0 && iw < p.W)
-      v = __ldg(reinterpret_cast<const uint4*>(in + ((n * p.H + ih) * p.W + iw) * p.C + (int64_t)g * p.Cg + (int64_t)c16 * 16));
-    *reinterpret_cast<uint4*>(a + (int64_t)m * p.Kp + (int64_t)r * 16) = v;
+    const int8_t* src = in + (int64_t)n * H * W * p.C + (int64_t)g * p.Cg + (int64_t)c16 * 16;
+    int8_t* dst = a + (int64_t)m * p.Kp + (int64_t)c16 * 16;
+    const int ih0 = (int)oh * p.sh - p.pt, iw0 = (int)ow * p.sw - p.pl;
+    for (int kh = 0; kh < KH; kh++) {
+      const int ih = ih0 + kh * p.dh;
+      const bool row_in = ih >= 0 && ih < H;
+      for (int kw = 0; kw < KW; kw++) {
+        const int iw = iw0 + kw * p.dw;
+        uint4 v = make_uint4(fill, fill, fill, fill);
+        if (row_in && iw >= 0 && iw < W) v = __ldg(reinterpret_cast<const uint4*>(src + ((int64_t)ih * W + iw) * p.C));
+        *reinterpret_cast<uint4*>(dst + (int64_t)(kh * KW + kw) * p.Cg) = v;
+      }
+    }
   }
 }
 
@@ -208,7 +252,9 @@ int launch_quantize_per_group(b200q_ctx* ctx, const float* x, int64_t n, int64_t
   const float qmin = -(float)(1 << (num_bits - 1)), qmax = (float)((1 << (num_bits - 1)) - 1);
   int64_t blocks = (groups + 7) / 8, cap = (int64_t)ctx->sm_count * 8;
   if (blocks > cap) blocks = cap;
-  group_quantize_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, n, group_size, groups, bound, qmin, qmax, q, scales64, scales32);
+  const bool vec = group_size % 4 == 0 && n % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(q) & 3u) == 0;
+  if (vec) group_quantize_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, n, group_size, groups, bound, qmin, qmax, q, scales64, scales32);
+  else group_quantize_kernel<false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, n, group_size, groups, bound, qmin, qmax, q, scales64, scales32);
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -245,7 +291,7 @@ int launch_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker,
   // With a multiple of 16 channels per group the rows are gathered 16 bytes at a time from a channel-last input; a
   // channel-first input (and its kernel tensor) is re-laid channel-last first, which costs one pass over each.
   const bool out_nchw = layout == 0;
-  const bool fast = p.Cg % 16 == 0 && N <= 65535 && O <= 65535;
+  const bool fast = p.Cg % 16 == 0 && N <= 65535 && O <= 65535 && M < (int64_t(1) << 31) && H * W < (int64_t(1) << 31);
   const bool relay = fast && layout == 0;
   const bool pad_w = p.Kp != p.Kg;                 // never with `fast`
   const bool direct_out = !out_nchw && groups == 1;
@@ -277,7 +323,7 @@ int launch_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker,
       a = const_cast<int8_t*>(in);
     } else {
       ProfScope prof(ctx, KK_WEIGHTS);
-      if (fast && aligned) conv_gather_nhwc16_kernel<<<flat_grid(ctx, M * (p.Kp / 16)), 256, 0, ctx->stream>>>(in, p, g, a);
+      if (fast && aligned) conv_gather_nhwc16_kernel<<<flat_grid(ctx, M * (p.Cg / 16)), 256, 0, ctx->stream>>>(in, p, g, a);
       else conv_gather_kernel<<<flat_grid(ctx, M * (p.Kp / 16)), 256, 0, ctx->stream>>>(in, p, g, a);
       ctx->launches++;
     }
