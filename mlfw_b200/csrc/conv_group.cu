@@ -197,6 +197,31 @@ __global__ void __launch_bounds__(256) conv_relay_i8_kernel(const int8_t* __rest
   }
 }
 
+// The same transpose four bytes at a time, for matrices whose extents are multiples of 4 (an image of C x H*W): a 64x64
+// tile is read as words along the source rows and written as words along the destination rows.
+__global__ void __launch_bounds__(256) conv_relay_i8x4_kernel(const int8_t* __restrict__ src, int64_t rows, int64_t cols,
+                                                              int8_t* __restrict__ dst) {
+  __shared__ uint32_t tile[64][17];     // 64 source rows x 64 columns; the pad keeps a column of words on distinct banks
+  const int64_t b = blockIdx.z, r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 64;
+  src += b * rows * cols;
+  dst += b * rows * cols;
+  for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+    const int r = i >> 4, w = i & 15;
+    const int64_t rr = r0 + r, cc = c0 + 4 * w;
+    tile[r][w] = (rr < rows && cc < cols) ? __ldg(reinterpret_cast<const uint32_t*>(src + rr * cols + cc)) : 0u;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+    const int c = i >> 4, w = i & 15;                   // destination row c0 + c, bytes 4w .. 4w+3 = source rows 4w .. 4w+3
+    const int64_t cc = c0 + c, rr = r0 + 4 * w;
+    if (cc >= cols || rr >= rows) continue;
+    const int sh = (c & 3) * 8;
+    const uint32_t v = ((tile[4 * w][c >> 2] >> sh) & 0xffu) | (((tile[4 * w + 1][c >> 2] >> sh) & 0xffu) << 8) |
+                       (((tile[4 * w + 2][c >> 2] >> sh) & 0xffu) << 16) | (((tile[4 * w + 3][c >> 2] >> sh) & 0xffu) << 24);
+    *reinterpret_cast<uint32_t*>(dst + cc * rows + rr) = v;
+  }
+}
+
 // Kernel rows of group g padded from Kg to Kp columns; the padding holds the kernel zero-point (its term vanishes).
 __global__ void __launch_bounds__(256) conv_pad_kernel_rows(const int8_t* __restrict__ ker, int64_t rows, int64_t Kg, int64_t Kp,
                                                             int zp_ker, int8_t* __restrict__ w) {
@@ -308,8 +333,13 @@ int launch_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker,
   if (relay) {
     ProfScope prof(ctx, KK_WEIGHTS);
     const int64_t HW = H * W, taps = KH * KW;
-    dim3 gi((unsigned)((HW + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)N);
-    conv_relay_i8_kernel<<<gi, 256, 0, ctx->stream>>>(in, C, HW, (int8_t*)ctx->ws_stage_out.ptr);
+    if (HW % 4 == 0 && C % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 3u) == 0) {
+      dim3 gi((unsigned)((HW + 63) / 64), (unsigned)((C + 63) / 64), (unsigned)N);
+      conv_relay_i8x4_kernel<<<gi, 256, 0, ctx->stream>>>(in, C, HW, (int8_t*)ctx->ws_stage_out.ptr);
+    } else {
+      dim3 gi((unsigned)((HW + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)N);
+      conv_relay_i8_kernel<<<gi, 256, 0, ctx->stream>>>(in, C, HW, (int8_t*)ctx->ws_stage_out.ptr);
+    }
     dim3 gk((unsigned)((taps + 31) / 32), (unsigned)((p.Cg + 31) / 32), (unsigned)O);
     conv_relay_i8_kernel<<<gk, 256, 0, ctx->stream>>>(ker, p.Cg, taps, (int8_t*)ctx->ws_stage_in.ptr);
     ctx->launches += 2;
