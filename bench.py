@@ -1085,6 +1085,29 @@ def _run():
         line["step_samples_ms"] = {"n": len(samples), "median": med, "iqr": q3 - q1, "min": float(min(samples)), "max": float(max(samples)),
                                    "note": "CUDA events around single synchronised steps; the headline times all steps back to back"}
 
+        # -------------------------------------------------------- the same steps handed over as a queue of independent batches
+        # (b200q_linear_f32_many: the quantize of batch i+1 overlaps the GEMM of batch i on a second stream); same buffers,
+        # same number of steps, one call; the headline above stays the one-batch-per-call figure
+        n_b = args.steps
+        bx, bo = [dxs[i % 2] for i in range(n_b)], [douts[i % 2] for i in range(n_b)]
+        for _ in range(2):
+            ctx.linear_f32_many(bx, dW, dws, db, act, M, N, K, bo)
+        ctx.sync()
+        ref_bits = douts[0].download()[::509, ::127].copy()
+        step(0)
+        ctx.sync()
+        same = bool(np.array_equal(douts[0].download()[::509, ::127].view(np.uint32), ref_bits.view(np.uint32)))
+        barrier()
+        ctx.sync()
+        ctx.timer_start()
+        ctx.linear_f32_many(bx, dW, dws, db, act, M, N, K, bo)
+        ms_many = max_over_ranks(ctx.timer_stop())
+        barrier()
+        line["queued_batches"] = {"ms_per_step": ms_many / n_b, "tokens_per_s": world * M / (ms_many / n_b * 1e-3), "steps": n_b,
+                                  "tops": world * 2.0 * M * N * K / (ms_many / n_b * 1e-3) / 1e12, "same_result_as_one_batch_per_call": same,
+                                  "api": "b200q_linear_f32_many: one call for all steps, the per-token quantize of batch i+1 on a second stream "
+                                         "while the GEMM of batch i runs"}
+
         # -------------------------------------------------------- sustained regime (N = 1: a seconds-long stretch under the power cap)
         if world == 1:
             line["sustained"] = run_sustained(ctx, step, M, N, K, ms_per_step, local_rank)

@@ -227,6 +227,12 @@ int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const f
  * activation and shape class (M below / from 1024 rows; row length 8, 12, 16 KB or other) it is going to use. */
 int b200q_linear_f32_noalloc(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const float* w_scales, const float* bias,
                              int act, int64_t M, int64_t N, int64_t K, float* out);
+/* `count` independent batches x[i] [M,K] -> out[i] [M,N] through the same weights (a serving loop's queue; no
+ * counterpart in the reference, whose compiled function takes one batch per call): the per-token quantize of batch i+1
+ * runs on a second stream of the context while the GEMM of batch i holds the tensor cores.  Results are those of
+ * b200q_linear_f32, batch by batch.  x and out are host arrays of device pointers.  Stream-ordered like every call. */
+int b200q_linear_f32_many(b200q_ctx* ctx, int count, const float* const* x, const int8_t* W_nk, const float* w_scales,
+                          const float* bias, int act, int64_t M, int64_t N, int64_t K, float* const* out);
 /* Same call with HOST activations and HOST result (what RuntimeModule.run hands a
  * backend: typed arrays, src/runtime/runtime.ts:239-268); weights stay on the device.
  * Copies both ways and synchronises.  Row blocks are pipelined: one on its way in, one computing, one on its way out.

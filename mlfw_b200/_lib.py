@@ -65,6 +65,7 @@ PROTOTYPES = {
     "b200q_linear_f32": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_linear_f32_noalloc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_linear_f32_host": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
+    "b200q_linear_f32_many": (c_int, [c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_quant_roundtrip_host": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "b200q_observer_reset": (c_int, [c_vp, c_vp]),
     "b200q_observe_minmax": (c_int, [c_vp, c_vp, c_i64, c_vp]),

@@ -182,6 +182,15 @@ void b200q_destroy(b200q_ctx* ctx) {
     if (ctx->ev_done[i]) cudaEventDestroy(ctx->ev_done[i]);
     if (ctx->ev_out[i]) cudaEventDestroy(ctx->ev_out[i]);
   }
+  for (int i = 0; i < 2; i++) {
+    if (ctx->ev_codes[i]) cudaEventDestroy(ctx->ev_codes[i]);
+    if (ctx->ev_used[i]) cudaEventDestroy(ctx->ev_used[i]);
+  }
+  if (ctx->ev_entry) cudaEventDestroy(ctx->ev_entry);
+  if (ctx->stream_side) {
+    cudaStreamSynchronize(ctx->stream_side);
+    cudaStreamDestroy(ctx->stream_side);
+  }
   host_stager_destroy(ctx->stager);
   if (ctx->pin_in) cudaFreeHost(ctx->pin_in);
   if (ctx->pin_out) cudaFreeHost(ctx->pin_out);
@@ -603,6 +612,55 @@ int b200q_linear_f32(b200q_ctx* ctx, const float* x, const int8_t* W_nk, const f
   float* s = (float*)ctx->ws_scales.ptr;
   if (int e = launch_quantize_per_token(ctx, x, M, K, q, s, -127, 127)) return e;
   return linear_core(ctx, q, s, W_nk, w_scales, bias, act, M, N, K, out, nullptr, 1.0);
+}
+
+// Independent batches through the same linear, as a serving loop has them queued: the per-token quantize of batch i+1
+// runs on a second stream while the GEMM of batch i holds the tensor cores -- the quantize is bound by HBM, the GEMM is
+// not, and a quantize block fits beside the GEMM's one CTA per SM.  Two sets of codes and scales alternate; events order
+// quantize i before GEMM i and GEMM i before quantize i+2 (which reuses its codes).  Every batch gets the result of
+// b200q_linear_f32.  Stream-ordered like every other call: the work before it on the context's stream is waited for
+// (once, at entry), the work after it sees all results.
+int b200q_linear_f32_many(b200q_ctx* ctx, int count, const float* const* x, const int8_t* W_nk, const float* w_scales,
+                          const float* bias, int act, int64_t M, int64_t N, int64_t K, float* const* out) {
+  if (use_device(ctx)) return 1;
+  B200Q_NOT_CAPTURING(ctx, "b200q_linear_f32_many");
+  B200Q_REQUIRE(count >= 0, "b200q_linear_f32_many: negative batch count");
+  B200Q_REQUIRE(count == 0 || (x && out), "b200q_linear_f32_many: null array of batches");
+  for (int i = 0; i < count; i++)
+    if (int e = check_linear("b200q_linear_f32_many", x[i], W_nk, w_scales, act, M, N, K, out[i])) return e;
+  B200Q_REQUIRE(K > 0 || M == 0, "b200q_linear_f32_many: rows of zero length have no range");
+  if (count == 0 || M == 0 || N == 0) return 0;
+  if (count == 1) return b200q_linear_f32(ctx, x[0], W_nk, w_scales, bias, act, M, N, K, out[0]);
+  if (!ctx->stream_side) {
+    B200Q_CHECK_CUDA(cudaStreamCreateWithFlags(&ctx->stream_side, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; i++) {
+      B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_codes[i], cudaEventDisableTiming));
+      B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_used[i], cudaEventDisableTiming));
+    }
+    B200Q_CHECK_CUDA(cudaEventCreateWithFlags(&ctx->ev_entry, cudaEventDisableTiming));
+  }
+  const size_t codes = ((size_t)M * K + 255) & ~size_t(255);
+  if (ws_reserve(ctx, ctx->ws_q, 2 * codes)) return 1;
+  if (ws_reserve(ctx, ctx->ws_scales, (size_t)2 * M * sizeof(float))) return 1;
+  // the second stream starts after everything queued so far (the inputs' producers, the workspaces' allocation)
+  B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_entry, ctx->stream));
+  B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream_side, ctx->ev_entry, 0));
+  cudaStream_t main_stream = ctx->stream;
+  for (int i = 0; i < count; i++) {
+    const int slot = i & 1;
+    int8_t* q = (int8_t*)ctx->ws_q.ptr + (size_t)slot * codes;
+    float* sc = (float*)ctx->ws_scales.ptr + (size_t)slot * M;
+    if (i >= 2) B200Q_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream_side, ctx->ev_used[slot], 0));
+    ctx->stream = ctx->stream_side;                 // the launcher enqueues on the context's current stream
+    const int qe = launch_quantize_per_token(ctx, x[i], M, K, q, sc, -127, 127);
+    ctx->stream = main_stream;
+    if (qe) return qe;
+    B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_codes[slot], ctx->stream_side));
+    B200Q_CHECK_CUDA(cudaStreamWaitEvent(main_stream, ctx->ev_codes[slot], 0));
+    if (int e = linear_core(ctx, q, sc, W_nk, w_scales, bias, act, M, N, K, out[i], nullptr, 1.0)) return e;
+    B200Q_CHECK_CUDA(cudaEventRecord(ctx->ev_used[slot], main_stream));
+  }
+  return 0;
 }
 
 // True when the copy engines can stream from / to the pointer directly: page-locked by cudaHostAlloc /

@@ -73,6 +73,9 @@ struct b200q_ctx {
   size_t pin_in_bytes = 0, pin_out_bytes = 0;
   b200q::HostStager* stager = nullptr;
   int host_threads = 0;                  // threads of the stager (0: chosen at first use)
+  // b200q_linear_f32_many: the stream the quantize of the next batch runs on, and the events between the two streams
+  cudaStream_t stream_side = nullptr;
+  cudaEvent_t ev_codes[2] = {}, ev_used[2] = {}, ev_entry = nullptr;
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
   uint32_t* status_dev = nullptr;        // device status word
   b200q::Workspace ws_q;                 // int8 activations of the fused linear

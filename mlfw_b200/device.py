@@ -318,6 +318,16 @@ class Context:
                                                 _ptr(out)), "b200q_linear_f32_noalloc")
 
     # ---- ops (host buffers in and out; weights on the device)
+    def linear_f32_many(self, xs, W_nk, w_scales, bias, act, M, N, K, outs):
+        """Independent batches through one linear: the quantize of batch i+1 overlaps the GEMM of batch i."""
+        n = len(xs)
+        if len(outs) != n:
+            raise ValueError("one output per batch")
+        px = (C.c_void_p * n)(*[_ptr(v) for v in xs])
+        po = (C.c_void_p * n)(*[_ptr(v) for v in outs])
+        check(self.lib.b200q_linear_f32_many(self.handle, n, px, _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act], M, N, K, po),
+              "b200q_linear_f32_many")
+
     def linear_f32_host(self, x_host, W_nk, w_scales, bias, act, M, N, K, out_host):
         check(self.lib.b200q_linear_f32_host(self.handle, _ptr(x_host), _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act], M, N,
                                              K, _ptr(out_host)), "b200q_linear_f32_host")

@@ -65,6 +65,7 @@ function bind(path: string) {
     int8LinearF32RequantToken: f('int b200q_int8_linear_f32_requant_token(void *ctx, const void *A, const void *a_scales, const void *W_nk, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void *out_f32, void *out_q, void *out_scales)'),
     linearF32: f('int b200q_linear_f32(void *ctx, const void *x, const void *W_nk, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void *out)'),
     linearF32Noalloc: f('int b200q_linear_f32_noalloc(void *ctx, const void *x, const void *W_nk, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void *out)'),
+    linearF32Many: f('int b200q_linear_f32_many(void *ctx, int count, void **x, const void *W_nk, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void **out)'),
     linearF32Host: f('int b200q_linear_f32_host(void *ctx, const void *x_host, const void *W_nk, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void *out_host)'),
     quantRoundtripHost: f('int b200q_quant_roundtrip_host(void *ctx, const void *x_host, int64_t M, int64_t K, void *q_host, void *scales_host, void *y_host)'),
     observerReset: f('int b200q_observer_reset(void *ctx, void *state)'),

@@ -261,6 +261,32 @@ def test_linear_f32_host_pipelines_row_blocks(ctx, in_locked, out_locked, M=5000
             h.free()
 
 
+@pytest.mark.parametrize("count,M,N,K", [(1, 300, 256, 512), (2, 1100, 512, 256), (5, 2048, 768, 1024), (4, 70, 100, 48)])
+def test_linear_f32_many_equals_batch_by_batch(ctx, count, M, N, K):
+    """Independent batches with the quantize of the next one overlapping the GEMM of the current one (two streams, two
+    sets of codes): every batch has the bits of b200q_linear_f32, also when the call is repeated and followed by a plain one."""
+    rng = np.random.default_rng(count * 1000 + M)
+    _, W, ws, bias = linear_case(rng, M, N, K)
+    dW, dws, db = ctx.to_device(W), ctx.to_device(ws), ctx.to_device(bias)
+    xs = [activations(rng, M, K) for _ in range(count)]
+    dxs = [ctx.to_device(x) for x in xs]
+    refs = []
+    dref = ctx.empty((M, N), np.float32)
+    for dx in dxs:
+        ctx.linear_f32(dx, dW, dws, db, "silu", M, N, K, dref)
+        ctx.sync()
+        refs.append(dref.download())
+    outs = [Guarded(ctx, (M, N), np.float32) for _ in range(count)]
+    for _ in range(2):
+        ctx.linear_f32_many(dxs, dW, dws, db, "silu", M, N, K, [o.ptr for o in outs])
+        ctx.linear_f32(dxs[0], dW, dws, db, "silu", M, N, K, dref)      # queued right behind: reuses the first set of codes
+        ctx.sync()
+        for o, r in zip(outs, refs):
+            assert (o.download().view(np.uint32) == r.view(np.uint32)).all()
+        assert (dref.download().view(np.uint32) == refs[0].view(np.uint32)).all()
+    ctx.check_status()
+
+
 def test_epilogue_separate_op(ctx, orc):
     """convert -> mul(scale vector) -> add(bias) -> activation as its own kernel (the reference's unfused chain)."""
     rng = np.random.default_rng(23)
