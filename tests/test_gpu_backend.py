@@ -1,7 +1,7 @@
 """The reference-facing interface end to end on the GPU: graphs as the quantization pass emits them, compiled with
 compile_with_b200, run with typed arrays, checked against the CPU oracle's evaluation of the same graph.
 
-test_c1_mlp is BASELINE config 1: X f32 [256,512] ~ N(0,1), W1 [512,1024], W2 [1024,256] ~ N(0,0.02), biases
+test_c1_mlp is benchmark configuration 1: X f32 [256,512] ~ N(0,1), W1 [512,1024], W2 [1024,256] ~ N(0,0.02), biases
 ~ U(-0.1,0.1), per-output-channel int8 weights, ReLU between the layers, f32 [256,256] out, seed 0."""
 import numpy as np
 import pytest

@@ -1,4 +1,4 @@
-"""The BASELINE configurations at their full sizes on the GPU.
+"""The five benchmark configurations at their full sizes on the GPU.
 
 Where the CPU oracle cannot evaluate a whole tensor in seconds, rows are sampled: every output row of the path
 depends only on its own input row and the replicated weights, so the oracle's result for a subset of rows is the
@@ -52,7 +52,7 @@ def test_c2_roundtrip_16384x4096(ctx, orc):
 @pytest.mark.parametrize("act", ["gelu_tanh", "gelu_sigmoid"])
 def test_c3_gemm_8192x4096x4096(ctx, orc, act):
     """Config 3 in full: activations N(0,1) quantized per token, int8 weights uniform in [-127,127], per-channel scales
-    U(1e-3,1e-2), bias N(0,0.01), GELU epilogue (tanh as BASELINE words it, sigmoid as the reference implements it)."""
+    U(1e-3,1e-2), bias N(0,0.01), GELU epilogue (tanh as the benchmark definition words it, sigmoid as the reference implements it)."""
     M, K, N = 8192, 4096, 4096
     x = synth.normal(seed(0, 100), (M, K))
     W = synth.randint_i8(seed(0, 1), (N, K))
