@@ -6,7 +6,7 @@
 //     a CompiledKernel whose metadata.kind is 'b200' carries a native program (the step list planGraph makes, as
 //     JSON in `source`); instantiate() turns it into a plan bound to a device context, runSync() marshals the typed
 //     arrays it is given (arguments, then outputs, then constant buffers: runtime.ts:239-259) into the plan;
-//   * the eager dispatcher - three ops under DispatchKey.CUSTOM_1 (src/dispatcher/dispatcher.ts:81-86,
+//   * the eager dispatcher - four ops under DispatchKey.CUSTOM_1 (src/dispatcher/dispatcher.ts:81-86,
 //     library.ts:30-59; CUSTOM_1..3 are free, dispatch_key.ts:8-10), entered with withB200(() => ...), so that
 //     src/tensor users reach the kernels without a new device name (the device -> key table is a frozen literal,
 //     dispatch_key.ts:36-43).
@@ -68,6 +68,8 @@ const SCHEMAS = [
   'b200_quantize_per_token(Tensor x) -> (Tensor, Tensor)',                                   // codes i8 [M,K], scales f32 [M]
   'b200_dequantize_per_token(Tensor q, Tensor scales) -> Tensor',
   'b200_int8_linear(Tensor x, Tensor w_q, Tensor w_scales, Tensor bias, str activation) -> Tensor',   // f32 [M,K] x i8 [N,K] -> f32 [M,N]
+  // i8 [N,C,H,W] x i8 [O,C/groups,KH,KW] -> i32 [N,O,OH,OW] (quantized_conv, src/compiler/ir/graph/ops/quantization.ts:156-190)
+  'b200_quantized_conv2d(Tensor x, Tensor kernel, int[] strides, int[][] padding, int[] dilation, int groups, int zp_in, int zp_kernel) -> Tensor',
 ];
 
 function onDevice<T>(s: Session, hostArrays: ArrayBufferView[], outBytes: number[], run: (ins: unknown[], outs: unknown[]) => void,
@@ -118,6 +120,18 @@ function int8Linear(_ks: unknown, x: Tensor, wq: Tensor, wScales: Tensor, bias: 
     (o) => { const y = new Float32Array(M * N); check(s.b, s.b.download(s.ctx, y, o[0], y.byteLength), 'b200q_download'); return wrapResult(y, [M, N], 'f32', x.device); });
 }
 
+function quantizedConv2d(_ks: unknown, x: Tensor, ker: Tensor, strides: number[], padding: number[][], dilation: number[], groups: number,
+                         zpIn: number, zpKer: number): Tensor {
+  const s = b200Session();
+  const [N, C, H, W] = x.shape, [O, , KH, KW] = ker.shape;
+  const ext = (size: number, p: number[], k: number, st: number, d: number) => Math.floor((size + p[0] + p[1] - ((k - 1) * d + 1)) / st) + 1;   // ops/linalg.ts:236-246
+  const OH = ext(H, padding[0], KH, strides[0], dilation[0]), OW = ext(W, padding[1], KW, strides[1], dilation[1]);
+  return onDevice(s, [tensorToContiguous(x) as Int8Array, tensorToContiguous(ker) as Int8Array], [N * O * OH * OW * 4],
+    (i, o) => check(s.b, s.b.quantizedConv2d(s.ctx, i[0], i[1], N, C, H, W, O, KH, KW, strides[0], strides[1], padding[0][0], padding[0][1],
+                                             padding[1][0], padding[1][1], dilation[0], dilation[1], groups, zpIn, zpKer, 0, o[0]), 'b200q_quantized_conv2d'),
+    (o) => { const y = new Int32Array(N * O * OH * OW); check(s.b, s.b.download(s.ctx, y, o[0], y.byteLength), 'b200q_download'); return wrapResult(y, [N, O, OH, OW], 'i32', x.device); });
+}
+
 let eagerRegistered = false;
 export function registerB200EagerOps(): void {
   if (eagerRegistered) return;
@@ -127,7 +141,8 @@ export function registerB200EagerOps(): void {
   new Library('mlc', 'IMPL')
     .impl('b200_quantize_per_token', DispatchKey.CUSTOM_1, quantizePerToken)
     .impl('b200_dequantize_per_token', DispatchKey.CUSTOM_1, dequantizePerToken)
-    .impl('b200_int8_linear', DispatchKey.CUSTOM_1, int8Linear);
+    .impl('b200_int8_linear', DispatchKey.CUSTOM_1, int8Linear)
+    .impl('b200_quantized_conv2d', DispatchKey.CUSTOM_1, quantizedConv2d);
 }
 
 /** Runs fn with the CUSTOM_1 key included, so that dispatcher.callOp('b200_int8_linear', ...) reaches the kernels above. */
