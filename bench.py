@@ -423,10 +423,26 @@ def run_c5_records(ctx, comm, rank, world, steps, warmup, modes=("mshard", "nsha
     l0 = ctx.launch_count()
     chain(dx, M, ref_out)
     launches_per_step = ctx.launch_count() - l0
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0:
+        sampler.start()
     ms_unsharded = timed_steps(ctx, comm, lambda i: chain(dx, M, ref_out), steps, warmup)
+    clocks = sampler.stop() if rank == 0 else None
     ref_host = ref_out.download()
+    # the same steps once more with an event pair around every kernel: where the step's time goes
+    ctx.profile_enable(True)
+    ctx.profile_reset()
+    for _ in range(min(steps, 5)):
+        chain(dx, M, ref_out)
+    fam = ctx.profile_read()
+    ctx.profile_enable(False)
+    pk = peaks()
     records = {"unsharded_on_each_gpu": {"ms_per_step": ms_unsharded, "tokens_per_s": M / (ms_unsharded * 1e-3),
-                                         "tops": ops_total / (ms_unsharded * 1e-3) / 1e12, "gpu_launches_per_step": launches_per_step}}
+                                         "tops": ops_total / (ms_unsharded * 1e-3) / 1e12, "gpu_launches_per_step": launches_per_step,
+                                         "frac_of_int8_proxy_burst": ops_total / (ms_unsharded * 1e-3) / 1e12 / (2 * pk["bf16_tflops"]),
+                                         "frac_of_int8_proxy_sustained": ops_total / (ms_unsharded * 1e-3) / 1e12 / (2 * pk["bf16_tflops_sustained"]),
+                                         "kernel_ms_per_step": {k: v[0] / min(steps, 5) for k, v in fam.items()},
+                                         "clocks": clocks}}
 
     def record(ms, extra):
         return {"ms_per_step": ms, "tokens_per_s": M / (ms * 1e-3), "tops": ops_total / (ms * 1e-3) / 1e12,
