@@ -270,6 +270,56 @@ def run_conv_bench(ctx, pk, iters=20):
     return out
 
 
+def run_c1(ctx, iters=200):
+    """Config 1, the two-layer MLP (256 tokens, 512 -> 1024 -> 256, ReLU, per-token activation scales): weights prepared
+    on the device, then the forward pass as plain launches and as one recorded graph per pass."""
+    from mlfw_b200 import synth
+    M, D0, D1, D2 = 256, 512, 1024, 256
+    x = ctx.to_device(synth.normal(synth.tensor_seed(0, 0), (M, D0)))
+    layers = []
+    for (n, k, sw, sb) in ((D1, D0, 1, 2), (D2, D1, 3, 4)):
+        w = ctx.to_device(synth.normal(synth.tensor_seed(0, sw), (n, k), 0.0, 0.02))
+        qw, ws = ctx.empty((n, k), np.int8), ctx.empty((n,), np.float32)
+        ctx.quantize_weights_per_channel(w, n, k, 0, qw, ws)
+        layers.append((qw, ws, ctx.to_device(synth.uniform(synth.tensor_seed(0, sb), (n,), -0.1, 0.1))))
+    q0, s0 = ctx.empty((M, D0), np.int8), ctx.empty((M,), np.float32)
+    q1, s1 = ctx.empty((M, D1), np.int8), ctx.empty((M,), np.float32)
+    y = ctx.empty((M, D2), np.float32)
+
+    def forward():
+        ctx.quantize_per_token(x, M, D0, q0, s0)
+        ctx.int8_linear_requant_token(q0, s0, layers[0][0], layers[0][1], layers[0][2], "relu", M, D1, D0, q1, s1)
+        ctx.int8_linear(q1, s1, layers[1][0], layers[1][1], layers[1][2], "none", M, D2, D1, y)
+
+    l0 = ctx.launch_count()
+    for _ in range(5):
+        forward()
+    ctx.sync()
+    launches = (ctx.launch_count() - l0) // 5
+    ctx.timer_start()
+    for _ in range(iters):
+        forward()
+    ms_plain = ctx.timer_stop() / iters
+    ref = y.download()
+    ctx.graph_begin()
+    forward()
+    graph = ctx.graph_end()
+    for _ in range(5):
+        ctx.graph_launch(graph)
+    ctx.sync()
+    ctx.timer_start()
+    for _ in range(iters):
+        ctx.graph_launch(graph)
+    ms_graph = ctx.timer_stop() / iters
+    same = bool(np.array_equal(y.download().view(np.uint32), ref.view(np.uint32)))
+    ctx.graph_destroy(graph)
+    ctx.check_status()
+    best = min(ms_plain, ms_graph)
+    return {"workload": "c1_mlp_256x512x1024x256_relu", "ms_per_pass_plain_launches": ms_plain, "ms_per_pass_recorded_graph": ms_graph,
+            "tokens_per_s": M / (best * 1e-3), "gpu_launches_per_pass": launches, "graph_result_same_bits": same,
+            "bound_by": "launch latency: 0.67 GOP and 1.3 MB of traffic per pass"}
+
+
 def run_roundtrip(ctx, pk, iters, warmup):
     """Standalone quantize -> dequantize of f32 [16384,4096] with 0.1% outliers (HBM bound); per-kernel GB/s."""
     from mlfw_b200 import synth
@@ -1123,6 +1173,9 @@ def _run():
                                   "tops": world * 2.0 * M * N * K / (ms_many / n_b * 1e-3) / 1e12, "same_result_as_one_batch_per_call": same,
                                   "api": "b200q_linear_f32_many: one call for all steps, the per-token quantize of batch i+1 on a second stream "
                                          "while the GEMM of batch i runs"}
+
+        if world == 1:
+            line["c1_mlp"] = run_c1(ctx)
 
         # -------------------------------------------------------- sustained regime (N = 1: a seconds-long stretch under the power cap)
         if world == 1:
