@@ -159,7 +159,9 @@ int b200q_transpose_i8(b200q_ctx* ctx, const int8_t* w_kn, int64_t K, int64_t N,
 
 /* ------------------------------------------------- contraction and tail
  * quantized_dot (ops/quantization.ts:103-154; lowering rules/quantization.ts:23-42):
- * C[m,n] = sum_k (A[m,k]-zpA) * (W[n,k]-zpW), int32.  W is [N,K]. */
+ * C[m,n] = sum_k (A[m,k]-zpA) * (W[n,k]-zpW), int32.  W is [N,K].  Tensor cores when K is a multiple of 16 and the
+ * operands are 16-byte aligned -- with zero-points as the plain product plus the three correction terms
+ * (-zpW * sum_k A, -zpA * sum_k W, K * zpA * zpW; two row-sum launches and one pass over C) -- the CUDA cores otherwise. */
 int b200q_int8_gemm_i32(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA,
                         int zpW, int32_t* C);
 /* quantized_conv with two spatial dimensions (ops/quantization.ts:156-190; lowering rules/quantization.ts:44-62 over

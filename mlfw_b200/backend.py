@@ -115,7 +115,7 @@ def compile_with_b200(module: Dict[str, GraphFunction], config: dict) -> "B200Ru
 # ----------------------------------------------------------------------------- planning
 @dataclass
 class Step:
-    kind: str                       # 'quantize_static' | 'quantize_token' | 'dequantize_static' | 'linear' | 'conv' | 'const'
+    kind: str                       # 'quantize_static' | 'quantize_token' | 'dequantize_static' | 'linear' | 'dot' | 'conv' | 'const'
     ins: List[Value]
     out: Value
     params: Dict[str, Any]
@@ -216,8 +216,6 @@ class _Planner:
         w = _const_array(rhs)
         if w is None or rhs.dtype != "i8" or len(rhs.shape) != 2:
             raise B200CompileError("quantized_dot needs a constant rank-2 int8 rhs (weights cross the boundary as buffers)")
-        if op.attrs.get("lhs_zero_point", 0) or op.attrs.get("rhs_zero_point", 0):
-            raise B200CompileError("quantized_dot with zero-points is outside the symmetric north-star path")
         if op.attrs.get("lhs_batch") or op.attrs.get("rhs_batch"):
             raise B200CompileError("batched quantized_dot is not supported: flatten leading dimensions to M")
         rc = list(op.attrs.get("rhs_contracting", [0]))
@@ -228,6 +226,16 @@ class _Planner:
         K = rhs.shape[rc[0]]
         N = rhs.shape[1 - rc[0]]
         M = int(np.prod(lhs.shape[:-1]))      # leading dimensions flatten to rows (cublas_split.ts:84-90 does the same)
+        zp_a, zp_w = int(op.attrs.get("lhs_zero_point", 0) or 0), int(op.attrs.get("rhs_zero_point", 0) or 0)
+        if zp_a or zp_w:
+            # asymmetric operands (rules/quantization.ts:29-40 subtracts the zero-points tap by tap): the int32 contraction
+            # is a step of its own, the `dequantize` that follows stays a static step
+            if lhs.dtype != "i8":
+                raise B200CompileError("quantized_dot with zero-points takes int8 operands (ui8 is not supported)")
+            self.done.add(id(op))
+            self.steps.append(Step("dot", [lhs], op.result, {"M": M, "N": N, "K": K, "w": w.astype(np.int8), "w_layout": w_layout,
+                                                             "zp_a": zp_a, "zp_w": zp_w}))
+            return
         lhs_scale = float(op.attrs.get("lhs_scale", 1.0))
         absorbed = [op]
         y = op.result
@@ -402,7 +410,7 @@ def steps_from_program(program: dict):
         args.append(vals[a["id"]])
     steps = []
     for st in program["steps"]:
-        if st["kind"] not in ("quantize_static", "quantize_token", "dequantize_static", "linear", "conv", "const"):
+        if st["kind"] not in ("quantize_static", "quantize_token", "dequantize_static", "linear", "dot", "conv", "const"):
             raise B200CompileError(f"native program: unknown step '{st['kind']}'")
         o = st["out"]
         vals[o["id"]] = Value(tuple(o["shape"]), o["dtype"])
@@ -450,7 +458,7 @@ class _FunctionPlan:
                 self.scales[id(st.out)] = ctx.empty((st.params["M"],), np.float32)
             if st.kind == "const":
                 self.buf[id(st.out)].upload(np.ascontiguousarray(st.params["data"], NP_DTYPE[st.out.dtype]).reshape(st.out.shape if st.out.shape else (1,)))
-            if st.kind == "linear":
+            if st.kind in ("linear", "dot"):
                 p = st.params
                 w = p["w"]
                 if p["w_layout"] == W_KN:       # re-lay [K,N] constants as [N,K] once, on the device
@@ -462,8 +470,9 @@ class _FunctionPlan:
                     p["dW"] = dst
                 else:
                     p["dW"] = ctx.to_device(w)
-                p["dws"] = ctx.to_device(p["w_scales"])
-                p["db"] = ctx.to_device(p["bias"]) if p["bias"] is not None else None
+                if st.kind == "linear":
+                    p["dws"] = ctx.to_device(p["w_scales"])
+                    p["db"] = ctx.to_device(p["bias"]) if p["bias"] is not None else None
         missing = [r for r in func.returns if id(r) not in self.buf]
         if missing:
             raise B200CompileError("a returned value is not produced by any native step")
@@ -500,6 +509,8 @@ class _FunctionPlan:
             if st.kind == "conv":
                 ctx.quantized_conv2d(x, self.buf[id(st.ins[1])], p["shape"], p["kernel_shape"], out, p["strides"], p["padding"],
                                      p["dilation"], p["groups"], p["zp_in"], p["zp_ker"], p["layout"])
+            elif st.kind == "dot":
+                ctx.int8_gemm_i32(x, p["dW"], p["M"], p["N"], p["K"], out, p["zp_a"], p["zp_w"])
             elif st.kind == "quantize_static":
                 ctx.quantize_static(x, int(np.prod(st.ins[0].shape)), p["scale"], p["zero_point"], p["kind"], out)
             elif st.kind == "quantize_token":

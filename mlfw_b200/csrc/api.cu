@@ -69,6 +69,15 @@ static bool use_umma(b200q_ctx* ctx, const void* A, const void* W, int64_t M, in
 
 // quantized_dot + tail, any shape: tensor cores when possible, otherwise the CUDA-core
 // kernel into a workspace followed by the tail kernel.
+int gemm_i32_any(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB, int32_t* C) {
+  if (!use_umma(ctx, A, W_nk, M, N, K)) return launch_gemm_i8_simt(ctx, A, W_nk, M, N, K, zpA, zpB, C);
+  if (zpA == 0 && zpB == 0) return launch_gemm_i8_umma(ctx, A, W_nk, M, N, K, nullptr, nullptr, nullptr, 0, nullptr, C, nullptr, 1.0);
+  // zero-points: the plain product on the tensor cores, then the three correction terms
+  if (ws_reserve(ctx, ctx->ws_range, (size_t)(M + N) * sizeof(int32_t))) return 1;
+  if (int e = launch_gemm_i8_umma(ctx, A, W_nk, M, N, K, nullptr, nullptr, nullptr, 0, nullptr, C, nullptr, 1.0)) return e;
+  return launch_zero_point_fix(ctx, A, W_nk, M, N, K, zpA, zpB, (int32_t*)ctx->ws_range.ptr, C);
+}
+
 static int linear_core(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W, const float* w_scales,
                        const float* bias, int act, int64_t M, int64_t N, int64_t K, float* out_f32, int8_t* out_q,
                        double q_scale) {
@@ -483,9 +492,7 @@ int b200q_int8_gemm_i32(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
     B200Q_CHECK_CUDA(cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(int32_t), ctx->stream));
     return 0;
   }
-  if (zpA == 0 && zpW == 0 && use_umma(ctx, A, W_nk, M, N, K))
-    return launch_gemm_i8_umma(ctx, A, W_nk, M, N, K, nullptr, nullptr, nullptr, 0, nullptr, C, nullptr, 1.0);
-  return launch_gemm_i8_simt(ctx, A, W_nk, M, N, K, zpA, zpW, C);
+  return gemm_i32_any(ctx, A, W_nk, M, N, K, zpA, zpW, C);
 }
 
 int b200q_quantize_per_group(b200q_ctx* ctx, const float* x, int64_t n, int64_t group_size, int num_bits, int8_t* q,

@@ -8,7 +8,7 @@
 //
 // The convolution runs as a contraction: a gather kernel lays the receptive fields out as the rows of an int8 matrix
 // ([N*OH*OW, C/groups*KH*KW], padded to a multiple of 16 columns, padding taps holding the input zero-point so that
-// their term vanishes), the tensor-core GEMM (or the CUDA-core one when a zero-point is not 0) multiplies it with the
+// their term vanishes), the tensor-core GEMM (with the zero-point correction terms when a zero-point is not 0) multiplies it with the
 // kernel tensor read in place as [O, C/groups*KH*KW], and channel-first output is transposed out of the GEMM's
 // channel-last result.  Groups are handled one contraction per group.  With a multiple of 16 channels per group the
 // gather moves 16 bytes at a time from a channel-last input; a channel-first input and its kernel tensor are re-laid
@@ -366,11 +366,7 @@ int launch_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker,
     }
     B200Q_CHECK_CUDA(cudaGetLastError());
     int32_t* c = direct_out ? out : (int32_t*)ctx->ws_acc.ptr;
-    if (zp_in == 0 && zp_ker == 0 && ctx->gemm_variant != 1 && gemm_umma_supported(a, w, M, p.Og, p.Kp)) {
-      if (int e = launch_gemm_i8_umma(ctx, a, w, M, p.Og, p.Kp, nullptr, nullptr, nullptr, 0, nullptr, c, nullptr, 1.0)) return e;
-    } else if (int e = launch_gemm_i8_simt(ctx, a, w, M, p.Og, p.Kp, zp_in, zp_ker, c)) {
-      return e;
-    }
+    if (int e = gemm_i32_any(ctx, a, w, M, p.Og, p.Kp, zp_in, zp_ker, c)) return e;
     if (!direct_out) {
       ProfScope prof(ctx, KK_WEIGHTS);
       if (out_nchw) {

@@ -98,7 +98,61 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const int32_t* __restrict
   }
 }
 
+// Zero-points on the tensor cores: sum_k (a - za)(w - zw) = sum_k a w - zw * sum_k a - za * sum_k w + K za zw, all in
+// 32-bit two's-complement arithmetic like the accumulator itself.  Row sums of an int8 matrix, one warp per row:
+__global__ void __launch_bounds__(256) row_sum_i8_kernel(const int8_t* __restrict__ a, int64_t rows, int64_t K, int32_t* __restrict__ sums) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const bool vec = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15u) == 0);
+  for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const int8_t* row = a + r * K;
+    int s = 0;
+    if (vec) {
+      for (int64_t k = 16 * lane; k < K; k += 512) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(row + k));
+        s = __dp4a((int)v.x, 0x01010101, s);
+        s = __dp4a((int)v.y, 0x01010101, s);
+        s = __dp4a((int)v.z, 0x01010101, s);
+        s = __dp4a((int)v.w, 0x01010101, s);
+      }
+    } else {
+      for (int64_t k = lane; k < K; k += 32) s += row[k];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) sums[r] = s;
+  }
+}
+
+// c[m,n] += K za zw - zw * row_a[m] - za * row_w[n]  (unsigned arithmetic: wraps like the reference's ToInt32 sum)
+__global__ void __launch_bounds__(256) zero_point_fix_kernel(int32_t* __restrict__ c, int64_t M, int64_t N, const int32_t* __restrict__ row_a,
+                                                             const int32_t* __restrict__ row_w, int za, int zw, uint32_t kzz) {
+  const int64_t total = M * N, stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t m = i / N, n = i - m * N;
+    c[i] = (int32_t)((uint32_t)c[i] + kzz - (uint32_t)zw * (uint32_t)row_a[m] - (uint32_t)za * (uint32_t)row_w[n]);
+  }
+}
+
 }  // namespace
+
+// `sums` receives M + N words (row sums of A, then of W); c is corrected in place.
+int launch_zero_point_fix(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,
+                          int32_t* sums, int32_t* C) {
+  ProfScope prof(ctx, KK_GEMM_SIMT);
+  if (M == 0 || N == 0) return 0;
+  const unsigned cap = (unsigned)ctx->sm_count * 8;
+  const int64_t ba = (M + 7) / 8, bw = (N + 7) / 8;
+  row_sum_i8_kernel<<<(unsigned)(ba < cap ? ba : cap), 256, 0, ctx->stream>>>(A, M, K, sums);
+  row_sum_i8_kernel<<<(unsigned)(bw < cap ? bw : cap), 256, 0, ctx->stream>>>(W_nk, N, K, sums + M);
+  int64_t blocks = (M * N + 255) / 256;
+  if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+  const uint32_t kzz = (uint32_t)K * (uint32_t)zpA * (uint32_t)zpB;
+  zero_point_fix_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(C, M, N, sums, sums + M, zpA, zpB, kzz);
+  ctx->launches += 3;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
 
 int launch_gemm_i8_simt(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,
                         int32_t* C) {

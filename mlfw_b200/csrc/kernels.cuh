@@ -36,6 +36,13 @@ int launch_minmax_observe(b200q_ctx* ctx, const float* x, int64_t n, float* stat
 
 int launch_gemm_i8_simt(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,
                         int32_t* C);
+// Turns the plain product sum_k a w in C into sum_k (a - zpA)(w - zpB): row sums of both operands and one pass over C.
+// `sums`: M + N words of scratch.
+int launch_zero_point_fix(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,
+                          int32_t* sums, int32_t* C);
+// int32 contraction with zero-points by whichever kernel takes the shape: the tensor cores (plus the zero-point
+// correction) when the operands are 16-byte aligned and K is a multiple of 16, the CUDA cores otherwise.
+int gemm_i32_any(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB, int32_t* C);
 // Exactly one of out_f32 / out_q is written (both may be given); out_q uses the static scale q_scale.
 int launch_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
                     const float* bias, int act, float* out_f32, int8_t* out_q, double q_scale);

@@ -7,6 +7,7 @@
 //   quantize · quantized_dot(constant i8 rhs) · convert · mul(broadcast_in_dim(constant f32[N]))
 //   [· add(broadcast(bias))] [· maximum(·,0) | x·sigmoid(1.702x) | x·sigmoid(x)] [· quantize]   -> one 'linear' step
 //   quantize(x) · quantize(kernel) · quantized_conv  -> 'conv' (int32; the `dequantize` after it is a step of its own)
+//   quantized_dot{zero-points} (asymmetric operands)  -> 'dot' (int32 on the tensor cores plus the zero-point terms)
 //   quantized_dot · dequantize{scale}                                                               -> 'linear' with a constant scale vector
 //   standalone quantize / dequantize                                                                 -> static steps
 // Anything else throws: the backend has no fallback.
@@ -28,6 +29,8 @@ type Step =
   | { kind: 'linear'; in: Value; out: Value; M: number; N: number; K: number; act: Act; dynamic: boolean;
       w: Int8Array; wIsKN: boolean; wScales: Float32Array; bias: Float32Array | null; requantScale: number | null;
       dW?: unknown; dWs?: unknown; dBias?: unknown }
+  // quantized_dot with zero-points (asymmetric operands): the int32 contraction alone; the `dequantize` after it is a static step
+  | { kind: 'dot'; in: Value; out: Value; M: number; N: number; K: number; w: Int8Array; wIsKN: boolean; zpA: number; zpW: number; dW?: unknown }
   // a constant that a native step reads as a buffer (a convolution's kernel, the f32 source of its `quantize`): uploaded once
   | { kind: 'const'; out: Value; data: ArrayBufferView }
   // quantized_conv (ops/quantization.ts:156-190): both operands are device buffers, the int32 result feeds a `dequantize`
@@ -117,9 +120,15 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
       const lhs = op.getOperand(0), rhs = op.getOperand(1);
       const w = constArray(rhs), rs = shapeOf(rhs), ls = shapeOf(lhs);
       if (!w || dtypeOf(rhs) !== 'i8' || rs.length !== 2) throw new Error('b200: quantized_dot needs a constant rank-2 int8 rhs');
-      if (op.getAttr<number>('lhs_zero_point') || op.getAttr<number>('rhs_zero_point')) throw new Error('b200: zero-points are outside the symmetric path');
       const rc = op.getAttr<number[]>('rhs_contracting') || [0];
       const K = rs[rc[0]], N = rs[1 - rc[0]], M = numel(ls.slice(0, -1));
+      const zpA = op.getAttr<number>('lhs_zero_point') || 0, zpW = op.getAttr<number>('rhs_zero_point') || 0;
+      if (zpA || zpW) {                                  // rules/quantization.ts:29-40 subtracts the zero-points tap by tap
+        if (dtypeOf(lhs) !== 'i8') throw new Error('b200: quantized_dot with zero-points takes int8 operands');
+        done.add(op);
+        steps.push({ kind: 'dot', in: lhs, out: op.getResult(0), M, N, K, w: Int8Array.from(w), wIsKN: rc[0] === 0, zpA, zpW });
+        continue;
+      }
       const lhsScale = op.getAttr<number>('lhs_scale') || 1;
       let y = op.getResult(0), sv: number[];
       done.add(op);
@@ -192,10 +201,12 @@ export function planGraph(module: GraphModule, options: B200Options, b: B200QBin
       if (st.kind === 'const') { buf.set(st.out, upload(st.data)); continue; }
       buf.set(st.out, alloc(bytesOf(st.out)));
       if (st.kind === 'quantize_token') tokScales.set(st.out, alloc(st.M * 4));
-      if (st.kind === 'linear') {                     // weights cross the boundary once, as buffers
+      if (st.kind === 'linear' || st.kind === 'dot') { // weights cross the boundary once, as buffers
         const raw = upload(st.w);
         if (st.wIsKN) { st.dW = alloc(st.w.byteLength); check(b, b.transposeI8(ctx, raw, st.K, st.N, st.dW), 'b200q_transpose_i8'); check(b, b.sync(ctx), 'b200q_sync'); check(b, b.free(ctx, raw), 'b200q_free'); }
         else st.dW = raw;
+      }
+      if (st.kind === 'linear') {
         st.dWs = upload(st.wScales);
         st.dBias = st.bias ? upload(st.bias) : null;
       }
@@ -210,6 +221,7 @@ export function planGraph(module: GraphModule, options: B200Options, b: B200QBin
           if (st.kind === 'const') continue;              // uploaded when the plan was built
           const x = buf.get(st.in), y = buf.get(st.out);
           if (st.kind === 'conv') runConv(bind, c, x, buf.get(st.ker), y, st);
+          else if (st.kind === 'dot') check(bind, bind.int8GemmI32(c, x, st.dW, st.M, st.N, st.K, st.zpA, st.zpW, y), 'b200q_int8_gemm_i32');
           else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, numel(shapeOf(st.in)), st.scale, st.zeroPoint, st.dst, y), 'b200q_quantize_static');
           else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, st.M, st.K, y, tokScales.get(st.out), -127, 127), 'b200q_quantize_per_token');
           else if (st.kind === 'dequantize_static') check(bind, bind.dequantizeStatic(c, x, st.src, numel(shapeOf(st.in)), st.scale, st.zeroPoint, y), 'b200q_dequantize_static');
@@ -254,6 +266,8 @@ export function programOf(f: GraphFunction, steps: Step[]): NativeProgram {
       w_layout: st.wIsKN ? 1 : 0, w: { ...b64(st.w), shape: st.wIsKN ? [st.K, st.N] : [st.N, st.K] }, w_scales: b64(st.wScales), bias: st.bias ? b64(st.bias) : null });
     else if (st.kind === 'quantize_token') Object.assign(params, { M: st.M, K: st.K });
     else if (st.kind === 'quantize_static') Object.assign(params, { scale: st.scale, zero_point: st.zeroPoint, kind: st.dst });
+    else if (st.kind === 'dot') Object.assign(params, { M: st.M, N: st.N, K: st.K, zp_a: st.zpA, zp_w: st.zpW, w_layout: st.wIsKN ? 1 : 0,
+      w: { ...b64(st.w), shape: st.wIsKN ? [st.K, st.N] : [st.N, st.K] } });
     else if (st.kind === 'const') return { kind: st.kind, ins: [], out: rec(st.out), params: { data: { ...b64(st.data), shape: shapeOf(st.out) } } };
     else if (st.kind === 'conv') {
       Object.assign(params, { shape: st.shape, kernel_shape: st.kernelShape, strides: st.strides, padding: st.padding, dilation: st.dilation,
@@ -279,10 +293,11 @@ export function planFromProgram(p: NativeProgram, b: B200QBinding, ctx: unknown)
     if (st.kind === 'const') { buf.set(st.out.id, upload(unb64(q.data, (x) => new Uint8Array(x))!)); return null; }
     buf.set(st.out.id, alloc(size(st.out)));
     if (st.kind === 'quantize_token') scales.set(st.out.id, alloc(q.M * 4));
-    if (st.kind !== 'linear') return null;
+    if (st.kind !== 'linear' && st.kind !== 'dot') return null;
     const w = unb64(q.w, (x) => new Int8Array(x))!;
     let dW = upload(w);
     if (q.w_layout === 1) { const t = alloc(w.byteLength); check(b, b.transposeI8(ctx, dW, q.K, q.N, t), 'b200q_transpose_i8'); check(b, b.sync(ctx), 'b200q_sync'); check(b, b.free(ctx, dW), 'b200q_free'); dW = t; }
+    if (st.kind === 'dot') return { dW, dWs: null, dBias: null };
     const bias = unb64(q.bias, (x) => new Float32Array(x));
     return { dW, dWs: upload(unb64(q.w_scales, (x) => new Float32Array(x))!), dBias: bias ? upload(bias) : null };
   });
@@ -295,6 +310,7 @@ export function planFromProgram(p: NativeProgram, b: B200QBinding, ctx: unknown)
         if (st.kind === 'const') return;
         const q = st.params as Record<string, any>, x = buf.get(st.ins[0]), y = buf.get(st.out.id), d = dev[i];
         if (st.kind === 'conv') runConv(bind, c, x, buf.get(st.ins[1]), y, { ...(q as ConvParams), kernelShape: q.kernel_shape, zpIn: q.zp_in, zpKer: q.zp_ker });
+        else if (st.kind === 'dot') check(bind, bind.int8GemmI32(c, x, d!.dW, q.M, q.N, q.K, q.zp_a, q.zp_w, y), 'b200q_int8_gemm_i32');
         else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, elems.get(st.ins[0])!, q.scale, q.zero_point, q.kind, y), 'b200q_quantize_static');
         else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, q.M, q.K, y, scales.get(st.out.id), -127, 127), 'b200q_quantize_per_token');
         else if (st.kind === 'dequantize_static') check(bind, bind.dequantizeStatic(c, x, q.kind, elems.get(st.ins[0])!, q.scale, q.zero_point, y), 'b200q_dequantize_static');

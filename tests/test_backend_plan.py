@@ -199,3 +199,30 @@ def test_conv_outside_the_contract_is_refused(orc):
     y = b.op("quantized_conv", [x, k], (1, 2, 4, 4), "i32", strides=[1, 1], padding=[[0, 0], [0, 0]], input_layout="NCHW", kernel_layout="HWIO")
     with pytest.raises(B200CompileError, match="layouts"):
         plan_function(b.ret(y), dynamic=False)
+
+
+def asymmetric_graph(orc, M=6, K=32, N=10):
+    """The per-tensor asymmetric form: quantize{zero_point}, quantized_dot{lhs_zero_point, rhs_zero_point} on constant
+    codes, dequantize{scale = lhs_scale * rhs_scale} (quantization_pass.ts:286-360 with an asymmetric scheme)."""
+    rng = np.random.default_rng(8)
+    a_scale, a_zp, w_scale, w_zp = 0.04, 7, 0.01, -3
+    wq = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    b = GraphBuilder("asym")
+    x = b.arg((M, K))
+    xq = b.op("quantize", [x], (M, K), "i8", scale=a_scale, zero_point=a_zp, scheme="per_tensor_asymmetric", target_dtype="i8")
+    wc = b.constant(wq.reshape(-1).tolist(), (K, N), "i8")
+    acc = b.op("quantized_dot", [xq, wc], (M, N), "i32", lhs_contracting=[1], rhs_contracting=[0], lhs_scale=a_scale, lhs_zero_point=a_zp,
+               rhs_scale=w_scale, rhs_zero_point=w_zp, output_scale=a_scale * w_scale, output_zero_point=0)
+    y = b.op("dequantize", [acc], (M, N), "f32", scale=a_scale * w_scale, zero_point=0)
+    return b.ret(y), {"wq": wq, "a_scale": a_scale, "a_zp": a_zp, "w_scale": w_scale, "w_zp": w_zp, "M": M, "K": K, "N": N}
+
+
+def test_zero_point_dot_is_a_step_of_its_own(orc):
+    import json
+    func, info = asymmetric_graph(orc)
+    steps = plan_function(func, dynamic=False)
+    assert [s.kind for s in steps] == ["quantize_static", "dot", "dequantize_static"]
+    assert steps[0].params["zero_point"] == 7 and steps[1].params["zp_a"] == 7 and steps[1].params["zp_w"] == -3
+    assert steps[1].out.dtype == "i32" and steps[2].params["kind"] == 2
+    args, returns, again = steps_from_program(json.loads(json.dumps(program_of(func.args, func.returns, steps))))
+    assert [s.kind for s in again] == [s.kind for s in steps] and (again[1].params["w"] == info["wq"]).all()

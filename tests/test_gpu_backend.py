@@ -147,3 +147,21 @@ def test_conv_pipeline_matches_the_reference_chain(orc, layout):
     again.run("conv", x, out2)
     assert (out2.view(np.uint32) == ref.view(np.uint32)).all()
     mod.release(); again.release()
+
+
+@pytest.mark.parametrize("M,K,N", [(6, 32, 10), (300, 512, 256)])
+def test_asymmetric_per_tensor_chain(orc, M, K, N):
+    """quantize{zp} -> quantized_dot{zps} -> dequantize through the target object (the larger shape goes through the
+    tensor cores plus the zero-point correction terms); every stage is the oracle's."""
+    from test_backend_plan import asymmetric_graph
+    func, info = asymmetric_graph(orc, M, K, N)
+    rng = np.random.default_rng(M)
+    x = (rng.standard_normal((M, K)) * 1.5).astype(np.float32)
+    mod = compile_with_b200({"asym": func}, {"target": B200Target()})
+    out = np.zeros((M, N), np.float32)
+    mod.run("asym", x, out)
+    xq = orc.quantize_static(x.reshape(-1), info["a_scale"], info["a_zp"]).reshape(M, K)
+    acc = orc.qdot_i32(xq, info["wq"], "KN", info["a_zp"], info["w_zp"])
+    ref = orc.dequantize_static(acc.reshape(-1), info["a_scale"] * info["w_scale"]).reshape(M, N)
+    assert (out.view(np.uint32) == ref.view(np.uint32)).all()
+    mod.release()

@@ -287,6 +287,26 @@ def test_linear_f32_many_equals_batch_by_batch(ctx, count, M, N, K):
     ctx.check_status()
 
 
+@pytest.mark.parametrize("M,N,K,za,zw", [(256, 512, 1024, 5, -9), (1100, 384, 4096, -128, 127), (129, 70, 48, 3, 0), (64, 64, 16, 0, -7)])
+def test_zero_points_on_the_tensor_cores(ctx, orc, M, N, K, za, zw):
+    """sum (a - za)(w - zw) as the plain tensor-core product plus the three correction terms equals the CUDA-core
+    kernel that subtracts tap by tap, and the oracle."""
+    rng = np.random.default_rng(M + K)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    dA, dW = ctx.to_device(A), ctx.to_device(W)
+    d0, d1 = Guarded(ctx, (M, N), np.int32), Guarded(ctx, (M, N), np.int32)
+    ctx.set_gemm_variant(0)
+    ctx.int8_gemm_i32(dA.ptr, dW.ptr, M, N, K, d0.ptr, za, zw)
+    ctx.set_gemm_variant(1)
+    ctx.int8_gemm_i32(dA.ptr, dW.ptr, M, N, K, d1.ptr, za, zw)
+    ctx.set_gemm_variant(0)
+    ctx.sync()
+    got = d0.download()
+    assert (got == d1.download()).all()
+    assert (got == orc.qdot_i32(A, W, "NK", za, zw)).all()
+
+
 def test_epilogue_separate_op(ctx, orc):
     """convert -> mul(scale vector) -> add(bias) -> activation as its own kernel (the reference's unfused chain)."""
     rng = np.random.default_rng(23)
