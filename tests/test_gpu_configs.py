@@ -102,6 +102,14 @@ def test_c4_gpt_block_linears(ctx, orc):
         ref, _, _, _ = orc.linear(x[rows], wq, wsc.astype(np.float32), bias, act)
         out = dout.download()
         assert (out[rows].view(np.uint32) == ref.view(np.uint32)).all(), name
+        # every output of the layer: the fused tensor-core path against the CUDA-core contraction + separate tail kernel
+        dout2 = ctx.empty((M, N), np.float32)
+        ctx.set_gemm_variant(1)
+        ctx.linear_f32(dx, dqw, dws, db, act, M, N, K, dout2)
+        ctx.set_gemm_variant(0)
+        ctx.sync()
+        assert (dout2.download().view(np.uint32) == out.view(np.uint32)).all(), name
+        dout2.free()
         # the float model is approximated to about a percent
         yf = x[rows].astype(np.float64) @ w.T.astype(np.float64) + bias
         if act == "none":
@@ -117,7 +125,14 @@ def test_c4_gpt_block_linears(ctx, orc):
     ctx.linear_f32(h_dev, dqw2, dws2, db2, "none", M, D, F, dy)
     ctx.sync()
     ref, _, _, _ = orc.linear(h_host[rows], dqw2.download(), dws2.download(), b2, "none")
-    assert (dy.download()[rows].view(np.uint32) == ref.view(np.uint32)).all()
+    y_host = dy.download()
+    assert (y_host[rows].view(np.uint32) == ref.view(np.uint32)).all()
+    dy2 = ctx.empty((M, D), np.float32)
+    ctx.set_gemm_variant(1)
+    ctx.linear_f32(h_dev, dqw2, dws2, db2, "none", M, D, F, dy2)
+    ctx.set_gemm_variant(0)
+    ctx.sync()
+    assert (dy2.download().view(np.uint32) == y_host.view(np.uint32)).all()
 
 
 def test_c5_wide_projection_pair(ctx, orc):
