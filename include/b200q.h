@@ -180,6 +180,10 @@ int b200q_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker, 
                            int64_t O, int64_t KH, int64_t KW, int stride_h, int stride_w, int pad_top, int pad_bottom,
                            int pad_left, int pad_right, int dil_h, int dil_w, int groups, int zp_in, int zp_ker, int layout,
                            int32_t* out);
+/* ui8 operands of quantized_dot / quantized_conv (QUANTIZED_INT_DTYPES, ops/quantization.ts:8,146-151): dst[i] = src[i] - 128
+ * as int8 (src may equal dst).  u - zp == (u - 128) - (zp - 128), so the contraction entry points take the shifted
+ * codes with the zero-point moved by 128 and give the reference's sums. */
+int b200q_shift_u8_to_i8(b200q_ctx* ctx, const uint8_t* src, int64_t n, int8_t* dst);
 /* The per-channel tail as separate ops (quantization_pass.ts:427-456, nn/functional/linear.ts:13-15):
  * out = act(fround(fround(acc * sv) + bias[n])) with sv = fround(a_scales[m] * w_scales[n]),
  * or sv = w_scales[n] when a_scales is null (static activation scale folded by the host). */

@@ -55,6 +55,7 @@ PROTOTYPES = {
     "b200q_quantize_per_group": (c_int, [c_vp, c_vp, c_i64, c_i64, c_int, c_vp, c_vp, c_vp]),
     "b200q_dequantize_per_group": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "b200q_quantized_conv2d": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 7 + [c_int] * 12 + [c_vp]),
+    "b200q_shift_u8_to_i8": (c_int, [c_vp, c_vp, c_i64, c_vp]),
     "b200q_int8_gemm_i32": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_int, c_vp]),
     "b200q_epilogue": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_int, c_vp]),
     "b200q_int8_linear": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),

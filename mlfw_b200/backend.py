@@ -115,7 +115,7 @@ def compile_with_b200(module: Dict[str, GraphFunction], config: dict) -> "B200Ru
 # ----------------------------------------------------------------------------- planning
 @dataclass
 class Step:
-    kind: str                       # 'quantize_static' | 'quantize_token' | 'dequantize_static' | 'linear' | 'dot' | 'conv' | 'const'
+    kind: str                       # 'quantize_static' | 'quantize_token' | 'dequantize_static' | 'linear' | 'dot' | 'conv' | 'const' | 'shift'
     ins: List[Value]
     out: Value
     params: Dict[str, Any]
@@ -214,7 +214,7 @@ class _Planner:
     def plan_dot(self, op: Op):
         lhs, rhs = op.operands
         w = _const_array(rhs)
-        if w is None or rhs.dtype != "i8" or len(rhs.shape) != 2:
+        if w is None or rhs.dtype not in ("i8", "ui8") or len(rhs.shape) != 2:
             raise B200CompileError("quantized_dot needs a constant rank-2 int8 rhs (weights cross the boundary as buffers)")
         if op.attrs.get("lhs_batch") or op.attrs.get("rhs_batch"):
             raise B200CompileError("batched quantized_dot is not supported: flatten leading dimensions to M")
@@ -227,11 +227,16 @@ class _Planner:
         N = rhs.shape[1 - rc[0]]
         M = int(np.prod(lhs.shape[:-1]))      # leading dimensions flatten to rows (cublas_split.ts:84-90 does the same)
         zp_a, zp_w = int(op.attrs.get("lhs_zero_point", 0) or 0), int(op.attrs.get("rhs_zero_point", 0) or 0)
+        if rhs.dtype == "ui8":                 # constant ui8 codes: moved by 128 here, on the host
+            w, zp_w = w - 128, zp_w - 128
+        if lhs.dtype == "ui8":
+            zp_a -= 128
         if zp_a or zp_w:
             # asymmetric operands (rules/quantization.ts:29-40 subtracts the zero-points tap by tap): the int32 contraction
             # is a step of its own, the `dequantize` that follows stays a static step
-            if lhs.dtype != "i8":
-                raise B200CompileError("quantized_dot with zero-points takes int8 operands (ui8 is not supported)")
+            if self.single_user(op.result, "dequantize") is None:
+                raise B200CompileError("quantized_dot with zero-points (or ui8 operands) must be followed by dequantize")
+            lhs, _ = self.as_i8(lhs)
             self.done.add(id(op))
             self.steps.append(Step("dot", [lhs], op.result, {"M": M, "N": N, "K": K, "w": w.astype(np.int8), "w_layout": w_layout,
                                                              "zp_a": zp_a, "zp_w": zp_w}))
@@ -298,13 +303,23 @@ class _Planner:
             self.consts.add(id(v))
             self.steps.append(Step("const", [], v, {"data": np.ascontiguousarray(_const_array(v), NP_DTYPE[v.dtype])}))
 
+    def as_i8(self, v: Value):
+        """ui8 operands of a contraction: a 'shift' step turns them into int8 codes 128 lower; the caller moves the
+        zero-point by the returned amount (u - zp == (u - 128) - (zp - 128))."""
+        if v.dtype != "ui8":
+            return v, 0
+        self.materialize(v)
+        shifted = Value(v.shape, "i8")
+        self.steps.append(Step("shift", [v], shifted, {"n": int(np.prod(v.shape))}))
+        return shifted, 128
+
     def plan_conv(self, op: Op):
         """quantized_conv (ops/quantization.ts:156-190): both operands are device buffers (the pass quantizes input
         and kernel with `quantize` ops, tests/compiler/passes/quantization/pass.test.js:428-440); the int32 result is
         read by the `dequantize` that follows as a step of its own."""
         x, k = op.operands
-        if x.dtype != "i8" or k.dtype != "i8":
-            raise B200CompileError("quantized_conv takes int8 operands (ui8 is not supported by the convolution kernels)")
+        if x.dtype not in ("i8", "ui8") or k.dtype not in ("i8", "ui8"):
+            raise B200CompileError("quantized_conv takes i8 / ui8 operands")
         layouts = (op.attrs.get("input_layout", "NCHW"), op.attrs.get("kernel_layout", "OIHW"))
         if layouts not in (("NCHW", "OIHW"), ("NHWC", "OHWI")) or len(x.shape) != 4 or len(k.shape) != 4:
             raise B200CompileError("quantized_conv: two spatial dimensions, layouts NCHW / OIHW or NHWC / OHWI")
@@ -317,10 +332,12 @@ class _Planner:
             (N, H, W, C), (O, KH, KW, _) = x.shape, k.shape
         self.materialize(x)
         self.materialize(k)
+        x, sx = self.as_i8(x)
+        k, sk = self.as_i8(k)
         self.steps.append(Step("conv", [x, k], op.result, {
             "shape": [N, C, H, W], "kernel_shape": [O, KH, KW], "strides": strides, "padding": padding, "dilation": dilation,
-            "groups": int(op.attrs.get("groups") or 1), "zp_in": int(op.attrs.get("input_zero_point", 0) or 0),
-            "zp_ker": int(op.attrs.get("kernel_zero_point", 0) or 0), "layout": layouts[0]}))
+            "groups": int(op.attrs.get("groups") or 1), "zp_in": int(op.attrs.get("input_zero_point", 0) or 0) - sx,
+            "zp_ker": int(op.attrs.get("kernel_zero_point", 0) or 0) - sk, "layout": layouts[0]}))
 
     def plan(self) -> List[Step]:
         for op in self.f.ops:
@@ -410,7 +427,7 @@ def steps_from_program(program: dict):
         args.append(vals[a["id"]])
     steps = []
     for st in program["steps"]:
-        if st["kind"] not in ("quantize_static", "quantize_token", "dequantize_static", "linear", "dot", "conv", "const"):
+        if st["kind"] not in ("quantize_static", "quantize_token", "dequantize_static", "linear", "dot", "conv", "const", "shift"):
             raise B200CompileError(f"native program: unknown step '{st['kind']}'")
         o = st["out"]
         vals[o["id"]] = Value(tuple(o["shape"]), o["dtype"])
@@ -506,7 +523,9 @@ class _FunctionPlan:
             x = self.buf[id(st.ins[0])]
             out = self.buf[id(st.out)]
             p = st.params
-            if st.kind == "conv":
+            if st.kind == "shift":
+                ctx.shift_u8_to_i8(x, p["n"], out)
+            elif st.kind == "conv":
                 ctx.quantized_conv2d(x, self.buf[id(st.ins[1])], p["shape"], p["kernel_shape"], out, p["strides"], p["padding"],
                                      p["dilation"], p["groups"], p["zp_in"], p["zp_ker"], p["layout"])
             elif st.kind == "dot":

@@ -539,6 +539,12 @@ int b200q_quantized_conv2d(b200q_ctx* ctx, const int8_t* in, const int8_t* ker, 
                                  dil_h, dil_w, groups, zp_in, zp_ker, layout, out);
 }
 
+int b200q_shift_u8_to_i8(b200q_ctx* ctx, const uint8_t* src, int64_t n, int8_t* dst) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(n >= 0 && (n == 0 || (src && dst)), "b200q_shift_u8_to_i8: bad length or null pointer");
+  return launch_shift_u8_i8(ctx, src, n, dst);
+}
+
 int b200q_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
                    const float* bias, int act, float* out) {
   if (use_device(ctx)) return 1;

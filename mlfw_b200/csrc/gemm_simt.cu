@@ -134,7 +134,32 @@ __global__ void __launch_bounds__(256) zero_point_fix_kernel(int32_t* __restrict
   }
 }
 
+// ui8 codes as int8 codes 128 lower (one bit flipped): u - zp == (u - 128) - (zp - 128), so an unsigned operand of a
+// contraction is the signed one with its zero-point moved by 128.
+__global__ void __launch_bounds__(256) shift_u8_i8_kernel(const uint8_t* __restrict__ src, int64_t n, int8_t* __restrict__ dst) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x, tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+  const int64_t n16 = vec ? n / 16 : 0;
+  for (int64_t i = tid; i < n16; i += stride) {
+    uint4 v = __ldcs(reinterpret_cast<const uint4*>(src) + i);
+    v.x ^= 0x80808080u; v.y ^= 0x80808080u; v.z ^= 0x80808080u; v.w ^= 0x80808080u;
+    reinterpret_cast<uint4*>(dst)[i] = v;
+  }
+  for (int64_t i = n16 * 16 + tid; i < n; i += stride) dst[i] = (int8_t)(src[i] ^ 0x80u);
+}
+
 }  // namespace
+
+int launch_shift_u8_i8(b200q_ctx* ctx, const uint8_t* src, int64_t n, int8_t* dst) {
+  ProfScope prof(ctx, KK_QUANT_STATIC);
+  if (n == 0) return 0;
+  int64_t blocks = (n / 16 + 255) / 256 + 1;
+  if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+  shift_u8_i8_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(src, n, dst);
+  ctx->launches++;
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
 
 // `sums` receives M + N words (row sums of A, then of W); c is corrected in place.
 int launch_zero_point_fix(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,

@@ -36,6 +36,8 @@ int launch_minmax_observe(b200q_ctx* ctx, const float* x, int64_t n, float* stat
 
 int launch_gemm_i8_simt(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,
                         int32_t* C);
+// dst[i] = (int8)(src[i] - 128): an unsigned operand of a contraction becomes a signed one with its zero-point 128 lower.
+int launch_shift_u8_i8(b200q_ctx* ctx, const uint8_t* src, int64_t n, int8_t* dst);
 // Turns the plain product sum_k a w in C into sum_k (a - zpA)(w - zpB): row sums of both operands and one pass over C.
 // `sums`: M + N words of scratch.
 int launch_zero_point_fix(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB,

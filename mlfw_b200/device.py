@@ -275,6 +275,10 @@ class Context:
     def transpose_i8(self, w_kn, K, N, w_nk):
         check(self.lib.b200q_transpose_i8(self.handle, _ptr(w_kn), K, N, _ptr(w_nk)), "b200q_transpose_i8")
 
+    def shift_u8_to_i8(self, src, n, dst):
+        """dst = src - 128 as int8 (ui8 operands of the contractions: move the zero-point by 128 as well)."""
+        check(self.lib.b200q_shift_u8_to_i8(self.handle, _ptr(src), n, _ptr(dst)), "b200q_shift_u8_to_i8")
+
     def int8_gemm_i32(self, A, W_nk, M, N, K, out, zpA=0, zpW=0):
         check(self.lib.b200q_int8_gemm_i32(self.handle, _ptr(A), _ptr(W_nk), M, N, K, zpA, zpW, _ptr(out)),
               "b200q_int8_gemm_i32")

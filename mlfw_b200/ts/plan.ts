@@ -31,6 +31,8 @@ type Step =
       dW?: unknown; dWs?: unknown; dBias?: unknown }
   // quantized_dot with zero-points (asymmetric operands): the int32 contraction alone; the `dequantize` after it is a static step
   | { kind: 'dot'; in: Value; out: Value; M: number; N: number; K: number; w: Int8Array; wIsKN: boolean; zpA: number; zpW: number; dW?: unknown }
+  // a ui8 operand of a contraction as int8 codes 128 lower (the zero-point moves along: u - zp == (u - 128) - (zp - 128))
+  | { kind: 'shift'; in: Value; out: Value; n: number }
   // a constant that a native step reads as a buffer (a convolution's kernel, the f32 source of its `quantize`): uploaded once
   | { kind: 'const'; out: Value; data: ArrayBufferView }
   // quantized_conv (ops/quantization.ts:156-190): both operands are device buffers, the int32 result feeds a `dequantize`
@@ -101,6 +103,17 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
     consts.add(v);
     steps.push({ kind: 'const', out: v, data: TYPED[dtypeOf(v) as keyof typeof TYPED].from(a) });
   };
+  const shifted = new Map<Value, Value>();
+  const asI8 = (v: Value): [Value, number] => {         // shifted values are keyed by a stand-in object for the new buffer
+    if (dtypeOf(v) !== 'ui8') return [v, 0];
+    materialize(v);
+    if (!shifted.has(v)) {
+      const nv = { type: { shape: shapeOf(v), dtype: 'i8' } } as unknown as Value;
+      shifted.set(v, nv);
+      steps.push({ kind: 'shift', in: v, out: nv, n: numel(shapeOf(v)) });
+    }
+    return [shifted.get(v)!, 128];
+  };
   for (const op of f.ops()) {
     if (done.has(op)) continue;
     const n = op.opName;
@@ -119,14 +132,19 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
     } else if (n === 'quantized_dot') {
       const lhs = op.getOperand(0), rhs = op.getOperand(1);
       const w = constArray(rhs), rs = shapeOf(rhs), ls = shapeOf(lhs);
-      if (!w || dtypeOf(rhs) !== 'i8' || rs.length !== 2) throw new Error('b200: quantized_dot needs a constant rank-2 int8 rhs');
+      if (!w || (dtypeOf(rhs) !== 'i8' && dtypeOf(rhs) !== 'ui8') || rs.length !== 2) throw new Error('b200: quantized_dot needs a constant rank-2 int8 rhs');
       const rc = op.getAttr<number[]>('rhs_contracting') || [0];
       const K = rs[rc[0]], N = rs[1 - rc[0]], M = numel(ls.slice(0, -1));
-      const zpA = op.getAttr<number>('lhs_zero_point') || 0, zpW = op.getAttr<number>('rhs_zero_point') || 0;
+      let zpA = op.getAttr<number>('lhs_zero_point') || 0, zpW = op.getAttr<number>('rhs_zero_point') || 0;
+      const wI8 = dtypeOf(rhs) === 'ui8' ? w.map((v) => v - 128) : w;       // constant ui8 codes: moved by 128 here, on the host
+      if (dtypeOf(rhs) === 'ui8') zpW -= 128;
+      if (dtypeOf(lhs) === 'ui8') zpA -= 128;
       if (zpA || zpW) {                                  // rules/quantization.ts:29-40 subtracts the zero-points tap by tap
-        if (dtypeOf(lhs) !== 'i8') throw new Error('b200: quantized_dot with zero-points takes int8 operands');
+        const nx = users(f, op.getResult(0), done).filter((u) => u !== op);
+        if (nx.length !== 1 || nx[0].opName !== 'dequantize') throw new Error('b200: quantized_dot with zero-points (or ui8 operands) must be followed by dequantize');
+        const [lhsI8] = asI8(lhs);
         done.add(op);
-        steps.push({ kind: 'dot', in: lhs, out: op.getResult(0), M, N, K, w: Int8Array.from(w), wIsKN: rc[0] === 0, zpA, zpW });
+        steps.push({ kind: 'dot', in: lhsI8, out: op.getResult(0), M, N, K, w: Int8Array.from(wI8), wIsKN: rc[0] === 0, zpA, zpW });
         continue;
       }
       const lhsScale = op.getAttr<number>('lhs_scale') || 1;
@@ -159,17 +177,18 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
       steps.push({ kind: 'linear', in: lhs, out: y, M, N, K, act: a.act, dynamic, w: Int8Array.from(w), wIsKN: rc[0] === 0, wScales, bias, requantScale });
     } else if (n === 'quantized_conv') {
       const x = op.getOperand(0), k = op.getOperand(1), xs = shapeOf(x), ks = shapeOf(k);
-      if (dtypeOf(x) !== 'i8' || dtypeOf(k) !== 'i8') throw new Error('b200: quantized_conv takes int8 operands');
+      if (!['i8', 'ui8'].includes(dtypeOf(x)) || !['i8', 'ui8'].includes(dtypeOf(k))) throw new Error('b200: quantized_conv takes i8 / ui8 operands');
       const il = op.getAttr<string>('input_layout') || 'NCHW', kl = op.getAttr<string>('kernel_layout') || 'OIHW';
       if (!((il === 'NCHW' && kl === 'OIHW') || (il === 'NHWC' && kl === 'OHWI')) || xs.length !== 4 || ks.length !== 4)
         throw new Error('b200: quantized_conv: two spatial dimensions, layouts NCHW / OIHW or NHWC / OHWI');
       const strides = op.getAttr<number[]>('strides')!, padding = op.getAttr<number[][]>('padding')!;
       const first = il === 'NCHW';
       materialize(x); materialize(k);
-      steps.push({ kind: 'conv', in: x, ker: k, out: op.getResult(0),
+      const [xI8, sx] = asI8(x), [kI8, sk] = asI8(k);
+      steps.push({ kind: 'conv', in: xI8, ker: kI8, out: op.getResult(0),
                    shape: first ? xs : [xs[0], xs[3], xs[1], xs[2]], kernelShape: first ? [ks[0], ks[2], ks[3]] : [ks[0], ks[1], ks[2]],
                    strides, padding, dilation: op.getAttr<number[]>('dilation') || strides.map(() => 1), groups: op.getAttr<number>('groups') || 1,
-                   zpIn: op.getAttr<number>('input_zero_point') || 0, zpKer: op.getAttr<number>('kernel_zero_point') || 0, layout: il as 'NCHW' | 'NHWC' });
+                   zpIn: (op.getAttr<number>('input_zero_point') || 0) - sx, zpKer: (op.getAttr<number>('kernel_zero_point') || 0) - sk, layout: il as 'NCHW' | 'NHWC' });
     } else {
       throw new Error(`b200: op '${n}' is outside the graph contract (quantize, dequantize, quantized_dot and its tail, quantized_conv)`);
     }
@@ -221,6 +240,7 @@ export function planGraph(module: GraphModule, options: B200Options, b: B200QBin
           if (st.kind === 'const') continue;              // uploaded when the plan was built
           const x = buf.get(st.in), y = buf.get(st.out);
           if (st.kind === 'conv') runConv(bind, c, x, buf.get(st.ker), y, st);
+          else if (st.kind === 'shift') check(bind, bind.shiftU8ToI8(c, x, st.n, y), 'b200q_shift_u8_to_i8');
           else if (st.kind === 'dot') check(bind, bind.int8GemmI32(c, x, st.dW, st.M, st.N, st.K, st.zpA, st.zpW, y), 'b200q_int8_gemm_i32');
           else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, numel(shapeOf(st.in)), st.scale, st.zeroPoint, st.dst, y), 'b200q_quantize_static');
           else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, st.M, st.K, y, tokScales.get(st.out), -127, 127), 'b200q_quantize_per_token');
@@ -269,6 +289,7 @@ export function programOf(f: GraphFunction, steps: Step[]): NativeProgram {
     else if (st.kind === 'dot') Object.assign(params, { M: st.M, N: st.N, K: st.K, zp_a: st.zpA, zp_w: st.zpW, w_layout: st.wIsKN ? 1 : 0,
       w: { ...b64(st.w), shape: st.wIsKN ? [st.K, st.N] : [st.N, st.K] } });
     else if (st.kind === 'const') return { kind: st.kind, ins: [], out: rec(st.out), params: { data: { ...b64(st.data), shape: shapeOf(st.out) } } };
+    else if (st.kind === 'shift') Object.assign(params, { n: st.n });
     else if (st.kind === 'conv') {
       Object.assign(params, { shape: st.shape, kernel_shape: st.kernelShape, strides: st.strides, padding: st.padding, dilation: st.dilation,
                               groups: st.groups, zp_in: st.zpIn, zp_ker: st.zpKer, layout: st.layout });
@@ -310,6 +331,7 @@ export function planFromProgram(p: NativeProgram, b: B200QBinding, ctx: unknown)
         if (st.kind === 'const') return;
         const q = st.params as Record<string, any>, x = buf.get(st.ins[0]), y = buf.get(st.out.id), d = dev[i];
         if (st.kind === 'conv') runConv(bind, c, x, buf.get(st.ins[1]), y, { ...(q as ConvParams), kernelShape: q.kernel_shape, zpIn: q.zp_in, zpKer: q.zp_ker });
+        else if (st.kind === 'shift') check(bind, bind.shiftU8ToI8(c, x, q.n, y), 'b200q_shift_u8_to_i8');
         else if (st.kind === 'dot') check(bind, bind.int8GemmI32(c, x, d!.dW, q.M, q.N, q.K, q.zp_a, q.zp_w, y), 'b200q_int8_gemm_i32');
         else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, elems.get(st.ins[0])!, q.scale, q.zero_point, q.kind, y), 'b200q_quantize_static');
         else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, q.M, q.K, y, scales.get(st.out.id), -127, 127), 'b200q_quantize_per_token');

@@ -192,8 +192,8 @@ def test_conv_outside_the_contract_is_refused(orc):
     x = b.arg((1, 2, 4, 4), "ui8")
     k = b.arg((2, 2, 1, 1), "i8")
     y = b.op("quantized_conv", [x, k], (1, 2, 4, 4), "i32", strides=[1, 1], padding=[[0, 0], [0, 0]], input_layout="NCHW", kernel_layout="OIHW")
-    with pytest.raises(B200CompileError, match="int8 operands"):
-        plan_function(b.ret(y), dynamic=False)
+    steps = plan_function(b.ret(y), dynamic=False)       # ui8 input: shifted by 128, zero-point moved along
+    assert [s.kind for s in steps] == ["shift", "conv"] and steps[1].params["zp_in"] == -128 and steps[1].ins[0] is steps[0].out
     b = GraphBuilder("c")
     x, k = b.arg((1, 2, 4, 4), "i8"), b.arg((2, 2, 1, 1), "i8")
     y = b.op("quantized_conv", [x, k], (1, 2, 4, 4), "i32", strides=[1, 1], padding=[[0, 0], [0, 0]], input_layout="NCHW", kernel_layout="HWIO")
@@ -226,3 +226,23 @@ def test_zero_point_dot_is_a_step_of_its_own(orc):
     assert steps[1].out.dtype == "i32" and steps[2].params["kind"] == 2
     args, returns, again = steps_from_program(json.loads(json.dumps(program_of(func.args, func.returns, steps))))
     assert [s.kind for s in again] == [s.kind for s in steps] and (again[1].params["w"] == info["wq"]).all()
+
+
+def test_ui8_operands_are_shifted(orc):
+    """quantize{ui8, zp} -> quantized_dot{lhs_zero_point} on ui8 constant codes -> dequantize: both operands become int8
+    codes 128 lower with zero-points 128 lower (the lhs by a device step, the constant on the host)."""
+    rng = np.random.default_rng(2)
+    M, K, N = 5, 16, 7
+    wq = rng.integers(0, 256, (N, K)).astype(np.uint8)
+    b = GraphBuilder("u8")
+    x = b.arg((M, K))
+    xq = b.op("quantize", [x], (M, K), "ui8", scale=0.03, zero_point=120, target_dtype="ui8")
+    wc = b.constant(wq.reshape(-1).tolist(), (N, K), "ui8")
+    acc = b.op("quantized_dot", [xq, wc], (M, N), "i32", lhs_contracting=[1], rhs_contracting=[1], lhs_scale=0.03, lhs_zero_point=120,
+               rhs_scale=0.01, rhs_zero_point=131)
+    y = b.op("dequantize", [acc], (M, N), "f32", scale=0.0003, zero_point=0)
+    steps = plan_function(b.ret(y), dynamic=False)
+    assert [s.kind for s in steps] == ["quantize_static", "shift", "dot", "dequantize_static"]
+    dot = steps[2]
+    assert dot.params["zp_a"] == -8 and dot.params["zp_w"] == 3 and dot.params["w"].dtype == np.int8
+    assert (dot.params["w"].astype(np.int32) == wq.astype(np.int32) - 128).all() and dot.ins[0] is steps[1].out

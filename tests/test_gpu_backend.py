@@ -165,3 +165,30 @@ def test_asymmetric_per_tensor_chain(orc, M, K, N):
     ref = orc.dequantize_static(acc.reshape(-1), info["a_scale"] * info["w_scale"]).reshape(M, N)
     assert (out.view(np.uint32) == ref.view(np.uint32)).all()
     mod.release()
+
+
+def test_ui8_operands_through_the_target_object(orc):
+    """quantize{ui8, zp} -> quantized_dot on ui8 constant codes -> dequantize: the backend shifts both operands by 128
+    (activations on the device, the constant on the host) and moves the zero-points along; sums as plain integer
+    arithmetic on the oracle's ui8 codes."""
+    rng = np.random.default_rng(21)
+    M, K, N = 260, 512, 128
+    a_scale, a_zp, w_scale, w_zp = 0.03, 120, 0.01, 131
+    wq = rng.integers(0, 256, (N, K)).astype(np.uint8)
+    b = GraphBuilder("u8")
+    x = b.arg((M, K))
+    xq = b.op("quantize", [x], (M, K), "ui8", scale=a_scale, zero_point=a_zp, target_dtype="ui8")
+    wc = b.constant(wq.reshape(-1).tolist(), (N, K), "ui8")
+    acc = b.op("quantized_dot", [xq, wc], (M, N), "i32", lhs_contracting=[1], rhs_contracting=[1], lhs_scale=a_scale, lhs_zero_point=a_zp,
+               rhs_scale=w_scale, rhs_zero_point=w_zp)
+    y = b.op("dequantize", [acc], (M, N), "f32", scale=a_scale * w_scale, zero_point=0)
+    mod = compile_with_b200({"u8": b.ret(y)}, {"target": B200Target()})
+    xv = (rng.standard_normal((M, K)) * 2).astype(np.float32)
+    out = np.zeros((M, N), np.float32)
+    mod.run("u8", xv, out)
+    codes = orc.quantize_static(xv.reshape(-1), a_scale, a_zp, dtype=1).reshape(M, K)
+    assert codes.dtype == np.uint8 and codes.min() >= 0 and codes.max() > 127
+    sums = ((codes.astype(np.int64) - a_zp) @ (wq.astype(np.int64) - w_zp).T).astype(np.int32)
+    ref = orc.dequantize_static(sums.reshape(-1), a_scale * w_scale).reshape(M, N)
+    assert (out.view(np.uint32) == ref.view(np.uint32)).all()
+    mod.release()
