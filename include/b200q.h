@@ -189,6 +189,11 @@ int b200q_shift_u8_to_i8(b200q_ctx* ctx, const uint8_t* src, int64_t n, int8_t* 
  * or sv = w_scales[n] when a_scales is null (static activation scale folded by the host). */
 int b200q_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
                    const float* bias, int act, float* out);
+/* The per-tensor tail (quantization_pass.ts:286-360): `dequantize{scale}` of the int32 sums -- fround((double)acc * scale)
+ * with the scale a binary64 immediate, as the compiled op evaluates it (quant_math.ts:29-34) -- then the same optional
+ * bias and activation. */
+int b200q_epilogue_tensor_scale(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, double scale, const float* bias,
+                                int act, float* out);
 /* quantized_dot + tail in one kernel.  A int8 [M,K], W int8 [N,K]. */
 int b200q_int8_linear(b200q_ctx* ctx, const int8_t* A, const float* a_scales, const int8_t* W_nk, const float* w_scales,
                       const float* bias, int act, int64_t M, int64_t N, int64_t K, float* out);

@@ -58,6 +58,7 @@ PROTOTYPES = {
     "b200q_shift_u8_to_i8": (c_int, [c_vp, c_vp, c_i64, c_vp]),
     "b200q_int8_gemm_i32": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_int, c_vp]),
     "b200q_epilogue": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_int, c_vp]),
+    "b200q_epilogue_tensor_scale": (c_int, [c_vp, c_vp, c_i64, c_i64, C.c_double, c_vp, c_int, c_vp]),
     "b200q_int8_linear": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_int8_linear_gathered": (c_int, [c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "b200q_int8_linear_requant_static": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_dbl, c_vp]),

@@ -115,7 +115,7 @@ def compile_with_b200(module: Dict[str, GraphFunction], config: dict) -> "B200Ru
 # ----------------------------------------------------------------------------- planning
 @dataclass
 class Step:
-    kind: str                       # 'quantize_static' | 'quantize_token' | 'dequantize_static' | 'linear' | 'dot' | 'conv' | 'const' | 'shift'
+    kind: str                       # 'quantize_static' | 'quantize_token' | 'dequantize_static' | 'linear' | 'dot' | 'tail' | 'conv' | 'const' | 'shift'
     ins: List[Value]
     out: Value
     params: Dict[str, Any]
@@ -231,24 +231,14 @@ class _Planner:
             w, zp_w = w - 128, zp_w - 128
         if lhs.dtype == "ui8":
             zp_a -= 128
-        if zp_a or zp_w:
-            # asymmetric operands (rules/quantization.ts:29-40 subtracts the zero-points tap by tap): the int32 contraction
-            # is a step of its own, the `dequantize` that follows stays a static step
-            if self.single_user(op.result, "dequantize") is None:
-                raise B200CompileError("quantized_dot with zero-points (or ui8 operands) must be followed by dequantize")
-            lhs, _ = self.as_i8(lhs)
-            self.done.add(id(op))
-            self.steps.append(Step("dot", [lhs], op.result, {"M": M, "N": N, "K": K, "w": w.astype(np.int8), "w_layout": w_layout,
-                                                             "zp_a": zp_a, "zp_w": zp_w}))
-            return
         lhs_scale = float(op.attrs.get("lhs_scale", 1.0))
         absorbed = [op]
         y = op.result
-        sv = None
-        # per-channel tail: convert -> mul(broadcast(constant f32[N]))
+        sv = None                              # per-channel scale vector (binary64 numbers of the graph constant)
+        tensor_scale = None                    # or the one binary64 scale of a per-tensor `dequantize`
         conv = self.single_user(y, "convert")
         deq = self.single_user(y, "dequantize")
-        if conv is not None:
+        if conv is not None:                   # per-channel tail: convert -> mul(broadcast(constant f32[N]))
             mul = self.single_user(conv.result, "mul")
             src = _broadcast_source(self.other(mul, conv.result)) if mul is not None else None
             arr = _const_array(src) if src is not None else None
@@ -257,10 +247,10 @@ class _Planner:
             sv = arr.reshape(-1)
             absorbed += [conv, mul]
             y = mul.result
-        elif deq is not None:                 # per-tensor path: dequantize(scale = lhs_scale * rhs_scale)
+        elif deq is not None:                  # per-tensor path: dequantize(scale = lhs_scale * rhs_scale)
             if deq.attrs.get("zero_point", 0):
                 raise B200CompileError("dequantize with a zero-point after quantized_dot is not supported")
-            sv = np.full(N, float(deq.attrs["scale"]), np.float64)
+            tensor_scale = float(deq.attrs["scale"])
             absorbed += [deq]
             y = deq.result
         else:
@@ -279,6 +269,19 @@ class _Planner:
         act, y, act_ops = self.match_activation(y)
         for o in act_ops:
             self.done.add(id(o))
+        if tensor_scale is not None or zp_a or zp_w:
+            # Two steps: the int32 contraction (tensor cores; zero-points through the correction terms; ui8 operands
+            # shifted by 128) and the tail as its own kernel.  The per-tensor `dequantize` multiplies by a binary64
+            # immediate (quant_math.ts:29-34), which the fused kernel's binary32 scale vector cannot reproduce.
+            if self.dynamic:
+                raise B200CompileError("per_token_dynamic needs the symmetric per-channel form of quantized_dot")
+            lhs, _ = self.as_i8(lhs)
+            acc = op.result
+            self.steps.append(Step("dot", [lhs], acc, {"M": M, "N": N, "K": K, "w": w.astype(np.int8), "w_layout": w_layout,
+                                                       "zp_a": zp_a, "zp_w": zp_w}))
+            self.steps.append(Step("tail", [acc], y, {"M": M, "N": N, "tensor_scale": tensor_scale, "bias": bias, "act": act,
+                                                      "w_scales": None if sv is None else sv.astype(np.float32)}))
+            return
         params = {"M": M, "N": N, "K": K, "w": w.astype(np.int8), "w_layout": w_layout, "bias": bias, "act": act,
                   "requant_scale": None, "a_dynamic": False}
         if self.dynamic:
@@ -427,7 +430,7 @@ def steps_from_program(program: dict):
         args.append(vals[a["id"]])
     steps = []
     for st in program["steps"]:
-        if st["kind"] not in ("quantize_static", "quantize_token", "dequantize_static", "linear", "dot", "conv", "const", "shift"):
+        if st["kind"] not in ("quantize_static", "quantize_token", "dequantize_static", "linear", "dot", "tail", "conv", "const", "shift"):
             raise B200CompileError(f"native program: unknown step '{st['kind']}'")
         o = st["out"]
         vals[o["id"]] = Value(tuple(o["shape"]), o["dtype"])
@@ -490,6 +493,10 @@ class _FunctionPlan:
                 if st.kind == "linear":
                     p["dws"] = ctx.to_device(p["w_scales"])
                     p["db"] = ctx.to_device(p["bias"]) if p["bias"] is not None else None
+            if st.kind == "tail":
+                p = st.params
+                p["dws"] = ctx.to_device(p["w_scales"]) if p["w_scales"] is not None else None
+                p["db"] = ctx.to_device(p["bias"]) if p["bias"] is not None else None
         missing = [r for r in func.returns if id(r) not in self.buf]
         if missing:
             raise B200CompileError("a returned value is not produced by any native step")
@@ -530,6 +537,11 @@ class _FunctionPlan:
                                      p["dilation"], p["groups"], p["zp_in"], p["zp_ker"], p["layout"])
             elif st.kind == "dot":
                 ctx.int8_gemm_i32(x, p["dW"], p["M"], p["N"], p["K"], out, p["zp_a"], p["zp_w"])
+            elif st.kind == "tail":
+                if p["dws"] is not None:
+                    ctx.epilogue(x, p["M"], p["N"], None, p["dws"], p["db"], p["act"], out)
+                else:
+                    ctx.epilogue_tensor_scale(x, p["M"], p["N"], p["tensor_scale"], p["db"], p["act"], out)
             elif st.kind == "quantize_static":
                 ctx.quantize_static(x, int(np.prod(st.ins[0].shape)), p["scale"], p["zero_point"], p["kind"], out)
             elif st.kind == "quantize_token":

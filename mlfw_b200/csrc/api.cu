@@ -554,6 +554,15 @@ int b200q_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, con
   return launch_epilogue(ctx, acc, M, N, a_scales, w_scales, bias, act, out, nullptr, 1.0);
 }
 
+int b200q_epilogue_tensor_scale(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, double scale, const float* bias, int act,
+                                float* out) {
+  if (use_device(ctx)) return 1;
+  B200Q_DIMS_OK(M, N, 0);
+  B200Q_REQUIRE(M == 0 || N == 0 || (acc && out), "b200q_epilogue_tensor_scale: null pointer");
+  B200Q_REQUIRE(act >= 0 && act <= 4, "b200q_epilogue_tensor_scale: unknown activation %d", act);
+  return launch_epilogue(ctx, acc, M, N, nullptr, nullptr, bias, act, out, nullptr, 1.0, scale);
+}
+
 static int check_linear(const char* who, const void* A, const void* W, const float* w_scales, int act, int64_t M, int64_t N,
                         int64_t K, const void* out) {
   B200Q_DIMS_OK(M, N, K);

@@ -76,7 +76,8 @@ __global__ void __launch_bounds__(256) gemm_i8_simt_kernel(const int8_t* __restr
 __global__ void __launch_bounds__(256) epilogue_kernel(const int32_t* __restrict__ acc, int64_t M, int64_t N,
                                                        const float* __restrict__ a_scales, const float* __restrict__ w_scales,
                                                        const float* __restrict__ bias, int act, float* __restrict__ out_f32,
-                                                       int8_t* __restrict__ out_q, double q_scale, float q_inv, int q_exact) {
+                                                       int8_t* __restrict__ out_q, double q_scale, float q_inv, int q_exact,
+                                                       double tensor_scale) {
   __shared__ double tbl[EXP2_TABLE_SIZE];
   fill_exp2_table(tbl, threadIdx.x, blockDim.x);
   __syncthreads();
@@ -84,8 +85,14 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const int32_t* __restrict
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int64_t m = i / N, n = i - m * N;
-    float sv = a_scales ? __fmul_rn(a_scales[m], w_scales[n]) : w_scales[n];
-    float y = scale_acc(acc[i], sv);
+    float y;
+    if (w_scales != nullptr) {
+      float sv = a_scales ? __fmul_rn(a_scales[m], w_scales[n]) : w_scales[n];
+      y = scale_acc(acc[i], sv);
+    } else {
+      // the compiled `dequantize` of a per-tensor scale (quant_math.ts:29-34): the scale is a binary64 immediate
+      y = __double2float_rn((double)acc[i] * tensor_scale);
+    }
     if (bias) y = __fadd_rn(y, bias[n]);
     y = apply_act(y, act, tbl);
     if (out_f32) out_f32[i] = y;
@@ -195,7 +202,7 @@ int launch_gemm_i8_simt(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
 }
 
 int launch_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
-                    const float* bias, int act, float* out_f32, int8_t* out_q, double q_scale) {
+                    const float* bias, int act, float* out_f32, int8_t* out_q, double q_scale, double tensor_scale) {
   ProfScope prof(ctx, KK_EPILOGUE);
   if (M == 0 || N == 0) return 0;
   float q_inv = 0.0f;
@@ -209,7 +216,7 @@ int launch_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, co
   int64_t cap = (int64_t)ctx->sm_count * 16;
   if (blocks > cap) blocks = cap;
   epilogue_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(acc, M, N, a_scales, w_scales, bias, act, out_f32, out_q, q_scale,
-                                                            q_inv, q_exact);
+                                                            q_inv, q_exact, tensor_scale);
   ctx->launches++;
   B200Q_CHECK_CUDA(cudaGetLastError());
   return 0;

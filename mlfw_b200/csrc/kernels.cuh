@@ -46,8 +46,9 @@ int launch_zero_point_fix(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, i
 // correction) when the operands are 16-byte aligned and K is a multiple of 16, the CUDA cores otherwise.
 int gemm_i32_any(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int64_t M, int64_t N, int64_t K, int zpA, int zpB, int32_t* C);
 // Exactly one of out_f32 / out_q is written (both may be given); out_q uses the static scale q_scale.
+// w_scales == null: one binary64 scale for the whole tensor (tensor_scale), applied as the compiled `dequantize` does.
 int launch_epilogue(b200q_ctx* ctx, const int32_t* acc, int64_t M, int64_t N, const float* a_scales, const float* w_scales,
-                    const float* bias, int act, float* out_f32, int8_t* out_q, double q_scale);
+                    const float* bias, int act, float* out_f32, int8_t* out_q, double q_scale, double tensor_scale = 0.0);
 
 bool gemm_umma_supported(const void* A, const void* W, int64_t M, int64_t N, int64_t K);
 // Tensor-core GEMM with the fused tail.  out_i32 != null: raw accumulators (tail arguments ignored).

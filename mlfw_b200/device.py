@@ -287,6 +287,11 @@ class Context:
         check(self.lib.b200q_epilogue(self.handle, _ptr(acc), M, N, _ptr(a_scales), _ptr(w_scales), _ptr(bias), ACT[act],
                                       _ptr(out)), "b200q_epilogue")
 
+    def epilogue_tensor_scale(self, acc, M, N, scale, bias, act, out):
+        """act(fround(fround((double)acc * scale) + bias)): the compiled per-tensor `dequantize` and what follows it."""
+        check(self.lib.b200q_epilogue_tensor_scale(self.handle, _ptr(acc), M, N, float(scale), _ptr(bias), ACT[act], _ptr(out)),
+              "b200q_epilogue_tensor_scale")
+
     def int8_linear(self, A, a_scales, W_nk, w_scales, bias, act, M, N, K, out):
         check(self.lib.b200q_int8_linear(self.handle, _ptr(A), _ptr(a_scales), _ptr(W_nk), _ptr(w_scales), _ptr(bias), ACT[act],
                                          M, N, K, _ptr(out)), "b200q_int8_linear")

@@ -59,6 +59,7 @@ function bind(path: string) {
     quantizedConv2d: f('int b200q_quantized_conv2d(void *ctx, const void *in, const void *ker, int64_t N, int64_t C, int64_t H, int64_t W, int64_t O, int64_t KH, int64_t KW, int stride_h, int stride_w, int pad_top, int pad_bottom, int pad_left, int pad_right, int dil_h, int dil_w, int groups, int zp_in, int zp_ker, int layout, void *out)'),
     shiftU8ToI8: f('int b200q_shift_u8_to_i8(void *ctx, const void *src, int64_t n, void *dst)'),
     epilogue: f('int b200q_epilogue(void *ctx, const void *acc, int64_t M, int64_t N, const void *a_scales, const void *w_scales, const void *bias, int act, void *out)'),
+    epilogueTensorScale: f('int b200q_epilogue_tensor_scale(void *ctx, const void *acc, int64_t M, int64_t N, double scale, const void *bias, int act, void *out)'),
     int8Linear: f('int b200q_int8_linear(void *ctx, const void *A, const void *a_scales, const void *W_nk, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void *out)'),
     int8LinearGathered: f('int b200q_int8_linear_gathered(void *ctx, const void *A, const void *a_scales, int a_blocks, const void *W_nk, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, void *out)'),
     int8LinearRequantStatic: f('int b200q_int8_linear_requant_static(void *ctx, const void *A, const void *a_scales, const void *W_nk, const void *w_scales, const void *bias, int act, int64_t M, int64_t N, int64_t K, double out_scale, void *out_q)'),

@@ -8,7 +8,7 @@
 //   [· add(broadcast(bias))] [· maximum(·,0) | x·sigmoid(1.702x) | x·sigmoid(x)] [· quantize]   -> one 'linear' step
 //   quantize(x) · quantize(kernel) · quantized_conv  -> 'conv' (int32; the `dequantize` after it is a step of its own)
 //   quantized_dot{zero-points} (asymmetric operands)  -> 'dot' (int32 on the tensor cores plus the zero-point terms)
-//   quantized_dot · dequantize{scale}                                                               -> 'linear' with a constant scale vector
+//   quantized_dot · dequantize{scale} [· add · activation]   -> 'dot' + 'tail' (the scale is a binary64 immediate: quant_math.ts:29-34)
 //   standalone quantize / dequantize                                                                 -> static steps
 // Anything else throws: the backend has no fallback.
 import { check } from './binding.js';
@@ -31,6 +31,9 @@ type Step =
       dW?: unknown; dWs?: unknown; dBias?: unknown }
   // quantized_dot with zero-points (asymmetric operands): the int32 contraction alone; the `dequantize` after it is a static step
   | { kind: 'dot'; in: Value; out: Value; M: number; N: number; K: number; w: Int8Array; wIsKN: boolean; zpA: number; zpW: number; dW?: unknown }
+  // the tail of a 'dot' as its own kernel: a per-channel binary32 scale vector, or the one binary64 scale of a per-tensor `dequantize`
+  | { kind: 'tail'; in: Value; out: Value; M: number; N: number; tensorScale: number | null; wScales: Float32Array | null; bias: Float32Array | null; act: Act;
+      dWs?: unknown; dBias?: unknown }
   // a ui8 operand of a contraction as int8 codes 128 lower (the zero-point moves along: u - zp == (u - 128) - (zp - 128))
   | { kind: 'shift'; in: Value; out: Value; n: number }
   // a constant that a native step reads as a buffer (a convolution's kernel, the f32 source of its `quantize`): uploaded once
@@ -139,16 +142,8 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
       const wI8 = dtypeOf(rhs) === 'ui8' ? w.map((v) => v - 128) : w;       // constant ui8 codes: moved by 128 here, on the host
       if (dtypeOf(rhs) === 'ui8') zpW -= 128;
       if (dtypeOf(lhs) === 'ui8') zpA -= 128;
-      if (zpA || zpW) {                                  // rules/quantization.ts:29-40 subtracts the zero-points tap by tap
-        const nx = users(f, op.getResult(0), done).filter((u) => u !== op);
-        if (nx.length !== 1 || nx[0].opName !== 'dequantize') throw new Error('b200: quantized_dot with zero-points (or ui8 operands) must be followed by dequantize');
-        const [lhsI8] = asI8(lhs);
-        done.add(op);
-        steps.push({ kind: 'dot', in: lhsI8, out: op.getResult(0), M, N, K, w: Int8Array.from(wI8), wIsKN: rc[0] === 0, zpA, zpW });
-        continue;
-      }
       const lhsScale = op.getAttr<number>('lhs_scale') || 1;
-      let y = op.getResult(0), sv: number[];
+      let y = op.getResult(0), sv: number[] | null = null, tensorScale: number | null = null;
       done.add(op);
       const next = users(f, y, done);
       if (next.length === 1 && next[0].opName === 'convert') {
@@ -157,7 +152,7 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
         if (!arr || arr.length !== N) throw new Error('b200: quantized_dot -> convert must be followed by mul with a per-channel scale vector');
         sv = arr; done.add(next[0]); done.add(mul[0]); y = mul[0].getResult(0);
       } else if (next.length === 1 && next[0].opName === 'dequantize' && !next[0].getAttr<number>('zero_point')) {
-        sv = new Array(N).fill(next[0].getAttr<number>('scale')); done.add(next[0]); y = next[0].getResult(0);
+        tensorScale = next[0].getAttr<number>('scale')!; done.add(next[0]); y = next[0].getResult(0);
       } else throw new Error('b200: quantized_dot must be followed by its dequantizing tail');
       let bias: Float32Array | null = null;
       const add = users(f, y, done);
@@ -167,8 +162,18 @@ function planFunction(f: GraphFunction, dynamic: boolean): Step[] {
       }
       const a = matchActivation(f, y, done);
       a.ops.forEach((o) => done.add(o)); y = a.res;
+      if (tensorScale !== null || zpA || zpW) {
+        // two steps: the int32 contraction (zero-points through correction terms, ui8 operands shifted) and the tail as
+        // its own kernel; the per-tensor `dequantize` multiplies by a binary64 immediate (quant_math.ts:29-34)
+        if (dynamic) throw new Error('b200: per_token_dynamic needs the symmetric per-channel form of quantized_dot');
+        const [lhsI8] = asI8(lhs);
+        const acc = op.getResult(0);
+        steps.push({ kind: 'dot', in: lhsI8, out: acc, M, N, K, w: Int8Array.from(wI8), wIsKN: rc[0] === 0, zpA, zpW });
+        steps.push({ kind: 'tail', in: acc, out: y, M, N, tensorScale, wScales: sv ? Float32Array.from(sv) : null, bias, act: a.act });
+        continue;
+      }
       // dynamic per-token: recover wScale[n] = scaleVec[n] / lhs_scale (both binary64 here), rounded to f32 once
-      const wScales = Float32Array.from(dynamic ? sv.map((s) => s / lhsScale) : sv);
+      const wScales = Float32Array.from(dynamic ? sv!.map((s) => s / lhsScale) : sv!);
       let requantScale: number | null = null;
       const nq = users(f, y, done);
       if (!dynamic && nq.length === 1 && nq[0].opName === 'quantize' && !nq[0].getAttr<number>('zero_point') && !returns.has(y)) {
@@ -229,6 +234,10 @@ export function planGraph(module: GraphModule, options: B200Options, b: B200QBin
         st.dWs = upload(st.wScales);
         st.dBias = st.bias ? upload(st.bias) : null;
       }
+      if (st.kind === 'tail') {
+        st.dWs = st.wScales ? upload(st.wScales) : null;
+        st.dBias = st.bias ? upload(st.bias) : null;
+      }
     }
     const rets = f.returnValues();
     plans.set(f.name, {
@@ -242,7 +251,10 @@ export function planGraph(module: GraphModule, options: B200Options, b: B200QBin
           if (st.kind === 'conv') runConv(bind, c, x, buf.get(st.ker), y, st);
           else if (st.kind === 'shift') check(bind, bind.shiftU8ToI8(c, x, st.n, y), 'b200q_shift_u8_to_i8');
           else if (st.kind === 'dot') check(bind, bind.int8GemmI32(c, x, st.dW, st.M, st.N, st.K, st.zpA, st.zpW, y), 'b200q_int8_gemm_i32');
-          else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, numel(shapeOf(st.in)), st.scale, st.zeroPoint, st.dst, y), 'b200q_quantize_static');
+          else if (st.kind === 'tail') {
+            if (st.dWs) check(bind, bind.epilogue(c, x, st.M, st.N, null, st.dWs, st.dBias, ACT[st.act], y), 'b200q_epilogue');
+            else check(bind, bind.epilogueTensorScale(c, x, st.M, st.N, st.tensorScale!, st.dBias, ACT[st.act], y), 'b200q_epilogue_tensor_scale');
+          } else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, numel(shapeOf(st.in)), st.scale, st.zeroPoint, st.dst, y), 'b200q_quantize_static');
           else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, st.M, st.K, y, tokScales.get(st.out), -127, 127), 'b200q_quantize_per_token');
           else if (st.kind === 'dequantize_static') check(bind, bind.dequantizeStatic(c, x, st.src, numel(shapeOf(st.in)), st.scale, st.zeroPoint, y), 'b200q_dequantize_static');
           else if (st.requantScale !== null) check(bind, bind.int8LinearRequantStatic(c, x, null, st.dW, st.dWs, st.dBias, ACT[st.act], st.M, st.N, st.K, st.requantScale, y), 'b200q_int8_linear_requant_static');
@@ -290,6 +302,8 @@ export function programOf(f: GraphFunction, steps: Step[]): NativeProgram {
       w: { ...b64(st.w), shape: st.wIsKN ? [st.K, st.N] : [st.N, st.K] } });
     else if (st.kind === 'const') return { kind: st.kind, ins: [], out: rec(st.out), params: { data: { ...b64(st.data), shape: shapeOf(st.out) } } };
     else if (st.kind === 'shift') Object.assign(params, { n: st.n });
+    else if (st.kind === 'tail') Object.assign(params, { M: st.M, N: st.N, tensor_scale: st.tensorScale, act: st.act,
+      w_scales: st.wScales ? b64(st.wScales) : null, bias: st.bias ? b64(st.bias) : null });
     else if (st.kind === 'conv') {
       Object.assign(params, { shape: st.shape, kernel_shape: st.kernelShape, strides: st.strides, padding: st.padding, dilation: st.dilation,
                               groups: st.groups, zp_in: st.zpIn, zp_ker: st.zpKer, layout: st.layout });
@@ -314,6 +328,10 @@ export function planFromProgram(p: NativeProgram, b: B200QBinding, ctx: unknown)
     if (st.kind === 'const') { buf.set(st.out.id, upload(unb64(q.data, (x) => new Uint8Array(x))!)); return null; }
     buf.set(st.out.id, alloc(size(st.out)));
     if (st.kind === 'quantize_token') scales.set(st.out.id, alloc(q.M * 4));
+    if (st.kind === 'tail') {
+      const ws = unb64(q.w_scales, (x) => new Float32Array(x)), tb = unb64(q.bias, (x) => new Float32Array(x));
+      return { dW: null, dWs: ws ? upload(ws) : null, dBias: tb ? upload(tb) : null };
+    }
     if (st.kind !== 'linear' && st.kind !== 'dot') return null;
     const w = unb64(q.w, (x) => new Int8Array(x))!;
     let dW = upload(w);
@@ -333,7 +351,10 @@ export function planFromProgram(p: NativeProgram, b: B200QBinding, ctx: unknown)
         if (st.kind === 'conv') runConv(bind, c, x, buf.get(st.ins[1]), y, { ...(q as ConvParams), kernelShape: q.kernel_shape, zpIn: q.zp_in, zpKer: q.zp_ker });
         else if (st.kind === 'shift') check(bind, bind.shiftU8ToI8(c, x, q.n, y), 'b200q_shift_u8_to_i8');
         else if (st.kind === 'dot') check(bind, bind.int8GemmI32(c, x, d!.dW, q.M, q.N, q.K, q.zp_a, q.zp_w, y), 'b200q_int8_gemm_i32');
-        else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, elems.get(st.ins[0])!, q.scale, q.zero_point, q.kind, y), 'b200q_quantize_static');
+        else if (st.kind === 'tail') {
+          if (d!.dWs) check(bind, bind.epilogue(c, x, q.M, q.N, null, d!.dWs, d!.dBias, ACT[q.act as Act], y), 'b200q_epilogue');
+          else check(bind, bind.epilogueTensorScale(c, x, q.M, q.N, q.tensor_scale, d!.dBias, ACT[q.act as Act], y), 'b200q_epilogue_tensor_scale');
+        } else if (st.kind === 'quantize_static') check(bind, bind.quantizeStatic(c, x, elems.get(st.ins[0])!, q.scale, q.zero_point, q.kind, y), 'b200q_quantize_static');
         else if (st.kind === 'quantize_token') check(bind, bind.quantizePerToken(c, x, q.M, q.K, y, scales.get(st.out.id), -127, 127), 'b200q_quantize_per_token');
         else if (st.kind === 'dequantize_static') check(bind, bind.dequantizeStatic(c, x, q.kind, elems.get(st.ins[0])!, q.scale, q.zero_point, y), 'b200q_dequantize_static');
         else if (q.requant_scale !== null) check(bind, bind.int8LinearRequantStatic(c, x, null, d!.dW, d!.dWs, d!.dBias, ACT[q.act as Act], q.M, q.N, q.K, q.requant_scale, y), 'b200q_int8_linear_requant_static');

@@ -72,8 +72,9 @@ def test_per_tensor_path(orc):
               output_scale=0.001)
     y = b.op("dequantize", [qd], (4, 6), "f32", scale=0.05 * 0.02, zero_point=0)
     steps = plan_function(b.ret(y), dynamic=False)
-    assert [s.kind for s in steps] == ["quantize_static", "linear"]
-    assert (steps[1].params["w_scales"] == np.float32(0.05 * 0.02)).all()
+    # the compiled `dequantize` multiplies by a binary64 immediate: the contraction and the tail are steps of their own
+    assert [s.kind for s in steps] == ["quantize_static", "dot", "tail"]
+    assert steps[2].params["tensor_scale"] == 0.05 * 0.02 and steps[2].params["w_scales"] is None and steps[2].ins[0] is steps[1].out
 
 
 def test_ops_outside_the_contract_are_refused(orc):
@@ -221,9 +222,9 @@ def test_zero_point_dot_is_a_step_of_its_own(orc):
     import json
     func, info = asymmetric_graph(orc)
     steps = plan_function(func, dynamic=False)
-    assert [s.kind for s in steps] == ["quantize_static", "dot", "dequantize_static"]
+    assert [s.kind for s in steps] == ["quantize_static", "dot", "tail"]
     assert steps[0].params["zero_point"] == 7 and steps[1].params["zp_a"] == 7 and steps[1].params["zp_w"] == -3
-    assert steps[1].out.dtype == "i32" and steps[2].params["kind"] == 2
+    assert steps[1].out.dtype == "i32" and steps[2].params["tensor_scale"] == 0.04 * 0.01 and steps[2].params["act"] == "none"
     args, returns, again = steps_from_program(json.loads(json.dumps(program_of(func.args, func.returns, steps))))
     assert [s.kind for s in again] == [s.kind for s in steps] and (again[1].params["w"] == info["wq"]).all()
 
@@ -242,7 +243,7 @@ def test_ui8_operands_are_shifted(orc):
                rhs_scale=0.01, rhs_zero_point=131)
     y = b.op("dequantize", [acc], (M, N), "f32", scale=0.0003, zero_point=0)
     steps = plan_function(b.ret(y), dynamic=False)
-    assert [s.kind for s in steps] == ["quantize_static", "shift", "dot", "dequantize_static"]
+    assert [s.kind for s in steps] == ["quantize_static", "shift", "dot", "tail"]
     dot = steps[2]
     assert dot.params["zp_a"] == -8 and dot.params["zp_w"] == 3 and dot.params["w"].dtype == np.int8
     assert (dot.params["w"].astype(np.int32) == wq.astype(np.int32) - 128).all() and dot.ins[0] is steps[1].out

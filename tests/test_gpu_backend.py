@@ -192,3 +192,39 @@ def test_ui8_operands_through_the_target_object(orc):
     ref = orc.dequantize_static(sums.reshape(-1), a_scale * w_scale).reshape(M, N)
     assert (out.view(np.uint32) == ref.view(np.uint32)).all()
     mod.release()
+
+
+@pytest.mark.parametrize("act", ["none", "relu", "silu"])
+def test_per_tensor_path_uses_the_binary64_scale(orc, act):
+    """quantize -> quantized_dot -> dequantize{scale} [-> add(bias) -> activation] (quantization_pass.ts:286-360): the
+    compiled dequantize is fround((double)acc * scale) with the scale a binary64 immediate; a binary32 scale vector
+    would miss that by an ulp on many outputs, so the tail runs as its own kernel with the binary64 scale."""
+    from graph_util import activation
+    rng = np.random.default_rng(31)
+    M, K, N = 200, 256, 96
+    a_scale, w_scale = 0.037, 0.0123                    # the product is not a binary32 number
+    wq = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    bias = rng.standard_normal(N).astype(np.float32)
+    b = GraphBuilder("pt")
+    x = b.arg((M, K))
+    xq = b.op("quantize", [x], (M, K), "i8", scale=a_scale, zero_point=0, target_dtype="i8")
+    wc = b.constant(wq.reshape(-1).tolist(), (K, N), "i8")
+    acc = b.op("quantized_dot", [xq, wc], (M, N), "i32", lhs_contracting=[1], rhs_contracting=[0], lhs_scale=a_scale, rhs_scale=w_scale)
+    y = b.op("dequantize", [acc], (M, N), "f32", scale=a_scale * w_scale, zero_point=0)
+    bc = b.constant(bias.astype(np.float64).tolist(), (N,), "f32")
+    bb = b.op("broadcast_in_dim", [bc], (M, N), "f32", broadcast_dimensions=[1], result_shape=[M, N])
+    y = b.op("add", [y, bb], (M, N), "f32")
+    y = activation(b, y, act)
+    mod = compile_with_b200({"pt": b.ret(y)}, {"target": B200Target()})
+    xv = (rng.standard_normal((M, K)) * 1.5).astype(np.float32)
+    out = np.zeros((M, N), np.float32)
+    mod.run("pt", xv, out)
+    codes = orc.quantize_static(xv.reshape(-1), a_scale).reshape(M, K)
+    sums = orc.qdot_i32(codes, wq, "KN")
+    deq = orc.dequantize_static(sums.reshape(-1), a_scale * w_scale).reshape(M, N)
+    ref = orc.activation((deq + bias).astype(np.float32), act)
+    assert (out.view(np.uint32) == ref.view(np.uint32)).all()
+    # and the binary32 scale would indeed have differed somewhere
+    wrong = (sums.astype(np.float64) * np.float64(np.float32(a_scale * w_scale))).astype(np.float32)
+    assert (wrong != deq).any()
+    mod.release()
