@@ -995,6 +995,7 @@ def _run():
     ap.add_argument("--no-north-star", action="store_true", help="skip the fixed-size multi-GPU records (c3_strong, c5_mshard, c5_nshard)")
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
     ap.add_argument("--quant-sweep", action="store_true", help="only the per-token quantize over row lengths 768..8192 and 8192 / 16384 rows")
+    ap.add_argument("--tile-group", type=int, default=-1, help="tile walking order of the tensor-core GEMM (b200q_set_tile_group)")
     ap.add_argument("--conv-bench", action="store_true", help="only quantized_conv2d on ResNet-sized layers (gather + contraction), both layouts")
     ap.add_argument("--roundtrip-only", action="store_true", help="only the standalone quantize -> dequantize round trip (profiler runs)")
     args = ap.parse_args()
@@ -1021,6 +1022,7 @@ def _run():
     ctx.set_tail_mode(args.tail_mode)
     ctx.set_requant_variant(args.requant_variant)
     ctx.set_epilogue_warps(args.epilogue_warps)
+    ctx.set_tile_group(args.tile_group)
     if args.roundtrip_only:
         line = {"metric": "quantize_dequantize_GBps", "roundtrip_c2": run_roundtrip(ctx, peaks(), args.steps, args.warmup)}
         ctx.close()

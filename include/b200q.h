@@ -63,6 +63,10 @@ int b200q_set_tail_mode(b200q_ctx* ctx, int mode);
  * (gelu_sigmoid, silu) when the contraction is short (K <= 1024: the tail, not the tensor pipe, sets the pace there),
  * eight otherwise; 8 or 16 = always that many.  Same results either way. */
 int b200q_set_epilogue_warps(b200q_ctx* ctx, int warps);
+/* Order in which the tensor-core GEMM's persistent CTAs walk the 256-row x 256-column tiles: -1 (default) = chosen by
+ * size (grouped when the weights exceed 48 MB, so that the tiles in flight share W tiles out of L2 instead of streaming
+ * all of W from HBM once per row block), 0 = row block by row block, g > 0 = groups of g row blocks.  Same results. */
+int b200q_set_tile_group(b200q_ctx* ctx, int row_blocks);
 /* Host threads (the caller's included) that stage pageable arrays of the host-buffer entry points through page-locked
  * memory: 0 (default) = half the host's cores, at most 8; takes effect before the first such call of the context. */
 int b200q_set_host_threads(b200q_ctx* ctx, int threads);

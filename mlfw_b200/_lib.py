@@ -28,6 +28,7 @@ PROTOTYPES = {
     "b200q_set_tail_mode": (c_int, [c_vp, c_int]),
     "b200q_set_epilogue_warps": (c_int, [c_vp, c_int]),
     "b200q_set_host_threads": (c_int, [c_vp, c_int]),
+    "b200q_set_tile_group": (c_int, [c_vp, c_int]),
     "b200q_set_requant_variant": (c_int, [c_vp, c_int]),
     "b200q_set_quant_variant": (c_int, [c_vp, c_int]),
     "b200q_launch_count": (C.c_uint64, [c_vp]),

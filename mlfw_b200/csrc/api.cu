@@ -262,6 +262,13 @@ int b200q_set_gemm_variant(b200q_ctx* ctx, int variant) {
   return 0;
 }
 
+int b200q_set_tile_group(b200q_ctx* ctx, int row_blocks) {
+  B200Q_REQUIRE(ctx != nullptr, "null context");
+  B200Q_REQUIRE(row_blocks >= -1 && row_blocks <= 65536, "b200q_set_tile_group: %d is not -1, 0 or a group size", row_blocks);
+  ctx->tile_group = row_blocks;
+  return 0;
+}
+
 int b200q_set_host_threads(b200q_ctx* ctx, int threads) {
   B200Q_REQUIRE(ctx != nullptr, "null context");
   B200Q_REQUIRE(threads >= 0 && threads <= 64, "b200q_set_host_threads: %d is not between 0 and 64", threads);

@@ -86,6 +86,7 @@ struct b200q_ctx {
   int requant_variant = 0;               // 0: ranges published by the GEMM epilogue + one-pass encode; 1: f32 result + full per-token quantize
   double wait_limit_s = 2.0;             // bound of every device-side wait
   int gemm_variant = 0;                  // 0 auto, 1 CUDA-core kernel only, 2 tensor cores with one CTA per tile, 3 with CTA pairs
+  int tile_group = -1;                   // tensor-core GEMM: row blocks per group of the tile walking order (-1 chosen by size, 0 row block by row block)
   int epilogue_warps = 0;                // tensor-core GEMM, f32 output: 0 = sixteen epilogue warps for the exact sigmoid tails at K <= 1024, eight otherwise; 8 / 16 = always that many
   int quant_variant = 0;                 // 0 auto (rows staged in shared memory when they fit), 1 unstaged kernel only, 2 staged with both passes from shared memory
   uint32_t quant_staged_ready = 0;        // instances of the staged quantize kernel whose shared-memory attribute is set

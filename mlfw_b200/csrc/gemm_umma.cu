@@ -93,9 +93,29 @@ struct GemmParams {
   // A + r * M * a_piece_cols (what an all-gather of column-sharded activations leaves); 1 = plain row-major [M, K].
   int a_pieces;
   int a_piece_cols;
+  // Order in which the persistent CTAs walk the tiles.  0: row block by row block (all column tiles of a row block are
+  // neighbours).  g > 0: groups of g row blocks, and inside a group column tile by column tile with the group's row
+  // blocks as neighbours -- the tiles in flight at one time then share few W tiles, which is what matters when W
+  // (N*K bytes) is larger than L2: walked row block by row block, the whole of W streams from HBM once per row block.
+  int group_m;
   uint32_t* status;
   unsigned long long wait_limit_ns;
 };
+
+// Row-block and column-tile index of tile number `tile` in the walking order above.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t& tm, int64_t& tn) {
+  if (p.group_m == 0) {
+    tm = tile / tiles_n;
+    tn = tile - tm * tiles_n;
+    return;
+  }
+  const int64_t per_group = (int64_t)p.group_m * tiles_n;
+  const int64_t g = tile / per_group, r = tile - g * per_group;
+  const int64_t m_first = g * p.group_m;
+  const int64_t gm = (tiles_m - m_first < p.group_m) ? tiles_m - m_first : p.group_m;   // the last group may be smaller
+  tn = r / gm;
+  tm = m_first + (r - tn * gm);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -353,8 +373,10 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (int64_t tile = tile_first; ok && tile < num_tiles; tile += tile_step) {
-        const int m0 = (int)(tile / tiles_n) * (BM * NCTA) + (int)cta_rank * BM;
-        const int n0 = (int)(tile % tiles_n) * BN + (int)cta_rank * C::B_ROWS;
+        int64_t tm, tn;
+        tile_coords(p, tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = (int)tm * (BM * NCTA) + (int)cta_rank * BM;
+        const int n0 = (int)tn * BN + (int)cta_rank * C::B_ROWS;
         for (int kb = 0; kb < num_kb; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -455,7 +477,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t tile_it = 0;
     for (int64_t tile = tile_first; tile < num_tiles; tile += tile_step, tile_it++) {
       const uint32_t slot = tile_it & 1u, tph = (tile_it >> 1) & 1u;
-      const int64_t m0 = (tile / tiles_n) * (BM * NCTA) + cta_rank * BM, n0 = (tile % tiles_n) * BN + col0;
+      int64_t tm, tn;
+      tile_coords(p, tile, tiles_m, tiles_n, tm, tn);
+      const int64_t m0 = tm * (BM * NCTA) + cta_rank * BM, n0 = tn * BN + col0;
       if (OUT_T != OUT_I32) {
         // Stage this warp's column scales and biases while the main loop of the tile still runs.
         __syncwarp();
@@ -823,6 +847,16 @@ int launch_gemm_i8_umma(b200q_ctx* ctx, const int8_t* A, const int8_t* W_nk, int
   p.acc_class = K <= 255 ? 0 : K <= 1024 ? 1 : 2;
   p.a_pieces = a_pieces;
   p.a_piece_cols = (int)(K / a_pieces);
+  {
+    // Walking order of the tiles: grouped when W is too large to stay in L2 (126 MB) next to the rest -- all row blocks
+    // in one group when A is small enough to stay resident beside the W tiles in flight, groups of 8 otherwise (the
+    // tiles in flight then touch about 8 row blocks and 9 column tiles: the smallest footprint a wave of 74 can have).
+    const int64_t tiles_m = (M + (int64_t)BM * ncta - 1) / ((int64_t)BM * ncta);
+    int g = ctx->tile_group;
+    if (g < 0) g = (N * K > (int64_t(48) << 20) && tiles_m > 1) ? (M * K <= (int64_t(48) << 20) ? (int)tiles_m : 8) : 0;
+    if (g > tiles_m) g = (int)tiles_m;
+    p.group_m = g;
+  }
   p.q_inv = 0.0f; p.q_exact = 0;
   if (out_q) {
     p.q_inv = (float)(1.0 / q_scale);

@@ -158,6 +158,10 @@ class Context:
         """0: exact sigmoid tails (default); 1: hardware exp / reciprocal for f32 outputs (within the 1e-5 bar, faster)."""
         check(self.lib.b200q_set_tail_mode(self.handle, mode), "b200q_set_tail_mode")
 
+    def set_tile_group(self, row_blocks: int):
+        """Tile walking order of the tensor-core GEMM: -1 by size, 0 row block by row block, g groups of g row blocks."""
+        check(self.lib.b200q_set_tile_group(self.handle, row_blocks), "b200q_set_tile_group")
+
     def set_host_threads(self, threads: int):
         """Host threads that stage pageable arrays of the host-buffer entry points (0: half the cores, at most 8)."""
         check(self.lib.b200q_set_host_threads(self.handle, threads), "b200q_set_host_threads")

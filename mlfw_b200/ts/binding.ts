@@ -28,6 +28,7 @@ function bind(path: string) {
     setGemmVariant: f('int b200q_set_gemm_variant(void *ctx, int variant)'),
     setTailMode: f('int b200q_set_tail_mode(void *ctx, int mode)'),
     setEpilogueWarps: f('int b200q_set_epilogue_warps(void *ctx, int warps)'),
+    setTileGroup: f('int b200q_set_tile_group(void *ctx, int row_blocks)'),
     setHostThreads: f('int b200q_set_host_threads(void *ctx, int threads)'),
     setRequantVariant: f('int b200q_set_requant_variant(void *ctx, int variant)'),
     setQuantVariant: f('int b200q_set_quant_variant(void *ctx, int variant)'),

@@ -307,6 +307,32 @@ def test_zero_points_on_the_tensor_cores(ctx, orc, M, N, K, za, zw):
     assert (got == orc.qdot_i32(A, W, "NK", za, zw)).all()
 
 
+@pytest.mark.parametrize("M,N,K", [(1300, 1100, 256), (2600, 520, 128), (256, 3000, 64)])
+def test_tile_walking_order_does_not_change_results(ctx, orc, M, N, K):
+    """The persistent CTAs may walk the tiles row block by row block or in groups of row blocks (groups that do not
+    divide the row blocks, a group larger than the matrix): same accumulators, same f32 results, same row ranges."""
+    rng = np.random.default_rng(M + N)
+    x, W, ws, bias = linear_case(rng, M, N, K)
+    q, _, s = orc.quantize_per_token(x)
+    dq, dsc, dW, dws, db = ctx.to_device(q), ctx.to_device(s), ctx.to_device(W), ctx.to_device(ws), ctx.to_device(bias)
+    ref_acc = orc.qdot_i32(q, W)
+    results = []
+    for g in (0, 1, 3, 8, 1000, -1):
+        ctx.set_tile_group(g)
+        dacc, dy = Guarded(ctx, (M, N), np.int32), Guarded(ctx, (M, N), np.float32)
+        dqo, dso = Guarded(ctx, (M, N), np.int8), Guarded(ctx, (M,), np.float32)
+        ctx.int8_gemm_i32(dq, dW, M, N, K, dacc.ptr)
+        ctx.int8_linear_f32_requant_token(dq, dsc, dW, dws, db, "silu", M, N, K, dy.ptr, dqo.ptr, dso.ptr)
+        ctx.sync()
+        assert (dacc.download() == ref_acc).all()
+        results.append((dy.download(), dqo.download(), dso.download()))
+    ctx.set_tile_group(-1)
+    for y, qo, so in results[1:]:
+        assert (y.view(np.uint32) == results[0][0].view(np.uint32)).all() and (qo == results[0][1]).all()
+        assert (so.view(np.uint32) == results[0][2].view(np.uint32)).all()
+    ctx.check_status()
+
+
 def test_epilogue_separate_op(ctx, orc):
     """convert -> mul(scale vector) -> add(bias) -> activation as its own kernel (the reference's unfused chain)."""
     rng = np.random.default_rng(23)
