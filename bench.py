@@ -270,6 +270,33 @@ def run_conv_bench(ctx, pk, iters=20):
     return out
 
 
+def run_tail_sweep(ctx, iters=4):
+    """Config 5's up-projection shape (M 4096, K 8192, N 28672) through b200q_int8_linear with every tail: what the
+    fused activation costs on top of the contraction."""
+    rng = np.random.default_rng(0)
+    M, N, K = 4096, 28672, 8192
+    A = ctx.to_device(rng.integers(-127, 128, (M, K), dtype=np.int8))
+    s = ctx.to_device(rng.uniform(0.01, 0.02, M).astype(np.float32))
+    W = ctx.to_device(rng.integers(-127, 128, (N, K), dtype=np.int8))
+    ws = ctx.to_device(rng.uniform(1e-4, 2e-4, N).astype(np.float32))
+    out = ctx.empty((M, N), np.float32)
+    res = {}
+    for act, mode in (("none", 0), ("relu", 0), ("gelu_tanh", 0), ("silu", 1), ("silu", 0), ("gelu_sigmoid", 0)):
+        ctx.set_tail_mode(mode)
+        for _ in range(2):
+            ctx.int8_linear(A, s, W, ws, None, act, M, N, K, out)
+        ctx.sync()
+        time.sleep(0.3)
+        ctx.timer_start()
+        for _ in range(iters):
+            ctx.int8_linear(A, s, W, ws, None, act, M, N, K, out)
+        ms = ctx.timer_stop() / iters
+        res[act + ("_hardware_exp" if mode else "")] = {"us": ms * 1e3, "TOPs": 2.0 * M * N * K / (ms * 1e-3) / 1e12}
+    ctx.set_tail_mode(0)
+    ctx.check_status()
+    return res
+
+
 def run_c1(ctx, iters=200):
     """Config 1, the two-layer MLP (256 tokens, 512 -> 1024 -> 256, ReLU, per-token activation scales): weights prepared
     on the device, then the forward pass as plain launches and as one recorded graph per pass."""
@@ -996,6 +1023,7 @@ def _run():
     ap.add_argument("--no-extras", action="store_true", help="skip the end-to-end, round-trip and CPU legs (profiler runs)")
     ap.add_argument("--quant-sweep", action="store_true", help="only the per-token quantize over row lengths 768..8192 and 8192 / 16384 rows")
     ap.add_argument("--tile-group", type=int, default=-1, help="tile walking order of the tensor-core GEMM (b200q_set_tile_group)")
+    ap.add_argument("--tail-sweep", action="store_true", help="only config 5's up-projection shape with every fused tail")
     ap.add_argument("--conv-bench", action="store_true", help="only quantized_conv2d on ResNet-sized layers (gather + contraction), both layouts")
     ap.add_argument("--roundtrip-only", action="store_true", help="only the standalone quantize -> dequantize round trip (profiler runs)")
     args = ap.parse_args()
@@ -1030,6 +1058,10 @@ def _run():
     if args.quant_sweep:
         line = {"metric": "quantize_per_token_GBps", "unit": "GB/s", "timing": "back to back, 40 launches per point",
                 "quant_sweep": run_quant_sweep(ctx, peaks())}
+        ctx.close()
+        return line
+    if args.tail_sweep:
+        line = {"metric": "int8_linear_TOPs", "unit": "TOP/s", "shape": "M 4096, K 8192, N 28672", "tail_sweep": run_tail_sweep(ctx)}
         ctx.close()
         return line
     if args.conv_bench:
