@@ -783,6 +783,16 @@ def run_e2e(ctx, comm, rank, world, local_rank, args, M, K, N, act, x_host, dW, 
     py = np.empty((M, N), np.float32)
     dt_pageable = timed(px, py)
     same_pageable = bool(np.array_equal(py[::997, ::97], sample))
+    # the same two arrays page-locked in place once (b200q_host_register), as a caller that reuses its buffers can do
+    t_reg = time.perf_counter()
+    ctx.host_register(px)
+    ctx.host_register(py)
+    t_reg = time.perf_counter() - t_reg
+    py[...] = 0.0
+    dt_registered = timed(px, py)
+    same_registered = bool(np.array_equal(py[::997, ::97], sample))
+    ctx.host_unregister(px)
+    ctx.host_unregister(py)
 
     # bound to the GPU's NUMA node: new page-locked buffers allocated after the binding
     numa = gpu_numa_info(local_rank)
@@ -807,6 +817,9 @@ def run_e2e(ctx, comm, rank, world, local_rank, args, M, K, N, act, x_host, dW, 
     out["e2e_pageable"] = {"value": world * M / dt_pageable, "unit": "tokens/s", "ms_per_step": dt_pageable * 1e3, "steps": e2e_steps,
                            "same_result_as_page_locked": same_pageable,
                            "host_threads": host_threads,
+                           "registered_in_place": {"ms_per_step": dt_registered * 1e3, "tokens_per_s": world * M / dt_registered,
+                                                   "same_result_as_page_locked": same_registered, "register_ms_once": t_reg * 1e3,
+                                                   "api": "b200q_host_register on the caller's two arrays, then the same calls"},
                            "api": "b200q_linear_f32_host with ordinary (pageable) numpy arrays, as a caller holding typed arrays would pass: "
                                   "row blocks staged through a page-locked ring by the context's copy threads"}
     return out

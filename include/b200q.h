@@ -92,6 +92,12 @@ int b200q_upload(b200q_ctx* ctx, void* dev, const void* host, size_t bytes);    
 int b200q_download(b200q_ctx* ctx, void* host, const void* dev, size_t bytes);   /* synchronous */
 int b200q_host_alloc(b200q_ctx* ctx, size_t bytes, void** host);                 /* page-locked host memory */
 int b200q_host_free(b200q_ctx* ctx, void* host);
+/* Page-locks an array the caller already holds (a typed array's backing store, src/tensor/core/storage.ts) for as long as
+ * it stays registered: the host-buffer entry points then hand it to the copy engines as it is instead of staging it
+ * through their own page-locked ring.  Worth it for buffers that are reused over many calls (registering costs about as
+ * much as a few calls); unregister before the memory is released. */
+int b200q_host_register(b200q_ctx* ctx, void* host, size_t bytes);
+int b200q_host_unregister(b200q_ctx* ctx, void* host);
 
 /* -------------------------------------------------------------------- timing
  * CUDA events on the context's stream (the reference times with a host clock:

@@ -40,6 +40,8 @@ PROTOTYPES = {
     "b200q_download": (c_int, [c_vp, c_vp, c_vp, c_sz]),
     "b200q_host_alloc": (c_int, [c_vp, c_sz, C.POINTER(c_vp)]),
     "b200q_host_free": (c_int, [c_vp, c_vp]),
+    "b200q_host_register": (c_int, [c_vp, c_vp, c_sz]),
+    "b200q_host_unregister": (c_int, [c_vp, c_vp]),
     "b200q_timer_start": (c_int, [c_vp]),
     "b200q_timer_stop": (c_int, [c_vp, C.POINTER(C.c_float)]),
     "b200q_profile_enable": (c_int, [c_vp, c_int]),

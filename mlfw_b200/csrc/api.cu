@@ -396,6 +396,30 @@ int b200q_host_free(b200q_ctx* ctx, void* host) {
   return 0;
 }
 
+int b200q_host_register(b200q_ctx* ctx, void* host, size_t bytes) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(host != nullptr && bytes > 0, "b200q_host_register: null pointer or empty range");
+  const cudaError_t e = cudaHostRegister(host, bytes, cudaHostRegisterDefault);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();   // a refused registration is the caller's to handle: it must not show up in a later launch check
+    set_error("b200q_host_register: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+
+int b200q_host_unregister(b200q_ctx* ctx, void* host) {
+  if (use_device(ctx)) return 1;
+  B200Q_REQUIRE(host != nullptr, "b200q_host_unregister: null pointer");
+  const cudaError_t e = cudaHostUnregister(host);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_error("b200q_host_unregister: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+
 // ---------------------------------------------------------------- timing
 int b200q_timer_start(b200q_ctx* ctx) {
   if (use_device(ctx)) return 1;

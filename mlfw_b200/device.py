@@ -131,6 +131,15 @@ class Context:
     def pinned(self, shape, dtype) -> PinnedArray:
         return PinnedArray(self, shape, dtype)
 
+    def host_register(self, arr: np.ndarray) -> None:
+        """Page-locks a contiguous numpy array in place (b200q_host_register): the host-buffer calls then copy from / to it
+        directly.  Call :meth:`host_unregister` before the array goes away."""
+        assert arr.flags["C_CONTIGUOUS"] and arr.nbytes > 0
+        check(self.lib.b200q_host_register(self.handle, arr.ctypes.data, arr.nbytes), "b200q_host_register")
+
+    def host_unregister(self, arr: np.ndarray) -> None:
+        check(self.lib.b200q_host_unregister(self.handle, arr.ctypes.data), "b200q_host_unregister")
+
     def sync(self):
         check(self.lib.b200q_sync(self.handle), "b200q_sync")
 

@@ -41,6 +41,8 @@ function bind(path: string) {
     download: f('int b200q_download(void *ctx, void *host, const void *dev, size_t bytes)'),
     hostAlloc: f('int b200q_host_alloc(void *ctx, size_t bytes, _Out_ void **host)'),
     hostFree: f('int b200q_host_free(void *ctx, void *host)'),
+    hostRegister: f('int b200q_host_register(void *ctx, void *host, size_t bytes)'),
+    hostUnregister: f('int b200q_host_unregister(void *ctx, void *host)'),
     timerStart: f('int b200q_timer_start(void *ctx)'),
     timerStop: f('int b200q_timer_stop(void *ctx, _Out_ float *elapsed_ms)'),
     profileEnable: f('int b200q_profile_enable(void *ctx, int on)'),

@@ -261,6 +261,33 @@ def test_linear_f32_host_pipelines_row_blocks(ctx, in_locked, out_locked, M=5000
             h.free()
 
 
+def test_linear_f32_host_with_arrays_registered_in_place(ctx, M=5000, N=384, K=256):
+    """Ordinary numpy arrays page-locked in place (b200q_host_register) take the direct path of the host-buffer entry
+    point and give the bits of the staged path; after unregistering they are ordinary arrays again."""
+    rng = np.random.default_rng(78)
+    x, W, ws, bias = linear_case(rng, M, N, K)
+    dW, dws, db = ctx.to_device(W), ctx.to_device(ws), ctx.to_device(bias)
+    staged = np.full((M, N), np.nan, np.float32)
+    ctx.linear_f32_host(x, dW.ptr, dws.ptr, db.ptr, "silu", M, N, K, staged)
+    out = np.full((M, N), np.nan, np.float32)
+    ctx.host_register(x)
+    ctx.host_register(out)
+    try:
+        for _ in range(2):
+            out[...] = np.nan
+            ctx.linear_f32_host(x, dW.ptr, dws.ptr, db.ptr, "silu", M, N, K, out)
+            assert (out.view(np.uint32) == staged.view(np.uint32)).all()
+    finally:
+        ctx.host_unregister(x)
+        ctx.host_unregister(out)
+    out[...] = np.nan
+    ctx.linear_f32_host(x, dW.ptr, dws.ptr, db.ptr, "silu", M, N, K, out)
+    assert (out.view(np.uint32) == staged.view(np.uint32)).all()
+    import mlfw_b200
+    with pytest.raises(mlfw_b200.B200QError):
+        ctx.host_unregister(out)          # not registered any more
+
+
 @pytest.mark.parametrize("count,M,N,K", [(1, 300, 256, 512), (2, 1100, 512, 256), (5, 2048, 768, 1024), (4, 70, 100, 48)])
 def test_linear_f32_many_equals_batch_by_batch(ctx, count, M, N, K):
     """Independent batches with the quantize of the next one overlapping the GEMM of the current one (two streams, two
